@@ -1,0 +1,189 @@
+/* vx_b200.h -- entry points that libvx_cuda_dispatch.so exports on top of the
+ * 24 symbols of vx_hardware_runtime.h.  All are additive: a program that uses
+ * only the reference interface never calls them.
+ *
+ *   vx_nn_*        the decode operators of stdlib/std/nn.vx, one C function per
+ *                  Vx function, with that function's parameter order and the
+ *                  C convention of a Vx `pub fn` (docs/lang/abi.md section 3.6):
+ *                  a tensor of rank r arrives as 3 + 2r values -- allocated
+ *                  pointer, aligned pointer, offset, r sizes, r strides -- and a
+ *                  scalar as one value.  Tensors must be packed and in GPU
+ *                  memory.  A shape that the Vx function's `assert` refuses
+ *                  stops the program here too.
+ *   vx_decoder_*   one whole decoder token (all layers, logits, argmax) as one
+ *                  CUDA graph of fused kernels; the host-side counterpart of
+ *                  transformer<D> in tests/backend/pass/llama2.vx:218-429 and
+ *                  of a program written with std::nn.
+ *   vx_b200_*      direct GEMM / flash-attention / utility calls on device
+ *                  pointers, for hosts that are not Vx programs.
+ *
+ * Work is queued on the stream of vx_cuda_set_stream (the legacy default
+ * stream when none is set) and the calls do not wait unless they say so.
+ */
+#ifndef VX_B200_H
+#define VX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A tensor parameter in the `pub fn` convention. */
+#define VX_TENSOR1(t)                                                          \
+  void *t##_allocated, void *t##_aligned, int64_t t##_offset, int64_t t##_n0,  \
+      int64_t t##_s0
+#define VX_TENSOR2(t)                                                          \
+  void *t##_allocated, void *t##_aligned, int64_t t##_offset, int64_t t##_n0,  \
+      int64_t t##_n1, int64_t t##_s0, int64_t t##_s1
+#define VX_TENSOR3(t)                                                          \
+  void *t##_allocated, void *t##_aligned, int64_t t##_offset, int64_t t##_n0,  \
+      int64_t t##_n1, int64_t t##_n2, int64_t t##_s0, int64_t t##_s1,          \
+      int64_t t##_s2
+#define VX_TENSOR4(t)                                                          \
+  void *t##_allocated, void *t##_aligned, int64_t t##_offset, int64_t t##_n0,  \
+      int64_t t##_n1, int64_t t##_n2, int64_t t##_n3, int64_t t##_s0,          \
+      int64_t t##_s1, int64_t t##_s2, int64_t t##_s3
+
+/* ---- std::nn operators (weights bf16, everything else f32) ----------------- */
+/* nn_matvec, stdlib/std/nn.vx:24 */
+void vx_nn_matvec(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(x), int32_t rows,
+                  int32_t cols);
+/* nn_matvec_add, nn.vx:54 */
+void vx_nn_matvec_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(x), int32_t rows,
+                      int32_t cols);
+/* nn_matvec_heads_add, nn.vx:86 */
+void vx_nn_matvec_heads_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR2(x),
+                            int32_t rows, int32_t heads, int32_t head_dim);
+/* nn_qkv, nn.vx:124 */
+void vx_nn_qkv(VX_TENSOR2(q), VX_TENSOR2(k), VX_TENSOR2(v), VX_TENSOR1(w),
+               VX_TENSOR1(b), VX_TENSOR1(x), int32_t q_heads, int32_t kv_heads,
+               int32_t head_dim, int32_t cols);
+/* nn_swiglu, nn.vx:169 */
+void vx_nn_swiglu(VX_TENSOR1(out), VX_TENSOR1(w), VX_TENSOR1(x), int32_t rows,
+                  int32_t cols);
+/* nn_rms_norm, nn.vx:212 */
+void vx_nn_rms_norm(VX_TENSOR1(y), VX_TENSOR1(x), VX_TENSOR1(w), int32_t n,
+                    float eps);
+/* nn_rope_and_store, nn.vx:245 */
+void vx_nn_rope_and_store(VX_TENSOR2(q_out), VX_TENSOR3(k_cache),
+                          VX_TENSOR3(v_cache), VX_TENSOR2(q), VX_TENSOR2(k),
+                          VX_TENSOR2(v), VX_TENSOR2(cos), VX_TENSOR2(sin),
+                          int32_t pos, int32_t q_heads, int32_t kv_heads,
+                          int32_t head_dim);
+/* nn_attention, nn.vx:349 (`part` from nn_attention_scratch, nn.vx:370) */
+void vx_nn_attention(VX_TENSOR2(out), VX_TENSOR4(part), VX_TENSOR2(q),
+                     VX_TENSOR3(k_cache), VX_TENSOR3(v_cache), int32_t pos,
+                     int32_t q_heads, int32_t kv_heads, int32_t head_dim);
+/* nn_argmax, nn.vx:870 */
+void vx_nn_argmax(VX_TENSOR1(out), VX_TENSOR1(logits), int32_t n);
+/* nn_embed, nn.vx:942 */
+void vx_nn_embed(VX_TENSOR1(x), VX_TENSOR1(table), VX_TENSOR1(token),
+                 int32_t dim);
+
+/* ---- a whole decoder token -------------------------------------------------- */
+typedef struct {
+  int32_t dim, hidden, n_layers, q_heads, kv_heads, head_dim, vocab, max_seq;
+  float eps;
+  float rope_theta;
+  /* 1: bf16 weights, half-split RoPE from tables (std::nn); 0: f32 weights,
+     interleaved RoPE computed from the position (llama2.vx). */
+  int32_t weights_bf16;
+  int32_t batch; /* 1, 2, 4, 8 or 16 sequences */
+  /* Tensor parallel: this process holds q_heads / tp_ranks query heads,
+     kv_heads / tp_ranks KV heads and hidden / tp_ranks MLP rows of every
+     layer, and the job of vx_collective_init sums the partial outputs.
+     1 = not sharded. The fields above are the WHOLE model's. */
+  int32_t tp_ranks;
+  /* How the partial sums are added across ranks: 0 = NCCL all-reduce. */
+  int32_t tp_reduce;
+} vx_decoder_config;
+
+/* Device pointers, one entry per layer where the field is an array; the caller
+   owns the memory. Shapes are this rank's share:
+   wq [q_local*hd, dim] (with wk == NULL: q, k and v rows in one matrix),
+   wk, wv [kv_local*hd, dim], bqkv bf16 or NULL, wo [dim, q_local*hd],
+   w_gate [hidden_local, dim] (with w_up == NULL: gate rows then up rows),
+   w_up [hidden_local, dim], w_down [dim, hidden_local]; norms [dim];
+   embed, lm_head [vocab, dim]; cos, sin f32 [max_seq, head_dim/2] or NULL. */
+typedef struct {
+  const void *embed;
+  const void *const *attn_norm;
+  const void *const *wq;
+  const void *const *wk;
+  const void *const *wv;
+  const void *const *bqkv;
+  const void *const *wo;
+  const void *const *ffn_norm;
+  const void *const *w_gate;
+  const void *const *w_up;
+  const void *const *w_down;
+  const void *final_norm;
+  const void *lm_head;
+  const float *cos;
+  const float *sin;
+} vx_decoder_weights;
+
+typedef struct vx_decoder vx_decoder;
+
+/* Allocates the KV cache and the activations on the current GPU. */
+vx_decoder *vx_decoder_create(const vx_decoder_config *config,
+                              const vx_decoder_weights *weights);
+void vx_decoder_destroy(vx_decoder *d);
+/* Every sequence back to position 0 (the cache is not cleared: rows past the
+   position are never read). */
+void vx_decoder_reset(vx_decoder *d);
+/* One token for each of the `batch` sequences. tokens_in (host, batch values)
+   feeds the step; NULL feeds the argmax of the previous step, which never left
+   the GPU. tokens_out (host) receives the argmax of this step when not NULL --
+   the call then waits for the GPU. Returns the position the step ran at. */
+int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
+                        int32_t *tokens_out);
+/* The logits of the last step: device memory, [batch, vocab] f32. */
+const float *vx_decoder_logits(const vx_decoder *d);
+/* The CUDA stream (a CUstream) that the decoder's steps run on, for a host
+   that wants to record events around them. */
+void *vx_decoder_stream(const vx_decoder *d);
+/* How many kernels one step launches (for accounting). */
+int32_t vx_decoder_kernels_per_step(const vx_decoder *d);
+
+/* ---- direct calls -------------------------------------------------------------
+ * All return 0, or -1 with the reason in vx_b200_last_error(). */
+const char *vx_b200_last_error(void);
+
+/* C[m,n] = A[m,k] * B[k,n], row-major device memory, strides in elements.
+   dtype is a VX_DTYPE_* code (f32, f64, f16, bf16). route: 0 = as a dispatch
+   would run it; for 16-bit types 1 = tcgen05 with B as stored, 2 = tcgen05
+   after transposing B into scratch ([n, k] elements), 3 = the plain kernel. */
+int32_t vx_b200_gemm(int32_t dtype, int32_t route, int64_t m, int64_t n,
+                     int64_t k, const void *a, int64_t lda, const void *b,
+                     int64_t ldb, void *c, int64_t ldc, void *scratch);
+/* Waits for the stream, then: 0 when every tensor-core kernel since the last
+   call ran to its end, else the code of the first wait that gave up. */
+int32_t vx_b200_kernel_status(void);
+
+/* Flash attention forward, bf16 [B, H, S, D] in and out, f32 softmax. */
+int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,
+                                void *out, int32_t B, int32_t H, int32_t S,
+                                int32_t D, float scale, int32_t causal);
+
+/* Column-split product for a job of g ranks: this rank holds A [m,k] and
+   B_local [k, n_local]; c_full [m, g*n_local] is complete on every rank
+   afterwards. c_local [m, n_local] and gathered [g, m, n_local] are scratch. */
+int32_t vx_b200_gemm_column_split(int32_t dtype, int64_t m, int64_t n_local,
+                                  int64_t k, const void *a, const void *b_local,
+                                  void *c_local, void *gathered, void *c_full);
+
+/* Seeded synthetic data made on the GPU: N(0, sigma^2) or U[lo, hi), written as
+   f32 or as bf16 (round to nearest even). */
+int32_t vx_b200_fill_normal(void *out, int32_t as_bf16, int64_t n, uint64_t seed,
+                            float sigma);
+int32_t vx_b200_fill_uniform(void *out, int32_t as_bf16, int64_t n,
+                             uint64_t seed, float lo, float hi);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* VX_B200_H */

@@ -1,0 +1,292 @@
+"""ctypes face of the CPU oracle (oracle/vx_oracle.cpp). TEST INFRASTRUCTURE.
+
+Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / reference
+legs import this module; nothing under vx_b200/ may.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import build as _build
+
+_LIB = None
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(_build.build())
+        _declare(_LIB)
+    return _LIB
+
+
+class LlamaConfig(C.Structure):
+    """llama2.c header order used by tests/backend/pass/llama2.vx."""
+    _fields_ = [(n, C.c_int32) for n in
+                ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads",
+                 "vocab_size", "seq_len")]
+
+
+class NnConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("dim", "hidden", "n_layers", "q_heads", "kv_heads",
+                 "head_dim", "vocab", "max_seq")] + \
+               [("eps", C.c_float), ("rope_theta", C.c_float)]
+
+
+def _declare(L):
+    i64, i32, f32 = C.c_int64, C.c_int32, C.c_float
+    vp = C.c_void_p
+    L.oracle_set_threads.argtypes = [C.c_int]
+    L.oracle_get_threads.restype = C.c_int
+    L.oracle_gemm_f32.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64, i64]
+    L.oracle_gemm_f32_rows.argtypes = L.oracle_gemm_f32.argtypes
+    L.oracle_gemm_f64.argtypes = L.oracle_gemm_f32.argtypes
+    L.oracle_gemm_bf16_rows.argtypes = [vp, i64, vp, i64, vp, i64, i64, i64,
+                                        vp, i64]
+    L.oracle_gemm_bf16_entry.argtypes = [vp, i64, vp, i64, i64, i64, i64]
+    L.oracle_gemm_bf16_entry.restype = f32
+    L.oracle_matvec_f32.argtypes = [vp, vp, vp, C.c_int, C.c_int]
+    L.oracle_f32_to_bf16.argtypes = [vp, vp, i64]
+    L.oracle_bf16_to_f32.argtypes = [vp, vp, i64]
+    L.oracle_random.argtypes = [C.c_uint32, i32, f32]
+    L.oracle_random.restype = f32
+    L.oracle_random_f32.argtypes = [vp, i64, C.c_uint32, f32]
+    L.oracle_llama_weight_count.argtypes = [C.POINTER(LlamaConfig)]
+    L.oracle_llama_weight_count.restype = i64
+    L.oracle_llama_forward.argtypes = [C.POINTER(LlamaConfig), vp, vp, vp, i32,
+                                       i32, vp]
+    L.oracle_llama_generate.argtypes = [C.POINTER(LlamaConfig), vp, vp, i32, vp]
+    L.oracle_argmax_f32.argtypes = [vp, i32]
+    L.oracle_argmax_f32.restype = i32
+    L.oracle_nn_matvec.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int]
+    L.oracle_nn_qkv.argtypes = [vp] * 6 + [C.c_int] * 4
+    L.oracle_nn_swiglu.argtypes = [vp, vp, vp, C.c_int, C.c_int]
+    L.oracle_nn_rms_norm.argtypes = [vp, vp, vp, C.c_int, f32]
+    L.oracle_nn_rope_and_store.argtypes = [vp] * 8 + [C.c_int] * 5
+    L.oracle_nn_attention.argtypes = [vp] * 4 + [C.c_int] * 4
+    L.oracle_attention_f64.argtypes = [vp] * 4 + [C.c_int] * 4
+    L.oracle_nn_argmax.argtypes = [vp, i32]
+    L.oracle_nn_argmax.restype = i32
+    L.oracle_nn_embed.argtypes = [vp, vp, i32, C.c_int]
+    L.oracle_rope_tables.argtypes = [vp, vp, C.c_int, C.c_int, C.c_double]
+    L.oracle_nn_layer_params.argtypes = [C.POINTER(NnConfig)]
+    L.oracle_nn_layer_params.restype = i64
+    L.oracle_nn_decode_step.argtypes = [C.POINTER(NnConfig)] + [vp] * 8 + \
+                                       [i32, i32, vp]
+    L.oracle_nn_decode_step.restype = i32
+    L.oracle_attention_rows.argtypes = [vp, vp, vp, C.c_int, C.c_int, f32,
+                                        C.c_int, vp, C.c_int, vp]
+    L.oracle_all_reduce_sum_f32.argtypes = [vp, C.c_int, vp, i64]
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def set_threads(n):
+    lib().oracle_set_threads(int(n))
+
+
+# ---- conversions -----------------------------------------------------------
+def f32_to_bf16(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().oracle_f32_to_bf16(_p(x), _p(out), x.size)
+    return out
+
+
+def bf16_to_f32(x):
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty(x.shape, dtype=np.float32)
+    lib().oracle_bf16_to_f32(_p(x), _p(out), x.size)
+    return out
+
+
+def random_f32(n, seed, scale):
+    out = np.empty(int(n), dtype=np.float32)
+    lib().oracle_random_f32(_p(out), out.size, seed, scale)
+    return out
+
+
+# ---- GEMM --------------------------------------------------------------------
+def gemm(a, b, fast=False):
+    """Row-major C = A @ B for float32 or float64 arrays (k ascending)."""
+    assert a.dtype == b.dtype and a.shape[1] == b.shape[0]
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    m, k = a.shape
+    n = b.shape[1]
+    c = np.empty((m, n), dtype=a.dtype)
+    if a.dtype == np.float32:
+        fn = lib().oracle_gemm_f32_rows if fast else lib().oracle_gemm_f32
+    else:
+        fn = lib().oracle_gemm_f64
+    fn(_p(a), k, _p(b), n, _p(c), n, m, n, k)
+    return c
+
+
+def gemm_bf16_rows(a16, b16, rows):
+    """Rows `rows` of bf16(A @ B) with an f32 accumulator; uint16 in and out."""
+    a16 = np.ascontiguousarray(a16, dtype=np.uint16)
+    b16 = np.ascontiguousarray(b16, dtype=np.uint16)
+    rows = np.ascontiguousarray(rows, dtype=np.int64)
+    k = a16.shape[1]
+    n = b16.shape[1]
+    c = np.empty((rows.size, n), dtype=np.uint16)
+    lib().oracle_gemm_bf16_rows(_p(a16), k, _p(b16), n, _p(c), n, n, k,
+                                _p(rows), rows.size)
+    return c
+
+
+def gemm_bf16_entry(a16, b16, i, j):
+    k = a16.shape[1]
+    return lib().oracle_gemm_bf16_entry(_p(a16), k, _p(b16), b16.shape[1],
+                                        int(i), int(j), k)
+
+
+def matvec_f32(w, x):
+    d, n = w.shape
+    out = np.empty(d, dtype=np.float32)
+    lib().oracle_matvec_f32(_p(out), _p(np.ascontiguousarray(x)),
+                            _p(np.ascontiguousarray(w)), n, d)
+    return out
+
+
+# ---- llama2.vx-style f32 decode ------------------------------------------------
+def llama_weight_count(cfg):
+    return lib().oracle_llama_weight_count(C.byref(cfg))
+
+
+def llama_generate(cfg, weights, first_token, steps, want_gaps=False):
+    weights = np.ascontiguousarray(weights, dtype=np.float32)
+    assert weights.size == llama_weight_count(cfg)
+    tokens = np.zeros(steps + 1, dtype=np.int32)
+    tokens[0] = first_token
+    gaps = np.zeros(steps, dtype=np.float32)
+    lib().oracle_llama_generate(C.byref(cfg), _p(weights), _p(tokens), steps,
+                                _p(gaps))
+    return (tokens, gaps) if want_gaps else tokens
+
+
+def llama_forward(cfg, weights, kc, vc, token, pos):
+    logits = np.empty(cfg.vocab_size, dtype=np.float32)
+    lib().oracle_llama_forward(C.byref(cfg), _p(weights), _p(kc), _p(vc),
+                               int(token), int(pos), _p(logits))
+    return logits
+
+
+# ---- std::nn operators -----------------------------------------------------------
+def nn_matvec(w16, x, rows, cols, y=None):
+    add = y is not None
+    out = np.array(y, dtype=np.float32) if add else np.empty(rows, np.float32)
+    lib().oracle_nn_matvec(_p(out), _p(w16), _p(np.ascontiguousarray(x, np.float32)),
+                           rows, cols, int(add))
+    return out
+
+
+def nn_qkv(w16, b16, x, q_heads, kv_heads, head_dim, cols):
+    q = np.empty((q_heads, head_dim), np.float32)
+    k = np.empty((kv_heads, head_dim), np.float32)
+    v = np.empty((kv_heads, head_dim), np.float32)
+    lib().oracle_nn_qkv(_p(q), _p(k), _p(v), _p(w16), _p(b16),
+                        _p(np.ascontiguousarray(x, np.float32)), q_heads,
+                        kv_heads, head_dim, cols)
+    return q, k, v
+
+
+def nn_swiglu(w16, x, rows, cols):
+    out = np.empty(rows, np.float32)
+    lib().oracle_nn_swiglu(_p(out), _p(w16),
+                           _p(np.ascontiguousarray(x, np.float32)), rows, cols)
+    return out
+
+
+def nn_rms_norm(x, w16, n, eps):
+    y = np.empty(n, np.float32)
+    lib().oracle_nn_rms_norm(_p(y), _p(np.ascontiguousarray(x, np.float32)),
+                             _p(w16), n, eps)
+    return y
+
+
+def rope_tables(max_seq, head_dim, theta):
+    cos = np.empty((max_seq, head_dim // 2), np.float32)
+    sin = np.empty_like(cos)
+    lib().oracle_rope_tables(_p(cos), _p(sin), max_seq, head_dim, float(theta))
+    return cos, sin
+
+
+def nn_rope_and_store(k_cache, v_cache, q, k, v, cos, sin, pos):
+    q_heads, head_dim = q.shape
+    kv_heads = k.shape[0]
+    q_out = np.empty_like(q)
+    lib().oracle_nn_rope_and_store(_p(q_out), _p(k_cache), _p(v_cache), _p(q),
+                                   _p(k), _p(v), _p(cos), _p(sin),
+                                   cos.shape[1], pos, q_heads, kv_heads,
+                                   head_dim)
+    return q_out
+
+
+def nn_attention(q, k_cache, v_cache, pos):
+    q_heads, head_dim = q.shape
+    kv_heads = k_cache.shape[1]
+    out = np.empty_like(q)
+    lib().oracle_nn_attention(_p(out), _p(q), _p(k_cache), _p(v_cache), pos,
+                              q_heads, kv_heads, head_dim)
+    return out
+
+
+def attention_f64(q, k_cache, v_cache, pos):
+    q_heads, head_dim = q.shape
+    kv_heads = k_cache.shape[1]
+    out = np.empty(q.shape, np.float64)
+    lib().oracle_attention_f64(_p(out), _p(q), _p(k_cache), _p(v_cache), pos,
+                               q_heads, kv_heads, head_dim)
+    return out
+
+
+def nn_argmax(logits):
+    logits = np.ascontiguousarray(logits, np.float32)
+    return lib().oracle_nn_argmax(_p(logits), logits.size)
+
+
+def nn_embed(table16, token, dim):
+    x = np.empty(dim, np.float32)
+    lib().oracle_nn_embed(_p(x), _p(table16), int(token), dim)
+    return x
+
+
+def nn_layer_params(cfg):
+    return lib().oracle_nn_layer_params(C.byref(cfg))
+
+
+def nn_decode_step(cfg, embed, layers, final_norm, lm_head, cos, sin, kc, vc,
+                   token, pos, want_logits=False):
+    logits = np.empty(cfg.vocab, np.float32) if want_logits else None
+    tok = lib().oracle_nn_decode_step(
+        C.byref(cfg), _p(embed), _p(layers), _p(final_norm), _p(lm_head),
+        _p(cos), _p(sin), _p(kc), _p(vc), int(token), int(pos),
+        _p(logits) if want_logits else None)
+    return (tok, logits) if want_logits else tok
+
+
+# ---- attention over sequences -------------------------------------------------------
+def attention_rows(q16, k16, v16, scale, causal, rows):
+    """q16,k16,v16: [S, D] uint16 (bf16) of one (batch, head)."""
+    S, D = q16.shape
+    rows = np.ascontiguousarray(rows, np.int32)
+    out = np.empty((rows.size, D), np.float32)
+    lib().oracle_attention_rows(_p(np.ascontiguousarray(q16)),
+                                _p(np.ascontiguousarray(k16)),
+                                _p(np.ascontiguousarray(v16)), S, D, scale,
+                                int(causal), _p(rows), rows.size, _p(out))
+    return out
+
+
+def all_reduce_sum_f32(inputs):
+    inputs = [np.ascontiguousarray(a, np.float32) for a in inputs]
+    ptrs = (C.c_void_p * len(inputs))(*[a.ctypes.data for a in inputs])
+    out = np.empty_like(inputs[0])
+    lib().oracle_all_reduce_sum_f32(ptrs, len(inputs), _p(out), out.size)
+    return out

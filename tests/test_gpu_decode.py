@@ -1,0 +1,126 @@
+"""Whole-token decoding on a B200 against the CPU oracle: identical greedy
+tokens."""
+import numpy as np
+import pytest
+
+from vx_b200 import llama
+
+pytestmark = pytest.mark.gpu
+
+
+def report(got, want, gaps=None):
+    got, want = list(got), list(want)
+    if got == want:
+        return ""
+    at = next(i for i, (g, w) in enumerate(zip(got, want)) if g != w)
+    gap = "" if gaps is None else ", top-2 logit gap there %.3g" % gaps[at]
+    return "first divergence at step %d: got %d, want %d%s" % (
+        at, got[at], want[at], gap)
+
+
+def test_config2_small_llama_100_tokens(oracle):
+    """dim 288, 6 layers, 6 heads, hidden 768, vocab 32000, seq 256, seed 42;
+    100 greedy tokens from BOS = 1 must equal the CPU program's."""
+    flat, offsets = llama.small_f32_weights()
+    cfg = oracle.LlamaConfig(288, 768, 6, 6, 6, 32000, 256)
+    want, gaps = oracle.llama_generate(cfg, flat, 1, 100, want_gaps=True)
+    dec = llama.small_f32_decoder(flat, offsets)
+    got = [1]
+    tok = dec.step([1])[0]
+    got.append(tok)
+    for _ in range(99):
+        tok = dec.step(None)[0]           # the argmax stays on the GPU
+        got.append(tok)
+    dec.close()
+    assert got == list(want), report(got, want, gaps)
+
+
+def test_small_llama_logits_close(oracle):
+    flat, offsets = llama.small_f32_weights(seed=43)
+    cfg = oracle.LlamaConfig(288, 768, 6, 6, 6, 32000, 256)
+    kv = 288
+    kc = np.zeros((6, 256, kv), np.float32)
+    vc = np.zeros_like(kc)
+    dec = llama.small_f32_decoder(flat, offsets)
+    for pos, tok in enumerate([1, 17, 31999, 5]):
+        want = oracle.llama_forward(cfg, flat, kc, vc, tok, pos)
+        dec.step([tok])
+        got = dec.logits()[0]
+        assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    dec.close()
+
+
+def nn_host_model(oracle, tensors, cfgd, max_seq):
+    """The oracle's view of a model that nn_bf16_model built on the GPU."""
+    import torch
+
+    def u16(t):
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+    L = cfgd["n_layers"]
+    qkv_rows = (cfgd["q_heads"] + 2 * cfgd["kv_heads"]) * cfgd["head_dim"]
+    layers = []
+    for l in range(L):
+        layers += [u16(tensors["attn_norm"][l]).reshape(-1),
+                   u16(tensors["wq"][l]).reshape(-1),
+                   np.zeros(qkv_rows, np.uint16),
+                   u16(tensors["wo"][l]).reshape(-1),
+                   u16(tensors["ffn_norm"][l]).reshape(-1),
+                   u16(tensors["w_gate"][l]).reshape(-1),
+                   u16(tensors["w_down"][l]).reshape(-1)]
+    flat = np.concatenate(layers)
+    cfg = oracle.NnConfig(cfgd["dim"], cfgd["hidden"], L, cfgd["q_heads"],
+                          cfgd["kv_heads"], cfgd["head_dim"], cfgd["vocab"],
+                          max_seq, 1e-5, 10000.0)
+    assert flat.size == L * oracle.nn_layer_params(cfg)
+    return dict(cfg=cfg, layers=flat, embed=u16(tensors["embed"]),
+                final_norm=u16(tensors["final_norm"]),
+                lm_head=u16(tensors["lm_head"]), cos=tensors["cos"],
+                sin=tensors["sin"])
+
+
+def oracle_generate(oracle, hm, prompt, steps, max_seq):
+    cfg = hm["cfg"]
+    shape = (cfg.n_layers, max_seq, cfg.kv_heads, cfg.head_dim)
+    kc, vc = np.zeros(shape, np.float32), np.zeros(shape, np.float32)
+    out, pos, tok = [], 0, None
+    for t in prompt:
+        tok = oracle.nn_decode_step(cfg, hm["embed"], hm["layers"],
+                                    hm["final_norm"], hm["lm_head"], hm["cos"],
+                                    hm["sin"], kc, vc, t, pos)
+        pos += 1
+    for _ in range(steps):
+        out.append(tok)
+        tok = oracle.nn_decode_step(cfg, hm["embed"], hm["layers"],
+                                    hm["final_norm"], hm["lm_head"], hm["cos"],
+                                    hm["sin"], kc, vc, tok, pos)
+        pos += 1
+    return out
+
+
+SMALL_NN = dict(dim=512, hidden=1408, n_layers=4, q_heads=8, kv_heads=4,
+                head_dim=64, vocab=4096)
+
+
+@pytest.mark.parametrize("batch", [1, 4])
+def test_nn_decoder_tokens_match_oracle(oracle, batch):
+    """A scaled-down std::nn model (bf16, grouped-query heads): a random prompt
+    fed token by token, then greedy steps; every sequence of a batch runs its
+    own prompt."""
+    max_seq = 96
+    dec, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=batch, **SMALL_NN)
+    hm = nn_host_model(oracle, tensors, SMALL_NN, max_seq)
+    rng = np.random.default_rng(8)
+    prompts = rng.integers(0, SMALL_NN["vocab"], (batch, 40))
+    steps = 24
+    got = [[] for _ in range(batch)]
+    for p in range(prompts.shape[1]):
+        toks = dec.step(list(prompts[:, p]))
+    for _ in range(steps):
+        for b in range(batch):
+            got[b].append(toks[b])
+        toks = dec.step(None)
+    dec.close()
+    for b in range(batch):
+        want = oracle_generate(oracle, hm, list(prompts[b]), steps, max_seq)
+        assert got[b] == want, "sequence %d: %s" % (b, report(got[b], want))

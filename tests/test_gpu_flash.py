@@ -1,0 +1,39 @@
+"""Flash attention forward on a B200 against the oracle's f32 attention over
+bf16-rounded inputs; tolerance 2e-2 max-abs, as the configuration states."""
+import numpy as np
+import pytest
+
+from vx_b200 import abi, ops
+
+pytestmark = pytest.mark.gpu
+
+
+def make_qkv(oracle, B, H, S, D):
+    out = []
+    for seed in (10, 11, 12):
+        x = np.random.default_rng(seed).standard_normal((B, H, S, D), dtype=np.float32)
+        out.append(oracle.f32_to_bf16(x))
+    return out
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("B,H,S", [(1, 2, 128), (1, 3, 256), (2, 2, 384),
+                                   (1, 2, 1024)])
+def test_flash_matches_oracle(oracle, B, H, S, causal):
+    D = 128
+    q, k, v = make_qkv(oracle, B, H, S, D)
+    tq, tk, tv = (abi.DeviceTensor.from_host(t, bf16=True) for t in (q, k, v))
+    to = abi.DeviceTensor.from_host(np.zeros((B, H, S, D), np.uint16), bf16=True)
+    scale = 1.0 / np.sqrt(D)
+    ops.flash_attention(tq, tk, tv, to, scale, causal)
+    assert ops.kernel_status() == 0
+    got = oracle.bf16_to_f32(to.to_host())
+    rows = np.unique(np.concatenate([np.arange(0, S, 37), [0, 63, 64, 127, S - 1]]))
+    for b in range(B):
+        for h in range(H):
+            want = oracle.attention_rows(q[b, h], k[b, h], v[b, h], scale,
+                                         causal, rows)
+            err = np.abs(got[b, h][rows] - want).max()
+            assert err <= 2e-2, (b, h, err)
+    for t in (tq, tk, tv, to):
+        t.free()

@@ -1,0 +1,182 @@
+"""The CPU oracle against every known answer the reference's own tests hold for
+this path (no GPU)."""
+import numpy as np
+
+
+def test_gpu_matmul_roles_known_answer(oracle):
+    # tests/backend/pass/gpu_matmul_roles.vx EXPECT: 38 56 83 128 9 7 10
+    a = np.arange(1, 7, dtype=np.float32).reshape(2, 3)
+    b = np.arange(1, 13, dtype=np.float32).reshape(3, 4)
+    c = oracle.gemm(a, b)
+    assert [c[0, 0], c[0, 3], c[1, 0], c[1, 3]] == [38, 56, 83, 128]
+    p = np.arange(1, 10, dtype=np.float32).reshape(3, 3)
+    q = np.diag(np.arange(1, 4, dtype=np.float32))
+    r = oracle.gemm(p, q)
+    assert [r[0, 2], r[2, 0], r[1, 1]] == [9, 7, 10]
+    # the wrong assignments that the test is built to expose give other numbers
+    wrong = oracle.gemm(q, p)
+    assert [wrong[0, 2], wrong[2, 0], wrong[1, 1]] == [3, 21, 10]
+
+
+def test_gpu_matmul_dtypes_known_answer(oracle):
+    # tests/backend/pass/gpu_matmul_dtypes.vx EXPECT: 19 50 197 4032
+    a = np.array([[1, 2], [3, 4]], dtype=np.float64)
+    b = np.array([[5, 6], [7, 8]], dtype=np.float64)
+    c = oracle.gemm(a, b)
+    assert (c[0, 0], c[1, 1]) == (19, 50)
+    e = np.eye(64, dtype=np.float32)
+    m = np.arange(64 * 64, dtype=np.float32).reshape(64, 64)
+    r = oracle.gemm(e, m)
+    assert (r[3, 5], r[63, 0]) == (197, 4032)
+
+
+def test_matmul_into_buffer_and_execution(oracle):
+    # matmul_into_buffer.vx EXPECT: 3 7 3 7; benchmarks/matmul_execution.vx: 24
+    w = np.array([[1, 2], [3, 4]], dtype=np.float32)
+    y = oracle.gemm(w, np.ones((2, 1), np.float32))
+    assert [y[0, 0], y[1, 0]] == [3, 7]
+    c = oracle.gemm(np.full((4, 4), 2, np.float32), np.full((4, 4), 3, np.float32))
+    assert (c == 24).all()
+
+
+def test_the_two_gemm_loops_give_the_same_bits(oracle):
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (96, 200)).astype(np.float32)
+    b = rng.uniform(-1, 1, (200, 72)).astype(np.float32)
+    assert np.array_equal(oracle.gemm(a, b), oracle.gemm(a, b, fast=True))
+
+
+def test_flat_matvec_is_the_gemm_with_one_column(oracle):
+    rng = np.random.default_rng(1)
+    w = rng.uniform(-1, 1, (50, 64)).astype(np.float32)
+    x = rng.uniform(-1, 1, 64).astype(np.float32)
+    assert np.array_equal(oracle.matvec_f32(w, x),
+                          oracle.gemm(w, x.reshape(-1, 1)).reshape(-1))
+
+
+def test_bf16_rounding_is_nearest_even(oracle):
+    # exact RNE, NaN stays NaN, the largest finite value rounds to infinity
+    x = np.array([1.0, 1.00390625, 1.01171875, -1.00390625, 3.4028235e38,
+                  np.inf, 3.3895314e38], dtype=np.float32)
+    got = oracle.f32_to_bf16(x)
+    assert list(got[:4]) == [0x3F80, 0x3F80, 0x3F82, 0xBF80]
+    assert got[4] == 0x7F80 and got[5] == 0x7F80
+    assert got[6] == 0x7F7F                      # the largest finite bf16
+    nan = oracle.f32_to_bf16(np.array([np.nan], np.float32))
+    assert np.isnan(oracle.bf16_to_f32(nan)[0])
+    # round trip of every bf16 pattern that is not a NaN
+    every = np.arange(65536, dtype=np.uint16)
+    f = oracle.bf16_to_f32(every)
+    keep = ~np.isnan(f)
+    assert np.array_equal(oracle.f32_to_bf16(f)[keep], every[keep])
+
+
+def test_small_integer_gemm_is_exact(oracle):
+    # benchmarks/gpu_gemm/cublas_gemm.cu:22-28: sums of small integers are exact
+    m, n, k = 64, 48, 512
+    a = ((np.arange(m)[:, None] * 3 + np.arange(k)[None, :] * 5) % 7 - 3).astype(np.float32)
+    b = ((np.arange(k)[:, None] * 2 + np.arange(n)[None, :]) % 5 - 2).astype(np.float32)
+    a16, b16 = oracle.f32_to_bf16(a), oracle.f32_to_bf16(b)
+    exact = a.astype(np.int64) @ b.astype(np.int64)
+    assert oracle.gemm_bf16_entry(a16, b16, 5, 7) == exact[5, 7]
+    rows = np.arange(m, dtype=np.int64)
+    got = oracle.bf16_to_f32(oracle.gemm_bf16_rows(a16, b16, rows))
+    want = oracle.bf16_to_f32(oracle.f32_to_bf16(exact.astype(np.float32)))
+    assert np.array_equal(got, want)
+
+
+def test_nn_argmax_known_answer(oracle):
+    # std_nn_kernels_match_loops_on_the_cpu.vx:39 "nn_argmax of 151936: 50645"
+    n = 151936
+    h = oracle.random_f32(n, 71, 1.0)
+    assert -1.0 <= h.min() and h.max() < 1.0
+    h[n - 7] = 3.0
+    h[n // 3] = 3.0
+    assert oracle.nn_argmax(h) == 50645
+
+
+def test_random_matches_its_definition(oracle):
+    # mix / random of the same file, :45-60, restated in Python integers
+    def mix(x):
+        h = (x * 2654435761) & 0xFFFFFFFF
+        h ^= h >> 15
+        h = (h * 2246822519) & 0xFFFFFFFF
+        h ^= h >> 13
+        return h
+    got = oracle.random_f32(100, 61, 2.0)
+    for i in (0, 1, 17, 99):
+        u = np.float32(mix((61 * 7919 + i) & 0xFFFFFFFF) >> 8)
+        want = (u * np.float32(0.00000011920929) - np.float32(1.0)) * np.float32(2.0)
+        assert got[i] == want
+
+
+def test_nn_ops_meet_the_reference_criterion(oracle):
+    """The f32 kernels-order oracle against f64 loops, with the reference test's
+    shapes and its bound 1e-5 * max|want| (:101-115)."""
+    def close(got, want):
+        want = np.asarray(want, np.float64)
+        assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+
+    rows, cols = 300, 896
+    w = oracle.f32_to_bf16(oracle.random_f32(rows * cols, 11, 0.1))
+    x = oracle.random_f32(cols, 12, 1.0)
+    wf = oracle.bf16_to_f32(w).astype(np.float64).reshape(rows, cols)
+    close(oracle.nn_matvec(w, x, rows, cols), wf @ x.astype(np.float64))
+    g = wf[:150] @ x.astype(np.float64)
+    u = wf[150:] @ x.astype(np.float64)
+    close(oracle.nn_swiglu(w, x, 150, cols), g / (1 + np.exp(-g)) * u)
+    xn = oracle.random_f32(3584, 45, 3.0)
+    wn = oracle.f32_to_bf16(oracle.random_f32(3584, 46, 1.0))
+    xd = xn.astype(np.float64)
+    close(oracle.nn_rms_norm(xn, wn, 3584, 1e-6),
+          xd / np.sqrt((xd * xd).mean() + 1e-6) * oracle.bf16_to_f32(wn))
+    for qh, kvh, hd, pos, max_seq in [(14, 2, 64, 37, 64), (32, 2, 64, 655, 704),
+                                      (28, 4, 128, 699, 768), (14, 2, 64, 0, 8)]:
+        q = oracle.random_f32(qh * hd, 61, 2.0).reshape(qh, hd)
+        kc = oracle.random_f32(max_seq * kvh * hd, 62, 2.0).reshape(max_seq, kvh, hd)
+        vc = oracle.random_f32(max_seq * kvh * hd, 63, 1.0).reshape(max_seq, kvh, hd)
+        close(oracle.nn_attention(q, kc, vc, pos),
+              oracle.attention_f64(q, kc, vc, pos))
+
+
+def test_rope_is_a_rotation(oracle):
+    qh, kvh, hd, pos, max_seq = 4, 2, 64, 5, 16
+    cos, sin = oracle.rope_tables(max_seq, hd, 10000.0)
+    q = oracle.random_f32(qh * hd, 51, 1.0).reshape(qh, hd)
+    k = oracle.random_f32(kvh * hd, 52, 1.0).reshape(kvh, hd)
+    v = oracle.random_f32(kvh * hd, 53, 1.0).reshape(kvh, hd)
+    kc = np.zeros((max_seq, kvh, hd), np.float32)
+    vc = np.zeros_like(kc)
+    qr = oracle.nn_rope_and_store(kc, vc, q, k, v, cos, sin, pos)
+    assert np.allclose(np.linalg.norm(qr, axis=1), np.linalg.norm(q, axis=1), rtol=1e-6)
+    assert np.array_equal(vc[pos], v) and not kc[pos + 1].any()
+    # position 0 turns nothing
+    q0 = oracle.nn_rope_and_store(kc, vc, q, k, v, cos, sin, 0)
+    assert np.array_equal(q0, q)
+
+
+def test_llama_generate_is_deterministic_and_causal(oracle):
+    cfg = oracle.LlamaConfig(64, 176, 2, 4, 4, 512, 32)
+    n = oracle.llama_weight_count(cfg)
+    w = (np.random.default_rng(42).standard_normal(n, dtype=np.float32) * 0.02).astype(np.float32)
+    a = oracle.llama_generate(cfg, w, 1, 12)
+    b = oracle.llama_generate(cfg, w, 1, 20)
+    assert a[0] == 1 and np.array_equal(a, b[:13])
+    assert ((0 <= b) & (b < 512)).all()
+
+
+def test_attention_rows_causal_prefix_property(oracle):
+    """Row i of causal attention over S rows equals row i over the first i+1."""
+    rng = np.random.default_rng(10)
+    S, D = 96, 32
+    q, k, v = (oracle.f32_to_bf16(rng.standard_normal((S, D), dtype=np.float32))
+               for _ in range(3))
+    full = oracle.attention_rows(q, k, v, 0.17, True, np.array([40]))
+    cut = oracle.attention_rows(q[:41], k[:41], v[:41], 0.17, False, np.array([40]))
+    assert np.array_equal(full, cut)
+
+
+def test_all_reduce_adds_in_rank_order(oracle):
+    parts = [np.full(5, 0.1 * (r + 1), np.float32) for r in range(4)]
+    want = ((parts[0] + parts[1]) + parts[2]) + parts[3]
+    assert np.array_equal(oracle.all_reduce_sum_f32(parts), want)

@@ -1,0 +1,457 @@
+/* decoder.cu -- one decoder token as one CUDA graph.
+ *
+ * The reference runs a Llama-2 token as 43 separate GEMM dispatches with the
+ * norms, RoPE, attention and SwiGLU on the host between them
+ * (tests/backend/pass/llama2.vx:218-429), or, with std::nn, as about a dozen
+ * kernel launches per layer.  Here a token is five fused kernels per layer
+ * (q/k/v + RoPE + cache store, attention, output projection + residual,
+ * gate/up + SwiGLU, down projection + residual) plus embed, logits and argmax,
+ * recorded once into a CUDA graph and replayed: the token fed to the next step
+ * and the positions live in device memory, so replaying needs no new
+ * parameters.  The attention grid depends on how far the sequence has got, so
+ * a graph is recorded per block of 256 positions.
+ *
+ * Tensor parallel (tp_ranks > 1): every rank holds a slice of the heads and of
+ * the MLP rows; the output and down projections produce partial sums that the
+ * job of vx_collective_init adds (an all-reduce inside the graph), and the
+ * logits are split by vocabulary with an exchange of each rank's best
+ * (value, index).
+ */
+#include "kernels.h"
+#include "vx_b200.h"
+#include "vx_collective.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <string>
+#include <vector>
+
+namespace vxb {
+cudaStream_t caller_stream();
+void note_kernel(const char *name);
+vx::NcclCollective *nccl_job();
+} // namespace vxb
+
+namespace {
+
+[[noreturn]] void stop(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  fputs("[Vx CUDA] FATAL: ", stderr);
+  vfprintf(stderr, fmt, ap);
+  fputc('\n', stderr);
+  va_end(ap);
+  abort();
+}
+#define CUDA_OK(expr)                                                          \
+  do {                                                                         \
+    const cudaError_t e_ = (expr);                                             \
+    if (e_ != cudaSuccess)                                                     \
+      stop("%s failed: %s", #expr, cudaGetErrorString(e_));                    \
+  } while (0)
+
+__global__ void advance_kernel(int32_t *positions, int batch) {
+  if (threadIdx.x < batch)
+    positions[threadIdx.x] += 1;
+}
+
+__global__ void add_kernel(float *x, const float *t, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n)
+    x[i] = x[i] + t[i];
+}
+
+/* pair[b] = (best local logit, its GLOBAL index as float bits). */
+__global__ void best_pair_kernel(float2 *pair, const int32_t *local_best,
+                                 const float *logits, int64_t stride,
+                                 int vocab_offset) {
+  const int b = threadIdx.x;
+  const int i = local_best[b];
+  pair[b] = make_float2(logits[b * stride + i],
+                        __int_as_float(i + vocab_offset));
+}
+/* gathered: [ranks][batch] pairs; the largest value wins, the lowest index on
+   a tie (rank order is index order, so the first rank with the value). */
+__global__ void pick_pair_kernel(int32_t *token, const float2 *gathered,
+                                 int ranks, int batch) {
+  const int b = threadIdx.x;
+  if (b >= batch)
+    return;
+  float best = gathered[b].x;
+  int at = __float_as_int(gathered[b].y);
+  for (int r = 1; r < ranks; ++r) {
+    const float2 p = gathered[r * batch + b];
+    if (p.x > best) {
+      best = p.x;
+      at = __float_as_int(p.y);
+    }
+  }
+  token[b] = at;
+}
+
+} // namespace
+
+struct vx_decoder {
+  vx_decoder_config c;
+  int ranks, q_local, kv_local, hidden_local, vocab_local, vocab_offset;
+  std::vector<const void *> attn_norm, wq, wk, wv, bqkv, wo, ffn_norm, w_gate,
+      w_up, w_down;
+  const void *embed, *final_norm, *lm_head;
+  const float *cos_t, *sin_t;
+  /* device state */
+  float *x, *q, *att, *h, *tmp, *logits, *k_cache, *v_cache, *scratch;
+  int32_t *tokens, *positions, *counters, *local_best;
+  float2 *pair, *pairs_all;
+  int64_t cache_layer_stride, cache_batch_stride;
+  int split;
+  int host_pos;
+  cudaStream_t stream;
+  std::map<int, cudaGraphExec_t> graphs;
+  int kernels_per_step;
+};
+
+namespace {
+
+void need(const char *why, const char *what) {
+  if (why)
+    stop("vx_decoder: %s: %s", what, why);
+}
+
+template <typename T> T *dev_alloc(size_t count) {
+  void *p = nullptr;
+  if (cudaMalloc(&p, count * sizeof(T)) != cudaSuccess)
+    stop("vx_decoder: out of device memory for %zu bytes", count * sizeof(T));
+  CUDA_OK(cudaMemset(p, 0, count * sizeof(T)));
+  return (T *)p;
+}
+
+void all_reduce(vx_decoder *d, float *buf, int64_t count) {
+  vx::NcclCollective *job = vxb::nccl_job();
+  const int r = job->api()->AllReduce(buf, buf, (size_t)count, vx::NcclFloat32,
+                                      vx::NcclSum, job->comm(), d->stream);
+  if (r)
+    stop("vx_decoder: ncclAllReduce failed: %s", job->api()->GetErrorString(r));
+}
+
+/* Queue one token on d->stream. */
+void record_step(vx_decoder *d, int max_pos) {
+  const vx_decoder_config &c = d->c;
+  const bool bf = c.weights_bf16 != 0;
+  const int B = c.batch, hd = c.head_dim;
+  cudaStream_t s = d->stream;
+  int launches = 0;
+
+  need(vxb::embed(d->x, d->embed, bf, d->tokens, c.dim, c.vocab, B, c.dim, s),
+       "embed");
+  ++launches;
+  for (int l = 0; l < c.n_layers; ++l) {
+    vxb::QkvArgs qa{};
+    qa.wq = d->wq[l];
+    qa.wk = d->wk[l];
+    qa.wv = d->wv[l];
+    qa.wbf16 = bf;
+    qa.bias = d->bqkv[l];
+    qa.q_heads = d->q_local;
+    qa.kv_heads = d->kv_local;
+    qa.head_dim = hd;
+    qa.cols = c.dim;
+    qa.x = d->x;
+    qa.x_stride = c.dim;
+    qa.batch = B;
+    qa.norm_w = d->attn_norm[l];
+    qa.norm_bf16 = bf;
+    qa.eps = c.eps;
+    qa.rope_mode = bf ? 0 : 1;
+    qa.cos_t = d->cos_t;
+    qa.sin_t = d->sin_t;
+    qa.cs_cols = hd / 2;
+    qa.theta = c.rope_theta;
+    qa.positions = d->positions;
+    qa.q_out = d->q;
+    qa.k_cache = d->k_cache + l * d->cache_layer_stride;
+    qa.v_cache = d->v_cache + l * d->cache_layer_stride;
+    qa.cache_batch_stride = d->cache_batch_stride;
+    qa.max_seq = c.max_seq;
+    need(vxb::qkv_rope_store(qa, s), "q/k/v");
+
+    vxb::AttnArgs aa{};
+    aa.q = d->q;
+    aa.k_cache = qa.k_cache;
+    aa.v_cache = qa.v_cache;
+    aa.cache_batch_stride = d->cache_batch_stride;
+    aa.out = d->att;
+    aa.q_heads = d->q_local;
+    aa.kv_heads = d->kv_local;
+    aa.head_dim = hd;
+    aa.batch = B;
+    aa.positions = d->positions;
+    aa.max_pos = max_pos;
+    aa.scratch = d->scratch;
+    aa.counters = d->counters;
+    aa.split = d->split;
+    need(vxb::attention_decode(aa, s), "attention");
+
+    vxb::MatvecArgs oa{};
+    oa.w = d->wo[l];
+    oa.wbf16 = bf;
+    oa.rows = c.dim;
+    oa.cols = d->q_local * hd;
+    oa.x = d->att;
+    oa.x_stride = oa.cols;
+    oa.batch = B;
+    oa.y = d->ranks > 1 ? d->tmp : d->x;
+    oa.y_stride = c.dim;
+    oa.mode = d->ranks > 1 ? 0 : 1;
+    need(vxb::matvec(oa, s), "the output projection");
+    launches += 3;
+    if (d->ranks > 1) {
+      all_reduce(d, d->tmp, (int64_t)B * c.dim);
+      add_kernel<<<(B * c.dim + 255) / 256, 256, 0, s>>>(d->x, d->tmp,
+                                                        (int64_t)B * c.dim);
+      launches += 2;
+    }
+
+    vxb::SwigluArgs sa{};
+    sa.w = d->w_gate[l];
+    sa.w_up = d->w_up[l];
+    sa.wbf16 = bf;
+    sa.rows = d->hidden_local;
+    sa.cols = c.dim;
+    sa.x = d->x;
+    sa.x_stride = c.dim;
+    sa.out = d->h;
+    sa.out_stride = d->hidden_local;
+    sa.batch = B;
+    sa.norm_w = d->ffn_norm[l];
+    sa.norm_bf16 = bf;
+    sa.eps = c.eps;
+    need(vxb::swiglu(sa, s), "gate/up");
+
+    vxb::MatvecArgs da{};
+    da.w = d->w_down[l];
+    da.wbf16 = bf;
+    da.rows = c.dim;
+    da.cols = d->hidden_local;
+    da.x = d->h;
+    da.x_stride = d->hidden_local;
+    da.batch = B;
+    da.y = d->ranks > 1 ? d->tmp : d->x;
+    da.y_stride = c.dim;
+    da.mode = d->ranks > 1 ? 0 : 1;
+    need(vxb::matvec(da, s), "the down projection");
+    launches += 2;
+    if (d->ranks > 1) {
+      all_reduce(d, d->tmp, (int64_t)B * c.dim);
+      add_kernel<<<(B * c.dim + 255) / 256, 256, 0, s>>>(d->x, d->tmp,
+                                                        (int64_t)B * c.dim);
+      launches += 2;
+    }
+  }
+
+  vxb::MatvecArgs la{};
+  la.w = d->lm_head;
+  la.wbf16 = bf;
+  la.rows = d->vocab_local;
+  la.cols = c.dim;
+  la.x = d->x;
+  la.x_stride = c.dim;
+  la.batch = B;
+  la.norm_w = d->final_norm;
+  la.norm_bf16 = bf;
+  la.eps = c.eps;
+  la.y = d->logits;
+  la.y_stride = d->vocab_local;
+  la.mode = 0;
+  need(vxb::matvec(la, s), "the logits");
+  if (d->ranks == 1) {
+    need(vxb::argmax(d->tokens, d->logits, d->vocab_local, B, d->vocab_local, s),
+         "argmax");
+    launches += 2;
+  } else {
+    need(vxb::argmax(d->local_best, d->logits, d->vocab_local, B,
+                     d->vocab_local, s),
+         "argmax");
+    best_pair_kernel<<<1, B, 0, s>>>(d->pair, d->local_best, d->logits,
+                                     d->vocab_local, d->vocab_offset);
+    vx::NcclCollective *job = vxb::nccl_job();
+    const int r = job->api()->AllGather(d->pair, d->pairs_all, (size_t)B * 2,
+                                        vx::NcclFloat32, job->comm(), s);
+    if (r)
+      stop("vx_decoder: ncclAllGather failed: %s",
+           job->api()->GetErrorString(r));
+    pick_pair_kernel<<<1, 32, 0, s>>>(d->tokens, d->pairs_all, d->ranks, B);
+    launches += 5;
+  }
+  advance_kernel<<<1, 32, 0, s>>>(d->positions, B);
+  ++launches;
+  d->kernels_per_step = launches;
+}
+
+cudaGraphExec_t graph_for(vx_decoder *d, int bucket) {
+  auto hit = d->graphs.find(bucket);
+  if (hit != d->graphs.end())
+    return hit->second;
+  int max_pos = (bucket + 1) * 256 - 1;
+  if (max_pos > d->c.max_seq - 1)
+    max_pos = d->c.max_seq - 1;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  CUDA_OK(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
+  record_step(d, max_pos);
+  CUDA_OK(cudaStreamEndCapture(d->stream, &graph));
+  CUDA_OK(cudaGraphInstantiate(&exec, graph, 0));
+  CUDA_OK(cudaGraphDestroy(graph));
+  d->graphs[bucket] = exec;
+  return exec;
+}
+
+} // namespace
+
+extern "C" {
+
+vx_decoder *vx_decoder_create(const vx_decoder_config *config,
+                              const vx_decoder_weights *w) {
+  if (!config || !w)
+    stop("vx_decoder_create: a null argument");
+  vx_decoder *d = new vx_decoder();
+  d->c = *config;
+  const vx_decoder_config &c = d->c;
+  d->ranks = c.tp_ranks > 1 ? c.tp_ranks : 1;
+  if (c.dim <= 0 || c.n_layers <= 0 || c.head_dim <= 0 || c.max_seq <= 0 ||
+      c.q_heads % d->ranks || c.kv_heads % d->ranks || c.hidden % d->ranks ||
+      c.vocab % d->ranks)
+    stop("vx_decoder_create: heads, hidden and vocab must divide by tp_ranks");
+  if (c.dim % 8 || c.hidden / d->ranks % 8 || (c.q_heads / d->ranks * c.head_dim) % 8)
+    stop("vx_decoder_create: dim, the local hidden size and the local "
+         "attention width must be multiples of 8");
+  if (c.batch != 1 && c.batch != 2 && c.batch != 4 && c.batch != 8 &&
+      c.batch != 16)
+    stop("vx_decoder_create: batch must be 1, 2, 4, 8 or 16");
+  if (c.weights_bf16 && (!w->cos || !w->sin))
+    stop("vx_decoder_create: the std::nn flavour needs cos and sin tables");
+  int rank = 0;
+  if (d->ranks > 1) {
+    vx::NcclCollective *job = vxb::nccl_job();
+    if (!job || job->ranks() != d->ranks)
+      stop("vx_decoder_create: tp_ranks is %d, but vx_collective_init joined "
+           "a job of %d",
+           d->ranks, job ? job->ranks() : 0);
+    rank = job->rank();
+  }
+  d->q_local = c.q_heads / d->ranks;
+  d->kv_local = c.kv_heads / d->ranks;
+  d->hidden_local = c.hidden / d->ranks;
+  d->vocab_local = c.vocab / d->ranks;
+  d->vocab_offset = rank * d->vocab_local;
+
+  auto copy = [&](std::vector<const void *> &dst, const void *const *src,
+                  bool required, const char *name) {
+    dst.assign(c.n_layers, nullptr);
+    if (!src) {
+      if (required)
+        stop("vx_decoder_create: weights->%s is null", name);
+      return;
+    }
+    for (int l = 0; l < c.n_layers; ++l)
+      dst[l] = src[l];
+  };
+  copy(d->attn_norm, w->attn_norm, true, "attn_norm");
+  copy(d->wq, w->wq, true, "wq");
+  copy(d->wk, w->wk, false, "wk");
+  copy(d->wv, w->wv, false, "wv");
+  copy(d->bqkv, w->bqkv, false, "bqkv");
+  copy(d->wo, w->wo, true, "wo");
+  copy(d->ffn_norm, w->ffn_norm, true, "ffn_norm");
+  copy(d->w_gate, w->w_gate, true, "w_gate");
+  copy(d->w_up, w->w_up, false, "w_up");
+  copy(d->w_down, w->w_down, true, "w_down");
+  d->embed = w->embed;
+  d->final_norm = w->final_norm;
+  d->lm_head = w->lm_head;
+  d->cos_t = w->cos;
+  d->sin_t = w->sin;
+  if (!d->embed || !d->final_norm || !d->lm_head)
+    stop("vx_decoder_create: embed, final_norm and lm_head are required");
+
+  const int B = c.batch;
+  const int tiles = d->q_local; /* upper bound on head tiles */
+  d->split = (int64_t)tiles * B < 128 ? 32 : 128;
+  d->cache_batch_stride = (int64_t)c.max_seq * d->kv_local * c.head_dim;
+  d->cache_layer_stride = d->cache_batch_stride * B;
+  d->x = dev_alloc<float>((size_t)B * c.dim);
+  d->tmp = dev_alloc<float>((size_t)B * c.dim);
+  d->q = dev_alloc<float>((size_t)B * d->q_local * c.head_dim);
+  d->att = dev_alloc<float>((size_t)B * d->q_local * c.head_dim);
+  d->h = dev_alloc<float>((size_t)B * d->hidden_local);
+  d->logits = dev_alloc<float>((size_t)B * d->vocab_local);
+  d->k_cache = dev_alloc<float>((size_t)d->cache_layer_stride * c.n_layers);
+  d->v_cache = dev_alloc<float>((size_t)d->cache_layer_stride * c.n_layers);
+  d->scratch = dev_alloc<float>(vxb::attn_scratch_floats(
+      B, d->q_local, c.head_dim, c.max_seq, d->split));
+  d->counters = dev_alloc<int32_t>((size_t)B * d->q_local + 32);
+  d->tokens = dev_alloc<int32_t>(32);
+  d->positions = dev_alloc<int32_t>(32);
+  d->local_best = dev_alloc<int32_t>(32);
+  d->pair = (float2 *)dev_alloc<float>(2 * 32);
+  d->pairs_all = (float2 *)dev_alloc<float>(2 * 32 * (size_t)d->ranks);
+  d->host_pos = 0;
+  d->kernels_per_step = 0;
+  CUDA_OK(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+  CUDA_OK(cudaDeviceSynchronize());
+  return d;
+}
+
+void vx_decoder_destroy(vx_decoder *d) {
+  if (!d)
+    return;
+  cudaStreamSynchronize(d->stream);
+  for (auto &g : d->graphs)
+    cudaGraphExecDestroy(g.second);
+  for (void *p : {(void *)d->x, (void *)d->tmp, (void *)d->q, (void *)d->att,
+                  (void *)d->h, (void *)d->logits, (void *)d->k_cache,
+                  (void *)d->v_cache, (void *)d->scratch, (void *)d->counters,
+                  (void *)d->tokens, (void *)d->positions,
+                  (void *)d->local_best, (void *)d->pair,
+                  (void *)d->pairs_all})
+    cudaFree(p);
+  cudaStreamDestroy(d->stream);
+  delete d;
+}
+
+void vx_decoder_reset(vx_decoder *d) {
+  CUDA_OK(cudaStreamSynchronize(d->stream));
+  CUDA_OK(cudaMemsetAsync(d->positions, 0, 32 * sizeof(int32_t), d->stream));
+  CUDA_OK(cudaStreamSynchronize(d->stream));
+  d->host_pos = 0;
+}
+
+int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
+                        int32_t *tokens_out) {
+  const int pos = d->host_pos;
+  if (pos >= d->c.max_seq)
+    stop("vx_decoder_step: position %d is past max_seq %d", pos, d->c.max_seq);
+  cudaGraphExec_t exec = graph_for(d, pos / 256);
+  if (tokens_in)
+    CUDA_OK(cudaMemcpyAsync(d->tokens, tokens_in, d->c.batch * sizeof(int32_t),
+                            cudaMemcpyHostToDevice, d->stream));
+  CUDA_OK(cudaGraphLaunch(exec, d->stream));
+  d->host_pos = pos + 1;
+  if (tokens_out) {
+    CUDA_OK(cudaMemcpyAsync(tokens_out, d->tokens, d->c.batch * sizeof(int32_t),
+                            cudaMemcpyDeviceToHost, d->stream));
+    const cudaError_t e = cudaStreamSynchronize(d->stream);
+    if (e != cudaSuccess)
+      stop("a kernel of the decoder faulted: %s", cudaGetErrorString(e));
+  }
+  return pos;
+}
+
+const float *vx_decoder_logits(const vx_decoder *d) { return d->logits; }
+void *vx_decoder_stream(const vx_decoder *d) { return (void *)d->stream; }
+int32_t vx_decoder_kernels_per_step(const vx_decoder *d) {
+  return d->kernels_per_step;
+}
+
+} /* extern "C" */

@@ -1,0 +1,168 @@
+/* kernels.h -- what the host side of the dispatch library asks of the sm_100a
+ * kernels.  Every launcher queues work on `stream` and returns; none waits,
+ * allocates or frees, so each can be recorded into a CUDA graph.  A launcher
+ * that can refuse returns NULL for "queued" or a sentence saying why not.
+ */
+#ifndef VXB_KERNELS_H
+#define VXB_KERNELS_H
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vxb {
+
+/* ---- C[m,n] = A[m,k] * B[k,n], all row-major, strides in elements --------- */
+const char *gemm_f32(const float *a, int64_t lda, const float *b, int64_t ldb,
+                     float *c, int64_t ldc, int64_t m, int64_t n, int64_t k,
+                     cudaStream_t stream);
+const char *gemm_f64(const double *a, int64_t lda, const double *b, int64_t ldb,
+                     double *c, int64_t ldc, int64_t m, int64_t n, int64_t k,
+                     cudaStream_t stream);
+/* 16-bit inputs (is_bf16: bf16, else f16), f32 accumulation, output of the
+   input type.  The tcgen05 path needs 16-byte aligned bases and row strides;
+   anything else takes the warp-tiled kernel below it. */
+const char *gemm_16(bool is_bf16, const void *a, int64_t lda, const void *b,
+                    int64_t ldb, void *c, int64_t ldc, int64_t m, int64_t n,
+                    int64_t k, cudaStream_t stream);
+/* Forced routes, for tests and benchmarks. route: 0 = pick, 1 = tcgen05 with
+   B read as stored (N-major operand), 2 = tcgen05 after transposing B into
+   `scratch` ([n,k], caller-owned), 3 = the plain tiled kernel. */
+const char *gemm_16_route(int route, bool is_bf16, const void *a, int64_t lda,
+                          const void *b, int64_t ldb, void *c, int64_t ldc,
+                          int64_t m, int64_t n, int64_t k, void *scratch,
+                          cudaStream_t stream);
+/* Status words of the tcgen05 kernels (device memory, one per device): 0 = ok;
+   otherwise the first wait that ran out. Read with gemm_status(). */
+int gemm_status(cudaStream_t stream);
+
+/* y[d] = W[d,n] . x[n], f32 (the flat entry point). */
+const char *matvec_f32(float *y, const float *x, const float *w, int n, int d,
+                       cudaStream_t stream);
+
+/* ---- decode operators ------------------------------------------------------
+ * W is bf16 (wbf16) or f32, row-major [rows, cols]; x and y are f32 with
+ * `batch` vectors, row b of x at x + b*x_stride.                            */
+struct MatvecArgs {
+  const void *w;
+  bool wbf16;
+  int rows, cols;
+  const float *x;
+  int64_t x_stride;
+  float *y;
+  int64_t y_stride;
+  int batch;
+  /* prologue: x is RMS-normalised with this weight first (NULL: x as is) */
+  const void *norm_w;
+  bool norm_bf16;
+  float eps;
+  /* epilogue */
+  int mode;            /* 0 y = s, 1 y += s, 2 y = s + bias */
+  const void *bias;    /* mode 2, bf16 */
+};
+const char *matvec(const MatvecArgs &a, cudaStream_t stream);
+
+/* out[r] = silu(g_r) * u_r, g from row r and u from row rows + r of w. */
+struct SwigluArgs {
+  const void *w;
+  bool wbf16;
+  int rows, cols;
+  const void *w_up; /* NULL: up rows follow the gate rows in w */
+  const float *x;
+  int64_t x_stride;
+  float *out;
+  int64_t out_stride;
+  int batch;
+  const void *norm_w;
+  bool norm_bf16;
+  float eps;
+};
+const char *swiglu(const SwigluArgs &a, cudaStream_t stream);
+
+const char *rms_norm(float *y, const float *x, const void *w, bool wbf16, int n,
+                     float eps, int batch, int64_t stride, cudaStream_t stream);
+
+/* q/k/v projection + bias + RoPE + KV-cache store in one kernel.
+   rope_mode 0: half-split pairs (i, i+hd/2) with cos/sin tables [*, hd/2];
+   rope_mode 1: interleaved pairs (i, i+1), angle pos * theta^(-(i%hd)/hd).
+   w rows: q heads, k heads, v heads (wk/wv NULL) or three matrices.
+   positions: device int32[batch] (the position of each sequence).
+   caches: [batch][max_seq, kv_heads, hd] f32. */
+struct QkvArgs {
+  const void *wq, *wk, *wv; /* wk == NULL: fused rows in wq */
+  bool wbf16;
+  const void *bias; /* bf16 or NULL */
+  int q_heads, kv_heads, head_dim, cols;
+  const float *x;
+  int64_t x_stride;
+  int batch;
+  const void *norm_w;
+  bool norm_bf16;
+  float eps;
+  int rope_mode;
+  const float *cos_t, *sin_t;
+  int cs_cols;
+  float theta;
+  const int32_t *positions;
+  float *q_out; /* [batch][q_heads*hd] */
+  float *k_cache, *v_cache;
+  int64_t cache_batch_stride;
+  int max_seq;
+};
+const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream);
+
+/* The unfused pieces, for the operator surface. */
+const char *rope_and_store(float *q_out, float *k_cache, float *v_cache,
+                           const float *q, const float *k, const float *v,
+                           const float *cos_t, const float *sin_t, int cs_cols,
+                           int pos, int q_heads, int kv_heads, int head_dim,
+                           cudaStream_t stream);
+
+/* Split-KV attention of one new token per sequence over rows 0..pos of the
+   cache, with the merge done by the last block of each head.
+   scratch: f32 [batch][q_heads][splits][head_dim + 2] plus int32 counters
+   [batch][q_heads] that are zero before the launch and zero after it. */
+struct AttnArgs {
+  const float *q; /* [batch][q_heads*hd] */
+  const float *k_cache, *v_cache;
+  int64_t cache_batch_stride;
+  float *out; /* [batch][q_heads*hd] */
+  int q_heads, kv_heads, head_dim, batch;
+  const int32_t *positions; /* device, [batch] */
+  int max_pos;              /* host bound on positions: sizes the grid */
+  float *scratch;
+  int32_t *counters;
+  int split; /* positions per block */
+};
+size_t attn_scratch_floats(int batch, int q_heads, int head_dim, int max_seq,
+                           int split);
+const char *attention_decode(const AttnArgs &a, cudaStream_t stream);
+
+const char *argmax(int32_t *out, const float *logits, int n, int batch,
+                   int64_t stride, cudaStream_t stream);
+const char *embed(float *x, const void *table, bool tbf16, const int32_t *token,
+                  int dim, int rows, int batch, int64_t x_stride,
+                  cudaStream_t stream);
+
+/* ---- flash attention forward, bf16, [B,H,S,D] ------------------------------ */
+const char *flash_attention_fwd(const void *q, const void *k, const void *v,
+                                void *out, int B, int H, int S, int D,
+                                float scale, bool causal, cudaStream_t stream);
+int flash_status(cudaStream_t stream);
+
+/* ---- small utilities --------------------------------------------------------*/
+const char *transpose_16(const void *in, int64_t ld_in, void *out,
+                         int64_t ld_out, int64_t rows, int64_t cols,
+                         cudaStream_t stream);
+/* out[i] = N(0, sigma^2) (or U[lo,hi)) from a counter-based generator, as f32
+   or rounded to bf16. Used to make synthetic weights on the device. */
+const char *fill_normal(void *out, bool as_bf16, int64_t n, uint64_t seed,
+                        float sigma, cudaStream_t stream);
+const char *fill_uniform(void *out, bool as_bf16, int64_t n, uint64_t seed,
+                         float lo, float hi, cudaStream_t stream);
+const char *interleave_gathered(const void *gathered, void *out, int ranks,
+                                int64_t m, int64_t n_local, int elem_bytes,
+                                cudaStream_t stream);
+
+} // namespace vxb
+
+#endif /* VXB_KERNELS_H */

@@ -1,0 +1,464 @@
+/* nn_api.cu -- the entry points of include/vx_b200.h: the std::nn operator
+ * surface in the `pub fn` C convention, the whole-token decoder, and the direct
+ * GEMM / attention / utility calls.  Checks here mirror the asserts of the Vx
+ * functions in stdlib/std/nn.vx (nn_check_matrix, nn_check_heads,
+ * nn_check_cache): a refused shape stops the program with the function's name.
+ */
+#include "kernels.h"
+#include "vx_b200.h"
+#include "vx_collective.h"
+#include "vx_hardware_runtime.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace vxb {
+cudaStream_t caller_stream();
+void note_kernel(const char *name);
+vx::NcclCollective *nccl_job();
+} // namespace vxb
+
+namespace {
+
+[[noreturn]] void stop(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  fputs("[Vx CUDA] FATAL: ", stderr);
+  vfprintf(stderr, fmt, ap);
+  fputc('\n', stderr);
+  va_end(ap);
+  abort();
+}
+
+thread_local std::string t_error;
+int32_t fail(const char *why) {
+  t_error = why ? why : "unknown";
+  return -1;
+}
+int32_t done(const char *why, const char *kernel) {
+  if (why)
+    return fail(why);
+  vxb::note_kernel(kernel);
+  return 0;
+}
+void must(const char *why, const char *fn) {
+  if (why)
+    stop("%s: %s", fn, why);
+  vxb::note_kernel(fn);
+}
+
+/* A packed tensor's data pointer; a gap between rows is refused as a `pub fn`
+   refuses it (docs/lang/abi.md section 3.6, "Packed tensors"). */
+template <typename T>
+T *packed(const char *fn, const char *name, void *aligned, int64_t offset,
+          int rank, const int64_t *sizes, const int64_t *strides) {
+  int64_t expect = 1;
+  bool empty = false;
+  for (int d = 0; d < rank; ++d)
+    empty |= sizes[d] == 0;
+  for (int d = rank - 1; d >= 0 && !empty; --d) {
+    if (sizes[d] != 1 && strides[d] != expect)
+      stop("%s: the tensor `%s` has a gap: stride %lld of axis %d, where a "
+           "packed tensor has %lld",
+           fn, name, (long long)strides[d], d, (long long)expect);
+    expect *= sizes[d];
+  }
+  return (T *)aligned + offset;
+}
+#define T1(T, t)                                                               \
+  packed<T>(FN, #t, t##_aligned, t##_offset, 1, &t##_n0, &t##_s0)
+#define T2(T, t)                                                               \
+  [&] {                                                                        \
+    const int64_t n_[2] = {t##_n0, t##_n1}, s_[2] = {t##_s0, t##_s1};          \
+    return packed<T>(FN, #t, t##_aligned, t##_offset, 2, n_, s_);              \
+  }()
+#define T3(T, t)                                                               \
+  [&] {                                                                        \
+    const int64_t n_[3] = {t##_n0, t##_n1, t##_n2},                            \
+                  s_[3] = {t##_s0, t##_s1, t##_s2};                            \
+    return packed<T>(FN, #t, t##_aligned, t##_offset, 3, n_, s_);              \
+  }()
+#define T4(T, t)                                                               \
+  [&] {                                                                        \
+    const int64_t n_[4] = {t##_n0, t##_n1, t##_n2, t##_n3},                    \
+                  s_[4] = {t##_s0, t##_s1, t##_s2, t##_s3};                    \
+    return packed<T>(FN, #t, t##_aligned, t##_offset, 4, n_, s_);              \
+  }()
+#define UNUSED_ALLOC(t) (void)t##_allocated
+
+/* nn_check_matrix: y has rows values, w rows*cols, x cols; cols % 8 == 0. */
+void check_matrix(const char *fn, int64_t y_len, int64_t w_len, int64_t x_len,
+                  int rows, int cols) {
+  if (rows <= 0 || cols <= 0 || cols % 8 != 0)
+    stop("%s: rows and cols must be positive, and cols a multiple of 8", fn);
+  if (y_len < rows || w_len < (int64_t)rows * cols || x_len < cols)
+    stop("%s: a tensor is smaller than rows and cols say", fn);
+}
+void check_heads(const char *fn, int64_t e0, int64_t e1, int heads, int hd) {
+  if (heads <= 0 || hd <= 0 || hd % 8 != 0 || hd > 128 || e0 < heads || e1 != hd)
+    stop("%s: a tensor of heads must be [heads, head_dim], with head_dim a "
+         "multiple of 8 and at most 128",
+         fn);
+}
+void check_cache(const char *fn, int64_t e0, int64_t e1, int64_t e2, int pos,
+                 int kv_heads, int hd) {
+  if (pos < 0 || pos >= e0 || e1 != kv_heads || e2 != hd)
+    stop("%s: the KV cache must be [max_seq, kv_heads, head_dim] with a row "
+         "for `pos`",
+         fn);
+}
+
+/* Zeroed counters for the attention kernel's "last block merges" step, one
+   buffer per GPU, kept for the life of the process. */
+int32_t *attention_counters() {
+  static std::mutex mu;
+  static std::map<int, int32_t *> per_device;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  int32_t *&p = per_device[dev];
+  if (!p) {
+    if (cudaMalloc(&p, 16384 * sizeof(int32_t)) != cudaSuccess ||
+        cudaMemset(p, 0, 16384 * sizeof(int32_t)) != cudaSuccess)
+      stop("out of device memory for the attention counters");
+  }
+  return p;
+}
+
+int32_t *device_i32(int value) {
+  /* A position that a kernel reads from device memory. One slot per GPU and
+     value would be wasteful; positions up to 64 Ki are made once per GPU. */
+  static std::mutex mu;
+  static std::map<int, int32_t *> per_device;
+  constexpr int kMost = 1 << 16;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  int32_t *&p = per_device[dev];
+  if (!p) {
+    std::vector<int32_t> iota(kMost);
+    for (int i = 0; i < kMost; ++i)
+      iota[i] = i;
+    if (cudaMalloc(&p, kMost * sizeof(int32_t)) != cudaSuccess ||
+        cudaMemcpy(p, iota.data(), kMost * sizeof(int32_t),
+                   cudaMemcpyHostToDevice) != cudaSuccess)
+      stop("out of device memory for the position table");
+  }
+  if (value < 0 || value >= kMost)
+    stop("a position of %d is outside 0..65535", value);
+  return p + value;
+}
+
+} // namespace
+
+extern "C" {
+
+const char *vx_b200_last_error(void) { return t_error.c_str(); }
+
+/* ------------------------------------------------------------------ std::nn */
+#define FN "nn_matvec"
+void vx_nn_matvec(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(x), int32_t rows,
+                  int32_t cols) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(x);
+  check_matrix(FN, y_n0, w_n0, x_n0, rows, cols);
+  vxb::MatvecArgs a{};
+  a.w = T1(uint16_t, w);
+  a.wbf16 = true;
+  a.rows = rows;
+  a.cols = cols;
+  a.x = T1(float, x);
+  a.x_stride = cols;
+  a.y = T1(float, y);
+  a.y_stride = rows;
+  a.batch = 1;
+  a.mode = 0;
+  must(vxb::matvec(a, vxb::caller_stream()), FN);
+}
+#undef FN
+
+#define FN "nn_matvec_add"
+void vx_nn_matvec_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(x), int32_t rows,
+                      int32_t cols) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(x);
+  check_matrix(FN, y_n0, w_n0, x_n0, rows, cols);
+  vxb::MatvecArgs a{};
+  a.w = T1(uint16_t, w);
+  a.wbf16 = true;
+  a.rows = rows;
+  a.cols = cols;
+  a.x = T1(float, x);
+  a.x_stride = cols;
+  a.y = T1(float, y);
+  a.y_stride = rows;
+  a.batch = 1;
+  a.mode = 1;
+  must(vxb::matvec(a, vxb::caller_stream()), FN);
+}
+#undef FN
+
+#define FN "nn_matvec_heads_add"
+void vx_nn_matvec_heads_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR2(x),
+                            int32_t rows, int32_t heads, int32_t head_dim) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(x);
+  const int cols = heads * head_dim;
+  check_heads(FN, x_n0, x_n1, heads, head_dim);
+  check_matrix(FN, y_n0, w_n0, cols, rows, cols);
+  vxb::MatvecArgs a{};
+  a.w = T1(uint16_t, w);
+  a.wbf16 = true;
+  a.rows = rows;
+  a.cols = cols;
+  a.x = T2(float, x); /* packed [heads, head_dim] is the flat vector */
+  a.x_stride = cols;
+  a.y = T1(float, y);
+  a.y_stride = rows;
+  a.batch = 1;
+  a.mode = 1;
+  must(vxb::matvec(a, vxb::caller_stream()), FN);
+}
+#undef FN
+
+#define FN "nn_qkv"
+void vx_nn_qkv(VX_TENSOR2(q), VX_TENSOR2(k), VX_TENSOR2(v), VX_TENSOR1(w),
+               VX_TENSOR1(b), VX_TENSOR1(x), int32_t q_heads, int32_t kv_heads,
+               int32_t head_dim, int32_t cols) {
+  UNUSED_ALLOC(q); UNUSED_ALLOC(k); UNUSED_ALLOC(v);
+  UNUSED_ALLOC(w); UNUSED_ALLOC(b); UNUSED_ALLOC(x);
+  const int heads = q_heads + 2 * kv_heads;
+  check_heads(FN, q_n0, q_n1, q_heads, head_dim);
+  check_heads(FN, k_n0, k_n1, kv_heads, head_dim);
+  check_heads(FN, v_n0, v_n1, kv_heads, head_dim);
+  check_matrix(FN, b_n0, w_n0, x_n0, heads * head_dim, cols);
+  /* Three row ranges of one matrix, each with its slice of the bias. */
+  const uint16_t *wp = T1(uint16_t, w), *bp = T1(uint16_t, b);
+  const float *xp = T1(float, x);
+  float *outs[3] = {T2(float, q), T2(float, k), T2(float, v)};
+  const int counts[3] = {q_heads, kv_heads, kv_heads};
+  int64_t row = 0;
+  for (int part = 0; part < 3; ++part) {
+    vxb::MatvecArgs a{};
+    a.w = wp + row * cols;
+    a.wbf16 = true;
+    a.rows = counts[part] * head_dim;
+    a.cols = cols;
+    a.x = xp;
+    a.x_stride = cols;
+    a.y = outs[part];
+    a.y_stride = a.rows;
+    a.batch = 1;
+    a.mode = 2;
+    a.bias = bp + row;
+    must(vxb::matvec(a, vxb::caller_stream()), FN);
+    row += a.rows;
+  }
+}
+#undef FN
+
+#define FN "nn_swiglu"
+void vx_nn_swiglu(VX_TENSOR1(out), VX_TENSOR1(w), VX_TENSOR1(x), int32_t rows,
+                  int32_t cols) {
+  UNUSED_ALLOC(out); UNUSED_ALLOC(w); UNUSED_ALLOC(x);
+  check_matrix(FN, out_n0, w_n0 / 2, x_n0, rows, cols);
+  vxb::SwigluArgs a{};
+  a.w = T1(uint16_t, w);
+  a.wbf16 = true;
+  a.rows = rows;
+  a.cols = cols;
+  a.x = T1(float, x);
+  a.x_stride = cols;
+  a.out = T1(float, out);
+  a.out_stride = rows;
+  a.batch = 1;
+  must(vxb::swiglu(a, vxb::caller_stream()), FN);
+}
+#undef FN
+
+#define FN "nn_rms_norm"
+void vx_nn_rms_norm(VX_TENSOR1(y), VX_TENSOR1(x), VX_TENSOR1(w), int32_t n,
+                    float eps) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(x); UNUSED_ALLOC(w);
+  if (n <= 0 || y_n0 < n || x_n0 < n || w_n0 < n)
+    stop("nn_rms_norm: a tensor has fewer than n values");
+  must(vxb::rms_norm(T1(float, y), T1(float, x), T1(uint16_t, w), true, n, eps,
+                     1, n, vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+#define FN "nn_rope_and_store"
+void vx_nn_rope_and_store(VX_TENSOR2(q_out), VX_TENSOR3(k_cache),
+                          VX_TENSOR3(v_cache), VX_TENSOR2(q), VX_TENSOR2(k),
+                          VX_TENSOR2(v), VX_TENSOR2(cos), VX_TENSOR2(sin),
+                          int32_t pos, int32_t q_heads, int32_t kv_heads,
+                          int32_t head_dim) {
+  UNUSED_ALLOC(q_out); UNUSED_ALLOC(k_cache); UNUSED_ALLOC(v_cache);
+  UNUSED_ALLOC(q); UNUSED_ALLOC(k); UNUSED_ALLOC(v);
+  UNUSED_ALLOC(cos); UNUSED_ALLOC(sin);
+  const int half = head_dim / 2;
+  check_heads(FN, q_n0, q_n1, q_heads, head_dim);
+  check_heads(FN, q_out_n0, q_out_n1, q_heads, head_dim);
+  check_heads(FN, k_n0, k_n1, kv_heads, head_dim);
+  check_heads(FN, v_n0, v_n1, kv_heads, head_dim);
+  check_cache(FN, k_cache_n0, k_cache_n1, k_cache_n2, pos, kv_heads, head_dim);
+  check_cache(FN, v_cache_n0, v_cache_n1, v_cache_n2, pos, kv_heads, head_dim);
+  if (pos >= cos_n0 || pos >= sin_n0 || half > cos_n1 || half > sin_n1 ||
+      cos_n1 != sin_n1)
+    stop("nn_rope_and_store: `cos` and `sin` need a row for `pos` with "
+         "head_dim / 2 values");
+  must(vxb::rope_and_store(T2(float, q_out), T3(float, k_cache),
+                           T3(float, v_cache), T2(float, q), T2(float, k),
+                           T2(float, v), T2(float, cos), T2(float, sin),
+                           (int)cos_n1, pos, q_heads, kv_heads, head_dim,
+                           vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+#define FN "nn_attention"
+void vx_nn_attention(VX_TENSOR2(out), VX_TENSOR4(part), VX_TENSOR2(q),
+                     VX_TENSOR3(k_cache), VX_TENSOR3(v_cache), int32_t pos,
+                     int32_t q_heads, int32_t kv_heads, int32_t head_dim) {
+  UNUSED_ALLOC(out); UNUSED_ALLOC(part); UNUSED_ALLOC(q);
+  UNUSED_ALLOC(k_cache); UNUSED_ALLOC(v_cache);
+  check_heads(FN, q_n0, q_n1, q_heads, head_dim);
+  check_heads(FN, out_n0, out_n1, q_heads, head_dim);
+  check_cache(FN, k_cache_n0, k_cache_n1, k_cache_n2, pos, kv_heads, head_dim);
+  check_cache(FN, v_cache_n0, v_cache_n1, v_cache_n2, pos, kv_heads, head_dim);
+  if (kv_heads <= 0 || q_heads % kv_heads != 0)
+    stop("nn_attention: q_heads must be a multiple of kv_heads");
+  if (head_dim % 32 != 0 || head_dim > 128)
+    stop("nn_attention: head_dim must be a multiple of 32, and at most 128");
+  /* The reference splits the positions 32 to a block below 640 and 64 from
+     there on, and sizes `part` for that (nn.vx:356-361); the same split keeps
+     this kernel inside the same scratch. */
+  const int n_pos = pos >= 640 ? 64 : 32;
+  const int group = q_heads / kv_heads;
+  if (part_n0 < (int64_t)kv_heads * ((group + 7) / 8) ||
+      part_n1 < (pos + n_pos) / n_pos || part_n2 < 8 || part_n3 < head_dim + 2)
+    stop("nn_attention: `part` is too small for this position. Make it with "
+         "nn_attention_scratch");
+  vxb::AttnArgs a{};
+  a.q = T2(float, q);
+  a.k_cache = T3(float, k_cache);
+  a.v_cache = T3(float, v_cache);
+  a.cache_batch_stride = 0;
+  a.out = T2(float, out);
+  a.q_heads = q_heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.batch = 1;
+  a.positions = device_i32(pos);
+  a.max_pos = pos;
+  a.scratch = T4(float, part);
+  a.counters = attention_counters();
+  a.split = n_pos;
+  must(vxb::attention_decode(a, vxb::caller_stream()), FN);
+}
+#undef FN
+
+#define FN "nn_argmax"
+void vx_nn_argmax(VX_TENSOR1(out), VX_TENSOR1(logits), int32_t n) {
+  UNUSED_ALLOC(out); UNUSED_ALLOC(logits);
+  if (n <= 0 || logits_n0 < n || out_n0 < 1)
+    stop("nn_argmax: `logits` has fewer than n values, or `out` is empty");
+  must(vxb::argmax(T1(int32_t, out), T1(float, logits), n, 1, n,
+                   vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+#define FN "nn_embed"
+void vx_nn_embed(VX_TENSOR1(x), VX_TENSOR1(table), VX_TENSOR1(token),
+                 int32_t dim) {
+  UNUSED_ALLOC(x); UNUSED_ALLOC(table); UNUSED_ALLOC(token);
+  if (dim <= 0 || x_n0 < dim || token_n0 < 1)
+    stop("nn_embed: `x` has fewer than dim values, or `token` is empty");
+  must(vxb::embed(T1(float, x), T1(uint16_t, table), true, T1(int32_t, token),
+                  dim, (int)(table_n0 / dim), 1, dim, vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+/* --------------------------------------------------------------- direct calls */
+int32_t vx_b200_gemm(int32_t dtype, int32_t route, int64_t m, int64_t n,
+                     int64_t k, const void *a, int64_t lda, const void *b,
+                     int64_t ldb, void *c, int64_t ldc, void *scratch) {
+  cudaStream_t s = vxb::caller_stream();
+  switch (dtype) {
+  case VX_DTYPE_F32:
+    return done(vxb::gemm_f32((const float *)a, lda, (const float *)b, ldb,
+                              (float *)c, ldc, m, n, k, s),
+                "a GEMM");
+  case VX_DTYPE_F64:
+    return done(vxb::gemm_f64((const double *)a, lda, (const double *)b, ldb,
+                              (double *)c, ldc, m, n, k, s),
+                "a GEMM");
+  case VX_DTYPE_F16:
+  case VX_DTYPE_BF16: {
+    const bool bf = dtype == VX_DTYPE_BF16;
+    return done(route == 0 ? vxb::gemm_16(bf, a, lda, b, ldb, c, ldc, m, n, k, s)
+                           : vxb::gemm_16_route(route, bf, a, lda, b, ldb, c,
+                                                ldc, m, n, k, scratch, s),
+                "a GEMM");
+  }
+  default:
+    return fail("vx_b200_gemm takes f32, f64, f16 or bf16");
+  }
+}
+
+int32_t vx_b200_kernel_status(void) {
+  const int g = vxb::gemm_status(vxb::caller_stream());
+  const int f = vxb::flash_status(vxb::caller_stream());
+  return g ? g : f;
+}
+
+int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,
+                                void *out, int32_t B, int32_t H, int32_t S,
+                                int32_t D, float scale, int32_t causal) {
+  return done(vxb::flash_attention_fwd(q, k, v, out, B, H, S, D, scale,
+                                       causal != 0, vxb::caller_stream()),
+              "flash attention");
+}
+
+int32_t vx_b200_gemm_column_split(int32_t dtype, int64_t m, int64_t n_local,
+                                  int64_t k, const void *a, const void *b_local,
+                                  void *c_local, void *gathered, void *c_full) {
+  if (dtype != VX_DTYPE_BF16)
+    return fail("the column-split product takes bf16");
+  cudaStream_t s = vxb::caller_stream();
+  if (const char *why = vxb::gemm_16(true, a, k, b_local, n_local, c_local,
+                                     n_local, m, n_local, k, s))
+    return fail(why);
+  vx::NcclCollective *job = vxb::nccl_job();
+  const int ranks = job ? job->ranks() : 0;
+  if (ranks < 1)
+    return fail("vx_collective_init has not run");
+  const std::string why =
+      job->all_gather(c_local, gathered, m * n_local, vx::NcclBfloat16,
+                      "vx_b200_gemm_column_split");
+  if (!why.empty())
+    return fail(why.c_str());
+  return done(vxb::interleave_gathered(gathered, c_full, ranks, m, n_local, 2, s),
+              "a column-split GEMM");
+}
+
+int32_t vx_b200_fill_normal(void *out, int32_t as_bf16, int64_t n, uint64_t seed,
+                            float sigma) {
+  return done(vxb::fill_normal(out, as_bf16 != 0, n, seed, sigma,
+                               vxb::caller_stream()),
+              "a fill");
+}
+int32_t vx_b200_fill_uniform(void *out, int32_t as_bf16, int64_t n,
+                             uint64_t seed, float lo, float hi) {
+  return done(vxb::fill_uniform(out, as_bf16 != 0, n, seed, lo, hi,
+                                vxb::caller_stream()),
+              "a fill");
+}
+
+} /* extern "C" */

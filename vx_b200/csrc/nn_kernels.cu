@@ -1,0 +1,861 @@
+/* nn_kernels.cu -- the decode operators of one transformer token: bandwidth
+ * bound, so every kernel is organised around streaming its weights (or its KV
+ * cache) once, with 16-byte loads that a warp issues over consecutive
+ * addresses, several in flight per lane, and warp-shuffle reductions.
+ *
+ * The arithmetic is the one the reference states in stdlib/std/nn.vx (bf16
+ * weights, f32 activations, f32 sums; half-split RoPE with tables) and in
+ * tests/backend/pass/llama2.vx:218-429 (f32 weights, interleaved RoPE computed
+ * from pos, eps added after the mean); each kernel names the functions it
+ * covers.  Where the reference launches one kernel per operator, these fuse
+ * what follows a projection into it: RMSNorm in front of the q/k/v and the
+ * gate/up projections, bias + RoPE + KV-cache store behind q/k/v, SwiGLU
+ * behind gate/up, the residual add behind the output and down projections, and
+ * the merge of the split-KV attention parts into the attention kernel itself.
+ *
+ * No float atomics and a fixed order in every reduction: the same inputs give
+ * the same bits on every run.
+ */
+#include "kernels.h"
+
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <mutex>
+
+namespace vxb {
+namespace {
+
+constexpr int WARPS = 8;             /* per block, projection kernels */
+constexpr int MAX_SMEM_X = 96 * 1024; /* x (all batch rows) staged per block */
+
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float bf_lo(uint32_t u) {
+  return __uint_as_float(u << 16);
+}
+__device__ __forceinline__ float bf_hi(uint32_t u) {
+  return __uint_as_float(u & 0xffff0000u);
+}
+__device__ __forceinline__ float bf16_at(const void *p, int64_t i) {
+  return __uint_as_float((uint32_t)((const uint16_t *)p)[i] << 16);
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+/* Sum over the block; every thread gets the result. `red` holds 32 floats. */
+__device__ float block_sum(float v, float *red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0)
+    red[warp] = v;
+  __syncthreads();
+  float t = 0.0f;
+  for (int w = 0; w < nwarps; ++w) /* fixed order */
+    t += red[w];
+  return t;
+}
+
+/* ---------------------------------------------------------------- row dots
+ * One kernel for every projection of the decoder.  An ITEM is a pair of weight
+ * rows whose results the epilogue needs together; a warp owns a contiguous,
+ * balanced range of items and streams both rows of an item at once. */
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_BIAS = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
+
+struct RowDotParams {
+  /* weights */
+  const void *w0, *w1, *w2; /* matvec: w0; swiglu: gate w0, up w1; qkv: q,k,v */
+  int rows, cols;
+  int items;
+  /* activations */
+  const float *x;
+  int64_t x_stride;
+  int batch;
+  int x_in_smem;
+  const void *norm_w;
+  int norm_bf16;
+  float eps;
+  /* outputs */
+  float *y;
+  int64_t y_stride;
+  const void *bias;
+  /* qkv */
+  int q_heads, kv_heads, head_dim, rope_mode;
+  const float *cos_t, *sin_t;
+  int cs_cols;
+  float theta;
+  const int32_t *positions;
+  float *k_cache, *v_cache;
+  int64_t cache_batch_stride;
+  int max_seq;
+};
+
+template <typename W> struct WTraits;
+template <> struct WTraits<__nv_bfloat16> {
+  static constexpr int kLoads = 1; /* 16-byte loads per 8 columns */
+};
+template <> struct WTraits<float> {
+  static constexpr int kLoads = 2;
+};
+
+/* acc[b] += sum over 8 columns of w * x[b]. */
+template <typename W, int B>
+__device__ __forceinline__ void fma8(const uint4 (&wv)[WTraits<W>::kLoads],
+                                     const float (&xv)[B][8], float (&acc)[B]) {
+  float wf[8];
+  if (WTraits<W>::kLoads == 1) {
+    wf[0] = bf_lo(wv[0].x); wf[1] = bf_hi(wv[0].x);
+    wf[2] = bf_lo(wv[0].y); wf[3] = bf_hi(wv[0].y);
+    wf[4] = bf_lo(wv[0].z); wf[5] = bf_hi(wv[0].z);
+    wf[6] = bf_lo(wv[0].w); wf[7] = bf_hi(wv[0].w);
+  } else {
+    const uint4 &a = wv[0], &b = wv[WTraits<W>::kLoads - 1];
+    wf[0] = __uint_as_float(a.x); wf[1] = __uint_as_float(a.y);
+    wf[2] = __uint_as_float(a.z); wf[3] = __uint_as_float(a.w);
+    wf[4] = __uint_as_float(b.x); wf[5] = __uint_as_float(b.y);
+    wf[6] = __uint_as_float(b.z); wf[7] = __uint_as_float(b.w);
+  }
+#pragma unroll
+  for (int b = 0; b < B; ++b)
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      acc[b] = fmaf(wf[e], xv[b][e], acc[b]);
+}
+
+template <typename W, int B, int EPI>
+__global__ void __launch_bounds__(WARPS * 32)
+rowdot_kernel(const RowDotParams p) {
+  extern __shared__ __align__(16) float xs[]; /* [B][cols] when x_in_smem */
+  __shared__ float red[32];
+  __shared__ float inv_rms[B];
+  constexpr int L = WTraits<W>::kLoads;
+  constexpr int UNROLL = B == 1 ? 4 : (B == 2 ? 2 : 1);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int cols = p.cols;
+
+  /* ---- prologue: x (normalised if asked) into shared memory ---- */
+  if (p.norm_w) {
+    for (int b = 0; b < B; ++b) {
+      float ss = 0.0f;
+      for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float v = p.x[b * p.x_stride + i];
+        if (p.x_in_smem)
+          xs[b * cols + i] = v;
+        ss = fmaf(v, v, ss);
+      }
+      ss = block_sum(ss, red);
+      if (threadIdx.x == 0)
+        inv_rms[b] = 1.0f / sqrtf(ss / (float)cols + p.eps);
+    }
+    __syncthreads();
+    /* nn_rms_norm (nn.vx:212-239): y = x * inv * w.  llama2.vx rmsnorm
+       (:476-498): w * (inv * x).  Both are two roundings of the same three
+       factors; the order below is the first one. */
+    for (int b = 0; b < B; ++b) {
+      const float inv = inv_rms[b];
+      for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float wn = p.norm_bf16 ? bf16_at(p.norm_w, i)
+                                     : ((const float *)p.norm_w)[i];
+        xs[b * cols + i] = xs[b * cols + i] * inv * wn;
+      }
+    }
+    __syncthreads();
+  } else if (p.x_in_smem) {
+    for (int b = 0; b < B; ++b)
+      for (int i = threadIdx.x; i < cols; i += blockDim.x)
+        xs[b * cols + i] = p.x[b * p.x_stride + i];
+    __syncthreads();
+  }
+  const float *xbase = p.x_in_smem ? xs : p.x;
+  const int64_t xstr = p.x_in_smem ? cols : p.x_stride;
+
+  /* ---- this warp's items ---- */
+  const int64_t total_warps = (int64_t)gridDim.x * WARPS;
+  const int64_t gw = (int64_t)blockIdx.x * WARPS + warp;
+  const int first = (int)(gw * p.items / total_warps);
+  const int last = (int)((gw + 1) * p.items / total_warps);
+
+  for (int item = first; item < last; ++item) {
+    /* which two rows */
+    const W *r0 = nullptr, *r1 = nullptr;
+    int head = 0, idx = 0, kind = 0; /* qkv: kind 0 q, 1 k, 2 v */
+    if (EPI == EPI_SWIGLU) {
+      r0 = (const W *)p.w0 + (int64_t)item * cols;
+      r1 = p.w1 ? (const W *)p.w1 + (int64_t)item * cols
+                : (const W *)p.w0 + (int64_t)(p.rows + item) * cols;
+    } else if (EPI == EPI_QKV) {
+      const int half = p.head_dim / 2;
+      head = item / half;
+      idx = item - head * half;
+      const int a = p.rope_mode == 0 ? idx : 2 * idx;
+      const int b = p.rope_mode == 0 ? idx + half : 2 * idx + 1;
+      const W *base;
+      int local = head;
+      if (head < p.q_heads) {
+        kind = 0;
+        base = (const W *)p.w0;
+      } else if (head < p.q_heads + p.kv_heads) {
+        kind = 1;
+        local = head - p.q_heads;
+        base = p.w1 ? (const W *)p.w1
+                    : (const W *)p.w0 + (int64_t)p.q_heads * p.head_dim * cols;
+      } else {
+        kind = 2;
+        local = head - p.q_heads - p.kv_heads;
+        base = p.w2 ? (const W *)p.w2
+                    : (const W *)p.w0 + (int64_t)(p.q_heads + p.kv_heads) *
+                                            p.head_dim * cols;
+      }
+      r0 = base + ((int64_t)local * p.head_dim + a) * cols;
+      r1 = base + ((int64_t)local * p.head_dim + b) * cols;
+    } else {
+      r0 = (const W *)p.w0 + (int64_t)(2 * item) * cols;
+      r1 = 2 * item + 1 < p.rows ? r0 + cols : nullptr;
+    }
+    const W *r1s = r1 ? r1 : r0; /* an odd tail streams row 0 twice */
+
+    float s0[B], s1[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b)
+      s0[b] = s1[b] = 0.0f;
+
+    for (int c0 = lane * 8; c0 < cols; c0 += 256 * UNROLL) {
+      uint4 wa[UNROLL][L], wb[UNROLL][L];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + u * 256;
+        if (c < cols) {
+#pragma unroll
+          for (int l = 0; l < L; ++l) {
+            wa[u][l] = ld_stream((const char *)(r0 + c) + 16 * l);
+            wb[u][l] = ld_stream((const char *)(r1s + c) + 16 * l);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = c0 + u * 256;
+        if (c < cols) {
+          float xv[B][8];
+#pragma unroll
+          for (int b = 0; b < B; ++b) {
+            const float4 lo =
+                *reinterpret_cast<const float4 *>(xbase + b * xstr + c);
+            const float4 hi =
+                *reinterpret_cast<const float4 *>(xbase + b * xstr + c + 4);
+            xv[b][0] = lo.x; xv[b][1] = lo.y; xv[b][2] = lo.z; xv[b][3] = lo.w;
+            xv[b][4] = hi.x; xv[b][5] = hi.y; xv[b][6] = hi.z; xv[b][7] = hi.w;
+          }
+          fma8<W, B>(wa[u], xv, s0);
+          fma8<W, B>(wb[u], xv, s1);
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      s0[b] = warp_sum(s0[b]);
+      s1[b] = warp_sum(s1[b]);
+    }
+    if (lane != 0)
+      continue;
+
+    /* ---- epilogue, lane 0 ---- */
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      if (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_BIAS) {
+        float *y = p.y + b * p.y_stride;
+        const int ra = 2 * item, rb = 2 * item + 1;
+        float v0 = s0[b], v1 = s1[b];
+        if (EPI == EPI_ADD) {
+          v0 = y[ra] + v0;
+          if (r1)
+            v1 = y[rb] + v1;
+        } else if (EPI == EPI_BIAS) {
+          v0 += bf16_at(p.bias, ra);
+          if (r1)
+            v1 += bf16_at(p.bias, rb);
+        }
+        y[ra] = v0;
+        if (r1)
+          y[rb] = v1;
+      } else if (EPI == EPI_SWIGLU) {
+        /* nn_swiglu (nn.vx:169-209): g / (1 + e^-g) * u. */
+        const float g = s0[b], u = s1[b];
+        p.y[b * p.y_stride + item] = g / (1.0f + expf(0.0f - g)) * u;
+      } else { /* EPI_QKV */
+        const int hd = p.head_dim, half = hd / 2;
+        const int ia = p.rope_mode == 0 ? idx : 2 * idx;
+        const int ib = p.rope_mode == 0 ? idx + half : 2 * idx + 1;
+        float va = s0[b], vb = s1[b];
+        if (p.bias) {
+          va += bf16_at(p.bias, (int64_t)head * hd + ia);
+          vb += bf16_at(p.bias, (int64_t)head * hd + ib);
+        }
+        const int pos = p.positions[b];
+        const int local = kind == 0 ? head
+                          : kind == 1 ? head - p.q_heads
+                                      : head - p.q_heads - p.kv_heads;
+        if (kind == 2) {
+          float *vrow = p.v_cache + b * p.cache_batch_stride +
+                        ((int64_t)pos * p.kv_heads + local) * hd;
+          vrow[ia] = va;
+          vrow[ib] = vb;
+          continue;
+        }
+        float c, s;
+        if (p.rope_mode == 0) {
+          /* nn_rope_and_store (nn.vx:245-280) */
+          c = p.cos_t[(int64_t)pos * p.cs_cols + idx];
+          s = p.sin_t[(int64_t)pos * p.cs_cols + idx];
+        } else {
+          /* llama2.vx:264-293 with rope_freq (llama_rt.vx:82-85): the CPU
+             functions are correctly rounded, so go through double. */
+          const float e = -((float)(2 * idx)) / (float)hd;
+          const float f = (float)pow(10000.0, (double)e);
+          const float angle = __fmul_rn((float)pos, f);
+          c = (float)cos((double)angle);
+          s = (float)sin((double)angle);
+        }
+        const float oa = __fsub_rn(__fmul_rn(va, c), __fmul_rn(vb, s));
+        const float ob = p.rope_mode == 0
+                             ? __fadd_rn(__fmul_rn(vb, c), __fmul_rn(va, s))
+                             : __fadd_rn(__fmul_rn(va, s), __fmul_rn(vb, c));
+        float *dst = kind == 0
+                         ? p.y + b * p.y_stride + (int64_t)local * hd
+                         : p.k_cache + b * p.cache_batch_stride +
+                               ((int64_t)pos * p.kv_heads + local) * hd;
+        dst[ia] = oa;
+        dst[ib] = ob;
+      }
+    }
+  }
+}
+
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 148;
+  }();
+  return n;
+}
+
+const char *check_launch(const char *what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess)
+    return nullptr;
+  static thread_local char msg[256];
+  snprintf(msg, sizeof msg, "%s: %s", what, cudaGetErrorString(e));
+  return msg;
+}
+
+template <typename W, int B, int EPI>
+const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
+  const size_t xbytes = (size_t)B * p.cols * sizeof(float);
+  p.x_in_smem = xbytes <= (size_t)MAX_SMEM_X;
+  if (p.norm_w && !p.x_in_smem)
+    return "a fused RMSNorm needs the activations of all sequences to fit in "
+           "96 KiB of shared memory";
+  const size_t smem = p.x_in_smem ? xbytes : 0;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    cudaFuncSetAttribute(rowdot_kernel<W, B, EPI>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         MAX_SMEM_X);
+  });
+  /* Two resident blocks per SM when the work is there; never more warps than
+     items need at two items each. */
+  int blocks = 2 * sm_count();
+  const int wanted = (p.items + WARPS - 1) / WARPS;
+  if (blocks > wanted)
+    blocks = wanted < 1 ? 1 : wanted;
+  rowdot_kernel<W, B, EPI><<<blocks, WARPS * 32, smem, stream>>>(p);
+  return check_launch("a projection launch");
+}
+
+template <typename W, int EPI>
+const char *launch_rowdot_w(RowDotParams &p, cudaStream_t stream) {
+  switch (p.batch) {
+  case 1: return launch_rowdot_b<W, 1, EPI>(p, stream);
+  case 2: return launch_rowdot_b<W, 2, EPI>(p, stream);
+  case 4: return launch_rowdot_b<W, 4, EPI>(p, stream);
+  case 8: return launch_rowdot_b<W, 8, EPI>(p, stream);
+  case 16: return launch_rowdot_b<W, 16, EPI>(p, stream);
+  default: return "the batch must be 1, 2, 4, 8 or 16";
+  }
+}
+
+template <int EPI>
+const char *launch_rowdot(RowDotParams &p, bool wbf16, cudaStream_t stream) {
+  if (p.cols % 8 != 0)
+    return "the number of columns must be a multiple of 8";
+  if (((uintptr_t)p.w0 | (uintptr_t)p.w1 | (uintptr_t)p.w2 | (uintptr_t)p.x) & 15)
+    return "weights and activations must be 16-byte aligned";
+  if (p.x_stride % 4 != 0 && p.batch > 1)
+    return "the stride between sequences must be a multiple of 4 values";
+  return wbf16 ? launch_rowdot_w<__nv_bfloat16, EPI>(p, stream)
+               : launch_rowdot_w<float, EPI>(p, stream);
+}
+
+/* ------------------------------------------------------------- rms_norm
+ * nn_rms_norm (nn.vx:212-239); one block per sequence. */
+__global__ void __launch_bounds__(1024)
+rms_norm_kernel(float *y, const float *x, const void *w, int wbf16, int n,
+                float eps, int64_t stride) {
+  __shared__ float red[32];
+  const float *xr = x + blockIdx.x * stride;
+  float *yr = y + blockIdx.x * stride;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    ss = fmaf(xr[i], xr[i], ss);
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float wn = wbf16 ? bf16_at(w, i) : ((const float *)w)[i];
+    yr[i] = xr[i] * inv * wn;
+  }
+}
+
+/* ------------------------------------------------------- rope_and_store
+ * nn_rope_and_store (nn.vx:245-280), unfused. */
+__global__ void rope_store_kernel(float *q_out, float *k_cache, float *v_cache,
+                                  const float *q, const float *k,
+                                  const float *v, const float *cos_t,
+                                  const float *sin_t, int cs_cols, int pos,
+                                  int q_heads, int kv_heads, int hd) {
+  const int h = blockIdx.x, i = threadIdx.x;
+  if (i >= hd)
+    return;
+  const int half = hd / 2;
+  const int j = i < half ? i : i - half;
+  const int partner = i < half ? i + half : i - half;
+  const float sign = i < half ? -1.0f : 1.0f;
+  const float c = cos_t[(int64_t)pos * cs_cols + j];
+  const float s = sin_t[(int64_t)pos * cs_cols + j];
+  if (h < q_heads) {
+    const float *qh = q + h * hd;
+    q_out[h * hd + i] =
+        __fadd_rn(__fmul_rn(qh[i], c), __fmul_rn(__fmul_rn(sign, qh[partner]), s));
+  } else {
+    const int g = h - q_heads;
+    const float *kh = k + g * hd;
+    const int64_t at = ((int64_t)pos * kv_heads + g) * hd + i;
+    k_cache[at] =
+        __fadd_rn(__fmul_rn(kh[i], c), __fmul_rn(__fmul_rn(sign, kh[partner]), s));
+    v_cache[at] = v[g * hd + i];
+  }
+}
+
+/* ------------------------------------------------------ decode attention
+ * nn_attention with its parts and merge (nn.vx:349-866), and the attention
+ * loops of llama2.vx:295-358.  A block owns one KV head, one run of `split`
+ * positions and up to GH query heads that share the KV head; each warp takes
+ * every fourth position, its lanes hold four values of head_dim each, keeps a
+ * running (max, sum, weighted V) per query head, and the four warps are merged
+ * in warp order.  The block that finishes last for a (sequence, head tile)
+ * merges the parts of all splits in split order. */
+constexpr int ATT_WARPS = 4;
+
+template <int GH>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attention_decode_kernel(const AttnArgs a) {
+  const int hd = a.head_dim, hd4 = hd / 4;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int split_idx = blockIdx.x, b = blockIdx.z;
+  const int group = a.q_heads / a.kv_heads;
+  const int tiles = (group + GH - 1) / GH;
+  const int g = blockIdx.y / tiles, tile = blockIdx.y - g * tiles;
+  const int h0 = g * group + tile * GH;
+  const int nh = min(GH, group - tile * GH);
+  const int pos = a.positions[b];
+  const int t_begin = split_idx * a.split;
+  if (t_begin > pos)
+    return;
+  const int t_end = min(t_begin + a.split, pos + 1);
+  const int splits = pos / a.split + 1;
+  const float scale = 1.0f / sqrtf((float)hd);
+  const bool active = lane < hd4;
+
+  const float *kc = a.k_cache + b * a.cache_batch_stride;
+  const float *vc = a.v_cache + b * a.cache_batch_stride;
+  const float *qb = a.q + (int64_t)b * a.q_heads * hd;
+
+  float4 qv[GH];
+  float m[GH], l[GH];
+  float4 acc[GH];
+#pragma unroll
+  for (int h = 0; h < GH; ++h) {
+    qv[h] = (active && h < nh)
+                ? *reinterpret_cast<const float4 *>(qb + (h0 + h) * hd + lane * 4)
+                : make_float4(0, 0, 0, 0);
+    m[h] = -3.0e38f;
+    l[h] = 0.0f;
+    acc[h] = make_float4(0, 0, 0, 0);
+  }
+
+  for (int t = t_begin + warp; t < t_end; t += ATT_WARPS) {
+    const int64_t row = ((int64_t)t * a.kv_heads + g) * hd + lane * 4;
+    const float4 kv = active ? *reinterpret_cast<const float4 *>(kc + row)
+                             : make_float4(0, 0, 0, 0);
+    const float4 vv = active ? *reinterpret_cast<const float4 *>(vc + row)
+                             : make_float4(0, 0, 0, 0);
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+      float d = qv[h].x * kv.x;
+      d = fmaf(qv[h].y, kv.y, d);
+      d = fmaf(qv[h].z, kv.z, d);
+      d = fmaf(qv[h].w, kv.w, d);
+      const float s = warp_sum(d) * scale;
+      const float mn = fmaxf(m[h], s);
+      const float fix = expf(m[h] - mn);
+      const float pw = expf(s - mn);
+      l[h] = l[h] * fix + pw;
+      acc[h].x = acc[h].x * fix + pw * vv.x;
+      acc[h].y = acc[h].y * fix + pw * vv.y;
+      acc[h].z = acc[h].z * fix + pw * vv.z;
+      acc[h].w = acc[h].w * fix + pw * vv.w;
+      m[h] = mn;
+    }
+  }
+
+  /* ---- merge the four warps, in warp order ---- */
+  __shared__ float sm_m[ATT_WARPS][GH], sm_l[ATT_WARPS][GH];
+  __shared__ __align__(16) float sm_acc[ATT_WARPS][GH][128];
+  __shared__ int is_last;
+#pragma unroll
+  for (int h = 0; h < GH; ++h) {
+    if (lane == 0) {
+      sm_m[warp][h] = m[h];
+      sm_l[warp][h] = l[h];
+    }
+    if (active)
+      *reinterpret_cast<float4 *>(&sm_acc[warp][h][lane * 4]) = acc[h];
+  }
+  __syncthreads();
+  const int row_floats = hd + 2;
+  float *part = a.scratch;
+  auto part_at = [&](int head, int sp) {
+    return part + (((int64_t)b * a.q_heads + head) * (a.max_pos / a.split + 1) +
+                   sp) * row_floats;
+  };
+  if (warp == 0) {
+    for (int h = 0; h < nh; ++h) {
+      float big = -3.0e38f;
+      for (int w = 0; w < ATT_WARPS; ++w)
+        big = fmaxf(big, sm_m[w][h]);
+      float total = 0.0f;
+      float4 o = make_float4(0, 0, 0, 0);
+      for (int w = 0; w < ATT_WARPS; ++w) {
+        const float f = expf(sm_m[w][h] - big);
+        total += f * sm_l[w][h];
+        if (active) {
+          const float4 v = *reinterpret_cast<const float4 *>(&sm_acc[w][h][lane * 4]);
+          o.x += f * v.x; o.y += f * v.y; o.z += f * v.z; o.w += f * v.w;
+        }
+      }
+      float *dst = part_at(h0 + h, split_idx);
+      if (active)
+        *reinterpret_cast<float4 *>(dst + lane * 4) = o;
+      if (lane == 0) {
+        dst[hd] = big;
+        dst[hd + 1] = total;
+      }
+    }
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) {
+      int32_t *counter = a.counters + (int64_t)b * a.kv_heads * tiles + blockIdx.y;
+      const int seen = atomicAdd(counter, 1);
+      is_last = seen == splits - 1;
+      if (is_last)
+        *counter = 0; /* ready for the next launch */
+    }
+  }
+  __syncthreads();
+  if (!is_last)
+    return;
+  __threadfence();
+
+  /* ---- the last block of this head tile merges the splits, in order ---- */
+  for (int h = warp; h < nh; h += ATT_WARPS) {
+    float big = -3.0e38f;
+    for (int sp = lane; sp < splits; sp += 32)
+      big = fmaxf(big, __ldcg(part_at(h0 + h, sp) + hd));
+    big = warp_max(big);
+    float total = 0.0f;
+    float4 o = make_float4(0, 0, 0, 0);
+    for (int sp = 0; sp < splits; ++sp) {
+      const float *src = part_at(h0 + h, sp);
+      const float f = expf(__ldcg(src + hd) - big);
+      total += f * __ldcg(src + hd + 1);
+      if (active) {
+        const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + lane * 4));
+        o.x += f * v.x; o.y += f * v.y; o.z += f * v.z; o.w += f * v.w;
+      }
+    }
+    if (active) {
+      float *dst = a.out + ((int64_t)b * a.q_heads + h0 + h) * hd + lane * 4;
+      *reinterpret_cast<float4 *>(dst) =
+          make_float4(o.x / total, o.y / total, o.z / total, o.w / total);
+    }
+  }
+}
+
+/* ---------------------------------------------------------------- argmax
+ * nn_argmax (nn.vx:870-897) and sample_argmax (llama2.vx:460-474): the lowest
+ * index of the largest value. One block per sequence. */
+__global__ void __launch_bounds__(1024)
+argmax_kernel(int32_t *out, const float *logits, int n, int64_t stride) {
+  __shared__ float best_v[32];
+  __shared__ int best_i[32];
+  const float *row = logits + blockIdx.x * stride;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = row[i];
+    if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) {
+      bv = v;
+      bi = i;
+    }
+  }
+  auto better = [](float v, int i, float ov, int oi) {
+    return oi != 0x7fffffff && (i == 0x7fffffff || ov > v || (ov == v && oi < i));
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(bv, bi, ov, oi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    best_v[warp] = bv;
+    best_i[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    bv = lane < nw ? best_v[lane] : -INFINITY;
+    bi = lane < nw ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(bv, bi, ov, oi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0)
+      out[blockIdx.x] = bi;
+  }
+}
+
+/* ----------------------------------------------------------------- embed
+ * nn_embed (nn.vx:942-958); a token outside the table gives a row of NaN
+ * instead of a read outside it. */
+__global__ void embed_kernel(float *x, const void *table, int tbf16,
+                             const int32_t *token, int dim, int rows,
+                             int64_t x_stride) {
+  const int b = blockIdx.y;
+  const int t = token[b];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim;
+       i += gridDim.x * blockDim.x) {
+    float v = __int_as_float(0x7fc00000);
+    if (t >= 0 && t < rows)
+      v = tbf16 ? bf16_at(table, (int64_t)t * dim + i)
+                : ((const float *)table)[(int64_t)t * dim + i];
+    x[b * x_stride + i] = v;
+  }
+}
+
+/* y[d] = W[d,n] . x for the flat entry point: the same row-dot kernel. */
+
+} // namespace
+
+const char *matvec(const MatvecArgs &a, cudaStream_t stream) {
+  if (a.rows <= 0 || a.batch <= 0)
+    return nullptr;
+  RowDotParams p{};
+  p.w0 = a.w;
+  p.rows = a.rows;
+  p.cols = a.cols;
+  p.items = (a.rows + 1) / 2;
+  p.x = a.x;
+  p.x_stride = a.x_stride;
+  p.batch = a.batch;
+  p.norm_w = a.norm_w;
+  p.norm_bf16 = a.norm_bf16;
+  p.eps = a.eps;
+  p.y = a.y;
+  p.y_stride = a.y_stride;
+  p.bias = a.bias;
+  switch (a.mode) {
+  case 0: return launch_rowdot<EPI_STORE>(p, a.wbf16, stream);
+  case 1: return launch_rowdot<EPI_ADD>(p, a.wbf16, stream);
+  case 2: return launch_rowdot<EPI_BIAS>(p, a.wbf16, stream);
+  default: return "unknown matvec mode";
+  }
+}
+
+const char *matvec_f32(float *y, const float *x, const float *w, int n, int d,
+                       cudaStream_t stream) {
+  if (n % 8 != 0 || (((uintptr_t)w | (uintptr_t)x) & 15)) {
+    /* Any n: the f32 GEMM with a one-column B. */
+    return gemm_f32(w, n, x, 1, y, 1, d, 1, n, stream);
+  }
+  MatvecArgs a{};
+  a.w = w;
+  a.wbf16 = false;
+  a.rows = d;
+  a.cols = n;
+  a.x = x;
+  a.x_stride = n;
+  a.y = y;
+  a.y_stride = d;
+  a.batch = 1;
+  return matvec(a, stream);
+}
+
+const char *swiglu(const SwigluArgs &a, cudaStream_t stream) {
+  if (a.rows <= 0 || a.batch <= 0)
+    return nullptr;
+  RowDotParams p{};
+  p.w0 = a.w;
+  p.w1 = a.w_up;
+  p.rows = a.rows;
+  p.cols = a.cols;
+  p.items = a.rows;
+  p.x = a.x;
+  p.x_stride = a.x_stride;
+  p.batch = a.batch;
+  p.norm_w = a.norm_w;
+  p.norm_bf16 = a.norm_bf16;
+  p.eps = a.eps;
+  p.y = a.out;
+  p.y_stride = a.out_stride;
+  return launch_rowdot<EPI_SWIGLU>(p, a.wbf16, stream);
+}
+
+const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream) {
+  if (a.head_dim % 2 != 0)
+    return "head_dim must be even";
+  RowDotParams p{};
+  p.w0 = a.wq;
+  p.w1 = a.wk;
+  p.w2 = a.wv;
+  p.rows = (a.q_heads + 2 * a.kv_heads) * a.head_dim;
+  p.cols = a.cols;
+  p.items = p.rows / 2;
+  p.x = a.x;
+  p.x_stride = a.x_stride;
+  p.batch = a.batch;
+  p.norm_w = a.norm_w;
+  p.norm_bf16 = a.norm_bf16;
+  p.eps = a.eps;
+  p.y = a.q_out;
+  p.y_stride = (int64_t)a.q_heads * a.head_dim;
+  p.bias = a.bias;
+  p.q_heads = a.q_heads;
+  p.kv_heads = a.kv_heads;
+  p.head_dim = a.head_dim;
+  p.rope_mode = a.rope_mode;
+  p.cos_t = a.cos_t;
+  p.sin_t = a.sin_t;
+  p.cs_cols = a.cs_cols;
+  p.theta = a.theta;
+  p.positions = a.positions;
+  p.k_cache = a.k_cache;
+  p.v_cache = a.v_cache;
+  p.cache_batch_stride = a.cache_batch_stride;
+  p.max_seq = a.max_seq;
+  return launch_rowdot<EPI_QKV>(p, a.wbf16, stream);
+}
+
+const char *rms_norm(float *y, const float *x, const void *w, bool wbf16, int n,
+                     float eps, int batch, int64_t stride, cudaStream_t stream) {
+  if (n <= 0 || batch <= 0)
+    return nullptr;
+  rms_norm_kernel<<<batch, 1024, 0, stream>>>(y, x, w, wbf16, n, eps, stride);
+  return check_launch("the RMSNorm launch");
+}
+
+const char *rope_and_store(float *q_out, float *k_cache, float *v_cache,
+                           const float *q, const float *k, const float *v,
+                           const float *cos_t, const float *sin_t, int cs_cols,
+                           int pos, int q_heads, int kv_heads, int head_dim,
+                           cudaStream_t stream) {
+  if (head_dim > 1024)
+    return "head_dim is larger than a block";
+  rope_store_kernel<<<q_heads + kv_heads, ((head_dim + 31) / 32) * 32, 0,
+                      stream>>>(q_out, k_cache, v_cache, q, k, v, cos_t, sin_t,
+                                cs_cols, pos, q_heads, kv_heads, head_dim);
+  return check_launch("the RoPE launch");
+}
+
+size_t attn_scratch_floats(int batch, int q_heads, int head_dim, int max_seq,
+                           int split) {
+  return (size_t)batch * q_heads * ((size_t)max_seq / split + 1) *
+         (head_dim + 2);
+}
+
+const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
+  if (a.head_dim % 4 != 0 || a.head_dim > 128)
+    return "head_dim must be a multiple of 4, and at most 128";
+  if (a.q_heads % a.kv_heads != 0)
+    return "q_heads must be a multiple of kv_heads";
+  if (a.split < 1)
+    return "the split must be at least one position";
+  const int group = a.q_heads / a.kv_heads;
+  const int gh = group >= 4 ? 4 : (group >= 2 ? 2 : 1);
+  const int tiles = (group + gh - 1) / gh;
+  const dim3 grid(a.max_pos / a.split + 1, a.kv_heads * tiles, a.batch);
+  if (gh == 4)
+    attention_decode_kernel<4><<<grid, ATT_WARPS * 32, 0, stream>>>(a);
+  else if (gh == 2)
+    attention_decode_kernel<2><<<grid, ATT_WARPS * 32, 0, stream>>>(a);
+  else
+    attention_decode_kernel<1><<<grid, ATT_WARPS * 32, 0, stream>>>(a);
+  return check_launch("the attention launch");
+}
+
+const char *argmax(int32_t *out, const float *logits, int n, int batch,
+                   int64_t stride, cudaStream_t stream) {
+  if (n <= 0 || batch <= 0)
+    return nullptr;
+  argmax_kernel<<<batch, 1024, 0, stream>>>(out, logits, n, stride);
+  return check_launch("the argmax launch");
+}
+
+const char *embed(float *x, const void *table, bool tbf16, const int32_t *token,
+                  int dim, int rows, int batch, int64_t x_stride,
+                  cudaStream_t stream) {
+  const dim3 grid((dim + 255) / 256, batch);
+  embed_kernel<<<grid, 256, 0, stream>>>(x, table, tbf16, token, dim, rows,
+                                         x_stride);
+  return check_launch("the embed launch");
+}
+
+} // namespace vxb
