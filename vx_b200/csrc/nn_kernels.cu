@@ -572,9 +572,12 @@ attention_decode_kernel(const AttnArgs a) {
           o.x += f * v.x; o.y += f * v.y; o.z += f * v.z; o.w += f * v.w;
         }
       }
+      /* A part row has head_dim + 2 floats, so rows are 8-byte aligned only. */
       float *dst = part_at(h0 + h, split_idx);
-      if (active)
-        *reinterpret_cast<float4 *>(dst + lane * 4) = o;
+      if (active) {
+        *reinterpret_cast<float2 *>(dst + lane * 4) = make_float2(o.x, o.y);
+        *reinterpret_cast<float2 *>(dst + lane * 4 + 2) = make_float2(o.z, o.w);
+      }
       if (lane == 0) {
         dst[hd] = big;
         dst[hd + 1] = total;
@@ -608,8 +611,10 @@ attention_decode_kernel(const AttnArgs a) {
       const float f = expf(__ldcg(src + hd) - big);
       total += f * __ldcg(src + hd + 1);
       if (active) {
-        const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + lane * 4));
-        o.x += f * v.x; o.y += f * v.y; o.z += f * v.z; o.w += f * v.w;
+        const float2 va = __ldcg(reinterpret_cast<const float2 *>(src + lane * 4));
+        const float2 vb =
+            __ldcg(reinterpret_cast<const float2 *>(src + lane * 4 + 2));
+        o.x += f * va.x; o.y += f * va.y; o.z += f * vb.x; o.w += f * vb.y;
       }
     }
     if (active) {
@@ -828,6 +833,10 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
     return "q_heads must be a multiple of kv_heads";
   if (a.split < 1)
     return "the split must be at least one position";
+  if (((uintptr_t)a.scratch & 7) || ((uintptr_t)a.q & 15) ||
+      ((uintptr_t)a.k_cache & 15) || ((uintptr_t)a.v_cache & 15) ||
+      ((uintptr_t)a.out & 15))
+    return "q, the caches and out must be 16-byte aligned, the scratch 8-byte";
   const int group = a.q_heads / a.kv_heads;
   const int gh = group >= 4 ? 4 : (group >= 2 ? 2 : 1);
   const int tiles = (group + gh - 1) / gh;
