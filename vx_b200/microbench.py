@@ -1,0 +1,123 @@
+"""Small, self-timing runs of one kernel each, for profiling a kernel on a case
+that ends quickly (a few launches, at most a few GB on the device, inputs
+larger than the 126 MB L2 where DRAM figures matter).
+
+  python -m vx_b200.microbench rowdot  [--layers 4] [--iters 3]
+  python -m vx_b200.microbench gemm    [--n 4096] [--iters 3]
+  python -m vx_b200.microbench flash   [--batch 1] [--heads 8] [--seq 4096]
+  python -m vx_b200.microbench attn    [--pos 600]
+Each prints one JSON line with the CUDA-event time per launch.
+"""
+import argparse
+import ctypes as C
+import json
+
+import numpy as np
+
+from . import abi, ops
+from .lib import lib
+
+
+def _timed(torch, stream, fn, iters):
+    lib().vx_cuda_set_stream(C.c_void_p(stream.cuda_stream))
+    try:
+        fn()
+        stream.synchronize()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(iters):
+            fn()
+        b.record(stream)
+        b.synchronize()
+        return a.elapsed_time(b) / iters
+    finally:
+        lib().vx_cuda_set_stream(None)
+
+
+def rowdot(torch, args):
+    """The gate/up projection + SwiGLU at Llama-2-7B shapes over `layers`
+    different matrices (180 MB each)."""
+    dim, hid = 4096, 11008
+    ws = [abi.DeviceTensor.empty((2 * hid * dim,), abi.BF16)
+          for _ in range(args.layers)]
+    for i, w in enumerate(ws):
+        ops.fill_normal(w, 100 + i, 0.02)
+    x = abi.DeviceTensor.empty((dim,), abi.F32)
+    ops.fill_normal(x, 99, 1.0)
+    out = abi.DeviceTensor.empty((hid,), abi.F32)
+    ms = _timed(torch, torch.cuda.Stream(),
+                lambda: [ops.nn_swiglu(out, w, x, hid, dim) for w in ws],
+                args.iters) / len(ws)
+    nbytes = 2 * hid * dim * 2 + dim * 4 + hid * 4
+    return dict(kernel="rowdot swiglu 22016x4096 bf16", us=ms * 1e3,
+                bytes=nbytes, gbs=nbytes / ms / 1e6)
+
+
+def gemm(torch, args):
+    n = args.n
+    ta, tb, tc = (abi.DeviceTensor.empty((n, n), abi.BF16) for _ in range(3))
+    ops.fill_uniform(ta, 3, -1.0, 1.0)
+    ops.fill_uniform(tb, 1003, -1.0, 1.0)
+    ms = _timed(torch, torch.cuda.Stream(),
+                lambda: ops.matmul_into(tc, ta, tb), args.iters)
+    return dict(kernel="tcgen05 gemm bf16 %d^3" % n, us=ms * 1e3,
+                tflops=2.0 * n ** 3 / ms / 1e9, status=ops.kernel_status())
+
+
+def flash(torch, args):
+    B, H, S, D = args.batch, args.heads, args.seq, 128
+    ts = [abi.DeviceTensor.empty((B, H, S, D), abi.BF16) for _ in range(4)]
+    for t, seed in zip(ts[:3], (10, 11, 12)):
+        ops.fill_normal(t, seed, 1.0)
+    scale = 1.0 / np.sqrt(D)
+    ms = _timed(torch, torch.cuda.Stream(),
+                lambda: ops.flash_attention(ts[0], ts[1], ts[2], ts[3], scale,
+                                            True), args.iters)
+    flops = 4.0 * B * H * D * S * (S + 1) / 2
+    return dict(kernel="flash fwd causal [%d,%d,%d,%d]" % (B, H, S, D),
+                us=ms * 1e3, tflops=flops / ms / 1e9, status=ops.kernel_status())
+
+
+def attn(torch, args):
+    qh = kvh = 32
+    hd, pos, max_seq = 128, args.pos, 1024
+    q = abi.DeviceTensor.empty((qh, hd), abi.F32)
+    out = abi.DeviceTensor.empty((qh, hd), abi.F32)
+    caches = []
+    for i in range(8):                      # 8 layers' caches: 268 MB
+        k = abi.DeviceTensor.empty((max_seq, kvh, hd), abi.F32)
+        v = abi.DeviceTensor.empty((max_seq, kvh, hd), abi.F32)
+        ops.fill_normal(k, 200 + i, 1.0)
+        ops.fill_normal(v, 300 + i, 1.0)
+        caches.append((k, v))
+    ops.fill_normal(q, 98, 1.0)
+    part = abi.DeviceTensor.empty(
+        ops.nn_attention_scratch_shape(max_seq, qh, kvh, hd), abi.F32)
+    ms = _timed(torch, torch.cuda.Stream(),
+                lambda: [ops.nn_attention(out, part, q, k, v, pos, qh, kvh, hd)
+                         for k, v in caches], args.iters) / len(caches)
+    nbytes = 2 * (pos + 1) * kvh * hd * 4
+    return dict(kernel="decode attention 32x128 at pos %d" % pos, us=ms * 1e3,
+                bytes=nbytes, gbs=nbytes / ms / 1e6)
+
+
+def main():
+    import torch
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["rowdot", "gemm", "flash", "attn"])
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--heads", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--pos", type=int, default=600)
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    print(json.dumps(dict(rowdot=rowdot, gemm=gemm, flash=flash,
+                          attn=attn)[args.case](torch, args)))
+
+
+if __name__ == "__main__":
+    main()
