@@ -168,6 +168,24 @@ int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,
                                 void *out, int32_t B, int32_t H, int32_t S,
                                 int32_t D, float scale, int32_t causal);
 
+/* Decode attention with no allocation of any kind, for hosts that cannot call
+   cudaMalloc: processes that handed all device memory to their own pool at
+   start-up, and loops that cannot take the device-wide wait an allocation
+   implies. The computation of vx_nn_attention on plain device pointers (q, out
+   [q_heads, head_dim]; caches [max_seq, kv_heads, head_dim]; f32); its scratch
+   is a fixed array inside the library image (2 MiB + 4 KiB per GPU, held until
+   the process exits). Limit: q_heads <= 256 and
+   q_heads * (pos / n + 1) * (head_dim + 2) <= 2^19 with n = 32 below position
+   640, else 64; beyond it: -1 and a message. All calls on a GPU share the
+   array, so calls that overlap on the GPU race: keep them in stream order. The
+   first call on a GPU sets the array up and should come before any stream
+   capture. This entry point has no counterpart in the reference. */
+int32_t vx_b200_attention_decode_static(float *out, const float *q,
+                                        const float *k_cache,
+                                        const float *v_cache, int32_t pos,
+                                        int32_t q_heads, int32_t kv_heads,
+                                        int32_t head_dim);
+
 /* Column-split product for a job of g ranks: this rank holds A [m,k] and
    B_local [k, n_local]; c_full [m, g*n_local] is complete on every rank
    afterwards. c_local [m, n_local] and gathered [g, m, n_local] are scratch. */

@@ -157,6 +157,10 @@ int32_t *device_i32(int value) {
 
 } // namespace
 
+namespace vxb {
+void set_last_error(const char *why) { t_error = why ? why : "unknown"; }
+} // namespace vxb
+
 extern "C" {
 
 const char *vx_b200_last_error(void) { return t_error.c_str(); }

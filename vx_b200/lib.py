@@ -38,6 +38,7 @@ EXTRA_SYMBOLS = [
     "vx_b200_last_error", "vx_b200_gemm", "vx_b200_kernel_status",
     "vx_b200_flash_attention", "vx_b200_gemm_column_split",
     "vx_b200_fill_normal", "vx_b200_fill_uniform",
+    "vx_b200_attention_decode_static",
 ]
 
 _lib = None
@@ -133,6 +134,9 @@ def lib():
     L.vx_b200_fill_normal.argtypes = [vp, i32, i64, u64, C.c_float]
     L.vx_b200_fill_uniform.restype = i32
     L.vx_b200_fill_uniform.argtypes = [vp, i32, i64, u64, C.c_float, C.c_float]
+    L.vx_b200_attention_decode_static.restype = i32
+    L.vx_b200_attention_decode_static.argtypes = [vp, vp, vp, vp, i32, i32, i32,
+                                                  i32]
     _lib = L
     return L
 
