@@ -17,6 +17,8 @@
  * the same bits on every run.
  */
 #include "kernels.h"
+#include "launch.cuh"
+#include "ptx.cuh"
 
 #include <cuda_bf16.h>
 
@@ -27,7 +29,7 @@
 namespace vxb {
 namespace {
 
-constexpr int WARPS = 8;             /* per block, projection kernels */
+constexpr int WARPS = 16;            /* per block, projection kernels */
 constexpr int MAX_SMEM_X = 96 * 1024; /* x (all batch rows) staged per block */
 
 __device__ __forceinline__ uint4 ld_stream(const void *p) {
@@ -108,48 +110,136 @@ struct RowDotParams {
   int max_seq;
 };
 
-template <typename W> struct WTraits;
-template <> struct WTraits<__nv_bfloat16> {
-  static constexpr int kLoads = 1; /* 16-byte loads per 8 columns */
-};
-template <> struct WTraits<float> {
-  static constexpr int kLoads = 2;
-};
-
-/* acc[b] += sum over 8 columns of w * x[b]. */
+/* acc[b] += sum over the E weights of one 16-byte word (8 bf16 or 4 f32) of
+   w * x[b]. */
 template <typename W, int B>
-__device__ __forceinline__ void fma8(const uint4 (&wv)[WTraits<W>::kLoads],
-                                     const float (&xv)[B][8], float (&acc)[B]) {
-  float wf[8];
-  if (WTraits<W>::kLoads == 1) {
-    wf[0] = bf_lo(wv[0].x); wf[1] = bf_hi(wv[0].x);
-    wf[2] = bf_lo(wv[0].y); wf[3] = bf_hi(wv[0].y);
-    wf[4] = bf_lo(wv[0].z); wf[5] = bf_hi(wv[0].z);
-    wf[6] = bf_lo(wv[0].w); wf[7] = bf_hi(wv[0].w);
+__device__ __forceinline__ void
+fma16(const uint4 &wv, const float (&xv)[B][16 / sizeof(W)], float (&acc)[B]) {
+  constexpr int E = 16 / (int)sizeof(W);
+  float wf[E];
+  if (E == 8) {
+    wf[0] = bf_lo(wv.x); wf[1] = bf_hi(wv.x);
+    wf[2] = bf_lo(wv.y); wf[3] = bf_hi(wv.y);
+    wf[E - 4] = bf_lo(wv.z); wf[E - 3] = bf_hi(wv.z);
+    wf[E - 2] = bf_lo(wv.w); wf[E - 1] = bf_hi(wv.w);
   } else {
-    const uint4 &a = wv[0], &b = wv[WTraits<W>::kLoads - 1];
-    wf[0] = __uint_as_float(a.x); wf[1] = __uint_as_float(a.y);
-    wf[2] = __uint_as_float(a.z); wf[3] = __uint_as_float(a.w);
-    wf[4] = __uint_as_float(b.x); wf[5] = __uint_as_float(b.y);
-    wf[6] = __uint_as_float(b.z); wf[7] = __uint_as_float(b.w);
+    wf[0] = __uint_as_float(wv.x); wf[1] = __uint_as_float(wv.y);
+    wf[2] = __uint_as_float(wv.z); wf[3] = __uint_as_float(wv.w);
   }
 #pragma unroll
   for (int b = 0; b < B; ++b)
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
+    for (int e = 0; e < E; ++e)
       acc[b] = fmaf(wf[e], xv[b][e], acc[b]);
 }
 
+/* The two weight rows of an item, and for q/k/v which head and pair it is. */
+template <typename W, int EPI> struct ItemRows {
+  const W *r0, *r1; /* r1 == nullptr: an odd last row */
+  int head, idx, kind; /* qkv: kind 0 q, 1 k, 2 v */
+};
+template <typename W, int EPI>
+__device__ __forceinline__ ItemRows<W, EPI> item_rows(const RowDotParams &p,
+                                                     int item) {
+  ItemRows<W, EPI> it;
+  const int cols = p.cols;
+  it.head = it.idx = it.kind = 0;
+  if (EPI == EPI_SWIGLU) {
+    it.r0 = (const W *)p.w0 + (int64_t)item * cols;
+    it.r1 = p.w1 ? (const W *)p.w1 + (int64_t)item * cols
+                 : (const W *)p.w0 + (int64_t)(p.rows + item) * cols;
+  } else if (EPI == EPI_QKV) {
+    const int half = p.head_dim / 2;
+    it.head = item / half;
+    it.idx = item - it.head * half;
+    const int a = p.rope_mode == 0 ? it.idx : 2 * it.idx;
+    const int b = p.rope_mode == 0 ? it.idx + half : 2 * it.idx + 1;
+    const W *base;
+    int local = it.head;
+    if (it.head < p.q_heads) {
+      base = (const W *)p.w0;
+    } else if (it.head < p.q_heads + p.kv_heads) {
+      it.kind = 1;
+      local = it.head - p.q_heads;
+      base = p.w1 ? (const W *)p.w1
+                  : (const W *)p.w0 + (int64_t)p.q_heads * p.head_dim * cols;
+    } else {
+      it.kind = 2;
+      local = it.head - p.q_heads - p.kv_heads;
+      base = p.w2 ? (const W *)p.w2
+                  : (const W *)p.w0 + (int64_t)(p.q_heads + p.kv_heads) *
+                                          p.head_dim * cols;
+    }
+    it.r0 = base + ((int64_t)local * p.head_dim + a) * cols;
+    it.r1 = base + ((int64_t)local * p.head_dim + b) * cols;
+  } else {
+    it.r0 = (const W *)p.w0 + (int64_t)(2 * item) * cols;
+    it.r1 = 2 * item + 1 < p.rows ? it.r0 + cols : nullptr;
+  }
+  return it;
+}
+
+/* Weights reach the SM through a per-warp ring in shared memory that bulk
+   copies (cp.async.bulk, completion counted on an mbarrier) fill: a warp keeps
+   RING_STAGES chunks of both rows of its item in flight, across item
+   boundaries, whatever its lanes are doing -- 128 KiB in flight per SM. */
+constexpr int RING_STAGES = 4;
+constexpr int CHUNK_BYTES = 1024; /* of one row */
+constexpr int RING_BYTES = WARPS * RING_STAGES * 2 * CHUNK_BYTES;
+
+__device__ int g_rowdot_status; /* non-zero: a ring wait gave up */
+
 template <typename W, int B, int EPI>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 1)
 rowdot_kernel(const RowDotParams p) {
-  extern __shared__ __align__(16) float xs[]; /* [B][cols] when x_in_smem */
+  extern __shared__ __align__(128) unsigned char smem_dyn[];
+  unsigned char *ring = smem_dyn;                    /* [warp][stage][2][chunk] */
+  float *xs = (float *)(smem_dyn + RING_BYTES);      /* [B][cols] when x_in_smem */
   __shared__ float red[32];
   __shared__ float inv_rms[B];
-  constexpr int L = WTraits<W>::kLoads;
-  constexpr int UNROLL = B == 1 ? 4 : (B == 2 ? 2 : 1);
+  __shared__ __align__(8) uint64_t bars[WARPS][RING_STAGES];
+  constexpr int E = 16 / (int)sizeof(W);             /* elements per 16 bytes */
+  constexpr int CHUNK_COLS = CHUNK_BYTES / (int)sizeof(W);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cols = p.cols;
+
+  /* ---- this warp's items, as a stream of (item, chunk) units ---- */
+  const int64_t total_warps = (int64_t)gridDim.x * WARPS;
+  const int64_t gw = (int64_t)blockIdx.x * WARPS + warp;
+  const int first = (int)(gw * p.items / total_warps);
+  const int last = (int)((gw + 1) * p.items / total_warps);
+  const int row_bytes = cols * (int)sizeof(W);
+  const int nch = (row_bytes + CHUNK_BYTES - 1) / CHUNK_BYTES;
+  const int units = (last - first) * nch;
+  unsigned char *my_ring = ring + warp * (RING_STAGES * 2 * CHUNK_BYTES);
+
+  if (lane == 0) {
+    for (int s = 0; s < RING_STAGES; ++s)
+      ptx::mbar_init(&bars[warp][s], 1);
+    ptx::fence_proxy_async_smem();
+    ptx::fence_barrier_init();
+  }
+  __syncwarp();
+  auto issue = [&](int u) {
+    if (u >= units || lane != 0)
+      return;
+    const int item = first + u / nch, ch = u - (u / nch) * nch;
+    const ItemRows<W, EPI> it = item_rows<W, EPI>(p, item);
+    const int bytes = min(CHUNK_BYTES, row_bytes - ch * CHUNK_BYTES);
+    const int s = u % RING_STAGES;
+    unsigned char *dst = my_ring + s * (2 * CHUNK_BYTES);
+    ptx::mbar_expect_tx(&bars[warp][s], 2 * bytes);
+    ptx::bulk_load(dst, (const char *)it.r0 + ch * CHUNK_BYTES, bytes,
+                   &bars[warp][s]);
+    ptx::bulk_load(dst + CHUNK_BYTES,
+                   (const char *)(it.r1 ? it.r1 : it.r0) + ch * CHUNK_BYTES,
+                   bytes, &bars[warp][s]);
+  };
+  /* The weights do not depend on the kernel before this one: start them. */
+  for (int u = 0; u < RING_STAGES; ++u)
+    issue(u);
+  chain_release();
+  chain_wait(); /* from here on: x, y, positions of the kernels before */
 
   /* ---- prologue: x (normalised if asked) into shared memory ---- */
   if (p.norm_w) {
@@ -187,92 +277,60 @@ rowdot_kernel(const RowDotParams p) {
   const float *xbase = p.x_in_smem ? xs : p.x;
   const int64_t xstr = p.x_in_smem ? cols : p.x_stride;
 
-  /* ---- this warp's items ---- */
-  const int64_t total_warps = (int64_t)gridDim.x * WARPS;
-  const int64_t gw = (int64_t)blockIdx.x * WARPS + warp;
-  const int first = (int)(gw * p.items / total_warps);
-  const int last = (int)((gw + 1) * p.items / total_warps);
+  float s0[B], s1[B];
+#pragma unroll
+  for (int b = 0; b < B; ++b)
+    s0[b] = s1[b] = 0.0f;
 
-  for (int item = first; item < last; ++item) {
-    /* which two rows */
-    const W *r0 = nullptr, *r1 = nullptr;
-    int head = 0, idx = 0, kind = 0; /* qkv: kind 0 q, 1 k, 2 v */
-    if (EPI == EPI_SWIGLU) {
-      r0 = (const W *)p.w0 + (int64_t)item * cols;
-      r1 = p.w1 ? (const W *)p.w1 + (int64_t)item * cols
-                : (const W *)p.w0 + (int64_t)(p.rows + item) * cols;
-    } else if (EPI == EPI_QKV) {
-      const int half = p.head_dim / 2;
-      head = item / half;
-      idx = item - head * half;
-      const int a = p.rope_mode == 0 ? idx : 2 * idx;
-      const int b = p.rope_mode == 0 ? idx + half : 2 * idx + 1;
-      const W *base;
-      int local = head;
-      if (head < p.q_heads) {
-        kind = 0;
-        base = (const W *)p.w0;
-      } else if (head < p.q_heads + p.kv_heads) {
-        kind = 1;
-        local = head - p.q_heads;
-        base = p.w1 ? (const W *)p.w1
-                    : (const W *)p.w0 + (int64_t)p.q_heads * p.head_dim * cols;
-      } else {
-        kind = 2;
-        local = head - p.q_heads - p.kv_heads;
-        base = p.w2 ? (const W *)p.w2
-                    : (const W *)p.w0 + (int64_t)(p.q_heads + p.kv_heads) *
-                                            p.head_dim * cols;
-      }
-      r0 = base + ((int64_t)local * p.head_dim + a) * cols;
-      r1 = base + ((int64_t)local * p.head_dim + b) * cols;
-    } else {
-      r0 = (const W *)p.w0 + (int64_t)(2 * item) * cols;
-      r1 = 2 * item + 1 < p.rows ? r0 + cols : nullptr;
+  for (int u = 0; u < units; ++u) {
+    const int item = first + u / nch, ch = u - (u / nch) * nch;
+    const int s = u % RING_STAGES;
+    if (!ptx::mbar_wait_alone(&bars[warp][s], (u / RING_STAGES) & 1)) {
+      atomicCAS(&g_rowdot_status, 0, 1);
+      break;
     }
-    const W *r1s = r1 ? r1 : r0; /* an odd tail streams row 0 twice */
-
-    float s0[B], s1[B];
+    const unsigned char *src = my_ring + s * (2 * CHUNK_BYTES);
+    const int bytes = min(CHUNK_BYTES, row_bytes - ch * CHUNK_BYTES);
 #pragma unroll
-    for (int b = 0; b < B; ++b)
-      s0[b] = s1[b] = 0.0f;
-
-    for (int c0 = lane * 8; c0 < cols; c0 += 256 * UNROLL) {
-      uint4 wa[UNROLL][L], wb[UNROLL][L];
+    for (int i = 0; i < CHUNK_BYTES / 512; ++i) {
+      const int off = i * 512 + lane * 16;
+      if (off < bytes) {
+        const uint4 wa = *reinterpret_cast<const uint4 *>(src + off);
+        const uint4 wb = *reinterpret_cast<const uint4 *>(src + CHUNK_BYTES + off);
+        const int c = ch * CHUNK_COLS + off / (int)sizeof(W);
+        float xv[B][E];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int c = c0 + u * 256;
-        if (c < cols) {
-#pragma unroll
-          for (int l = 0; l < L; ++l) {
-            wa[u][l] = ld_stream((const char *)(r0 + c) + 16 * l);
-            wb[u][l] = ld_stream((const char *)(r1s + c) + 16 * l);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int c = c0 + u * 256;
-        if (c < cols) {
-          float xv[B][8];
-#pragma unroll
-          for (int b = 0; b < B; ++b) {
-            const float4 lo =
-                *reinterpret_cast<const float4 *>(xbase + b * xstr + c);
+        for (int b = 0; b < B; ++b) {
+          const float4 lo =
+              *reinterpret_cast<const float4 *>(xbase + b * xstr + c);
+          xv[b][0] = lo.x; xv[b][1] = lo.y; xv[b][2] = lo.z; xv[b][3] = lo.w;
+          if (E == 8) {
             const float4 hi =
                 *reinterpret_cast<const float4 *>(xbase + b * xstr + c + 4);
-            xv[b][0] = lo.x; xv[b][1] = lo.y; xv[b][2] = lo.z; xv[b][3] = lo.w;
-            xv[b][4] = hi.x; xv[b][5] = hi.y; xv[b][6] = hi.z; xv[b][7] = hi.w;
+            xv[b][E - 4] = hi.x; xv[b][E - 3] = hi.y;
+            xv[b][E - 2] = hi.z; xv[b][E - 1] = hi.w;
           }
-          fma8<W, B>(wa[u], xv, s0);
-          fma8<W, B>(wb[u], xv, s1);
         }
+        fma16<W, B>(wa, xv, s0);
+        fma16<W, B>(wb, xv, s1);
       }
     }
+    /* Every lane has read the stage: it may be filled again. */
+    __syncwarp();
+    issue(u + RING_STAGES);
+    if (ch != nch - 1)
+      continue;
+
+    /* ---- the item is complete: reduce, then the epilogue on lane 0 ---- */
+    const ItemRows<W, EPI> it = item_rows<W, EPI>(p, item);
+    const W *r1 = it.r1;
+    const int head = it.head, idx = it.idx, kind = it.kind;
+    float t0[B], t1[B];
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      s0[b] = warp_sum(s0[b]);
-      s1[b] = warp_sum(s1[b]);
+      t0[b] = warp_sum(s0[b]);
+      t1[b] = warp_sum(s1[b]);
+      s0[b] = s1[b] = 0.0f;
     }
     if (lane != 0)
       continue;
@@ -283,7 +341,7 @@ rowdot_kernel(const RowDotParams p) {
       if (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_BIAS) {
         float *y = p.y + b * p.y_stride;
         const int ra = 2 * item, rb = 2 * item + 1;
-        float v0 = s0[b], v1 = s1[b];
+        float v0 = t0[b], v1 = t1[b];
         if (EPI == EPI_ADD) {
           v0 = y[ra] + v0;
           if (r1)
@@ -298,13 +356,13 @@ rowdot_kernel(const RowDotParams p) {
           y[rb] = v1;
       } else if (EPI == EPI_SWIGLU) {
         /* nn_swiglu (nn.vx:169-209): g / (1 + e^-g) * u. */
-        const float g = s0[b], u = s1[b];
+        const float g = t0[b], u = t1[b];
         p.y[b * p.y_stride + item] = g / (1.0f + expf(0.0f - g)) * u;
       } else { /* EPI_QKV */
         const int hd = p.head_dim, half = hd / 2;
         const int ia = p.rope_mode == 0 ? idx : 2 * idx;
         const int ib = p.rope_mode == 0 ? idx + half : 2 * idx + 1;
-        float va = s0[b], vb = s1[b];
+        float va = t0[b], vb = t1[b];
         if (p.bias) {
           va += bf16_at(p.bias, (int64_t)head * hd + ia);
           vb += bf16_at(p.bias, (int64_t)head * hd + ib);
@@ -375,20 +433,21 @@ const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
   if (p.norm_w && !p.x_in_smem)
     return "a fused RMSNorm needs the activations of all sequences to fit in "
            "96 KiB of shared memory";
-  const size_t smem = p.x_in_smem ? xbytes : 0;
+  const size_t smem = RING_BYTES + (p.x_in_smem ? xbytes : 0);
   static std::once_flag once;
   std::call_once(once, [] {
     cudaFuncSetAttribute(rowdot_kernel<W, B, EPI>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         MAX_SMEM_X);
+                         RING_BYTES + MAX_SMEM_X);
   });
-  /* Two resident blocks per SM when the work is there; never more warps than
-     items need at two items each. */
-  int blocks = 2 * sm_count();
+  /* One block of 16 warps per SM (the ring takes 128 KiB of its shared
+     memory); fewer blocks when there are fewer items than warps. */
+  int blocks = sm_count();
   const int wanted = (p.items + WARPS - 1) / WARPS;
   if (blocks > wanted)
     blocks = wanted < 1 ? 1 : wanted;
-  rowdot_kernel<W, B, EPI><<<blocks, WARPS * 32, smem, stream>>>(p);
+  launch_chained(rowdot_kernel<W, B, EPI>, dim3(blocks), dim3(WARPS * 32), smem,
+                 stream, p);
   return check_launch("a projection launch");
 }
 
@@ -422,6 +481,9 @@ __global__ void __launch_bounds__(1024)
 rms_norm_kernel(float *y, const float *x, const void *w, int wbf16, int n,
                 float eps, int64_t stride) {
   __shared__ float red[32];
+  chain_release();
+  chain_wait();
+
   const float *xr = x + blockIdx.x * stride;
   float *yr = y + blockIdx.x * stride;
   float ss = 0.0f;
@@ -442,6 +504,8 @@ __global__ void rope_store_kernel(float *q_out, float *k_cache, float *v_cache,
                                   const float *v, const float *cos_t,
                                   const float *sin_t, int cs_cols, int pos,
                                   int q_heads, int kv_heads, int hd) {
+  chain_release();
+  chain_wait();
   const int h = blockIdx.x, i = threadIdx.x;
   if (i >= hd)
     return;
@@ -478,6 +542,8 @@ constexpr int ATT_WARPS = 4;
 template <int GH>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_decode_kernel(const AttnArgs a) {
+  chain_release();
+  chain_wait();
   const int hd = a.head_dim, hd4 = hd / 4;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int split_idx = blockIdx.x, b = blockIdx.z;
@@ -630,6 +696,8 @@ attention_decode_kernel(const AttnArgs a) {
  * index of the largest value. One block per sequence. */
 __global__ void __launch_bounds__(1024)
 argmax_kernel(int32_t *out, const float *logits, int n, int64_t stride) {
+  chain_release();
+  chain_wait();
   __shared__ float best_v[32];
   __shared__ int best_i[32];
   const float *row = logits + blockIdx.x * stride;
@@ -684,6 +752,8 @@ argmax_kernel(int32_t *out, const float *logits, int n, int64_t stride) {
 __global__ void embed_kernel(float *x, const void *table, int tbf16,
                              const int32_t *token, int dim, int rows,
                              int64_t x_stride) {
+  chain_release();
+  chain_wait();
   const int b = blockIdx.y;
   const int t = token[b];
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim;
@@ -803,7 +873,8 @@ const char *rms_norm(float *y, const float *x, const void *w, bool wbf16, int n,
                      float eps, int batch, int64_t stride, cudaStream_t stream) {
   if (n <= 0 || batch <= 0)
     return nullptr;
-  rms_norm_kernel<<<batch, 1024, 0, stream>>>(y, x, w, wbf16, n, eps, stride);
+  launch_chained(rms_norm_kernel, dim3(batch), dim3(1024), 0, stream, y, x, w,
+                 (int)wbf16, n, eps, stride);
   return check_launch("the RMSNorm launch");
 }
 
@@ -814,9 +885,10 @@ const char *rope_and_store(float *q_out, float *k_cache, float *v_cache,
                            cudaStream_t stream) {
   if (head_dim > 1024)
     return "head_dim is larger than a block";
-  rope_store_kernel<<<q_heads + kv_heads, ((head_dim + 31) / 32) * 32, 0,
-                      stream>>>(q_out, k_cache, v_cache, q, k, v, cos_t, sin_t,
-                                cs_cols, pos, q_heads, kv_heads, head_dim);
+  launch_chained(rope_store_kernel, dim3(q_heads + kv_heads),
+                 dim3(((head_dim + 31) / 32) * 32), 0, stream, q_out, k_cache,
+                 v_cache, q, k, v, cos_t, sin_t, cs_cols, pos, q_heads,
+                 kv_heads, head_dim);
   return check_launch("the RoPE launch");
 }
 
@@ -842,11 +914,14 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
   const int tiles = (group + gh - 1) / gh;
   const dim3 grid(a.max_pos / a.split + 1, a.kv_heads * tiles, a.batch);
   if (gh == 4)
-    attention_decode_kernel<4><<<grid, ATT_WARPS * 32, 0, stream>>>(a);
+    launch_chained(attention_decode_kernel<4>, grid, dim3(ATT_WARPS * 32), 0,
+                   stream, a);
   else if (gh == 2)
-    attention_decode_kernel<2><<<grid, ATT_WARPS * 32, 0, stream>>>(a);
+    launch_chained(attention_decode_kernel<2>, grid, dim3(ATT_WARPS * 32), 0,
+                   stream, a);
   else
-    attention_decode_kernel<1><<<grid, ATT_WARPS * 32, 0, stream>>>(a);
+    launch_chained(attention_decode_kernel<1>, grid, dim3(ATT_WARPS * 32), 0,
+                   stream, a);
   return check_launch("the attention launch");
 }
 
@@ -854,7 +929,8 @@ const char *argmax(int32_t *out, const float *logits, int n, int batch,
                    int64_t stride, cudaStream_t stream) {
   if (n <= 0 || batch <= 0)
     return nullptr;
-  argmax_kernel<<<batch, 1024, 0, stream>>>(out, logits, n, stride);
+  launch_chained(argmax_kernel, dim3(batch), dim3(1024), 0, stream, out, logits,
+                 n, stride);
   return check_launch("the argmax launch");
 }
 
@@ -862,8 +938,8 @@ const char *embed(float *x, const void *table, bool tbf16, const int32_t *token,
                   int dim, int rows, int batch, int64_t x_stride,
                   cudaStream_t stream) {
   const dim3 grid((dim + 255) / 256, batch);
-  embed_kernel<<<grid, 256, 0, stream>>>(x, table, tbf16, token, dim, rows,
-                                         x_stride);
+  launch_chained(embed_kernel, grid, dim3(256), 0, stream, x, table, (int)tbf16,
+                 token, dim, rows, x_stride);
   return check_launch("the embed launch");
 }
 

@@ -99,6 +99,15 @@ __device__ inline void tma_load_4d(void *dst, const CUtensorMap *map, int c0,
                "r"(smem_addr(bar))
                : "memory");
 }
+/* An untiled bulk copy of `bytes` (a multiple of 16; both addresses 16-byte
+   aligned) from global memory into this CTA's shared memory. */
+__device__ inline void bulk_load(void *dst, const void *src, uint32_t bytes,
+                                 uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::"
+               "bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
+               "l"(src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
 __device__ inline void tma_prefetch_desc(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

@@ -141,6 +141,31 @@ def small_f32_decoder(flat, offsets, dim=288, hidden=768, n_layers=6, n_heads=6,
     return Decoder(cfg, weights, keep=dev)
 
 
+# ---- tensor-parallel slices --------------------------------------------------------
+def tp_slices(q_heads, kv_heads, head_dim, hidden, vocab, rank, ranks):
+    """Which part of every matrix rank `rank` of `ranks` holds. Column-split
+    projections (q, k, v, gate, up, classifier) give row ranges of the stored
+    [rows, cols] matrix; row-split projections (output, down) give column
+    ranges, and their partial products are summed across ranks."""
+    assert q_heads % ranks == 0 and kv_heads % ranks == 0
+    assert hidden % ranks == 0 and vocab % ranks == 0
+    ql, kvl, hl, vl = (q_heads // ranks, kv_heads // ranks, hidden // ranks,
+                       vocab // ranks)
+    q0 = rank * ql * head_dim
+    k0 = q_heads * head_dim + rank * kvl * head_dim
+    v0 = (q_heads + kv_heads) * head_dim + rank * kvl * head_dim
+    return dict(
+        q_rows=(q0, q0 + ql * head_dim),              # of the fused qkv matrix
+        k_rows=(k0, k0 + kvl * head_dim),
+        v_rows=(v0, v0 + kvl * head_dim),
+        wo_cols=(rank * ql * head_dim, (rank + 1) * ql * head_dim),
+        gate_rows=(rank * hl, (rank + 1) * hl),       # of the fused gate/up
+        up_rows=(hidden + rank * hl, hidden + (rank + 1) * hl),
+        down_cols=(rank * hl, (rank + 1) * hl),
+        vocab_rows=(rank * vl, (rank + 1) * vl),
+        q_local=ql, kv_local=kvl, hidden_local=hl, vocab_local=vl)
+
+
 # ---- the std::nn model -------------------------------------------------------------
 def rope_tables(max_seq, head_dim, theta):
     """cos/sin [max_seq, head_dim/2] as the reference's test makes them
@@ -173,48 +198,44 @@ def nn_bf16_model(dim, hidden, n_layers, q_heads, kv_heads, head_dim, vocab,
     def ones(n):
         return torch.ones(n, dtype=torch.bfloat16, device=dev)
 
-    ql, kvl, hl = q_heads // tp_ranks, kv_heads // tp_ranks, hidden // tp_ranks
-    vl = vocab // tp_ranks
+    sl = tp_slices(q_heads, kv_heads, head_dim, hidden, vocab, tp_rank, tp_ranks)
+
+    def rows(t, r):
+        return t[r[0]:r[1]].clone()
+
+    def cols(t, r):
+        return t[:, r[0]:r[1]].contiguous()
+
     keep = {k: [] for k in ("attn_norm", "wq", "wk", "wv", "wo", "ffn_norm",
                             "w_gate", "w_up", "w_down")}
     for l in range(n_layers):
         base = 16 * (l + 1)
         wqkv = normal(((q_heads + 2 * kv_heads) * head_dim, dim), base + 0)
-        q0 = tp_rank * ql * head_dim
-        k0 = q_heads * head_dim + tp_rank * kvl * head_dim
-        v0 = (q_heads + kv_heads) * head_dim + tp_rank * kvl * head_dim
+        wo = normal((dim, q_heads * head_dim), base + 1)
+        wgu = normal((2 * hidden, dim), base + 2)
+        wd = normal((dim, hidden), base + 3)
         if tp_ranks == 1:
             keep["wq"].append(wqkv)           # fused rows: q, k, v
             keep["wk"].append(None)
             keep["wv"].append(None)
-        else:
-            keep["wq"].append(wqkv[q0:q0 + ql * head_dim].clone())
-            keep["wk"].append(wqkv[k0:k0 + kvl * head_dim].clone())
-            keep["wv"].append(wqkv[v0:v0 + kvl * head_dim].clone())
-            del wqkv
-        wo = normal((dim, q_heads * head_dim), base + 1)
-        keep["wo"].append(wo if tp_ranks == 1 else
-                          wo[:, tp_rank * ql * head_dim:
-                             (tp_rank + 1) * ql * head_dim].contiguous())
-        wgu = normal((2 * hidden, dim), base + 2)
-        if tp_ranks == 1:
+            keep["wo"].append(wo)
             keep["w_gate"].append(wgu)        # gate rows then up rows
             keep["w_up"].append(None)
+            keep["w_down"].append(wd)
         else:
-            keep["w_gate"].append(wgu[tp_rank * hl:(tp_rank + 1) * hl].clone())
-            keep["w_up"].append(
-                wgu[hidden + tp_rank * hl:hidden + (tp_rank + 1) * hl].clone())
-            del wgu
-        wd = normal((dim, hidden), base + 3)
-        keep["w_down"].append(wd if tp_ranks == 1 else
-                              wd[:, tp_rank * hl:(tp_rank + 1) * hl].contiguous())
+            keep["wq"].append(rows(wqkv, sl["q_rows"]))
+            keep["wk"].append(rows(wqkv, sl["k_rows"]))
+            keep["wv"].append(rows(wqkv, sl["v_rows"]))
+            keep["wo"].append(cols(wo, sl["wo_cols"]))
+            keep["w_gate"].append(rows(wgu, sl["gate_rows"]))
+            keep["w_up"].append(rows(wgu, sl["up_rows"]))
+            keep["w_down"].append(cols(wd, sl["down_cols"]))
         keep["attn_norm"].append(ones(dim))
         keep["ffn_norm"].append(ones(dim))
-        del wo, wd
+        del wqkv, wo, wgu, wd
     embed = normal((vocab, dim), 1)
     lm_full = normal((vocab, dim), 2)
-    lm_head = lm_full if tp_ranks == 1 else \
-        lm_full[tp_rank * vl:(tp_rank + 1) * vl].clone()
+    lm_head = lm_full if tp_ranks == 1 else rows(lm_full, sl["vocab_rows"])
     del lm_full
     final_norm = ones(dim)
     cos_h, sin_h = rope_tables(max_seq, head_dim, theta)
