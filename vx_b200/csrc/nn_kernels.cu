@@ -202,6 +202,15 @@ rowdot_kernel(const RowDotParams p) {
   constexpr int CHUNK_COLS = CHUNK_BYTES / (int)sizeof(W);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cols = p.cols;
+  /* x in shared memory: for bf16 weights a lane needs 8 consecutive values per
+     word; they are stored as two float4 halves 128 floats apart within each
+     group of 256, so that the 32 lanes of a warp read consecutive float4s. */
+  const int xs_stride = (cols + 255) / 256 * 256;
+  auto xs_at = [](int i) {
+    return E == 8 ? (i & ~255) | (((i >> 2) & 1) << 7) | (((i >> 3) & 31) << 2) |
+                        (i & 3)
+                  : i;
+  };
 
   /* ---- this warp's items, as a stream of (item, chunk) units ---- */
   const int64_t total_warps = (int64_t)gridDim.x * WARPS;
@@ -220,24 +229,42 @@ rowdot_kernel(const RowDotParams p) {
     ptx::fence_barrier_init();
   }
   __syncwarp();
-  auto issue = [&](int u) {
-    if (u >= units || lane != 0)
+  /* The loading side walks the same units RING_STAGES ahead, with its own
+     counters (no divisions on the way). Lane 0 issues the copies. */
+  const int last_bytes = row_bytes - (nch - 1) * CHUNK_BYTES;
+  int ld_u = 0, ld_item = first, ld_ch = 0, ld_stage = 0;
+  const char *ld_r0 = nullptr, *ld_r1 = nullptr;
+  if (units > 0) {
+    const ItemRows<W, EPI> it = item_rows<W, EPI>(p, first);
+    ld_r0 = (const char *)it.r0;
+    ld_r1 = (const char *)(it.r1 ? it.r1 : it.r0);
+  }
+  auto issue_next = [&]() {
+    if (ld_u >= units)
       return;
-    const int item = first + u / nch, ch = u - (u / nch) * nch;
-    const ItemRows<W, EPI> it = item_rows<W, EPI>(p, item);
-    const int bytes = min(CHUNK_BYTES, row_bytes - ch * CHUNK_BYTES);
-    const int s = u % RING_STAGES;
-    unsigned char *dst = my_ring + s * (2 * CHUNK_BYTES);
-    ptx::mbar_expect_tx(&bars[warp][s], 2 * bytes);
-    ptx::bulk_load(dst, (const char *)it.r0 + ch * CHUNK_BYTES, bytes,
-                   &bars[warp][s]);
-    ptx::bulk_load(dst + CHUNK_BYTES,
-                   (const char *)(it.r1 ? it.r1 : it.r0) + ch * CHUNK_BYTES,
-                   bytes, &bars[warp][s]);
+    if (lane == 0) {
+      const int bytes = ld_ch == nch - 1 ? last_bytes : CHUNK_BYTES;
+      unsigned char *dst = my_ring + ld_stage * (2 * CHUNK_BYTES);
+      uint64_t *bar = &bars[warp][ld_stage];
+      ptx::mbar_expect_tx(bar, 2 * bytes);
+      ptx::bulk_load(dst, ld_r0 + ld_ch * CHUNK_BYTES, bytes, bar);
+      ptx::bulk_load(dst + CHUNK_BYTES, ld_r1 + ld_ch * CHUNK_BYTES, bytes, bar);
+    }
+    ++ld_u;
+    ld_stage = ld_stage + 1 == RING_STAGES ? 0 : ld_stage + 1;
+    if (++ld_ch == nch) {
+      ld_ch = 0;
+      ++ld_item;
+      if (ld_u < units) {
+        const ItemRows<W, EPI> it = item_rows<W, EPI>(p, ld_item);
+        ld_r0 = (const char *)it.r0;
+        ld_r1 = (const char *)(it.r1 ? it.r1 : it.r0);
+      }
+    }
   };
   /* The weights do not depend on the kernel before this one: start them. */
   for (int u = 0; u < RING_STAGES; ++u)
-    issue(u);
+    issue_next();
   chain_release();
   chain_wait(); /* from here on: x, y, positions of the kernels before */
 
@@ -248,7 +275,7 @@ rowdot_kernel(const RowDotParams p) {
       for (int i = threadIdx.x; i < cols; i += blockDim.x) {
         const float v = p.x[b * p.x_stride + i];
         if (p.x_in_smem)
-          xs[b * cols + i] = v;
+          xs[b * xs_stride + xs_at(i)] = v;
         ss = fmaf(v, v, ss);
       }
       ss = block_sum(ss, red);
@@ -264,60 +291,80 @@ rowdot_kernel(const RowDotParams p) {
       for (int i = threadIdx.x; i < cols; i += blockDim.x) {
         const float wn = p.norm_bf16 ? bf16_at(p.norm_w, i)
                                      : ((const float *)p.norm_w)[i];
-        xs[b * cols + i] = xs[b * cols + i] * inv * wn;
+        xs[b * xs_stride + xs_at(i)] = xs[b * xs_stride + xs_at(i)] * inv * wn;
       }
     }
     __syncthreads();
   } else if (p.x_in_smem) {
     for (int b = 0; b < B; ++b)
       for (int i = threadIdx.x; i < cols; i += blockDim.x)
-        xs[b * cols + i] = p.x[b * p.x_stride + i];
+        xs[b * xs_stride + xs_at(i)] = p.x[b * p.x_stride + i];
     __syncthreads();
   }
   const float *xbase = p.x_in_smem ? xs : p.x;
-  const int64_t xstr = p.x_in_smem ? cols : p.x_stride;
+  const int64_t xstr = p.x_in_smem ? xs_stride : p.x_stride;
+  /* where a lane finds the x of its 16-byte word, and its second half */
+  const bool x_perm = E == 8 && p.x_in_smem;
+  const int lane_x = x_perm ? lane * 4 : lane * E;
+  const int hi_off = x_perm ? 128 : 4;
 
   float s0[B], s1[B];
 #pragma unroll
   for (int b = 0; b < B; ++b)
     s0[b] = s1[b] = 0.0f;
 
+  /* One 16-byte word of both rows at byte `off` of the stage, times x. */
+  auto word = [&](const unsigned char *src, const float *xcol, int off) {
+    const uint4 wa = *reinterpret_cast<const uint4 *>(src + off);
+    const uint4 wb = *reinterpret_cast<const uint4 *>(src + CHUNK_BYTES + off);
+    const float *xw = xcol + off / (int)sizeof(W);
+    float xv[B][E];
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const float4 lo = *reinterpret_cast<const float4 *>(xw + b * xstr);
+      xv[b][0] = lo.x; xv[b][1] = lo.y; xv[b][2] = lo.z; xv[b][3] = lo.w;
+      if (E == 8) {
+        const float4 hi =
+            *reinterpret_cast<const float4 *>(xw + b * xstr + hi_off);
+        xv[b][E - 4] = hi.x; xv[b][E - 3] = hi.y;
+        xv[b][E - 2] = hi.z; xv[b][E - 1] = hi.w;
+      }
+    }
+    fma16<W, B>(wa, xv, s0);
+    fma16<W, B>(wb, xv, s1);
+  };
+
+  int next_item = first, next_ch = 0, next_stage = 0;
+  uint32_t next_phase = 0;
   for (int u = 0; u < units; ++u) {
-    const int item = first + u / nch, ch = u - (u / nch) * nch;
-    const int s = u % RING_STAGES;
-    if (!ptx::mbar_wait_alone(&bars[warp][s], (u / RING_STAGES) & 1)) {
+    const int item = next_item, ch = next_ch, s = next_stage;
+    const uint32_t phase = next_phase;
+    if (++next_ch == nch) {
+      next_ch = 0;
+      ++next_item;
+    }
+    if (++next_stage == RING_STAGES) {
+      next_stage = 0;
+      next_phase ^= 1;
+    }
+    if (!ptx::mbar_try_wait(&bars[warp][s], phase) &&
+        !ptx::mbar_wait_alone(&bars[warp][s], phase)) {
       atomicCAS(&g_rowdot_status, 0, 1);
       break;
     }
-    const unsigned char *src = my_ring + s * (2 * CHUNK_BYTES);
-    const int bytes = min(CHUNK_BYTES, row_bytes - ch * CHUNK_BYTES);
+    const unsigned char *src = my_ring + s * (2 * CHUNK_BYTES) + lane * 16;
+    const float *xcol = xbase + ch * CHUNK_COLS + lane_x;
+    if (ch != nch - 1 || last_bytes == CHUNK_BYTES) {
 #pragma unroll
-    for (int i = 0; i < CHUNK_BYTES / 512; ++i) {
-      const int off = i * 512 + lane * 16;
-      if (off < bytes) {
-        const uint4 wa = *reinterpret_cast<const uint4 *>(src + off);
-        const uint4 wb = *reinterpret_cast<const uint4 *>(src + CHUNK_BYTES + off);
-        const int c = ch * CHUNK_COLS + off / (int)sizeof(W);
-        float xv[B][E];
-#pragma unroll
-        for (int b = 0; b < B; ++b) {
-          const float4 lo =
-              *reinterpret_cast<const float4 *>(xbase + b * xstr + c);
-          xv[b][0] = lo.x; xv[b][1] = lo.y; xv[b][2] = lo.z; xv[b][3] = lo.w;
-          if (E == 8) {
-            const float4 hi =
-                *reinterpret_cast<const float4 *>(xbase + b * xstr + c + 4);
-            xv[b][E - 4] = hi.x; xv[b][E - 3] = hi.y;
-            xv[b][E - 2] = hi.z; xv[b][E - 1] = hi.w;
-          }
-        }
-        fma16<W, B>(wa, xv, s0);
-        fma16<W, B>(wb, xv, s1);
-      }
+      for (int i = 0; i < CHUNK_BYTES / 512; ++i)
+        word(src, xcol, i * 512);
+    } else {
+      for (int off = 0; off + lane * 16 < last_bytes; off += 512)
+        word(src, xcol, off);
     }
     /* Every lane has read the stage: it may be filled again. */
     __syncwarp();
-    issue(u + RING_STAGES);
+    issue_next();
     if (ch != nch - 1)
       continue;
 
@@ -428,7 +475,7 @@ const char *check_launch(const char *what) {
 
 template <typename W, int B, int EPI>
 const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
-  const size_t xbytes = (size_t)B * p.cols * sizeof(float);
+  const size_t xbytes = (size_t)B * ((p.cols + 255) / 256 * 256) * sizeof(float);
   p.x_in_smem = xbytes <= (size_t)MAX_SMEM_X;
   if (p.norm_w && !p.x_in_smem)
     return "a fused RMSNorm needs the activations of all sequences to fit in "
@@ -440,8 +487,9 @@ const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                          RING_BYTES + MAX_SMEM_X);
   });
-  /* One block of 16 warps per SM (the ring takes 128 KiB of its shared
-     memory); fewer blocks when there are fewer items than warps. */
+  /* One block of 16 warps per SM with a 128 KiB ring (measured faster than
+     two blocks of 8 warps with 64 KiB each: 31.7 vs 34.3 us on the 7B gate/up
+     projection). Fewer blocks when there are fewer items than warps. */
   int blocks = sm_count();
   const int wanted = (p.items + WARPS - 1) / WARPS;
   if (blocks > wanted)
@@ -543,7 +591,9 @@ template <int GH>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_decode_kernel(const AttnArgs a) {
   chain_release();
-  chain_wait();
+  /* The position was written by the step before this one, and every cache row
+     below it by earlier steps: those may be read before the kernels of this
+     step have finished. Row `pos` and q come from the kernel just before. */
   const int hd = a.head_dim, hd4 = hd / 4;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int split_idx = blockIdx.x, b = blockIdx.z;
@@ -565,6 +615,32 @@ attention_decode_kernel(const AttnArgs a) {
   const float *vc = a.v_cache + b * a.cache_batch_stride;
   const float *qb = a.q + (int64_t)b * a.q_heads * hd;
 
+  /* A warp takes every fourth position, NB of them at a time so that their
+     loads are in flight together. */
+  constexpr int NB = 4;
+  float4 kv[NB], vv[NB];
+  auto load_batch = [&](int t0, bool old_rows_only) {
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+      const int t = t0 + j * ATT_WARPS;
+      const bool take = active && t < t_end &&
+                        (old_rows_only ? t < pos : t == pos || t0 != t_begin + warp);
+      if (take) {
+        const int64_t row = ((int64_t)t * a.kv_heads + g) * hd + lane * 4;
+        kv[j] = *reinterpret_cast<const float4 *>(kc + row);
+        vv[j] = *reinterpret_cast<const float4 *>(vc + row);
+      } else if (!old_rows_only && !(active && t < t_end)) {
+        kv[j] = vv[j] = make_float4(0, 0, 0, 0);
+      }
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < NB; ++j)
+    kv[j] = vv[j] = make_float4(0, 0, 0, 0);
+  load_batch(t_begin + warp, true);
+  chain_wait();
+  load_batch(t_begin + warp, false); /* only row `pos`, if it is in this batch */
+
   float4 qv[GH];
   float m[GH], l[GH];
   float4 acc[GH];
@@ -578,28 +654,39 @@ attention_decode_kernel(const AttnArgs a) {
     acc[h] = make_float4(0, 0, 0, 0);
   }
 
-  for (int t = t_begin + warp; t < t_end; t += ATT_WARPS) {
-    const int64_t row = ((int64_t)t * a.kv_heads + g) * hd + lane * 4;
-    const float4 kv = active ? *reinterpret_cast<const float4 *>(kc + row)
-                             : make_float4(0, 0, 0, 0);
-    const float4 vv = active ? *reinterpret_cast<const float4 *>(vc + row)
-                             : make_float4(0, 0, 0, 0);
+  for (int t0 = t_begin + warp; t0 < t_end; t0 += NB * ATT_WARPS) {
+    if (t0 != t_begin + warp)
+      load_batch(t0, false);
 #pragma unroll
     for (int h = 0; h < GH; ++h) {
-      float d = qv[h].x * kv.x;
-      d = fmaf(qv[h].y, kv.y, d);
-      d = fmaf(qv[h].z, kv.z, d);
-      d = fmaf(qv[h].w, kv.w, d);
-      const float s = warp_sum(d) * scale;
-      const float mn = fmaxf(m[h], s);
-      const float fix = expf(m[h] - mn);
-      const float pw = expf(s - mn);
-      l[h] = l[h] * fix + pw;
-      acc[h].x = acc[h].x * fix + pw * vv.x;
-      acc[h].y = acc[h].y * fix + pw * vv.y;
-      acc[h].z = acc[h].z * fix + pw * vv.z;
-      acc[h].w = acc[h].w * fix + pw * vv.w;
-      m[h] = mn;
+      float d[NB];
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        d[j] = qv[h].x * kv[j].x;
+        d[j] = fmaf(qv[h].y, kv[j].y, d[j]);
+        d[j] = fmaf(qv[h].z, kv[j].z, d[j]);
+        d[j] = fmaf(qv[h].w, kv[j].w, d[j]);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+          d[j] += __shfl_xor_sync(0xffffffffu, d[j], o);
+#pragma unroll
+      for (int j = 0; j < NB; ++j) {
+        if (t0 + j * ATT_WARPS >= t_end)
+          continue;
+        const float s = d[j] * scale;
+        const float mn = fmaxf(m[h], s);
+        const float fix = expf(m[h] - mn);
+        const float pw = expf(s - mn);
+        l[h] = l[h] * fix + pw;
+        acc[h].x = acc[h].x * fix + pw * vv[j].x;
+        acc[h].y = acc[h].y * fix + pw * vv[j].y;
+        acc[h].z = acc[h].z * fix + pw * vv[j].z;
+        acc[h].w = acc[h].w * fix + pw * vv[j].w;
+        m[h] = mn;
+      }
     }
   }
 
