@@ -195,8 +195,7 @@ rowdot_kernel(const RowDotParams p) {
   extern __shared__ __align__(128) unsigned char smem_dyn[];
   unsigned char *ring = smem_dyn;                    /* [warp][stage][2][chunk] */
   float *xs = (float *)(smem_dyn + RING_BYTES);      /* [B][cols] when x_in_smem */
-  __shared__ float red[32];
-  __shared__ float inv_rms[B];
+  __shared__ float ssq[B][WARPS]; /* per-warp sums of squares of x */
   __shared__ __align__(8) uint64_t bars[WARPS][RING_STAGES];
   constexpr int E = 16 / (int)sizeof(W);             /* elements per 16 bytes */
   constexpr int CHUNK_COLS = CHUNK_BYTES / (int)sizeof(W);
@@ -269,32 +268,38 @@ rowdot_kernel(const RowDotParams p) {
   chain_wait(); /* from here on: x, y, positions of the kernels before */
 
   /* ---- prologue: x (normalised if asked) into shared memory ---- */
+  float inv[B];
+#pragma unroll
+  for (int b = 0; b < B; ++b)
+    inv[b] = 1.0f;
   if (p.norm_w) {
+    /* RMSNorm (nn_rms_norm, nn.vx:212-239; rmsnorm, llama2.vx:476-498) is
+       y_i = x_i * inv * w_i with inv = 1/sqrt(mean(x^2) + eps). The factor inv
+       is common to a whole row product, so the ring is fed x_i * w_i and inv
+       multiplies the finished dot product: the weights start to be consumed
+       after one pass over x and one barrier, while the sum of squares is only
+       needed by the first epilogue. */
     for (int b = 0; b < B; ++b) {
       float ss = 0.0f;
       for (int i = threadIdx.x; i < cols; i += blockDim.x) {
         const float v = p.x[b * p.x_stride + i];
-        if (p.x_in_smem)
-          xs[b * xs_stride + xs_at(i)] = v;
-        ss = fmaf(v, v, ss);
-      }
-      ss = block_sum(ss, red);
-      if (threadIdx.x == 0)
-        inv_rms[b] = 1.0f / sqrtf(ss / (float)cols + p.eps);
-    }
-    __syncthreads();
-    /* nn_rms_norm (nn.vx:212-239): y = x * inv * w.  llama2.vx rmsnorm
-       (:476-498): w * (inv * x).  Both are two roundings of the same three
-       factors; the order below is the first one. */
-    for (int b = 0; b < B; ++b) {
-      const float inv = inv_rms[b];
-      for (int i = threadIdx.x; i < cols; i += blockDim.x) {
         const float wn = p.norm_bf16 ? bf16_at(p.norm_w, i)
                                      : ((const float *)p.norm_w)[i];
-        xs[b * xs_stride + xs_at(i)] = xs[b * xs_stride + xs_at(i)] * inv * wn;
+        xs[b * xs_stride + xs_at(i)] = v * wn;
+        ss = fmaf(v, v, ss);
       }
+      ss = warp_sum(ss);
+      if (lane == 0)
+        ssq[b][warp] = ss;
     }
     __syncthreads();
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      float ss = 0.0f;
+      for (int w = 0; w < WARPS; ++w) /* fixed order */
+        ss += ssq[b][w];
+      inv[b] = 1.0f / sqrtf(ss / (float)cols + p.eps);
+    }
   } else if (p.x_in_smem) {
     for (int b = 0; b < B; ++b)
       for (int i = threadIdx.x; i < cols; i += blockDim.x)
@@ -375,8 +380,8 @@ rowdot_kernel(const RowDotParams p) {
     float t0[B], t1[B];
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      t0[b] = warp_sum(s0[b]);
-      t1[b] = warp_sum(s1[b]);
+      t0[b] = warp_sum(s0[b]) * inv[b];
+      t1[b] = warp_sum(s1[b]) * inv[b];
       s0[b] = s1[b] = 0.0f;
     }
     if (lane != 0)
