@@ -96,7 +96,11 @@ typedef struct {
      layer, and the job of vx_collective_init sums the partial outputs.
      1 = not sharded. The fields above are the WHOLE model's. */
   int32_t tp_ranks;
-  /* How the partial sums are added across ranks: 0 = NCCL all-reduce. */
+  /* How the partial sums of the row-split projections are added across ranks:
+     0 = an NCCL all-reduce after the projection kernel; 1 = the projection
+     kernel itself stores its results into every rank's receive buffer over
+     NVLink (peer memory mapped through CUDA IPC) and one small kernel per rank
+     adds them once every rank's flag has arrived. */
   int32_t tp_reduce;
 } vx_decoder_config;
 

@@ -104,6 +104,12 @@ struct vx_decoder {
   float *x, *q, *att, *h, *tmp, *logits, *k_cache, *v_cache, *scratch;
   int32_t *tokens, *positions, *counters, *local_best;
   float2 *pair, *pairs_all;
+  /* tp_reduce == 1: partial sums exchanged through peer memory */
+  bool push;
+  vxb::TpPush tp;
+  void *recv;                       /* this rank's slots + flags (IPC-shared) */
+  void *peer_recv[vxb::kMaxTpRanks];
+  int32_t *tp_epoch, *tp_done;
   int64_t cache_layer_stride, cache_batch_stride;
   int split;
   int host_pos;
@@ -133,6 +139,77 @@ void all_reduce(vx_decoder *d, float *buf, int64_t count) {
                                       vx::NcclSum, job->comm(), d->stream);
   if (r)
     stop("vx_decoder: ncclAllReduce failed: %s", job->api()->GetErrorString(r));
+}
+
+/* x += the sum over ranks of the partial projection just computed: either the
+   partials were pushed into every rank's receive slots by the projection
+   kernel itself and one small kernel adds them, or NCCL sums d->tmp and a
+   second kernel adds it. Returns the number of launches. */
+int add_partials(vx_decoder *d) {
+  if (d->ranks == 1)
+    return 0;
+  const int64_t n = (int64_t)d->c.batch * d->c.dim;
+  if (d->push) {
+    need(vxb::tp_reduce_add(d->x, d->tp.slots[d->tp.rank],
+                            d->tp.flags[d->tp.rank], d->tp_epoch, d->ranks, n,
+                            d->stream),
+         "adding the partial sums");
+    return 1;
+  }
+  all_reduce(d, d->tmp, n);
+  add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, d->stream>>>(d->x, d->tmp, n);
+  return 2;
+}
+
+/* The receive buffers of the pushed exchange: every rank allocates slots and
+   flags, shares them through CUDA IPC (the handles travel by an NCCL
+   all-gather), and maps every other rank's. */
+void open_peer_buffers(vx_decoder *d, int rank) {
+  const int64_t n = (int64_t)d->c.batch * d->c.dim;
+  const size_t slot_bytes = (size_t)2 * d->ranks * n * sizeof(float);
+  const size_t bytes = slot_bytes + 256;
+  CUDA_OK(cudaMalloc(&d->recv, bytes));
+  CUDA_OK(cudaMemset(d->recv, 0, bytes));
+  d->tp_epoch = dev_alloc<int32_t>(2);
+  d->tp_done = d->tp_epoch + 1;
+  cudaIpcMemHandle_t mine;
+  CUDA_OK(cudaIpcGetMemHandle(&mine, d->recv));
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  float *one = dev_alloc<float>(16), *all = dev_alloc<float>(16 * (size_t)d->ranks);
+  CUDA_OK(cudaMemcpy(one, &mine, 64, cudaMemcpyHostToDevice));
+  vx::NcclCollective *job = vxb::nccl_job();
+  int r = job->api()->AllGather(one, all, 16, vx::NcclFloat32, job->comm(),
+                                d->stream);
+  if (r)
+    stop("vx_decoder: ncclAllGather failed: %s", job->api()->GetErrorString(r));
+  CUDA_OK(cudaStreamSynchronize(d->stream));
+  std::vector<cudaIpcMemHandle_t> handles(d->ranks);
+  CUDA_OK(cudaMemcpy(handles.data(), all, 64 * (size_t)d->ranks,
+                     cudaMemcpyDeviceToHost));
+  for (int p = 0; p < d->ranks; ++p) {
+    if (p == rank) {
+      d->peer_recv[p] = d->recv;
+    } else {
+      const cudaError_t e = cudaIpcOpenMemHandle(
+          &d->peer_recv[p], handles[p], cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess)
+        stop("vx_decoder: cannot map the receive buffer of rank %d: %s. The "
+             "ranks must be GPUs of one machine with peer access.",
+             p, cudaGetErrorString(e));
+    }
+    d->tp.slots[p] = (float *)d->peer_recv[p];
+    d->tp.flags[p] = (int32_t *)((char *)d->peer_recv[p] + slot_bytes);
+  }
+  d->tp.ranks = d->ranks;
+  d->tp.rank = rank;
+  d->tp.count = n;
+  d->tp.epoch = d->tp_epoch;
+  d->tp.done = d->tp_done;
+  cudaFree(one);
+  cudaFree(all);
+  /* Nobody writes into a buffer before everybody has mapped it. */
+  all_reduce(d, d->tmp, 1);
+  CUDA_OK(cudaStreamSynchronize(d->stream));
 }
 
 /* Queue one token on d->stream. */
@@ -203,15 +280,11 @@ void record_step(vx_decoder *d, int max_pos) {
     oa.batch = B;
     oa.y = d->ranks > 1 ? d->tmp : d->x;
     oa.y_stride = c.dim;
-    oa.mode = d->ranks > 1 ? 0 : 1;
+    oa.mode = d->push ? 3 : (d->ranks > 1 ? 0 : 1);
+    oa.push = &d->tp;
     need(vxb::matvec(oa, s), "the output projection");
     launches += 3;
-    if (d->ranks > 1) {
-      all_reduce(d, d->tmp, (int64_t)B * c.dim);
-      add_kernel<<<(B * c.dim + 255) / 256, 256, 0, s>>>(d->x, d->tmp,
-                                                        (int64_t)B * c.dim);
-      launches += 2;
-    }
+    launches += add_partials(d);
 
     vxb::SwigluArgs sa{};
     sa.w = d->w_gate[l];
@@ -239,15 +312,11 @@ void record_step(vx_decoder *d, int max_pos) {
     da.batch = B;
     da.y = d->ranks > 1 ? d->tmp : d->x;
     da.y_stride = c.dim;
-    da.mode = d->ranks > 1 ? 0 : 1;
+    da.mode = d->push ? 3 : (d->ranks > 1 ? 0 : 1);
+    da.push = &d->tp;
     need(vxb::matvec(da, s), "the down projection");
     launches += 2;
-    if (d->ranks > 1) {
-      all_reduce(d, d->tmp, (int64_t)B * c.dim);
-      add_kernel<<<(B * c.dim + 255) / 256, 256, 0, s>>>(d->x, d->tmp,
-                                                        (int64_t)B * c.dim);
-      launches += 2;
-    }
+    launches += add_partials(d);
   }
 
   vxb::MatvecArgs la{};
@@ -399,6 +468,12 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
   d->host_pos = 0;
   d->kernels_per_step = 0;
   CUDA_OK(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+  d->push = false;
+  d->recv = nullptr;
+  if (d->ranks > 1 && c.tp_reduce == 1) {
+    open_peer_buffers(d, rank);
+    d->push = true;
+  }
   CUDA_OK(cudaDeviceSynchronize());
   return d;
 }
@@ -407,6 +482,16 @@ void vx_decoder_destroy(vx_decoder *d) {
   if (!d)
     return;
   cudaStreamSynchronize(d->stream);
+  if (d->push) {
+    /* No rank unmaps or frees while another may still write into it. */
+    all_reduce(d, d->tmp, 1);
+    cudaStreamSynchronize(d->stream);
+    for (int p = 0; p < d->ranks; ++p)
+      if (p != d->tp.rank)
+        cudaIpcCloseMemHandle(d->peer_recv[p]);
+    cudaFree(d->recv);
+    cudaFree(d->tp_epoch);
+  }
   for (auto &g : d->graphs)
     cudaGraphExecDestroy(g.second);
   for (void *p : {(void *)d->x, (void *)d->tmp, (void *)d->q, (void *)d->att,

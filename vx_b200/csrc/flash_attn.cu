@@ -282,16 +282,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
 
       const int k0 = j * BKV;
       const bool diagonal = causal && k0 + BKV - 1 > q_base + w * BQ;
+      /* Raw scores; the scale (positive) is folded into the exponent's FMA.
+         Four running maxima keep the chain short. */
       float sv[64];
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
-        float v = __uint_as_float(raw[c >> 5][c & 31]) * scale_log2;
+        float v = __uint_as_float(raw[c >> 5][c & 31]);
         if (diagonal && k0 + c > q_row)
           v = -INFINITY;
         sv[c] = v;
-        mx = fmaxf(mx, v);
+        mx4[c & 3] = fmaxf(mx4[c & 3], v);
       }
+      const float mx =
+          fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
       /* Keep the maximum in use unless the new one is more than 2^8 above it. */
       const bool grow = mx > m_used + 8.0f;
       const float m_new = grow ? mx : m_used;
@@ -327,16 +331,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       m_used = m_new;
 
-      float part = 0.0f;
+      /* p = 2^(s * scale - m); the row sum adds the f32 weights in four
+         independent chains, the bf16 copies go to the P V product. */
+      float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       uint32_t packed[32];
+      const float neg_m = -m_used;
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = ex2(sv[c] - m_used), p1 = ex2(sv[c + 1] - m_used);
+        const float p0 = ex2(fmaf(sv[c], scale_log2, neg_m));
+        const float p1 = ex2(fmaf(sv[c + 1], scale_log2, neg_m));
+        part4[(c >> 1) & 3] += p0 + p1;
         const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
-        /* The sum uses the rounded weights: they are what multiplies V. */
-        part += __low2float(pr) + __high2float(pr);
         packed[c >> 1] = *reinterpret_cast<const uint32_t *>(&pr);
       }
+      const float part = (part4[0] + part4[1]) + (part4[2] + part4[3]);
       l_sum = l_sum * fix + part;
       /* Row r of P is one 128-byte swizzle row: 16-byte chunk c sits at chunk
          position c ^ (r % 8). */

@@ -56,9 +56,34 @@ struct MatvecArgs {
   bool norm_bf16;
   float eps;
   /* epilogue */
-  int mode;            /* 0 y = s, 1 y += s, 2 y = s + bias */
+  int mode;            /* 0 y = s, 1 y += s, 2 y = s + bias, 3 push to peers */
   const void *bias;    /* mode 2, bf16 */
+  const struct TpPush *push; /* mode 3 */
 };
+
+/* Mode 3: the projection is one rank's partial of a row-split product. Every
+   finished value goes straight into slot `rank` of EVERY rank's receive buffer
+   (plain stores over NVLink into peer memory; no y is written), and when the
+   whole kernel has finished, the flag [set][rank] of every rank gets the call
+   number. Receive buffers: slots f32 [2 sets][ranks][count], flags int32
+   [2 sets][ranks]; call c (1, 2, ...) uses set c & 1. `epoch` (device int32)
+   holds the number of calls completed so far; tp_reduce_add() advances it. */
+constexpr int kMaxTpRanks = 8;
+struct TpPush {
+  float *slots[kMaxTpRanks];   /* per rank: its receive slots */
+  int32_t *flags[kMaxTpRanks]; /* per rank: its flags */
+  int ranks, rank;
+  int64_t count;               /* values per slot: batch * rows */
+  const int32_t *epoch;        /* this rank's, device memory */
+  int32_t *done;               /* this rank's block counter, zero between calls */
+};
+/* x[i] += sum over ranks, in rank order, of slot[r][i], after every rank's flag
+   for call epoch + 1 has arrived (a bounded wait: on expiry the status word is
+   set and the sum is taken anyway); then epoch += 1. One block. */
+const char *tp_reduce_add(float *x, const float *my_slots,
+                          const int32_t *my_flags, int32_t *epoch, int ranks,
+                          int64_t count, cudaStream_t stream);
+int tp_status(cudaStream_t stream);
 const char *matvec(const MatvecArgs &a, cudaStream_t stream);
 
 /* out[r] = silu(g_r) * u_r, g from row r and u from row rows + r of w. */

@@ -419,7 +419,8 @@ int32_t vx_b200_gemm(int32_t dtype, int32_t route, int64_t m, int64_t n,
 int32_t vx_b200_kernel_status(void) {
   const int g = vxb::gemm_status(vxb::caller_stream());
   const int f = vxb::flash_status(vxb::caller_stream());
-  return g ? g : f;
+  const int t = vxb::tp_status(vxb::caller_stream());
+  return g ? g : (f ? f : t);
 }
 
 int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,

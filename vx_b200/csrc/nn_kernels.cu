@@ -80,7 +80,8 @@ __device__ float block_sum(float v, float *red) {
  * One kernel for every projection of the decoder.  An ITEM is a pair of weight
  * rows whose results the epilogue needs together; a warp owns a contiguous,
  * balanced range of items and streams both rows of an item at once. */
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_BIAS = 2, EPI_SWIGLU = 3, EPI_QKV = 4 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_BIAS = 2, EPI_SWIGLU = 3, EPI_QKV = 4,
+       EPI_PUSH = 5 };
 
 struct RowDotParams {
   /* weights */
@@ -108,6 +109,8 @@ struct RowDotParams {
   float *k_cache, *v_cache;
   int64_t cache_batch_stride;
   int max_seq;
+  /* EPI_PUSH */
+  TpPush tp;
 };
 
 /* acc[b] += sum over the E weights of one 16-byte word (8 bf16 or 4 f32) of
@@ -266,6 +269,8 @@ rowdot_kernel(const RowDotParams p) {
     issue_next();
   chain_release();
   chain_wait(); /* from here on: x, y, positions of the kernels before */
+  const int push_call = EPI == EPI_PUSH ? *p.tp.epoch + 1 : 0;
+  const int64_t push_set = push_call & 1;
 
   /* ---- prologue: x (normalised if asked) into shared memory ---- */
   float inv[B];
@@ -390,7 +395,18 @@ rowdot_kernel(const RowDotParams p) {
     /* ---- epilogue, lane 0 ---- */
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      if (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_BIAS) {
+      if (EPI == EPI_PUSH) {
+        /* This rank's partial of a row-split product, stored into slot
+           `rank` of every rank's receive buffer (peer memory over NVLink). */
+        const int ra = 2 * item;
+        const int64_t at =
+            (push_set * p.tp.ranks + p.tp.rank) * p.tp.count + b * p.y_stride + ra;
+        for (int r = 0; r < p.tp.ranks; ++r) {
+          p.tp.slots[r][at] = t0[b];
+          if (r1)
+            p.tp.slots[r][at + 1] = t1[b];
+        }
+      } else if (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_BIAS) {
         float *y = p.y + b * p.y_stride;
         const int ra = 2 * item, rb = 2 * item + 1;
         float v0 = t0[b], v1 = t1[b];
@@ -454,6 +470,27 @@ rowdot_kernel(const RowDotParams p) {
                                ((int64_t)pos * p.kv_heads + local) * hd;
         dst[ia] = oa;
         dst[ib] = ob;
+      }
+    }
+  }
+
+  if (EPI == EPI_PUSH) {
+    /* When the last block has finished, every value of this rank is in every
+       rank's slot: tell them, with the call number as the flag's value. */
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int arrived = atomicAdd(p.tp.done, 1);
+      if (arrived == (int)gridDim.x - 1) {
+        *p.tp.done = 0;
+        __threadfence_system();
+        const int call = push_call;
+        for (int r = 0; r < p.tp.ranks; ++r) {
+          int32_t *flag = p.tp.flags[r] + push_set * p.tp.ranks + p.tp.rank;
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag),
+                       "r"(call)
+                       : "memory");
+        }
       }
     }
   }
@@ -526,6 +563,48 @@ const char *launch_rowdot(RowDotParams &p, bool wbf16, cudaStream_t stream) {
     return "the stride between sequences must be a multiple of 4 values";
   return wbf16 ? launch_rowdot_w<__nv_bfloat16, EPI>(p, stream)
                : launch_rowdot_w<float, EPI>(p, stream);
+}
+
+/* ---------------------------------------------------- the receiving side
+ * of a pushed projection: wait (bounded) until every rank's flag carries this
+ * call's number, then x += the ranks' partials in rank order -- every rank
+ * adds the same values in the same order, so x stays identical on all ranks. */
+__device__ int g_tp_status; /* non-zero: a flag never arrived */
+
+__global__ void __launch_bounds__(1024)
+tp_reduce_add_kernel(float *x, const float *slots, const int32_t *flags,
+                     int32_t *epoch, int ranks, int64_t count) {
+  chain_release();
+  chain_wait();
+  const int call = *epoch + 1;
+  const int64_t set = call & 1;
+  if ((int)threadIdx.x < ranks) {
+    const int32_t *flag = flags + set * ranks + threadIdx.x;
+    const long long t0 = clock64();
+    for (;;) {
+      int32_t seen;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag)
+                   : "memory");
+      if (seen >= call)
+        break;
+      if (clock64() - t0 > ptx::kWaitCycles) {
+        atomicCAS(&g_tp_status, 0, 0x51);
+        break;
+      }
+      __nanosleep(40);
+    }
+  }
+  __syncthreads();
+  const float *mine = slots + set * ranks * count;
+  for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
+    float v = x[i];
+    for (int r = 0; r < ranks; ++r)
+      v += __ldcg(mine + r * count + i);
+    x[i] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    *epoch = call;
 }
 
 /* ------------------------------------------------------------- rms_norm
@@ -883,6 +962,11 @@ const char *matvec(const MatvecArgs &a, cudaStream_t stream) {
   case 0: return launch_rowdot<EPI_STORE>(p, a.wbf16, stream);
   case 1: return launch_rowdot<EPI_ADD>(p, a.wbf16, stream);
   case 2: return launch_rowdot<EPI_BIAS>(p, a.wbf16, stream);
+  case 3:
+    if (!a.push || a.push->ranks < 1 || a.push->ranks > kMaxTpRanks)
+      return "a pushed projection needs the receive buffers of 1 to 8 ranks";
+    p.tp = *a.push;
+    return launch_rowdot<EPI_PUSH>(p, a.wbf16, stream);
   default: return "unknown matvec mode";
   }
 }
@@ -959,6 +1043,33 @@ const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream) {
   p.cache_batch_stride = a.cache_batch_stride;
   p.max_seq = a.max_seq;
   return launch_rowdot<EPI_QKV>(p, a.wbf16, stream);
+}
+
+const char *tp_reduce_add(float *x, const float *my_slots,
+                          const int32_t *my_flags, int32_t *epoch, int ranks,
+                          int64_t count, cudaStream_t stream) {
+  if (ranks < 1 || ranks > kMaxTpRanks)
+    return "1 to 8 ranks";
+  launch_chained(tp_reduce_add_kernel, dim3(1), dim3(1024), 0, stream, x,
+                 my_slots, my_flags, epoch, ranks, count);
+  return check_launch("the partial-sum launch");
+}
+
+int tp_status(cudaStream_t stream) {
+  int v = 0, zero = 0;
+  if (cudaStreamSynchronize(stream) != cudaSuccess)
+    return -1;
+  if (cudaMemcpyFromSymbol(&v, g_tp_status, sizeof v) != cudaSuccess)
+    return -1;
+  if (v)
+    cudaMemcpyToSymbol(g_tp_status, &zero, sizeof zero);
+  int r = 0;
+  if (cudaMemcpyFromSymbol(&r, g_rowdot_status, sizeof r) == cudaSuccess && r) {
+    cudaMemcpyToSymbol(g_rowdot_status, &zero, sizeof zero);
+    if (!v)
+      v = 0x52;
+  }
+  return v;
 }
 
 const char *rms_norm(float *y, const float *x, const void *w, bool wbf16, int n,

@@ -178,7 +178,7 @@ def rope_tables(max_seq, head_dim, theta):
 
 def nn_bf16_model(dim, hidden, n_layers, q_heads, kv_heads, head_dim, vocab,
                   max_seq, seed=7, batch=1, tp_rank=0, tp_ranks=1,
-                  theta=10000.0, eps=1e-5, device=None):
+                  theta=10000.0, eps=1e-5, device=None, tp_reduce=1):
     """Build the model on the GPU (torch only holds the memory). Every value is
     a function of (seed, tensor, element index), so all tensor-parallel degrees
     see the same model; a rank keeps its slice. Returns (Decoder, tensors) where
@@ -257,7 +257,7 @@ def nn_bf16_model(dim, hidden, n_layers, q_heads, kv_heads, head_dim, vocab,
                         q_heads=q_heads, kv_heads=kv_heads, head_dim=head_dim,
                         vocab=vocab, max_seq=max_seq, eps=eps, rope_theta=theta,
                         weights_bf16=1, batch=batch, tp_ranks=tp_ranks,
-                        tp_reduce=0)
+                        tp_reduce=tp_reduce if tp_ranks > 1 else 0)
     tensors = dict(keep, embed=embed, lm_head=lm_head, final_norm=final_norm,
                    cos=cos_h, sin=sin_h)
     return Decoder(cfg, weights, keep=tensors), tensors
