@@ -124,3 +124,29 @@ def test_nn_decoder_tokens_match_oracle(oracle, batch):
     for b in range(batch):
         want = oracle_generate(oracle, hm, list(prompts[b]), steps, max_seq)
         assert got[b] == want, "sequence %d: %s" % (b, report(got[b], want))
+
+
+WIDE_NN = dict(dim=2048, hidden=2816, n_layers=2, q_heads=16, kv_heads=4,
+               head_dim=128, vocab=2048)
+
+
+def test_nn_decoder_batch16_unfused_norm(oracle):
+    """Sixteen sequences of 2048-wide activations exceed the shared memory the
+    projection kernels give the fused RMSNorm, so the decoder normalises with
+    a kernel of its own; the tokens must still be the oracle's."""
+    batch, max_seq, steps = 16, 48, 10
+    dec, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=batch, **WIDE_NN)
+    hm = nn_host_model(oracle, tensors, WIDE_NN, max_seq)
+    rng = np.random.default_rng(21)
+    prompts = rng.integers(0, WIDE_NN["vocab"], (batch, 12))
+    got = [[] for _ in range(batch)]
+    for p in range(prompts.shape[1]):
+        toks = dec.step(list(prompts[:, p]))
+    for _ in range(steps):
+        for b in range(batch):
+            got[b].append(toks[b])
+        toks = dec.step(None)
+    dec.close()
+    for b in (0, 7, 15):
+        want = oracle_generate(oracle, hm, list(prompts[b]), steps, max_seq)
+        assert got[b] == want, "sequence %d: %s" % (b, report(got[b], want))

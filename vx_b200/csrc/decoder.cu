@@ -101,7 +101,8 @@ struct vx_decoder {
   const void *embed, *final_norm, *lm_head;
   const float *cos_t, *sin_t;
   /* device state */
-  float *x, *q, *att, *h, *tmp, *logits, *k_cache, *v_cache, *scratch;
+  float *x, *xn, *q, *att, *h, *tmp, *logits, *k_cache, *v_cache, *scratch;
+  bool fused_norm; /* the activations of all sequences fit the projections' shared memory */
   int32_t *tokens, *positions, *counters, *local_best;
   float2 *pair, *pairs_all;
   /* tp_reduce == 1: partial sums exchanged through peer memory */
@@ -212,6 +213,19 @@ void open_peer_buffers(vx_decoder *d, int rank) {
   CUDA_OK(cudaStreamSynchronize(d->stream));
 }
 
+/* The input of a projection that follows an RMSNorm: x itself when the
+   projection kernel applies the norm (its shared memory holds the activations
+   of all sequences), else x normalised by a kernel of its own into d->xn. */
+const float *normed(vx_decoder *d, const void *norm_w, int &launches) {
+  if (d->fused_norm)
+    return d->x;
+  need(vxb::rms_norm(d->xn, d->x, norm_w, d->c.weights_bf16 != 0, d->c.dim,
+                     d->c.eps, d->c.batch, d->c.dim, d->stream),
+       "RMSNorm");
+  ++launches;
+  return d->xn;
+}
+
 /* Queue one token on d->stream. */
 void record_step(vx_decoder *d, int max_pos) {
   const vx_decoder_config &c = d->c;
@@ -234,10 +248,10 @@ void record_step(vx_decoder *d, int max_pos) {
     qa.kv_heads = d->kv_local;
     qa.head_dim = hd;
     qa.cols = c.dim;
-    qa.x = d->x;
+    qa.x = normed(d, d->attn_norm[l], launches);
     qa.x_stride = c.dim;
     qa.batch = B;
-    qa.norm_w = d->attn_norm[l];
+    qa.norm_w = d->fused_norm ? d->attn_norm[l] : nullptr;
     qa.norm_bf16 = bf;
     qa.eps = c.eps;
     qa.rope_mode = bf ? 0 : 1;
@@ -292,12 +306,12 @@ void record_step(vx_decoder *d, int max_pos) {
     sa.wbf16 = bf;
     sa.rows = d->hidden_local;
     sa.cols = c.dim;
-    sa.x = d->x;
+    sa.x = normed(d, d->ffn_norm[l], launches);
     sa.x_stride = c.dim;
     sa.out = d->h;
     sa.out_stride = d->hidden_local;
     sa.batch = B;
-    sa.norm_w = d->ffn_norm[l];
+    sa.norm_w = d->fused_norm ? d->ffn_norm[l] : nullptr;
     sa.norm_bf16 = bf;
     sa.eps = c.eps;
     need(vxb::swiglu(sa, s), "gate/up");
@@ -324,10 +338,10 @@ void record_step(vx_decoder *d, int max_pos) {
   la.wbf16 = bf;
   la.rows = d->vocab_local;
   la.cols = c.dim;
-  la.x = d->x;
+  la.x = normed(d, d->final_norm, launches);
   la.x_stride = c.dim;
   la.batch = B;
-  la.norm_w = d->final_norm;
+  la.norm_w = d->fused_norm ? d->final_norm : nullptr;
   la.norm_bf16 = bf;
   la.eps = c.eps;
   la.y = d->logits;
@@ -451,6 +465,8 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
   d->cache_layer_stride = d->cache_batch_stride * B;
   d->x = dev_alloc<float>((size_t)B * c.dim);
   d->tmp = dev_alloc<float>((size_t)B * c.dim);
+  d->xn = dev_alloc<float>((size_t)B * c.dim);
+  d->fused_norm = (size_t)B * ((c.dim + 255) / 256 * 256) * sizeof(float) <= 96 * 1024;
   d->q = dev_alloc<float>((size_t)B * d->q_local * c.head_dim);
   d->att = dev_alloc<float>((size_t)B * d->q_local * c.head_dim);
   d->h = dev_alloc<float>((size_t)B * d->hidden_local);
@@ -494,7 +510,7 @@ void vx_decoder_destroy(vx_decoder *d) {
   }
   for (auto &g : d->graphs)
     cudaGraphExecDestroy(g.second);
-  for (void *p : {(void *)d->x, (void *)d->tmp, (void *)d->q, (void *)d->att,
+  for (void *p : {(void *)d->x, (void *)d->xn, (void *)d->tmp, (void *)d->q, (void *)d->att,
                   (void *)d->h, (void *)d->logits, (void *)d->k_cache,
                   (void *)d->v_cache, (void *)d->scratch, (void *)d->counters,
                   (void *)d->tokens, (void *)d->positions,

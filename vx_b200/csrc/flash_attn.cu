@@ -32,12 +32,17 @@
 
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 namespace vxb {
 
 bool make_map_16(CUtensorMap *map, const void *base, int64_t inner, int64_t rows,
                  int64_t ld, int box_inner, int box_rows, bool is_bf16);
+const char *flash_attention_fwd_v2(const void *q, const void *k, const void *v,
+                                   void *out, int B, int H, int S, float scale,
+                                   bool causal, cudaStream_t stream);
+int flash2_status();
 
 namespace {
 
@@ -65,10 +70,13 @@ template <int NQ> struct FlashBars {
   uint64_t pv_done[NQ];
   uint32_t tmem_base;
   int stop;
+  float xmax[NQ][2][2][BQ]; /* [tile][parity][half][row]: a half's row max */
+  float xsum[NQ][2][BQ];    /* [tile][half][row]: a half's row sum */
 };
 
 template <int NQ> constexpr int flash_smem_bytes() {
-  return NQ * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + NQ * P_BYTES + 1024 + 512;
+  return NQ * Q_BYTES + KV_STAGES * KV_STAGE_BYTES + NQ * P_BYTES + 1024 +
+         (int)sizeof(FlashBars<NQ>) + 256;
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -84,7 +92,7 @@ __device__ __forceinline__ float ex2(float x) {
   } while (0)
 
 template <int NQ>
-__global__ void __launch_bounds__(64 + NQ * 128, 1)
+__global__ void __launch_bounds__(64 + NQ * 256, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
                  const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v,
@@ -121,9 +129,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
     for (int w = 0; w < NQ; ++w) {
       for (int b = 0; b < 2; ++b) {
         ptx::mbar_init(&bars->s_full[w][b], 1);
-        ptx::mbar_init(&bars->s_free[w][b], 4);
+        ptx::mbar_init(&bars->s_free[w][b], 8);
       }
-      ptx::mbar_init(&bars->p_full[w], 4);
+      ptx::mbar_init(&bars->p_full[w], 8);
       ptx::mbar_init(&bars->pv_done[w], 1);
     }
     bars->stop = 0;
@@ -250,14 +258,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
   } else {
-    /* ------------------------------------------------ softmax warpgroups */
-    const int w = (warp - 2) / 4;        /* which Q tile */
-    const int quarter = warp & 3;        /* TMEM lanes this warp may touch */
-    const int row = quarter * 32 + lane; /* row within the Q tile */
+    /* ------------------------------------------------ softmax warpgroups
+       Eight warps per Q tile: two threads share a query row, each with 32 of
+       the tile's 64 KV columns (and 64 of the 128 output columns). They agree
+       on the row maximum through shared memory once per tile; their partial
+       row sums meet only at the end. */
+    const int w = (warp - 2) / 8;          /* which Q tile */
+    const int half = ((warp - 2) & 7) / 4; /* which 32 KV columns */
+    const int quarter = warp & 3;          /* TMEM lanes this warp may touch */
+    const int row = quarter * 32 + lane;   /* row within the Q tile */
     const int q_row = q_base + w * BQ + row;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_tmem = tmem + lane_base + w * 256;
-    const uint32_t o_tmem = s_tmem + 128;
+    const uint32_t s_tmem = tmem + lane_base + w * 256 + half * 32;
+    const uint32_t o_tmem = tmem + lane_base + w * 256 + 128 + half * 64;
     uint8_t *p_row = sm_p + w * P_BYTES + row * 128;
     const int n_mine = n_tiles[w];
     float m_used = -INFINITY, l_sum = 0.0f;
@@ -265,37 +278,42 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
 
     for (int j = 0; j < n_mine; ++j) {
       const int buf = j & 1;
-      if (!ptx::mbar_wait(&bars->s_full[w][buf], (j >> 1) & 1, stop)) {
+      if (ok && !ptx::mbar_wait(&bars->s_full[w][buf], (j >> 1) & 1, stop)) {
         FLASH_GIVE_UP(FS_S_FULL);
         ok = false;
-        break;
+      }
+      if (!ok) {
+        /* Gave up: keep meeting the partner at the tile's barrier. */
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + w), "r"(256) : "memory");
+        continue;
       }
       ptx::tc_fence_after_sync();
-      uint32_t raw[2][32];
-      ptx::tmem_ld_32x32b_x32(s_tmem + buf * BKV, raw[0]);
-      ptx::tmem_ld_32x32b_x32(s_tmem + buf * BKV + 32, raw[1]);
+      uint32_t raw[32];
+      ptx::tmem_ld_32x32b_x32(s_tmem + buf * BKV, raw);
       ptx::tmem_ld_wait();
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0)
         ptx::mbar_arrive(&bars->s_free[w][buf]);
 
-      const int k0 = j * BKV;
-      const bool diagonal = causal && k0 + BKV - 1 > q_base + w * BQ;
+      const int k0 = j * BKV + half * 32;
+      const bool diagonal = causal && j * BKV + BKV - 1 > q_base + w * BQ;
       /* Raw scores; the scale (positive) is folded into the exponent's FMA.
          Four running maxima keep the chain short. */
-      float sv[64];
+      float sv[32];
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float v = __uint_as_float(raw[c >> 5][c & 31]);
+      for (int c = 0; c < 32; ++c) {
+        float v = __uint_as_float(raw[c]);
         if (diagonal && k0 + c > q_row)
           v = -INFINITY;
         sv[c] = v;
         mx4[c & 3] = fmaxf(mx4[c & 3], v);
       }
-      const float mx =
-          fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      bars->xmax[w][buf][half][row] = mine;
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + w), "r"(256) : "memory");
+      const float mx = fmaxf(mine, bars->xmax[w][buf][half ^ 1][row]) * scale_log2;
       /* Keep the maximum in use unless the new one is more than 2^8 above it. */
       const bool grow = mx > m_used + 8.0f;
       const float m_new = grow ? mx : m_used;
@@ -305,12 +323,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         if (!ptx::mbar_wait(&bars->pv_done[w], (j - 1) & 1, stop)) {
           FLASH_GIVE_UP(FS_PV_DONE);
           ok = false;
-          break;
+          continue;
         }
         ptx::tc_fence_after_sync();
         if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t o[32];
             ptx::tmem_ld_32x32b_x32(o_tmem + c * 32, o);
             ptx::tmem_ld_wait();
@@ -334,10 +352,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       /* p = 2^(s * scale - m); the row sum adds the f32 weights in four
          independent chains, the bf16 copies go to the P V product. */
       float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      uint32_t packed[32];
+      uint32_t packed[16];
       const float neg_m = -m_used;
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
+      for (int c = 0; c < 32; c += 2) {
         const float p0 = ex2(fmaf(sv[c], scale_log2, neg_m));
         const float p1 = ex2(fmaf(sv[c + 1], scale_log2, neg_m));
         part4[(c >> 1) & 3] += p0 + p1;
@@ -347,12 +365,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
       const float part = (part4[0] + part4[1]) + (part4[2] + part4[3]);
       l_sum = l_sum * fix + part;
       /* Row r of P is one 128-byte swizzle row: 16-byte chunk c sits at chunk
-         position c ^ (r % 8). */
+         position c ^ (r % 8). This thread has chunks 4*half .. 4*half + 3. */
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         const uint4 v = make_uint4(packed[c * 4], packed[c * 4 + 1],
                                    packed[c * 4 + 2], packed[c * 4 + 3]);
-        *reinterpret_cast<uint4 *>(p_row + ((c ^ (row & 7)) << 4)) = v;
+        *reinterpret_cast<uint4 *>(p_row + (((half * 4 + c) ^ (row & 7)) << 4)) = v;
       }
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
@@ -361,6 +379,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         ptx::mbar_arrive(&bars->p_full[w]);
     }
 
+    /* The two halves of a row add their sums; a warpgroup that gave up still
+       comes to the barrier so that its partner does not wait for it. */
+    bars->xsum[w][half][row] = l_sum;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + w), "r"(256) : "memory");
+    l_sum += bars->xsum[w][half ^ 1][row];
     if (ok && n_mine > 0) {
       if (!ptx::mbar_wait(&bars->pv_done[w], (n_mine - 1) & 1, stop)) {
         FLASH_GIVE_UP(FS_PV_DONE);
@@ -368,9 +391,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
         ptx::tc_fence_after_sync();
         const float inv = 1.0f / l_sum;
         __nv_bfloat16 *dst =
-            out + ((int64_t)head_row + q_row) * HD;
+            out + ((int64_t)head_row + q_row) * HD + half * 64;
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t o[32];
           ptx::tmem_ld_32x32b_x32(o_tmem + c * 32, o);
           ptx::tmem_ld_wait();
@@ -414,7 +437,7 @@ const char *launch_flash(const CUtensorMap &mq, const CUtensorMap &mk,
   if (attr_err != cudaSuccess)
     return "flash attention could not get its shared memory";
   const dim3 grid(S / (BQ * NQ), B * H);
-  flash_fwd_kernel<NQ><<<grid, 64 + NQ * 128, flash_smem_bytes<NQ>(), stream>>>(
+  flash_fwd_kernel<NQ><<<grid, 64 + NQ * 256, flash_smem_bytes<NQ>(), stream>>>(
       mq, mk, mv, (__nv_bfloat16 *)out, S, scale * 1.4426950408889634f,
       causal ? 1 : 0);
   const cudaError_t e = cudaGetLastError();
@@ -442,8 +465,17 @@ const char *flash_attention_fwd(const void *q, const void *k, const void *v,
       !make_map_16(&mk, k, HD, rows, HD, 64, BKV, true) ||
       !make_map_16(&mv, v, HD, rows, HD, 64, BKV, true))
     return "cuTensorMapEncodeTiled refused q, k or v";
-  if (S % (2 * BQ) == 0)
+  if (S % (2 * BQ) == 0) {
+    /* Sequences that are whole pairs of Q tiles take the second kernel
+       (flash_attn_v2.cu); VXB_FLASH_V1=1 keeps the first. */
+    static const bool v1 = [] {
+      const char *e = getenv("VXB_FLASH_V1");
+      return e && *e && *e != '0';
+    }();
+    if (!v1)
+      return flash_attention_fwd_v2(q, k, v, out, B, H, S, scale, causal, stream);
     return launch_flash<2>(mq, mk, mv, out, B, H, S, scale, causal, stream);
+  }
   return launch_flash<1>(mq, mk, mv, out, B, H, S, scale, causal, stream);
 }
 
@@ -455,7 +487,8 @@ int flash_status(cudaStream_t stream) {
     return -1;
   if (v)
     cudaMemcpyToSymbol(g_flash_status, &zero, sizeof zero);
-  return v;
+  const int v2 = flash2_status();
+  return v ? v : v2;
 }
 
 } // namespace vxb

@@ -1,0 +1,472 @@
+/* flash_attn_v2.cu -- attention forward, second organisation of the same
+ * arithmetic as flash_attn.cu (f32 online softmax in the exp2 domain, bf16
+ * probabilities, lazy rescale of O), built around what limits a one-CTA
+ * tcgen05.mma: every instruction re-reads its shared-memory operands, and at
+ * M = 128 the A operand alone is 4 KiB per K step.  A timeline of the first
+ * kernel showed its MMA thread busy the whole iteration, issuing 64-column
+ * score products that spend three times their arithmetic time fetching Q.
+ *
+ * So here: KV tiles of 128 rows (half the Q traffic per score), and the
+ * probabilities never go through shared memory -- they are written back into
+ * tensor memory over the scores they came from, packed two bf16 per column,
+ * and the P V product takes its A operand from there, so it only fetches V.
+ *
+ * TMEM per Q tile: 128 columns of scores (their first 64 then hold P) and 128
+ * columns of O; two Q tiles fill the 512 columns.  Shared memory: Q 64 KiB, a
+ * K ring and a V ring of two 32 KiB tiles each.  The MMA thread alternates
+ * between the two Q tiles -- P V of tile j, then at once the scores of tile
+ * j+1 of the same Q tile -- so that one warpgroup's softmax runs under the
+ * other's products.
+ */
+#include "kernels.h"
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+namespace vxb {
+
+bool make_map_16(CUtensorMap *map, const void *base, int64_t inner, int64_t rows,
+                 int64_t ld, int box_inner, int box_rows, bool is_bf16);
+
+namespace {
+
+constexpr int HD = 128;  /* head_dim */
+constexpr int BQ = 128;  /* query rows per tile */
+constexpr int BKV = 128; /* KV rows per tile */
+constexpr int NQ = 2;    /* Q tiles per CTA */
+constexpr int RING = 2;  /* tiles in the K ring and in the V ring */
+constexpr int TILE_BYTES = 128 * HD * 2; /* 32 KiB: a Q, K or V tile */
+constexpr int THREADS = 64 + NQ * 128;
+
+enum { F2_Q = 0x61, F2_K_FREE, F2_V_FREE, F2_K_FULL, F2_V_FULL, F2_P_FULL,
+       F2_S_FULL, F2_PV_DONE };
+
+__device__ int g_flash2_status;
+
+struct Bars {
+  uint64_t q_full;
+  uint64_t k_full[RING], k_free[RING], v_full[RING], v_free[RING];
+  uint64_t s_full[NQ], p_full[NQ], pv_done[NQ];
+  uint32_t tmem_base;
+  int stop;
+};
+constexpr int SMEM_BYTES =
+    NQ * TILE_BYTES + 2 * RING * TILE_BYTES + 1024 + (int)sizeof(Bars) + 256;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+/* One pass over the 128 scores of a row, in four loads of 32 columns with the
+   next load in flight under the arithmetic of the one before:
+   p = 2^(s * scale_log2 + neg_m), rounded to bf16 pairs into `packed`; `sum`
+   gets the f32 row sum and `rel_max` the largest exponent met. DIAG: columns
+   above `limit` are outside the causal triangle. */
+template <bool DIAG>
+__device__ __forceinline__ void
+probabilities(uint32_t s_tmem, float scale_log2, float neg_m, int limit,
+              uint32_t (&packed)[BKV / 2], float &rel_max, float &sum) {
+  uint32_t raw[2][32];
+  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  ptx::tmem_ld_32x32b_x32(s_tmem, raw[0]);
+#pragma unroll
+  for (int c = 0; c < BKV / 32; ++c) {
+    ptx::tmem_ld_wait_for(raw[c & 1]);
+    if (c + 1 < BKV / 32)
+      ptx::tmem_ld_32x32b_x32(s_tmem + (c + 1) * 32, raw[(c + 1) & 1]);
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      float r0 = fmaf(__uint_as_float(raw[c & 1][e]), scale_log2, neg_m);
+      float r1 = fmaf(__uint_as_float(raw[c & 1][e + 1]), scale_log2, neg_m);
+      if (DIAG) {
+        if (c * 32 + e > limit)
+          r0 = -INFINITY;
+        if (c * 32 + e + 1 > limit)
+          r1 = -INFINITY;
+      }
+      mx4[(e >> 1) & 3] = fmaxf(mx4[(e >> 1) & 3], fmaxf(r0, r1));
+      const float p0 = ex2(r0), p1 = ex2(r1);
+      part4[(e >> 1) & 3] += p0 + p1;
+      const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+      packed[c * 16 + (e >> 1)] = *reinterpret_cast<const uint32_t *>(&pr);
+    }
+  }
+  rel_max = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+  sum = (part4[0] + part4[1]) + (part4[2] + part4[3]);
+}
+
+/* The largest of a row's 128 scores (as stored, before scaling). */
+template <bool DIAG>
+__device__ __forceinline__ float row_max(uint32_t s_tmem, int limit) {
+  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+  for (int c = 0; c < BKV / 32; ++c) {
+    uint32_t raw[32];
+    ptx::tmem_ld_32x32b_x32(s_tmem + c * 32, raw);
+    ptx::tmem_ld_wait_for(raw);
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      float v = __uint_as_float(raw[e]);
+      if (DIAG && c * 32 + e > limit)
+        v = -INFINITY;
+      mx4[e & 3] = fmaxf(mx4[e & 3], v);
+    }
+  }
+  return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+}
+
+#define GIVE_UP(code)                                                          \
+  do {                                                                         \
+    atomicCAS(&g_flash2_status, 0, (code));                                    \
+    *stop = 1;                                                                 \
+  } while (0)
+
+__global__ void __launch_bounds__(THREADS, 1)
+flash2_kernel(const __grid_constant__ CUtensorMap map_q,
+              const __grid_constant__ CUtensorMap map_k,
+              const __grid_constant__ CUtensorMap map_v,
+              __nv_bfloat16 *__restrict__ out, int S, float scale_log2,
+              int causal) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t *sm_q = smem;
+  uint8_t *sm_k = sm_q + NQ * TILE_BYTES;
+  uint8_t *sm_v = sm_k + RING * TILE_BYTES;
+  Bars *bars = reinterpret_cast<Bars *>(sm_v + RING * TILE_BYTES);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int q_block = gridDim.x - 1 - blockIdx.x; /* heavy tiles first */
+  const int q_base = q_block * BQ * NQ;
+  const int64_t head_row = (int64_t)blockIdx.y * S;
+  int n_tiles[NQ], n_max = 0;
+#pragma unroll
+  for (int w = 0; w < NQ; ++w) {
+    n_tiles[w] = causal ? (q_base + w * BQ) / BKV + 1 : S / BKV;
+    n_max = max(n_max, n_tiles[w]);
+  }
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < RING; ++s) {
+      ptx::mbar_init(&bars->k_full[s], 1);
+      ptx::mbar_init(&bars->k_free[s], 1);
+      ptx::mbar_init(&bars->v_full[s], 1);
+      ptx::mbar_init(&bars->v_free[s], 1);
+    }
+    for (int w = 0; w < NQ; ++w) {
+      ptx::mbar_init(&bars->s_full[w], 1);
+      ptx::mbar_init(&bars->p_full[w], 4);
+      ptx::mbar_init(&bars->pv_done[w], 1);
+    }
+    bars->stop = 0;
+    ptx::fence_proxy_async_smem();
+    ptx::fence_barrier_init();
+  }
+  if (warp == 1)
+    ptx::tmem_alloc(&bars->tmem_base, 512);
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+  volatile int *stop = &bars->stop;
+
+  if (warp == 0) {
+    /* ------------------------------------------------------------ loader */
+    if (lane == 0) {
+      ptx::tma_prefetch_desc(&map_q);
+      ptx::tma_prefetch_desc(&map_k);
+      ptx::tma_prefetch_desc(&map_v);
+      ptx::mbar_expect_tx(&bars->q_full, NQ * TILE_BYTES);
+      for (int w = 0; w < NQ; ++w)
+        for (int h = 0; h < 2; ++h)
+          ptx::tma_load_2d(sm_q + w * TILE_BYTES + h * (TILE_BYTES / 2), &map_q,
+                           h * 64, (int)(head_row + q_base + w * BQ),
+                           &bars->q_full);
+      int k_issued = 0, v_issued = 0;
+      for (int j = 0; j < n_max; ++j) {
+        const int s = j % RING;
+        const uint32_t ph = ((j / RING) & 1) ^ 1;
+        const int row = (int)(head_row + j * BKV);
+        if (!ptx::mbar_wait(&bars->k_free[s], ph, stop)) {
+          GIVE_UP(F2_K_FREE);
+          break;
+        }
+        ptx::mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
+        for (int h = 0; h < 2; ++h)
+          ptx::tma_load_2d(sm_k + s * TILE_BYTES + h * (TILE_BYTES / 2), &map_k,
+                           h * 64, row, &bars->k_full[s]);
+        ++k_issued;
+        if (!ptx::mbar_wait(&bars->v_free[s], ph, stop)) {
+          GIVE_UP(F2_V_FREE);
+          break;
+        }
+        ptx::mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
+        for (int h = 0; h < 2; ++h)
+          ptx::tma_load_2d(sm_v + s * TILE_BYTES + h * (TILE_BYTES / 2), &map_v,
+                           h * 64, row, &bars->v_full[s]);
+        ++v_issued;
+      }
+      /* Stay until every copy this thread started has landed. */
+      ptx::mbar_wait_alone(&bars->q_full, 0);
+      for (int back = 0; back < RING && back < k_issued; ++back) {
+        const int j = k_issued - 1 - back;
+        ptx::mbar_wait_alone(&bars->k_full[j % RING], (j / RING) & 1);
+      }
+      for (int back = 0; back < RING && back < v_issued; ++back) {
+        const int j = v_issued - 1 - back;
+        ptx::mbar_wait_alone(&bars->v_full[j % RING], (j / RING) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    /* -------------------------------------------------------- MMA issuer */
+    if (lane == 0) {
+      const uint32_t idesc_s = ptx::idesc_f16(true, false, false, BQ, BKV);
+      const uint32_t idesc_o = ptx::idesc_f16(true, false, true, BQ, HD);
+      bool ok = ptx::mbar_wait(&bars->q_full, 0, stop);
+      if (!ok)
+        GIVE_UP(F2_Q);
+      ptx::tc_fence_after_sync();
+      /* S_w(j) = Q_w K_j^T into the score columns of Q tile w. */
+      auto scores = [&](int w, int j) {
+        const uint32_t q_addr = ptx::smem_addr(sm_q + w * TILE_BYTES);
+        const uint32_t k_addr = ptx::smem_addr(sm_k + (j % RING) * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk / 4) * (TILE_BYTES / 2) + (kk % 4) * 32;
+          ptx::umma_f16_ss(tmem + w * 256,
+                           ptx::smem_desc_sw128(q_addr + off, 16, 1024),
+                           ptx::smem_desc_sw128(k_addr + off, 16, 1024), idesc_s,
+                           kk != 0);
+        }
+        ptx::umma_commit(&bars->s_full[w]);
+      };
+      /* K_j is free once the last Q tile that uses it has its scores. */
+      auto scores_of_tile = [&](int w, int j) -> bool {
+        if (j >= n_tiles[w])
+          return true;
+        bool first = true;
+        for (int v = 0; v < w; ++v)
+          first = first && j >= n_tiles[v];
+        if (first && !ptx::mbar_wait(&bars->k_full[j % RING], (j / RING) & 1, stop)) {
+          GIVE_UP(F2_K_FULL);
+          return false;
+        }
+        ptx::tc_fence_after_sync();
+        scores(w, j);
+        bool last = true;
+        for (int v = w + 1; v < NQ; ++v)
+          last = last && j >= n_tiles[v];
+        if (last)
+          ptx::umma_commit(&bars->k_free[j % RING]);
+        return true;
+      };
+      for (int w = 0; ok && w < NQ; ++w)
+        ok = scores_of_tile(w, 0);
+      for (int j = 0; ok && j < n_max; ++j) {
+        for (int w = 0; ok && w < NQ; ++w) {
+          if (j >= n_tiles[w])
+            continue;
+          bool first = true;
+          for (int v = 0; v < w; ++v)
+            first = first && j >= n_tiles[v];
+          if (first && !ptx::mbar_wait(&bars->v_full[j % RING], (j / RING) & 1, stop)) {
+            GIVE_UP(F2_V_FULL);
+            ok = false;
+            break;
+          }
+          if (!ptx::mbar_wait(&bars->p_full[w], j & 1, stop)) {
+            GIVE_UP(F2_P_FULL);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t v_addr = ptx::smem_addr(sm_v + (j % RING) * TILE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BKV / 16; ++kk) {
+            /* A = P from tensor memory: 16 bf16 of a row are 8 columns.
+               B = V, N-major: two 64-column blocks 16 KiB apart, 8-row groups
+               1 KiB apart; a K step is 16 KV rows = 2 KiB. */
+            ptx::umma_f16_ts(tmem + w * 256 + 128, tmem + w * 256 + kk * 8,
+                             ptx::smem_desc_sw128(v_addr + kk * 2048,
+                                                  TILE_BYTES / 2, 1024),
+                             idesc_o, (j | kk) != 0);
+          }
+          ptx::umma_commit(&bars->pv_done[w]);
+          bool last = true;
+          for (int v = w + 1; v < NQ; ++v)
+            last = last && j >= n_tiles[v];
+          if (last)
+            ptx::umma_commit(&bars->v_free[j % RING]);
+          /* at once the next scores of the same Q tile: its softmax then runs
+             under the other tile's products */
+          ok = scores_of_tile(w, j + 1);
+        }
+      }
+    }
+  } else {
+    /* ------------------------------------------------ softmax warpgroups
+       Four warps per Q tile, one thread per query row. */
+    const int w = (warp - 2) / 4;  /* which Q tile */
+    const int quarter = warp & 3;  /* TMEM lanes this warp may touch */
+    const int row = quarter * 32 + lane;
+    const int q_row = q_base + w * BQ + row;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_tmem = tmem + lane_base + w * 256; /* P goes over it */
+    const uint32_t o_tmem = s_tmem + 128;
+    const int n_mine = n_tiles[w];
+    float m_used = -INFINITY, l_sum = 0.0f;
+    bool ok = true;
+
+    for (int j = 0; ok && j < n_mine; ++j) {
+      if (!ptx::mbar_wait(&bars->s_full[w], j & 1, stop)) {
+        GIVE_UP(F2_S_FULL);
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const int limit = q_row - j * BKV; /* causal: columns above it are out */
+      const bool diagonal = causal && j * BKV + BKV - 1 > q_base + w * BQ;
+      uint32_t packed[BKV / 2];
+      float rel_max = 0.0f, sum = 0.0f;
+      /* First guess: the maximum in use still holds, so one pass over the
+         scores gives P, its row sum and, on the side, the row maximum. */
+      bool redo = j == 0;
+      if (!redo) {
+        if (diagonal)
+          probabilities<true>(s_tmem, scale_log2, -m_used, limit, packed, rel_max, sum);
+        else
+          probabilities<false>(s_tmem, scale_log2, -m_used, limit, packed, rel_max, sum);
+        redo = __any_sync(0xffffffffu, rel_max > 8.0f);
+      }
+      if (redo) {
+        /* Some row of this warp outgrew its maximum by more than 2^8 (or this
+           is the first tile): take the maximum first, rescale what has been
+           accumulated, and compute P again. The scores are still in tensor
+           memory: P has not been stored yet. */
+        const float mx = (diagonal ? row_max<true>(s_tmem, limit)
+                                   : row_max<false>(s_tmem, limit)) * scale_log2;
+        const bool grow = mx > m_used + 8.0f;
+        const float m_new = grow ? mx : m_used;
+        const float fix = grow ? ex2(m_used - m_new) : 1.0f;
+        if (j > 0) {
+          /* P V of the tile before has finished whenever these scores exist
+             (one pipe, in order); the wait makes that visible here. */
+          if (!ptx::mbar_wait(&bars->pv_done[w], (j - 1) & 1, stop)) {
+            GIVE_UP(F2_PV_DONE);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            ptx::tmem_ld_32x32b_x32(o_tmem + c * 32, o);
+            ptx::tmem_ld_wait_for(o);
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              o[e] = __float_as_uint(__uint_as_float(o[e]) * fix);
+            ptx::tmem_st_32x32b_x32(o_tmem + c * 32, o);
+          }
+          ptx::tmem_st_wait();
+        }
+        l_sum *= fix;
+        m_used = m_new;
+        if (diagonal)
+          probabilities<true>(s_tmem, scale_log2, -m_used, limit, packed, rel_max, sum);
+        else
+          probabilities<false>(s_tmem, scale_log2, -m_used, limit, packed, rel_max, sum);
+      }
+      l_sum += sum;
+      /* P, two bf16 per column, over the first half of the score columns. */
+      ptx::tmem_st_32x32b_x32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
+      ptx::tmem_st_32x32b_x32(s_tmem + 32,
+                              *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        ptx::mbar_arrive(&bars->p_full[w]);
+    }
+
+    if (ok && n_mine > 0) {
+      if (!ptx::mbar_wait(&bars->pv_done[w], (n_mine - 1) & 1, stop)) {
+        GIVE_UP(F2_PV_DONE);
+      } else {
+        ptx::tc_fence_after_sync();
+        const float inv = 1.0f / l_sum;
+        __nv_bfloat16 *dst = out + ((int64_t)head_row + q_row) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          ptx::tmem_ld_32x32b_x32(o_tmem + c * 32, o);
+          ptx::tmem_ld_wait_for(o);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __nv_bfloat162 pr = __floats2bfloat162_rn(
+                  __uint_as_float(o[q4 * 8 + 2 * e]) * inv,
+                  __uint_as_float(o[q4 * 8 + 2 * e + 1]) * inv);
+              pk[e] = *reinterpret_cast<const uint32_t *>(&pr);
+            }
+            *reinterpret_cast<uint4 *>(dst + c * 32 + q4 * 8) =
+                make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem, 512);
+  }
+}
+
+} // namespace
+
+/* S must be a multiple of 256; q, k, v, out [B*H*S, 128] bf16. */
+const char *flash_attention_fwd_v2(const void *q, const void *k, const void *v,
+                                   void *out, int B, int H, int S, float scale,
+                                   bool causal, cudaStream_t stream) {
+  const int64_t rows = (int64_t)B * H * S;
+  CUtensorMap mq, mk, mv;
+  if (!make_map_16(&mq, q, HD, rows, HD, 64, BQ, true) ||
+      !make_map_16(&mk, k, HD, rows, HD, 64, BKV, true) ||
+      !make_map_16(&mv, v, HD, rows, HD, 64, BKV, true))
+    return "cuTensorMapEncodeTiled refused q, k or v";
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(
+        flash2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  if (attr_err != cudaSuccess)
+    return "flash attention could not get its shared memory";
+  const dim3 grid(S / (BQ * NQ), B * H);
+  flash2_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(
+      mq, mk, mv, (__nv_bfloat16 *)out, S, scale * 1.4426950408889634f,
+      causal ? 1 : 0);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+int flash2_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_flash2_status, sizeof v) != cudaSuccess)
+    return -1;
+  if (v)
+    cudaMemcpyToSymbol(g_flash2_status, &zero, sizeof zero);
+  return v;
+}
+
+} // namespace vxb
