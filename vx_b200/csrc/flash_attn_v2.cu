@@ -36,7 +36,7 @@ constexpr int HD = 128;  /* head_dim */
 constexpr int BQ = 128;  /* query rows per tile */
 constexpr int BKV = 128; /* KV rows per tile */
 constexpr int NQ = 2;    /* Q tiles per CTA */
-constexpr int RING = 2;  /* tiles in the K ring and in the V ring */
+constexpr int RING = 2;  /* tiles in the K ring and in the V ring (a power of 2) */
 constexpr int TILE_BYTES = 128 * HD * 2; /* 32 KiB: a Q, K or V tile */
 constexpr int THREADS = 64 + NQ * 128;
 
@@ -61,14 +61,15 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-/* One pass over the 128 scores of a row, in four loads of 32 columns with the
+/* One pass over the 128 scores of a row, in eight loads of 16 columns with the
    next load in flight under the arithmetic of the one before:
    p = 2^(s * scale_log2 + neg_m), rounded to bf16 pairs into `packed`; `sum`
-   gets the f32 row sum and `rel_max` the largest exponent met. DIAG: columns
-   above `limit` are outside the causal triangle. */
-template <bool DIAG>
+   gets the f32 row sum and `rel_max` the largest exponent met. The body is
+   long (everything is unrolled so that P stays in registers) and the kernel
+   holds two copies of it, which is why masking is not a third and fourth:
+   the instruction cache is a resource here. */
 __device__ __forceinline__ void
-probabilities(uint32_t s_tmem, float scale_log2, float neg_m, int limit,
+probabilities(uint32_t s_tmem, float scale_log2, float neg_m,
               uint32_t (&packed)[BKV / 2], float &rel_max, float &sum) {
   uint32_t raw[2][32];
   float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -81,14 +82,8 @@ probabilities(uint32_t s_tmem, float scale_log2, float neg_m, int limit,
       ptx::tmem_ld_32x32b_x32(s_tmem + (c + 1) * 32, raw[(c + 1) & 1]);
 #pragma unroll
     for (int e = 0; e < 32; e += 2) {
-      float r0 = fmaf(__uint_as_float(raw[c & 1][e]), scale_log2, neg_m);
-      float r1 = fmaf(__uint_as_float(raw[c & 1][e + 1]), scale_log2, neg_m);
-      if (DIAG) {
-        if (c * 32 + e > limit)
-          r0 = -INFINITY;
-        if (c * 32 + e + 1 > limit)
-          r1 = -INFINITY;
-      }
+      const float r0 = fmaf(__uint_as_float(raw[c & 1][e]), scale_log2, neg_m);
+      const float r1 = fmaf(__uint_as_float(raw[c & 1][e + 1]), scale_log2, neg_m);
       mx4[(e >> 1) & 3] = fmaxf(mx4[(e >> 1) & 3], fmaxf(r0, r1));
       const float p0 = ex2(r0), p1 = ex2(r1);
       part4[(e >> 1) & 3] += p0 + p1;
@@ -101,8 +96,7 @@ probabilities(uint32_t s_tmem, float scale_log2, float neg_m, int limit,
 }
 
 /* The largest of a row's 128 scores (as stored, before scaling). */
-template <bool DIAG>
-__device__ __forceinline__ float row_max(uint32_t s_tmem, int limit) {
+__device__ __forceinline__ float row_max(uint32_t s_tmem) {
   float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
   for (int c = 0; c < BKV / 32; ++c) {
@@ -110,14 +104,29 @@ __device__ __forceinline__ float row_max(uint32_t s_tmem, int limit) {
     ptx::tmem_ld_32x32b_x32(s_tmem + c * 32, raw);
     ptx::tmem_ld_wait_for(raw);
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      float v = __uint_as_float(raw[e]);
-      if (DIAG && c * 32 + e > limit)
-        v = -INFINITY;
-      mx4[e & 3] = fmaxf(mx4[e & 3], v);
-    }
+    for (int e = 0; e < 32; ++e)
+      mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[e]));
   }
   return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+}
+
+/* A tile on the diagonal of a causal block: the scores of the columns above
+   `limit` become -inf where they lie, in tensor memory, so that the passes
+   above need no second form. */
+__device__ __forceinline__ void mask_scores(uint32_t s_tmem, int limit) {
+#pragma unroll 1
+  for (int c = 0; c < BKV / 32; ++c) {
+    uint32_t raw[32];
+    ptx::tmem_ld_32x32b_x32(s_tmem + c * 32, raw);
+    ptx::tmem_ld_wait_for(raw);
+    const int first_out = limit + 1 - c * 32;
+#pragma unroll
+    for (int e = 0; e < 32; ++e)
+      if (e >= first_out)
+        raw[e] = 0xff800000u;
+    ptx::tmem_st_32x32b_x32(s_tmem + c * 32, raw);
+  }
+  ptx::tmem_st_wait();
 }
 
 #define GIVE_UP(code)                                                          \
@@ -144,12 +153,10 @@ flash2_kernel(const __grid_constant__ CUtensorMap map_q,
   const int q_block = gridDim.x - 1 - blockIdx.x; /* heavy tiles first */
   const int q_base = q_block * BQ * NQ;
   const int64_t head_row = (int64_t)blockIdx.y * S;
-  int n_tiles[NQ], n_max = 0;
-#pragma unroll
-  for (int w = 0; w < NQ; ++w) {
-    n_tiles[w] = causal ? (q_base + w * BQ) / BKV + 1 : S / BKV;
-    n_max = max(n_max, n_tiles[w]);
-  }
+  /* KV tiles that Q tile 0 and Q tile 1 meet: n0 <= n1 <= n0 + 1. */
+  const int n0 = causal ? q_base / BKV + 1 : S / BKV;
+  const int n1 = causal ? (q_base + BQ) / BKV + 1 : S / BKV;
+  const int n_max = n1;
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(&bars->q_full, 1);
@@ -232,81 +239,77 @@ flash2_kernel(const __grid_constant__ CUtensorMap map_q,
       if (!ok)
         GIVE_UP(F2_Q);
       ptx::tc_fence_after_sync();
-      /* S_w(j) = Q_w K_j^T into the score columns of Q tile w. */
-      auto scores = [&](int w, int j) {
-        const uint32_t q_addr = ptx::smem_addr(sm_q + w * TILE_BYTES);
-        const uint32_t k_addr = ptx::smem_addr(sm_k + (j % RING) * TILE_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk / 4) * (TILE_BYTES / 2) + (kk % 4) * 32;
-          ptx::umma_f16_ss(tmem + w * 256,
-                           ptx::smem_desc_sw128(q_addr + off, 16, 1024),
-                           ptx::smem_desc_sw128(k_addr + off, 16, 1024), idesc_s,
-                           kk != 0);
-        }
-        ptx::umma_commit(&bars->s_full[w]);
-      };
-      /* K_j is free once the last Q tile that uses it has its scores. */
-      auto scores_of_tile = [&](int w, int j) -> bool {
-        if (j >= n_tiles[w])
-          return true;
-        bool first = true;
-        for (int v = 0; v < w; ++v)
-          first = first && j >= n_tiles[v];
-        if (first && !ptx::mbar_wait(&bars->k_full[j % RING], (j / RING) & 1, stop)) {
+      /* Descriptors of the tiles' first K step; a step adds to the address
+         field (16-byte units), which cannot carry out of its 14 bits. */
+      const uint64_t q_desc[NQ] = {
+          ptx::smem_desc_sw128(ptx::smem_addr(sm_q), 16, 1024),
+          ptx::smem_desc_sw128(ptx::smem_addr(sm_q + TILE_BYTES), 16, 1024)};
+      const uint64_t k_desc[RING] = {
+          ptx::smem_desc_sw128(ptx::smem_addr(sm_k), 16, 1024),
+          ptx::smem_desc_sw128(ptx::smem_addr(sm_k + TILE_BYTES), 16, 1024)};
+      const uint64_t v_desc[RING] = {
+          ptx::smem_desc_sw128(ptx::smem_addr(sm_v), TILE_BYTES / 2, 1024),
+          ptx::smem_desc_sw128(ptx::smem_addr(sm_v + TILE_BYTES), TILE_BYTES / 2,
+                               1024)};
+      /* S_w(j) = Q_w K_j^T into the score columns of Q tile w. `wait`: this is
+         the first use of K_j; `release`: the last. */
+      auto scores = [&](int w, int j, bool wait, bool release) -> bool {
+        const int s = j & (RING - 1);
+        if (wait && !ptx::mbar_wait(&bars->k_full[s], (j / RING) & 1, stop)) {
           GIVE_UP(F2_K_FULL);
           return false;
         }
         ptx::tc_fence_after_sync();
-        scores(w, j);
-        bool last = true;
-        for (int v = w + 1; v < NQ; ++v)
-          last = last && j >= n_tiles[v];
-        if (last)
-          ptx::umma_commit(&bars->k_free[j % RING]);
+        const uint64_t qd = w ? q_desc[1] : q_desc[0];
+        const uint64_t kd = s ? k_desc[1] : k_desc[0];
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = ((kk / 4) * (TILE_BYTES / 2) + (kk % 4) * 32) >> 4;
+          ptx::umma_f16_ss(tmem + w * 256, qd + off, kd + off, idesc_s, kk != 0);
+        }
+        ptx::umma_commit(&bars->s_full[w]);
+        if (release)
+          ptx::umma_commit(&bars->k_free[s]);
         return true;
       };
-      for (int w = 0; ok && w < NQ; ++w)
-        ok = scores_of_tile(w, 0);
-      for (int j = 0; ok && j < n_max; ++j) {
-        for (int w = 0; ok && w < NQ; ++w) {
-          if (j >= n_tiles[w])
-            continue;
-          bool first = true;
-          for (int v = 0; v < w; ++v)
-            first = first && j >= n_tiles[v];
-          if (first && !ptx::mbar_wait(&bars->v_full[j % RING], (j / RING) & 1, stop)) {
-            GIVE_UP(F2_V_FULL);
-            ok = false;
-            break;
-          }
-          if (!ptx::mbar_wait(&bars->p_full[w], j & 1, stop)) {
-            GIVE_UP(F2_P_FULL);
-            ok = false;
-            break;
-          }
-          ptx::tc_fence_after_sync();
-          const uint32_t v_addr = ptx::smem_addr(sm_v + (j % RING) * TILE_BYTES);
-#pragma unroll
-          for (int kk = 0; kk < BKV / 16; ++kk) {
-            /* A = P from tensor memory: 16 bf16 of a row are 8 columns.
-               B = V, N-major: two 64-column blocks 16 KiB apart, 8-row groups
-               1 KiB apart; a K step is 16 KV rows = 2 KiB. */
-            ptx::umma_f16_ts(tmem + w * 256 + 128, tmem + w * 256 + kk * 8,
-                             ptx::smem_desc_sw128(v_addr + kk * 2048,
-                                                  TILE_BYTES / 2, 1024),
-                             idesc_o, (j | kk) != 0);
-          }
-          ptx::umma_commit(&bars->pv_done[w]);
-          bool last = true;
-          for (int v = w + 1; v < NQ; ++v)
-            last = last && j >= n_tiles[v];
-          if (last)
-            ptx::umma_commit(&bars->v_free[j % RING]);
-          /* at once the next scores of the same Q tile: its softmax then runs
-             under the other tile's products */
-          ok = scores_of_tile(w, j + 1);
+      /* O_w += P_w(j) V_j. A = P from tensor memory: 16 bf16 of a row are 8
+         columns. B = V, N-major: two 64-column blocks 16 KiB apart, 8-row
+         groups 1 KiB apart; a K step is 16 KV rows = 2 KiB. */
+      auto weighted = [&](int w, int j, bool wait, bool release) -> bool {
+        const int s = j & (RING - 1);
+        if (wait && !ptx::mbar_wait(&bars->v_full[s], (j / RING) & 1, stop)) {
+          GIVE_UP(F2_V_FULL);
+          return false;
         }
+        if (!ptx::mbar_wait(&bars->p_full[w], j & 1, stop)) {
+          GIVE_UP(F2_P_FULL);
+          return false;
+        }
+        ptx::tc_fence_after_sync();
+        const uint64_t vd = s ? v_desc[1] : v_desc[0];
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          ptx::umma_f16_ts(tmem + w * 256 + 128, tmem + w * 256 + kk * 8,
+                           vd + kk * (2048 >> 4), idesc_o, (j | kk) != 0);
+        ptx::umma_commit(&bars->pv_done[w]);
+        if (release)
+          ptx::umma_commit(&bars->v_free[s]);
+        return true;
+      };
+      /* Tile 0 leads, tile 1 follows; each P V is followed at once by the next
+         scores of the same Q tile, so that its softmax runs under the other
+         tile's products. Tile 1 is the last user of every K and V tile, and
+         the first user of the one tile 0 does not meet. */
+      ok = ok && scores(0, 0, true, false) && scores(1, 0, false, true);
+      for (int j = 0; ok && j < n1; ++j) {
+        if (j < n0) {
+          ok = weighted(0, j, true, false);
+          if (ok && j + 1 < n0)
+            ok = scores(0, j + 1, true, false);
+        }
+        ok = ok && weighted(1, j, j >= n0, true);
+        if (ok && j + 1 < n1)
+          ok = scores(1, j + 1, j + 1 >= n0, true);
       }
     }
   } else {
@@ -319,7 +322,7 @@ flash2_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_tmem = tmem + lane_base + w * 256; /* P goes over it */
     const uint32_t o_tmem = s_tmem + 128;
-    const int n_mine = n_tiles[w];
+    const int n_mine = w ? n1 : n0;
     float m_used = -INFINITY, l_sum = 0.0f;
     bool ok = true;
 
@@ -334,29 +337,27 @@ flash2_kernel(const __grid_constant__ CUtensorMap map_q,
       const bool diagonal = causal && j * BKV + BKV - 1 > q_base + w * BQ;
       uint32_t packed[BKV / 2];
       float rel_max = 0.0f, sum = 0.0f;
+      if (diagonal)
+        mask_scores(s_tmem, limit);
       /* First guess: the maximum in use still holds, so one pass over the
-         scores gives P, its row sum and, on the side, the row maximum. */
+         scores gives P, its row sum and, on the side, the row maximum. If
+         some row of this warp outgrew its maximum by more than 2^8 (or this
+         is the first tile), take the maximum first, rescale what has been
+         accumulated, and make the pass again: the scores are still in tensor
+         memory, P has not been stored yet. (Written as a loop over two
+         attempts, the compiler kept P live across the back edge and spilled:
+         586 instead of 925 TFLOP/s.) */
       bool redo = j == 0;
       if (!redo) {
-        if (diagonal)
-          probabilities<true>(s_tmem, scale_log2, -m_used, limit, packed, rel_max, sum);
-        else
-          probabilities<false>(s_tmem, scale_log2, -m_used, limit, packed, rel_max, sum);
+        probabilities(s_tmem, scale_log2, -m_used, packed, rel_max, sum);
         redo = __any_sync(0xffffffffu, rel_max > 8.0f);
       }
       if (redo) {
-        /* Some row of this warp outgrew its maximum by more than 2^8 (or this
-           is the first tile): take the maximum first, rescale what has been
-           accumulated, and compute P again. The scores are still in tensor
-           memory: P has not been stored yet. */
-        const float mx = (diagonal ? row_max<true>(s_tmem, limit)
-                                   : row_max<false>(s_tmem, limit)) * scale_log2;
+        const float mx = row_max(s_tmem) * scale_log2;
         const bool grow = mx > m_used + 8.0f;
         const float m_new = grow ? mx : m_used;
         const float fix = grow ? ex2(m_used - m_new) : 1.0f;
         if (j > 0) {
-          /* P V of the tile before has finished whenever these scores exist
-             (one pipe, in order); the wait makes that visible here. */
           if (!ptx::mbar_wait(&bars->pv_done[w], (j - 1) & 1, stop)) {
             GIVE_UP(F2_PV_DONE);
             ok = false;
@@ -377,10 +378,7 @@ flash2_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         l_sum *= fix;
         m_used = m_new;
-        if (diagonal)
-          probabilities<true>(s_tmem, scale_log2, -m_used, limit, packed, rel_max, sum);
-        else
-          probabilities<false>(s_tmem, scale_log2, -m_used, limit, packed, rel_max, sum);
+        probabilities(s_tmem, scale_log2, -m_used, packed, rel_max, sum);
       }
       l_sum += sum;
       /* P, two bf16 per column, over the first half of the score columns. */
