@@ -254,7 +254,7 @@ def bench_dominant_kernel(torch, tensors, peaks, shape, iters=3):
     x = abi.DeviceTensor.empty((dim,), abi.F32)
     ops.fill_normal(x, 99, 1.0)
     out = abi.DeviceTensor.empty((hid,), abi.F32)
-    ws = [abi.DeviceTensor(t.data_ptr(), (2 * hid * dim,), abi.BF16, abi.gpu(0))
+    ws = [abi.DeviceTensor(t.data_ptr(), (2 * hid * dim,), abi.BF16, abi.home_gpu())
           for t in tensors["w_gate"]]
     stream = torch.cuda.Stream()
     lib().vx_cuda_set_stream(C.c_void_p(stream.cuda_stream))
@@ -285,6 +285,8 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    from vx_b200 import abi
+    abi.set_home_gpu(local)
     multi = world > 1
     if multi:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))

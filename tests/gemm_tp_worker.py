@@ -17,7 +17,9 @@ from vx_b200.lib import check, lib  # noqa: E402
 def main():
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
-    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    here = abi.gpu(local)  # this rank's tensors live on its own GPU
     collective.join_job(rank, world)
     m, n, k = 384, 512 * world, 640
     nl = n // world
@@ -25,11 +27,11 @@ def main():
     a = rng.integers(-3, 4, (m, k)).astype(np.float32)
     b = rng.integers(-2, 3, (k, n)).astype(np.float32)
     bf = lambda x: (x.view(np.uint32) >> 16).astype(np.uint16)  # exact: small integers
-    ta = abi.DeviceTensor.from_host(bf(a), bf16=True)
-    tb = abi.DeviceTensor.from_host(bf(np.ascontiguousarray(b[:, rank * nl:(rank + 1) * nl])), bf16=True)
-    tcl = abi.DeviceTensor.empty((m, nl), abi.BF16)
-    tg = abi.DeviceTensor.empty((world, m, nl), abi.BF16)
-    tc = abi.DeviceTensor.empty((m, n), abi.BF16)
+    ta = abi.DeviceTensor.from_host(bf(a), topo=here, bf16=True)
+    tb = abi.DeviceTensor.from_host(bf(np.ascontiguousarray(b[:, rank * nl:(rank + 1) * nl])), topo=here, bf16=True)
+    tcl = abi.DeviceTensor.empty((m, nl), abi.BF16, here)
+    tg = abi.DeviceTensor.empty((world, m, nl), abi.BF16, here)
+    tc = abi.DeviceTensor.empty((m, n), abi.BF16, here)
     check(lib().vx_b200_gemm_column_split(abi.BF16, m, nl, k, ta.ptr, tb.ptr,
                                           tcl.ptr, tg.ptr, tc.ptr))
     got = tc.to_host()

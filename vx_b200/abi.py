@@ -25,6 +25,21 @@ def gpu(i=0):
     return TOPO_GPU_BASE + i
 
 
+_home_gpu = 0
+
+
+def set_home_gpu(i):
+    """The GPU that tensors made without an explicit topology go to. A job
+    with one process per GPU sets it to the process's own GPU (its local
+    rank); GPU[0] otherwise."""
+    global _home_gpu
+    _home_gpu = int(i)
+
+
+def home_gpu():
+    return gpu(_home_gpu)
+
+
 def memref_tag(elem, rank, slot=False):
     return (rank << 16) | (elem << 8) | (SLOT_BIT if slot else 0)
 
@@ -79,7 +94,7 @@ class DeviceTensor:
 
     @classmethod
     def empty(cls, shape, elem, topo=None):
-        topo = gpu(0) if topo is None else topo
+        topo = home_gpu() if topo is None else topo
         n = 1
         for s in shape:
             n *= s
@@ -89,7 +104,7 @@ class DeviceTensor:
 
     @classmethod
     def from_host(cls, array, topo=None, bf16=False, asynchronous=False):
-        topo = gpu(0) if topo is None else topo
+        topo = home_gpu() if topo is None else topo
         array = np.ascontiguousarray(array)
         elem = code_of(array.dtype, bf16)
         fn = (lib().vx_plugin_alloc_and_transfer_async if asynchronous

@@ -1,9 +1,16 @@
 """stdlib/std/collective.vx:35-79 over the eight vx_collective_* calls."""
+import os
+
 from . import abi
 from .lib import lib
 
 
 def join_job(rank, ranks):
+    """Join the job (one process per GPU). Under a launcher that sets
+    LOCAL_RANK, tensors made without an explicit topology go to that GPU from
+    here on."""
+    if "LOCAL_RANK" in os.environ:
+        abi.set_home_gpu(int(os.environ["LOCAL_RANK"]))
     lib().vx_collective_init(rank, ranks)
 
 

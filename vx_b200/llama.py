@@ -64,7 +64,7 @@ class Decoder:
         out = np.empty(n, np.float32)
         lib().vx_plugin_transfer_device_to_host(
             lib().vx_decoder_logits(self.handle),
-            out.ctypes.data_as(C.c_void_p), out.nbytes, abi.gpu(0))
+            out.ctypes.data_as(C.c_void_p), out.nbytes, abi.home_gpu())
         return out.reshape(self.cfg.batch, -1)
 
     @property

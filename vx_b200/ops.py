@@ -35,7 +35,7 @@ def matmul_host(a, b, topo=None, bf16=False, slot=True):
     """`c = a @ b` on operands in HOST memory: the library stages them, runs the
     product on the GPU, and either publishes a malloc'ed result through a slot
     (outkind=slot) or fills a host buffer. Returns a numpy array."""
-    topo = abi.gpu(0) if topo is None else topo
+    topo = abi.home_gpu() if topo is None else topo
     a = np.ascontiguousarray(a)
     b = np.ascontiguousarray(b)
     elem = abi.code_of(a.dtype, bf16)
@@ -82,7 +82,7 @@ def matvec_flat(w, x):
 
 
 def wait(topo=None):
-    t = C.c_int32(abi.gpu(0) if topo is None else topo)
+    t = C.c_int32(abi.home_gpu() if topo is None else topo)
     lib().vx_plugin_control(0x05, C.addressof(t))
 
 
