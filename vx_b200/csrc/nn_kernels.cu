@@ -286,12 +286,28 @@ rowdot_kernel(const RowDotParams p) {
        needed by the first epilogue. */
     for (int b = 0; b < B; ++b) {
       float ss = 0.0f;
-      for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-        const float v = p.x[b * p.x_stride + i];
-        const float wn = p.norm_bf16 ? bf16_at(p.norm_w, i)
-                                     : ((const float *)p.norm_w)[i];
-        xs[b * xs_stride + xs_at(i)] = v * wn;
-        ss = fmaf(v, v, ss);
+      const float *px = p.x + b * p.x_stride;
+      /* Eight loads in flight per thread: x was written by the kernel before
+         and comes from L2, a microsecond away; one load at a time made this
+         loop the longest part of a short projection. The sum keeps its order. */
+      for (int i0 = threadIdx.x; i0 < cols; i0 += 8 * blockDim.x) {
+        float v[8], wn[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int i = i0 + k * blockDim.x;
+          v[k] = i < cols ? px[i] : 0.0f;
+          wn[k] = i >= cols ? 0.0f
+                  : p.norm_bf16 ? bf16_at(p.norm_w, i)
+                                : ((const float *)p.norm_w)[i];
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int i = i0 + k * blockDim.x;
+          if (i < cols) {
+            xs[b * xs_stride + xs_at(i)] = v[k] * wn[k];
+            ss = fmaf(v[k], v[k], ss);
+          }
+        }
       }
       ss = warp_sum(ss);
       if (lane == 0)
@@ -306,9 +322,23 @@ rowdot_kernel(const RowDotParams p) {
       inv[b] = 1.0f / sqrtf(ss / (float)cols + p.eps);
     }
   } else if (p.x_in_smem) {
-    for (int b = 0; b < B; ++b)
-      for (int i = threadIdx.x; i < cols; i += blockDim.x)
-        xs[b * xs_stride + xs_at(i)] = p.x[b * p.x_stride + i];
+    for (int b = 0; b < B; ++b) {
+      const float *px = p.x + b * p.x_stride;
+      for (int i0 = threadIdx.x; i0 < cols; i0 += 8 * blockDim.x) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int i = i0 + k * blockDim.x;
+          v[k] = i < cols ? px[i] : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int i = i0 + k * blockDim.x;
+          if (i < cols)
+            xs[b * xs_stride + xs_at(i)] = v[k];
+        }
+      }
+    }
     __syncthreads();
   }
   const float *xbase = p.x_in_smem ? xs : p.x;
@@ -671,19 +701,30 @@ __global__ void rope_store_kernel(float *q_out, float *k_cache, float *v_cache,
  * merges the parts of all splits in split order. */
 constexpr int ATT_WARPS = 4;
 
-template <int GH>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
-attention_decode_kernel(const AttnArgs a) {
-  chain_release();
+/* What the four warps of one unit share. */
+template <int GH> struct AttnShared {
+  float m[ATT_WARPS][GH], l[ATT_WARPS][GH];
+  __align__(16) float acc[ATT_WARPS][GH][128];
+  int is_last;
+};
+__device__ __forceinline__ void sync_four_warps(int bar_id) {
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(ATT_WARPS * 32) : "memory");
+}
+
+/* One unit of work: (split, KV head and head tile `y`, sequence b), done by the
+   four warps that meet at named barrier `bar_id`. CHAINED: the caller is a
+   kernel of its own in a chain of dependent launches. */
+template <int GH, bool CHAINED>
+__device__ __forceinline__ void
+attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
+               int lane, AttnShared<GH> &sh, int bar_id) {
   /* The position was written by the step before this one, and every cache row
      below it by earlier steps: those may be read before the kernels of this
      step have finished. Row `pos` and q come from the kernel just before. */
   const int hd = a.head_dim, hd4 = hd / 4;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int split_idx = blockIdx.x, b = blockIdx.z;
   const int group = a.q_heads / a.kv_heads;
   const int tiles = (group + GH - 1) / GH;
-  const int g = blockIdx.y / tiles, tile = blockIdx.y - g * tiles;
+  const int g = y / tiles, tile = y - g * tiles;
   const int h0 = g * group + tile * GH;
   const int nh = min(GH, group - tile * GH);
   const int pos = a.positions[b];
@@ -708,7 +749,8 @@ attention_decode_kernel(const AttnArgs a) {
     for (int j = 0; j < NB; ++j) {
       const int t = t0 + j * ATT_WARPS;
       const bool take = active && t < t_end &&
-                        (old_rows_only ? t < pos : t == pos || t0 != t_begin + warp);
+                        (old_rows_only ? t < pos
+                                       : t == pos || t0 != t_begin + warp || !CHAINED);
       if (take) {
         const int64_t row = ((int64_t)t * a.kv_heads + g) * hd + lane * 4;
         kv[j] = *reinterpret_cast<const float4 *>(kc + row);
@@ -721,17 +763,22 @@ attention_decode_kernel(const AttnArgs a) {
 #pragma unroll
   for (int j = 0; j < NB; ++j)
     kv[j] = vv[j] = make_float4(0, 0, 0, 0);
-  load_batch(t_begin + warp, true);
-  chain_wait();
-  load_batch(t_begin + warp, false); /* only row `pos`, if it is in this batch */
+  if (CHAINED) {
+    load_batch(t_begin + warp, true);
+    chain_wait();
+  }
+  load_batch(t_begin + warp, false); /* CHAINED: only row `pos`, if it is here */
 
   float4 qv[GH];
   float m[GH], l[GH];
   float4 acc[GH];
 #pragma unroll
   for (int h = 0; h < GH; ++h) {
+    /* q is rewritten for every layer: read it past L1, which may still hold
+       the layer before when the layers share a kernel */
     qv[h] = (active && h < nh)
-                ? *reinterpret_cast<const float4 *>(qb + (h0 + h) * hd + lane * 4)
+                ? __ldcg(reinterpret_cast<const float4 *>(qb + (h0 + h) * hd +
+                                                          lane * 4))
                 : make_float4(0, 0, 0, 0);
     m[h] = -3.0e38f;
     l[h] = 0.0f;
@@ -775,9 +822,10 @@ attention_decode_kernel(const AttnArgs a) {
   }
 
   /* ---- merge the four warps, in warp order ---- */
-  __shared__ float sm_m[ATT_WARPS][GH], sm_l[ATT_WARPS][GH];
-  __shared__ __align__(16) float sm_acc[ATT_WARPS][GH][128];
-  __shared__ int is_last;
+  float (&sm_m)[ATT_WARPS][GH] = sh.m;
+  float (&sm_l)[ATT_WARPS][GH] = sh.l;
+  float (&sm_acc)[ATT_WARPS][GH][128] = sh.acc;
+  int &is_last = sh.is_last;
 #pragma unroll
   for (int h = 0; h < GH; ++h) {
     if (lane == 0) {
@@ -787,7 +835,7 @@ attention_decode_kernel(const AttnArgs a) {
     if (active)
       *reinterpret_cast<float4 *>(&sm_acc[warp][h][lane * 4]) = acc[h];
   }
-  __syncthreads();
+  sync_four_warps(bar_id);
   const int row_floats = hd + 2;
   float *part = a.scratch;
   auto part_at = [&](int head, int sp) {
@@ -823,14 +871,14 @@ attention_decode_kernel(const AttnArgs a) {
     __threadfence();
     __syncwarp();
     if (lane == 0) {
-      int32_t *counter = a.counters + (int64_t)b * a.kv_heads * tiles + blockIdx.y;
+      int32_t *counter = a.counters + (int64_t)b * a.kv_heads * tiles + y;
       const int seen = atomicAdd(counter, 1);
       is_last = seen == splits - 1;
       if (is_last)
         *counter = 0; /* ready for the next launch */
     }
   }
-  __syncthreads();
+  sync_four_warps(bar_id);
   if (!is_last)
     return;
   __threadfence();
@@ -843,6 +891,7 @@ attention_decode_kernel(const AttnArgs a) {
     big = warp_max(big);
     float total = 0.0f;
     float4 o = make_float4(0, 0, 0, 0);
+#pragma unroll 4
     for (int sp = 0; sp < splits; ++sp) {
       const float *src = part_at(h0 + h, sp);
       const float f = expf(__ldcg(src + hd) - big);
@@ -860,6 +909,15 @@ attention_decode_kernel(const AttnArgs a) {
           make_float4(o.x / total, o.y / total, o.z / total, o.w / total);
     }
   }
+}
+
+template <int GH>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attention_decode_kernel(const AttnArgs a) {
+  __shared__ AttnShared<GH> sh;
+  chain_release();
+  attention_unit<GH, true>(a, blockIdx.x, blockIdx.y, blockIdx.z,
+                           threadIdx.x >> 5, threadIdx.x & 31, sh, 0);
 }
 
 /* ---------------------------------------------------------------- argmax
@@ -937,9 +995,8 @@ __global__ void embed_kernel(float *x, const void *table, int tbf16,
   }
 }
 
-/* y[d] = W[d,n] . x for the flat entry point: the same row-dot kernel. */
-
 } // namespace
+
 
 const char *matvec(const MatvecArgs &a, cudaStream_t stream) {
   if (a.rows <= 0 || a.batch <= 0)

@@ -108,6 +108,12 @@ __device__ inline void bulk_load(void *dst, const void *src, uint32_t bytes,
                "l"(src), "r"(bytes), "r"(smem_addr(bar))
                : "memory");
 }
+/* Ask L2 for `bytes` (a multiple of 16, from a 16-byte aligned address):
+   nothing is written anywhere the program can see. */
+__device__ inline void bulk_prefetch_l2(const void *src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes)
+               : "memory");
+}
 __device__ inline void tma_prefetch_desc(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
