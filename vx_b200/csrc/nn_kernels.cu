@@ -741,8 +741,9 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
   const float *qb = a.q + (int64_t)b * a.q_heads * hd;
 
   /* A warp takes every fourth position, NB of them at a time so that their
-     loads are in flight together. */
-  constexpr int NB = 4;
+     loads are in flight together: with 32 positions per block that is one
+     round trip to memory per warp. */
+  constexpr int NB = 8;
   float4 kv[NB], vv[NB];
   auto load_batch = [&](int t0, bool old_rows_only) {
 #pragma unroll
@@ -891,7 +892,7 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
     big = warp_max(big);
     float total = 0.0f;
     float4 o = make_float4(0, 0, 0, 0);
-#pragma unroll 4
+#pragma unroll 8
     for (int sp = 0; sp < splits; ++sp) {
       const float *src = part_at(h0 + h, sp);
       const float f = expf(__ldcg(src + hd) - big);
