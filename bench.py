@@ -275,7 +275,41 @@ def bench_dominant_kernel(torch, tensors, peaks, shape, iters=3):
                 achieved=achieved, peak=peaks["hbm_gbs"], unit="GB/s",
                 frac=achieved / peaks["hbm_gbs"], peak_source=peaks["source"],
                 bytes_per_launch=bytes_per_launch, us_per_launch=per_launch_ms * 1e3,
-                launches_timed=launches, traffic=None)
+                launches_timed=launches,
+                # dram__bytes_read.sum of one launch under ncu (180 405 248 B) plus the
+                # 44 KB it writes; the profiler's own save/restore writes are left out
+                # (profiles/rowdot_swiglu_llama7b.md)
+                traffic=180405248 + 4 * shape["hidden"],
+                traffic_source="ncu capture of this kernel on 4 of these matrices")
+
+
+def bench_decode_batch(torch, llama, shape, peaks, batch):
+    """The same model with `batch` sequences decoded together (the second
+    half of the 7B configuration): aggregate tokens/s after a 512-token prompt
+    per sequence, argmax fed back on the GPU."""
+    dec, tensors = llama.nn_bf16_model(max_seq=MAX_SEQ, batch=batch, **shape)
+    stream = torch.cuda.ExternalStream(dec.stream)
+    prompts = np.random.default_rng(8).integers(0, shape["vocab"], (batch, PROMPT))
+    steps = 32
+    try:
+        for p in range(PROMPT):
+            dec.step([int(t) for t in prompts[:, p]], fetch=False)
+        for _ in range(4):
+            dec.step(None, fetch=False)
+        torch.cuda.synchronize()
+        ms = event_ms(torch, stream,
+                      lambda: [dec.step(None, fetch=False) for _ in range(steps)])
+    finally:
+        dec.close()
+        del tensors
+        torch.cuda.empty_cache()
+    per_step_bytes = llama.weight_bytes_per_token(**shape)
+    kv = 2 * shape["n_layers"] * shape["kv_heads"] * shape["head_dim"] * 4 * \
+        (PROMPT + 4 + steps / 2.0 + 1) * batch
+    gbs = (per_step_bytes + kv) / (ms / steps) / 1e6
+    return dict(workload="same model, %d sequences per step" % batch,
+                tokens_per_s=batch * steps / (ms / 1e3), ms_per_step=ms / steps,
+                steps=steps, hbm_gbs=gbs, frac_of_measured_hbm=gbs / peaks["hbm_gbs"])
 
 
 def run_ours(args):
@@ -377,6 +411,7 @@ def run_ours(args):
 
     if rank == 0 and not multi and not args.no_extras:
         try:
+            line["decode_batch16"] = bench_decode_batch(torch, llama, shape, peaks, 16)
             line["gemm"] = bench_gemm(torch, peaks)
             line["flash_attention"] = bench_flash(torch, peaks)
         except RuntimeError as e:        # reported, never hidden

@@ -99,8 +99,11 @@ typedef struct {
   /* How the partial sums of the row-split projections are added across ranks:
      0 = an NCCL all-reduce after the projection kernel; 1 = the projection
      kernel itself stores its results into every rank's receive buffer over
-     NVLink (peer memory mapped through CUDA IPC) and one small kernel per rank
-     adds them once every rank's flag has arrived. */
+     NVLink (peer memory mapped through CUDA IPC); the next projection (the
+     one with the RMSNorm in front) waits for every rank's flag and adds the
+     partials in its own prologue, in rank order. Where that projection cannot
+     take the norm (batch too large for its shared memory) a small kernel of
+     its own adds them instead. */
   int32_t tp_reduce;
 } vx_decoder_config;
 

@@ -25,6 +25,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <map>
+#include <utility>
 #include <string>
 #include <vector>
 
@@ -101,7 +102,7 @@ struct vx_decoder {
   const void *embed, *final_norm, *lm_head;
   const float *cos_t, *sin_t;
   /* device state */
-  float *x, *xn, *q, *att, *h, *tmp, *logits, *k_cache, *v_cache, *scratch;
+  float *x, *x2, *xn, *q, *att, *h, *tmp, *logits, *k_cache, *v_cache, *scratch;
   bool fused_norm; /* the activations of all sequences fit the projections' shared memory */
   int32_t *tokens, *positions, *counters, *local_best;
   float2 *pair, *pairs_all;
@@ -110,7 +111,10 @@ struct vx_decoder {
   vxb::TpPush tp;
   void *recv;                       /* this rank's slots + flags (IPC-shared) */
   void *peer_recv[vxb::kMaxTpRanks];
-  int32_t *tp_epoch, *tp_done;
+  int32_t *tp_epoch, *tp_done, *tp_gather_done;
+  /* the pushed partials are added by the next projection's prologue instead
+     of a kernel of their own */
+  bool fold;
   int64_t cache_layer_stride, cache_batch_stride;
   int split;
   int host_pos;
@@ -171,8 +175,9 @@ void open_peer_buffers(vx_decoder *d, int rank) {
   const size_t bytes = slot_bytes + 256;
   CUDA_OK(cudaMalloc(&d->recv, bytes));
   CUDA_OK(cudaMemset(d->recv, 0, bytes));
-  d->tp_epoch = dev_alloc<int32_t>(2);
+  d->tp_epoch = dev_alloc<int32_t>(4);
   d->tp_done = d->tp_epoch + 1;
+  d->tp_gather_done = d->tp_epoch + 2;
   cudaIpcMemHandle_t mine;
   CUDA_OK(cudaIpcGetMemHandle(&mine, d->recv));
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
@@ -237,6 +242,41 @@ void record_step(vx_decoder *d, int max_pos) {
   need(vxb::embed(d->x, d->embed, bf, d->tokens, c.dim, c.vocab, B, c.dim, s),
        "embed");
   ++launches;
+  /* Folded exchange: the residual stream alternates between x and x2. A
+     projection whose input still lacks the partials of the one before reads
+     x_cur, adds them in its prologue and leaves the sum in the other buffer.
+     A step has 2 * n_layers such hand-overs, so it ends where it began. */
+  float *x_cur = d->x, *x_other = d->x2;
+  bool owed = false;
+  vxb::TpGather fold{};
+  if (d->fold) {
+    fold.slots = d->tp.slots[d->tp.rank];
+    fold.flags = d->tp.flags[d->tp.rank];
+    fold.epoch = d->tp_epoch;
+    fold.done = d->tp_gather_done;
+    fold.ranks = d->ranks;
+    fold.count = (int64_t)B * c.dim;
+  }
+  auto take_partials = [&]() -> const vxb::TpGather * {
+    if (!owed)
+      return nullptr;
+    fold.x_out = x_other;
+    return &fold;
+  };
+  auto partials_taken = [&]() {
+    if (owed) {
+      std::swap(x_cur, x_other);
+      owed = false;
+    }
+  };
+  /* after a pushed projection: either the next prologue adds the partials,
+     or a kernel of its own does, now */
+  auto after_push = [&]() {
+    if (d->fold)
+      owed = true;
+    else
+      launches += add_partials(d);
+  };
   for (int l = 0; l < c.n_layers; ++l) {
     vxb::QkvArgs qa{};
     qa.wq = d->wq[l];
@@ -248,7 +288,8 @@ void record_step(vx_decoder *d, int max_pos) {
     qa.kv_heads = d->kv_local;
     qa.head_dim = hd;
     qa.cols = c.dim;
-    qa.x = normed(d, d->attn_norm[l], launches);
+    qa.x = d->fold ? x_cur : normed(d, d->attn_norm[l], launches);
+    qa.gather = take_partials();
     qa.x_stride = c.dim;
     qa.batch = B;
     qa.norm_w = d->fused_norm ? d->attn_norm[l] : nullptr;
@@ -266,6 +307,7 @@ void record_step(vx_decoder *d, int max_pos) {
     qa.cache_batch_stride = d->cache_batch_stride;
     qa.max_seq = c.max_seq;
     need(vxb::qkv_rope_store(qa, s), "q/k/v");
+    partials_taken();
 
     vxb::AttnArgs aa{};
     aa.q = d->q;
@@ -298,7 +340,7 @@ void record_step(vx_decoder *d, int max_pos) {
     oa.push = &d->tp;
     need(vxb::matvec(oa, s), "the output projection");
     launches += 3;
-    launches += add_partials(d);
+    after_push();
 
     vxb::SwigluArgs sa{};
     sa.w = d->w_gate[l];
@@ -306,7 +348,8 @@ void record_step(vx_decoder *d, int max_pos) {
     sa.wbf16 = bf;
     sa.rows = d->hidden_local;
     sa.cols = c.dim;
-    sa.x = normed(d, d->ffn_norm[l], launches);
+    sa.x = d->fold ? x_cur : normed(d, d->ffn_norm[l], launches);
+    sa.gather = take_partials();
     sa.x_stride = c.dim;
     sa.out = d->h;
     sa.out_stride = d->hidden_local;
@@ -315,6 +358,7 @@ void record_step(vx_decoder *d, int max_pos) {
     sa.norm_bf16 = bf;
     sa.eps = c.eps;
     need(vxb::swiglu(sa, s), "gate/up");
+    partials_taken();
 
     vxb::MatvecArgs da{};
     da.w = d->w_down[l];
@@ -330,7 +374,7 @@ void record_step(vx_decoder *d, int max_pos) {
     da.push = &d->tp;
     need(vxb::matvec(da, s), "the down projection");
     launches += 2;
-    launches += add_partials(d);
+    after_push();
   }
 
   vxb::MatvecArgs la{};
@@ -338,7 +382,8 @@ void record_step(vx_decoder *d, int max_pos) {
   la.wbf16 = bf;
   la.rows = d->vocab_local;
   la.cols = c.dim;
-  la.x = normed(d, d->final_norm, launches);
+  la.x = d->fold ? x_cur : normed(d, d->final_norm, launches);
+  la.gather = take_partials();
   la.x_stride = c.dim;
   la.batch = B;
   la.norm_w = d->fused_norm ? d->final_norm : nullptr;
@@ -348,6 +393,7 @@ void record_step(vx_decoder *d, int max_pos) {
   la.y_stride = d->vocab_local;
   la.mode = 0;
   need(vxb::matvec(la, s), "the logits");
+  partials_taken();
   if (d->ranks == 1) {
     need(vxb::argmax(d->tokens, d->logits, d->vocab_local, B, d->vocab_local, s),
          "argmax");
@@ -465,6 +511,7 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
   d->cache_layer_stride = d->cache_batch_stride * B;
   d->x = dev_alloc<float>((size_t)B * c.dim);
   d->tmp = dev_alloc<float>((size_t)B * c.dim);
+  d->x2 = dev_alloc<float>((size_t)B * c.dim);
   d->xn = dev_alloc<float>((size_t)B * c.dim);
   d->fused_norm = (size_t)B * ((c.dim + 255) / 256 * 256) * sizeof(float) <= 96 * 1024;
   d->q = dev_alloc<float>((size_t)B * d->q_local * c.head_dim);
@@ -490,6 +537,8 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
     open_peer_buffers(d, rank);
     d->push = true;
   }
+  const char *nofold = getenv("VXB_TP_FOLD");
+  d->fold = d->push && d->fused_norm && !(nofold && nofold[0] == '0');
   CUDA_OK(cudaDeviceSynchronize());
   return d;
 }
@@ -510,7 +559,7 @@ void vx_decoder_destroy(vx_decoder *d) {
   }
   for (auto &g : d->graphs)
     cudaGraphExecDestroy(g.second);
-  for (void *p : {(void *)d->x, (void *)d->xn, (void *)d->tmp, (void *)d->q, (void *)d->att,
+  for (void *p : {(void *)d->x, (void *)d->x2, (void *)d->xn, (void *)d->tmp, (void *)d->q, (void *)d->att,
                   (void *)d->h, (void *)d->logits, (void *)d->k_cache,
                   (void *)d->v_cache, (void *)d->scratch, (void *)d->counters,
                   (void *)d->tokens, (void *)d->positions,

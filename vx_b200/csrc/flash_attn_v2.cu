@@ -259,7 +259,8 @@ flash2_kernel(const __grid_constant__ CUtensorMap map_q,
           GIVE_UP(F2_K_FULL);
           return false;
         }
-        ptx::tc_fence_after_sync();
+        if (wait)
+          ptx::tc_fence_after_sync();
         const uint64_t qd = w ? q_desc[1] : q_desc[0];
         const uint64_t kd = s ? k_desc[1] : k_desc[0];
 #pragma unroll
@@ -275,14 +276,28 @@ flash2_kernel(const __grid_constant__ CUtensorMap map_q,
       /* O_w += P_w(j) V_j. A = P from tensor memory: 16 bf16 of a row are 8
          columns. B = V, N-major: two 64-column blocks 16 KiB apart, 8-row
          groups 1 KiB apart; a K step is 16 KV rows = 2 KiB. */
-      auto weighted = [&](int w, int j, bool wait, bool release) -> bool {
+      /* `k_next`: the scores that follow use K tile j + 1 for the first time;
+         its barrier is polled together with the two this product needs, so
+         that the three round trips to the barriers overlap. */
+      auto weighted = [&](int w, int j, bool wait, bool release,
+                          bool k_next) -> bool {
         const int s = j & (RING - 1);
-        if (wait && !ptx::mbar_wait(&bars->v_full[s], (j / RING) & 1, stop)) {
+        const int sk = (j + 1) & (RING - 1);
+        const bool p_in = ptx::mbar_try_wait(&bars->p_full[w], j & 1);
+        const bool v_in =
+            !wait || ptx::mbar_try_wait(&bars->v_full[s], (j / RING) & 1);
+        const bool k_in =
+            !k_next || ptx::mbar_try_wait(&bars->k_full[sk], ((j + 1) / RING) & 1);
+        if (!v_in && !ptx::mbar_wait(&bars->v_full[s], (j / RING) & 1, stop)) {
           GIVE_UP(F2_V_FULL);
           return false;
         }
-        if (!ptx::mbar_wait(&bars->p_full[w], j & 1, stop)) {
+        if (!p_in && !ptx::mbar_wait(&bars->p_full[w], j & 1, stop)) {
           GIVE_UP(F2_P_FULL);
+          return false;
+        }
+        if (!k_in && !ptx::mbar_wait(&bars->k_full[sk], ((j + 1) / RING) & 1, stop)) {
+          GIVE_UP(F2_K_FULL);
           return false;
         }
         ptx::tc_fence_after_sync();
@@ -303,13 +318,14 @@ flash2_kernel(const __grid_constant__ CUtensorMap map_q,
       ok = ok && scores(0, 0, true, false) && scores(1, 0, false, true);
       for (int j = 0; ok && j < n1; ++j) {
         if (j < n0) {
-          ok = weighted(0, j, true, false);
+          ok = weighted(0, j, true, false, j + 1 < n0);
           if (ok && j + 1 < n0)
-            ok = scores(0, j + 1, true, false);
+            ok = scores(0, j + 1, false, false); /* K polled with the product */
         }
-        ok = ok && weighted(1, j, j >= n0, true);
+        const bool k_first = j + 1 < n1 && j + 1 >= n0;
+        ok = ok && weighted(1, j, j >= n0, true, k_first);
         if (ok && j + 1 < n1)
-          ok = scores(1, j + 1, j + 1 >= n0, true);
+          ok = scores(1, j + 1, false, true);
       }
     }
   } else {

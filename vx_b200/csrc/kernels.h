@@ -59,6 +59,7 @@ struct MatvecArgs {
   int mode;            /* 0 y = s, 1 y += s, 2 y = s + bias, 3 push to peers */
   const void *bias;    /* mode 2, bf16 */
   const struct TpPush *push; /* mode 3 */
+  const struct TpGather *gather; /* NULL, or: x is x + the ranks' partials */
 };
 
 /* Mode 3: the projection is one rank's partial of a row-split product. Every
@@ -76,6 +77,21 @@ struct TpPush {
   int64_t count;               /* values per slot: batch * rows */
   const int32_t *epoch;        /* this rank's, device memory */
   int32_t *done;               /* this rank's block counter, zero between calls */
+};
+/* The receiving side folded into the NEXT projection's prologue: its input is
+   x_in + the ranks' partials (same order as tp_reduce_add, so the same bits),
+   taken after every rank's flag for call epoch + 1 has arrived (bounded wait).
+   Block 0 also stores the sum to x_out, a buffer other than x_in (the
+   residual stream for what follows); the block that finishes last advances
+   epoch. For projections with a fused RMSNorm. */
+struct TpGather {
+  const float *slots;   /* this rank's receive slots */
+  const int32_t *flags; /* this rank's flags */
+  int32_t *epoch;       /* calls completed so far */
+  int32_t *done;        /* block counter, zero between launches */
+  int ranks;
+  int64_t count;        /* values per slot: batch * cols */
+  float *x_out;
 };
 /* x[i] += sum over ranks, in rank order, of slot[r][i], after every rank's flag
    for call epoch + 1 has arrived (a bounded wait: on expiry the status word is
@@ -100,6 +116,7 @@ struct SwigluArgs {
   const void *norm_w;
   bool norm_bf16;
   float eps;
+  const struct TpGather *gather;
 };
 const char *swiglu(const SwigluArgs &a, cudaStream_t stream);
 
@@ -132,6 +149,7 @@ struct QkvArgs {
   float *k_cache, *v_cache;
   int64_t cache_batch_stride;
   int max_seq;
+  const struct TpGather *gather;
 };
 const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream);
 

@@ -111,6 +111,8 @@ struct RowDotParams {
   int max_seq;
   /* EPI_PUSH */
   TpPush tp;
+  /* x = x + the ranks' partials of the projection before (ranks 0: no) */
+  TpGather gather;
 };
 
 /* acc[b] += sum over the E weights of one 16-byte word (8 bf16 or 4 f32) of
@@ -191,6 +193,7 @@ constexpr int CHUNK_BYTES = 1024; /* of one row */
 constexpr int RING_BYTES = WARPS * RING_STAGES * 2 * CHUNK_BYTES;
 
 __device__ int g_rowdot_status; /* non-zero: a ring wait gave up */
+__device__ int g_tp_status;     /* non-zero: a peer's flag never arrived */
 
 template <typename W, int B, int EPI>
 __global__ void __launch_bounds__(WARPS * 32, 1)
@@ -271,6 +274,33 @@ rowdot_kernel(const RowDotParams p) {
   chain_wait(); /* from here on: x, y, positions of the kernels before */
   const int push_call = EPI == EPI_PUSH ? *p.tp.epoch + 1 : 0;
   const int64_t push_set = push_call & 1;
+  /* The partials of the projection before this one, if its sum is folded in
+     here: wait (bounded) until every rank's flag carries the call's number. */
+  const int gather_call = p.gather.ranks ? *p.gather.epoch + 1 : 0;
+  const float *gslots = nullptr;
+  if (p.gather.ranks) {
+    if ((int)threadIdx.x < p.gather.ranks) {
+      const int32_t *flag =
+          p.gather.flags + (gather_call & 1) * p.gather.ranks + threadIdx.x;
+      const long long t0 = clock64();
+      for (;;) {
+        int32_t seen;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];"
+                     : "=r"(seen)
+                     : "l"(flag)
+                     : "memory");
+        if (seen >= gather_call)
+          break;
+        if (clock64() - t0 > ptx::kWaitCycles) {
+          atomicCAS(&g_tp_status, 0, 0x53);
+          break;
+        }
+        __nanosleep(20);
+      }
+    }
+    __syncthreads();
+    gslots = p.gather.slots + (int64_t)(gather_call & 1) * p.gather.ranks * p.gather.count;
+  }
 
   /* ---- prologue: x (normalised if asked) into shared memory ---- */
   float inv[B];
@@ -299,6 +329,19 @@ rowdot_kernel(const RowDotParams p) {
           wn[k] = i >= cols ? 0.0f
                   : p.norm_bf16 ? bf16_at(p.norm_w, i)
                                 : ((const float *)p.norm_w)[i];
+        }
+        if (gslots) {
+          /* x + partials in rank order; block 0 keeps the sum for later */
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int i = i0 + k * blockDim.x;
+            if (i < cols) {
+              for (int r = 0; r < p.gather.ranks; ++r)
+                v[k] += __ldcg(gslots + r * p.gather.count + b * p.x_stride + i);
+              if (blockIdx.x == 0)
+                p.gather.x_out[b * p.x_stride + i] = v[k];
+            }
+          }
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -504,6 +547,18 @@ rowdot_kernel(const RowDotParams p) {
     }
   }
 
+  if (p.gather.ranks) {
+    /* Every block has read the epoch and the slots once the last one is here. */
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const int arrived = atomicAdd(p.gather.done, 1);
+      if (arrived == (int)gridDim.x - 1) {
+        *p.gather.done = 0;
+        *p.gather.epoch = gather_call;
+      }
+    }
+  }
   if (EPI == EPI_PUSH) {
     /* When the last block has finished, every value of this rank is in every
        rank's slot: tell them, with the call number as the flag's value. */
@@ -599,8 +654,6 @@ const char *launch_rowdot(RowDotParams &p, bool wbf16, cudaStream_t stream) {
  * of a pushed projection: wait (bounded) until every rank's flag carries this
  * call's number, then x += the ranks' partials in rank order -- every rank
  * adds the same values in the same order, so x stays identical on all ranks. */
-__device__ int g_tp_status; /* non-zero: a flag never arrived */
-
 __global__ void __launch_bounds__(1024)
 tp_reduce_add_kernel(float *x, const float *slots, const int32_t *flags,
                      int32_t *epoch, int ranks, int64_t count) {
@@ -1016,6 +1069,11 @@ const char *matvec(const MatvecArgs &a, cudaStream_t stream) {
   p.y = a.y;
   p.y_stride = a.y_stride;
   p.bias = a.bias;
+  if (a.gather) {
+    if (!a.norm_w)
+      return "partials are folded into a projection with a fused RMSNorm only";
+    p.gather = *a.gather;
+  }
   switch (a.mode) {
   case 0: return launch_rowdot<EPI_STORE>(p, a.wbf16, stream);
   case 1: return launch_rowdot<EPI_ADD>(p, a.wbf16, stream);
@@ -1065,6 +1123,11 @@ const char *swiglu(const SwigluArgs &a, cudaStream_t stream) {
   p.eps = a.eps;
   p.y = a.out;
   p.y_stride = a.out_stride;
+  if (a.gather) {
+    if (!a.norm_w)
+      return "partials are folded into a projection with a fused RMSNorm only";
+    p.gather = *a.gather;
+  }
   return launch_rowdot<EPI_SWIGLU>(p, a.wbf16, stream);
 }
 
@@ -1100,6 +1163,11 @@ const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream) {
   p.v_cache = a.v_cache;
   p.cache_batch_stride = a.cache_batch_stride;
   p.max_seq = a.max_seq;
+  if (a.gather) {
+    if (!a.norm_w)
+      return "partials are folded into a projection with a fused RMSNorm only";
+    p.gather = *a.gather;
+  }
   return launch_rowdot<EPI_QKV>(p, a.wbf16, stream);
 }
 
