@@ -155,9 +155,8 @@ int add_partials(vx_decoder *d) {
     return 0;
   const int64_t n = (int64_t)d->c.batch * d->c.dim;
   if (d->push) {
-    need(vxb::tp_reduce_add(d->x, d->tp.slots[d->tp.rank],
-                            d->tp.flags[d->tp.rank], d->tp_epoch, d->ranks, n,
-                            d->stream),
+    need(vxb::tp_reduce_add(d->x, d->tp.slots[d->tp.rank], d->tp_epoch,
+                            d->ranks, n, d->stream),
          "adding the partial sums");
     return 1;
   }
@@ -166,13 +165,12 @@ int add_partials(vx_decoder *d) {
   return 2;
 }
 
-/* The receive buffers of the pushed exchange: every rank allocates slots and
-   flags, shares them through CUDA IPC (the handles travel by an NCCL
+/* The receive buffers of the pushed exchange: every rank allocates its slots
+   of (value, call) pairs (zero: call numbers start at 1), shares them through CUDA IPC (the handles travel by an NCCL
    all-gather), and maps every other rank's. */
 void open_peer_buffers(vx_decoder *d, int rank) {
   const int64_t n = (int64_t)d->c.batch * d->c.dim;
-  const size_t slot_bytes = (size_t)2 * d->ranks * n * sizeof(float);
-  const size_t bytes = slot_bytes + 256;
+  const size_t bytes = (size_t)2 * d->ranks * n * sizeof(vxb::TpPair);
   CUDA_OK(cudaMalloc(&d->recv, bytes));
   CUDA_OK(cudaMemset(d->recv, 0, bytes));
   d->tp_epoch = dev_alloc<int32_t>(4);
@@ -203,14 +201,12 @@ void open_peer_buffers(vx_decoder *d, int rank) {
              "ranks must be GPUs of one machine with peer access.",
              p, cudaGetErrorString(e));
     }
-    d->tp.slots[p] = (float *)d->peer_recv[p];
-    d->tp.flags[p] = (int32_t *)((char *)d->peer_recv[p] + slot_bytes);
+    d->tp.slots[p] = (vxb::TpPair *)d->peer_recv[p];
   }
   d->tp.ranks = d->ranks;
   d->tp.rank = rank;
   d->tp.count = n;
   d->tp.epoch = d->tp_epoch;
-  d->tp.done = d->tp_done;
   cudaFree(one);
   cudaFree(all);
   /* Nobody writes into a buffer before everybody has mapped it. */
@@ -251,7 +247,6 @@ void record_step(vx_decoder *d, int max_pos) {
   vxb::TpGather fold{};
   if (d->fold) {
     fold.slots = d->tp.slots[d->tp.rank];
-    fold.flags = d->tp.flags[d->tp.rank];
     fold.epoch = d->tp_epoch;
     fold.done = d->tp_gather_done;
     fold.ranks = d->ranks;

@@ -64,41 +64,42 @@ struct MatvecArgs {
 
 /* Mode 3: the projection is one rank's partial of a row-split product. Every
    finished value goes straight into slot `rank` of EVERY rank's receive buffer
-   (plain stores over NVLink into peer memory; no y is written), and when the
-   whole kernel has finished, the flag [set][rank] of every rank gets the call
-   number. Receive buffers: slots f32 [2 sets][ranks][count], flags int32
-   [2 sets][ranks]; call c (1, 2, ...) uses set c & 1. `epoch` (device int32)
-   holds the number of calls completed so far; tp_reduce_add() advances it. */
+   (stores over NVLink into peer memory; no y is written) as an 8-byte pair
+   (value, call number): an aligned 8-byte store arrives whole, so the pair is
+   its own flag and the exchange needs no fence, no counter and no separate
+   signal. Receive buffers: pairs [2 sets][ranks][count]; call c (1, 2, ...)
+   uses set c & 1, so that a rank that is one call ahead does not overwrite
+   what a slower rank still reads. `epoch` (device int32) holds the number of
+   calls completed so far. */
 constexpr int kMaxTpRanks = 8;
+struct TpPair {
+  float value;
+  int32_t call;
+};
 struct TpPush {
-  float *slots[kMaxTpRanks];   /* per rank: its receive slots */
-  int32_t *flags[kMaxTpRanks]; /* per rank: its flags */
+  TpPair *slots[kMaxTpRanks]; /* per rank: its receive slots */
   int ranks, rank;
-  int64_t count;               /* values per slot: batch * rows */
-  const int32_t *epoch;        /* this rank's, device memory */
-  int32_t *done;               /* this rank's block counter, zero between calls */
+  int64_t count;              /* values per slot: batch * rows */
+  const int32_t *epoch;       /* this rank's, device memory */
 };
 /* The receiving side folded into the NEXT projection's prologue: its input is
-   x_in + the ranks' partials (same order as tp_reduce_add, so the same bits),
-   taken after every rank's flag for call epoch + 1 has arrived (bounded wait).
-   Block 0 also stores the sum to x_out, a buffer other than x_in (the
-   residual stream for what follows); the block that finishes last advances
-   epoch. For projections with a fused RMSNorm. */
+   x_in + the ranks' partials, in rank order, each taken when its pair carries
+   call epoch + 1 (a bounded wait: on expiry the status word is set and the
+   value is used as it is). Block 0 also stores the sum to x_out, a buffer
+   other than x_in (the residual stream for what follows); the block that
+   finishes last advances epoch. For projections with a fused RMSNorm. */
 struct TpGather {
-  const float *slots;   /* this rank's receive slots */
-  const int32_t *flags; /* this rank's flags */
-  int32_t *epoch;       /* calls completed so far */
-  int32_t *done;        /* block counter, zero between launches */
+  const TpPair *slots; /* this rank's receive slots */
+  int32_t *epoch;      /* calls completed so far */
+  int32_t *done;       /* block counter, zero between launches */
   int ranks;
-  int64_t count;        /* values per slot: batch * cols */
+  int64_t count;       /* values per slot: batch * cols */
   float *x_out;
 };
-/* x[i] += sum over ranks, in rank order, of slot[r][i], after every rank's flag
-   for call epoch + 1 has arrived (a bounded wait: on expiry the status word is
-   set and the sum is taken anyway); then epoch += 1. One block. */
-const char *tp_reduce_add(float *x, const float *my_slots,
-                          const int32_t *my_flags, int32_t *epoch, int ranks,
-                          int64_t count, cudaStream_t stream);
+/* The same sum as a kernel of its own: x[i] += the ranks' partials in rank
+   order; then epoch += 1. One block. */
+const char *tp_reduce_add(float *x, const TpPair *my_slots, int32_t *epoch,
+                          int ranks, int64_t count, cudaStream_t stream);
 int tp_status(cudaStream_t stream);
 const char *matvec(const MatvecArgs &a, cudaStream_t stream);
 

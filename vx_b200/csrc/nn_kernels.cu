@@ -138,6 +138,36 @@ fma16(const uint4 &wv, const float (&xv)[B][16 / sizeof(W)], float (&acc)[B]) {
       acc[b] = fmaf(wf[e], xv[b][e], acc[b]);
 }
 
+/* A (value, call) pair of the pushed exchange: stored and loaded as one 8-byte
+   access that bypasses L1, so it arrives whole and is seen when it arrives. */
+__device__ __forceinline__ void pair_store(TpPair *at, float v, int call) {
+  asm volatile("st.volatile.global.v2.b32 [%0], {%1, %2};" ::"l"(at),
+               "r"(__float_as_uint(v)), "r"(call)
+               : "memory");
+}
+__device__ __forceinline__ bool pair_load(const TpPair *at, int call, float &v) {
+  uint32_t bits;
+  int seen;
+  asm volatile("ld.volatile.global.v2.b32 {%0, %1}, [%2];"
+               : "=r"(bits), "=r"(seen)
+               : "l"(at)
+               : "memory");
+  v = __uint_as_float(bits);
+  return seen == call;
+}
+/* Spin (bounded) until the pair carries `call`. */
+__device__ __noinline__ float pair_wait(const TpPair *at, int call, int *status) {
+  float v;
+  const long long t0 = clock64();
+  while (!pair_load(at, call, v)) {
+    if (clock64() - t0 > ptx::kWaitCycles) {
+      atomicCAS(status, 0, 0x53);
+      break;
+    }
+  }
+  return v;
+}
+
 /* The two weight rows of an item, and for q/k/v which head and pair it is. */
 template <typename W, int EPI> struct ItemRows {
   const W *r0, *r1; /* r1 == nullptr: an odd last row */
@@ -274,33 +304,13 @@ rowdot_kernel(const RowDotParams p) {
   chain_wait(); /* from here on: x, y, positions of the kernels before */
   const int push_call = EPI == EPI_PUSH ? *p.tp.epoch + 1 : 0;
   const int64_t push_set = push_call & 1;
-  /* The partials of the projection before this one, if its sum is folded in
-     here: wait (bounded) until every rank's flag carries the call's number. */
+  /* The partials of the projection before this one, if their sum is folded in
+     here: pairs of set (call & 1). */
   const int gather_call = p.gather.ranks ? *p.gather.epoch + 1 : 0;
-  const float *gslots = nullptr;
-  if (p.gather.ranks) {
-    if ((int)threadIdx.x < p.gather.ranks) {
-      const int32_t *flag =
-          p.gather.flags + (gather_call & 1) * p.gather.ranks + threadIdx.x;
-      const long long t0 = clock64();
-      for (;;) {
-        int32_t seen;
-        asm volatile("ld.acquire.sys.global.s32 %0, [%1];"
-                     : "=r"(seen)
-                     : "l"(flag)
-                     : "memory");
-        if (seen >= gather_call)
-          break;
-        if (clock64() - t0 > ptx::kWaitCycles) {
-          atomicCAS(&g_tp_status, 0, 0x53);
-          break;
-        }
-        __nanosleep(20);
-      }
-    }
-    __syncthreads();
-    gslots = p.gather.slots + (int64_t)(gather_call & 1) * p.gather.ranks * p.gather.count;
-  }
+  const TpPair *gslots =
+      p.gather.ranks ? p.gather.slots + (int64_t)(gather_call & 1) *
+                                            p.gather.ranks * p.gather.count
+                     : nullptr;
 
   /* ---- prologue: x (normalised if asked) into shared memory ---- */
   float inv[B];
@@ -331,14 +341,35 @@ rowdot_kernel(const RowDotParams p) {
                                 : ((const float *)p.norm_w)[i];
         }
         if (gslots) {
-          /* x + partials in rank order; block 0 keeps the sum for later */
+          /* x + partials in rank order (each pair is waited for where it has
+             not arrived yet); block 0 keeps the sum for later */
+          for (int r = 0; r < p.gather.ranks; ++r) {
+            float part[8];
+            bool in[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int i = i0 + k * blockDim.x;
-            if (i < cols) {
-              for (int r = 0; r < p.gather.ranks; ++r)
-                v[k] += __ldcg(gslots + r * p.gather.count + b * p.x_stride + i);
-              if (blockIdx.x == 0)
+            for (int k = 0; k < 8; ++k) {
+              const int i = i0 + k * blockDim.x;
+              in[k] = i >= cols ||
+                      pair_load(gslots + r * p.gather.count + b * p.x_stride + i,
+                                gather_call, part[k]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int i = i0 + k * blockDim.x;
+              if (i < cols) {
+                if (!in[k])
+                  part[k] = pair_wait(gslots + r * p.gather.count +
+                                          b * p.x_stride + i,
+                                      gather_call, &g_tp_status);
+                v[k] += part[k];
+              }
+            }
+          }
+          if (blockIdx.x == 0) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int i = i0 + k * blockDim.x;
+              if (i < cols)
                 p.gather.x_out[b * p.x_stride + i] = v[k];
             }
           }
@@ -475,9 +506,9 @@ rowdot_kernel(const RowDotParams p) {
         const int64_t at =
             (push_set * p.tp.ranks + p.tp.rank) * p.tp.count + b * p.y_stride + ra;
         for (int r = 0; r < p.tp.ranks; ++r) {
-          p.tp.slots[r][at] = t0[b];
+          pair_store(p.tp.slots[r] + at, t0[b], push_call);
           if (r1)
-            p.tp.slots[r][at + 1] = t1[b];
+            pair_store(p.tp.slots[r] + at + 1, t1[b], push_call);
         }
       } else if (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_BIAS) {
         float *y = p.y + b * p.y_stride;
@@ -559,26 +590,6 @@ rowdot_kernel(const RowDotParams p) {
       }
     }
   }
-  if (EPI == EPI_PUSH) {
-    /* When the last block has finished, every value of this rank is in every
-       rank's slot: tell them, with the call number as the flag's value. */
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int arrived = atomicAdd(p.tp.done, 1);
-      if (arrived == (int)gridDim.x - 1) {
-        *p.tp.done = 0;
-        __threadfence_system();
-        const int call = push_call;
-        for (int r = 0; r < p.tp.ranks; ++r) {
-          int32_t *flag = p.tp.flags[r] + push_set * p.tp.ranks + p.tp.rank;
-          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag),
-                       "r"(call)
-                       : "memory");
-        }
-      }
-    }
-  }
 }
 
 int sm_count() {
@@ -651,38 +662,26 @@ const char *launch_rowdot(RowDotParams &p, bool wbf16, cudaStream_t stream) {
 }
 
 /* ---------------------------------------------------- the receiving side
- * of a pushed projection: wait (bounded) until every rank's flag carries this
- * call's number, then x += the ranks' partials in rank order -- every rank
- * adds the same values in the same order, so x stays identical on all ranks. */
+ * of a pushed projection as a kernel of its own (for projections that cannot
+ * take the sum in their prologue): x += the ranks' partials in rank order,
+ * each pair waited for (bounded) until it carries this call's number -- every
+ * rank adds the same values in the same order, so x stays identical on all
+ * ranks. */
 __global__ void __launch_bounds__(1024)
-tp_reduce_add_kernel(float *x, const float *slots, const int32_t *flags,
-                     int32_t *epoch, int ranks, int64_t count) {
+tp_reduce_add_kernel(float *x, const TpPair *slots, int32_t *epoch, int ranks,
+                     int64_t count) {
   chain_release();
   chain_wait();
   const int call = *epoch + 1;
-  const int64_t set = call & 1;
-  if ((int)threadIdx.x < ranks) {
-    const int32_t *flag = flags + set * ranks + threadIdx.x;
-    const long long t0 = clock64();
-    for (;;) {
-      int32_t seen;
-      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag)
-                   : "memory");
-      if (seen >= call)
-        break;
-      if (clock64() - t0 > ptx::kWaitCycles) {
-        atomicCAS(&g_tp_status, 0, 0x51);
-        break;
-      }
-      __nanosleep(40);
-    }
-  }
-  __syncthreads();
-  const float *mine = slots + set * ranks * count;
+  const TpPair *mine = slots + (int64_t)(call & 1) * ranks * count;
   for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
     float v = x[i];
-    for (int r = 0; r < ranks; ++r)
-      v += __ldcg(mine + r * count + i);
+    for (int r = 0; r < ranks; ++r) {
+      float part;
+      if (!pair_load(mine + r * count + i, call, part))
+        part = pair_wait(mine + r * count + i, call, &g_tp_status);
+      v += part;
+    }
     x[i] = v;
   }
   __syncthreads();
@@ -1171,13 +1170,12 @@ const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream) {
   return launch_rowdot<EPI_QKV>(p, a.wbf16, stream);
 }
 
-const char *tp_reduce_add(float *x, const float *my_slots,
-                          const int32_t *my_flags, int32_t *epoch, int ranks,
-                          int64_t count, cudaStream_t stream) {
+const char *tp_reduce_add(float *x, const TpPair *my_slots, int32_t *epoch,
+                          int ranks, int64_t count, cudaStream_t stream) {
   if (ranks < 1 || ranks > kMaxTpRanks)
     return "1 to 8 ranks";
   launch_chained(tp_reduce_add_kernel, dim3(1), dim3(1024), 0, stream, x,
-                 my_slots, my_flags, epoch, ranks, count);
+                 my_slots, epoch, ranks, count);
   return check_launch("the partial-sum launch");
 }
 
