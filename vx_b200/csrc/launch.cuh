@@ -57,6 +57,30 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block,
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+/* The same for a kernel whose blocks form clusters of `cluster_x` along x
+   (grid.x a multiple of it): the blocks of a cluster run together and can read
+   one another's shared memory. */
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                   unsigned cluster_x, cudaStream_t stream,
+                                   Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_x;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chain_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 } // namespace vxb
 
 #endif /* VXB_LAUNCH_CUH */

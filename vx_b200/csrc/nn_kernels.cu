@@ -20,10 +20,12 @@
 #include "launch.cuh"
 #include "ptx.cuh"
 
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace vxb {
@@ -766,7 +768,7 @@ __device__ __forceinline__ void sync_four_warps(int bar_id) {
 /* One unit of work: (split, KV head and head tile `y`, sequence b), done by the
    four warps that meet at named barrier `bar_id`. CHAINED: the caller is a
    kernel of its own in a chain of dependent launches. */
-template <int GH, bool CHAINED>
+template <int GH, bool CHAINED, int CL = 0>
 __device__ __forceinline__ void
 attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
                int lane, AttnShared<GH> &sh, int bar_id) {
@@ -780,10 +782,14 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
   const int h0 = g * group + tile * GH;
   const int nh = min(GH, group - tile * GH);
   const int pos = a.positions[b];
-  const int t_begin = split_idx * a.split;
-  if (t_begin > pos)
+  /* CL > 0: the unit is one block of a cluster of CL that covers the whole
+     head; block r takes the r-th run of ceil((pos + 1) / CL) positions (maybe
+     none), and the runs are merged through distributed shared memory. */
+  const int run = CL > 0 ? (pos + CL) / CL : a.split;
+  const int t_begin = split_idx * run;
+  if (CL == 0 && t_begin > pos)
     return;
-  const int t_end = min(t_begin + a.split, pos + 1);
+  const int t_end = max(t_begin, min(t_begin + run, pos + 1));
   const int splits = pos / a.split + 1;
   const float scale = 1.0f / sqrtf((float)hd);
   const bool active = lane < hd4;
@@ -895,6 +901,74 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
     return part + (((int64_t)b * a.q_heads + head) * (a.max_pos / a.split + 1) +
                    sp) * row_floats;
   };
+  if (CL > 0) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    if (warp == 0) {
+      /* the block's part, left in row 0 of its own shared arrays */
+      for (int h = 0; h < nh; ++h) {
+        float big = -3.0e38f;
+        for (int w = 0; w < ATT_WARPS; ++w)
+          big = fmaxf(big, sm_m[w][h]);
+        float total = 0.0f;
+        float4 o = make_float4(0, 0, 0, 0);
+        for (int w = 0; w < ATT_WARPS; ++w) {
+          const float f = expf(sm_m[w][h] - big);
+          total += f * sm_l[w][h];
+          if (active) {
+            const float4 v =
+                *reinterpret_cast<const float4 *>(&sm_acc[w][h][lane * 4]);
+            o.x += f * v.x; o.y += f * v.y; o.z += f * v.z; o.w += f * v.w;
+          }
+        }
+        __syncwarp();
+        if (active)
+          *reinterpret_cast<float4 *>(&sm_acc[0][h][lane * 4]) = o;
+        if (lane == 0) {
+          sm_m[0][h] = big;
+          sm_l[0][h] = total;
+        }
+      }
+    }
+    cluster.sync();
+    if (cluster.block_rank() == 0) {
+      /* block 0 merges the runs in order: warp h takes head h */
+      for (int h = warp; h < nh; h += ATT_WARPS) {
+        constexpr int NP = CL > 0 ? CL : 1; /* CL == 0 never gets here */
+        float pm[NP], pl[NP];
+        float4 pa[NP];
+#pragma unroll
+        for (int r = 0; r < CL; ++r) {
+          const AttnShared<GH> *peer = cluster.map_shared_rank(&sh, r);
+          pm[r] = peer->m[0][h];
+          pl[r] = peer->l[0][h];
+          pa[r] = active
+                      ? *reinterpret_cast<const float4 *>(&peer->acc[0][h][lane * 4])
+                      : make_float4(0, 0, 0, 0);
+        }
+        float big = -3.0e38f;
+#pragma unroll
+        for (int r = 0; r < CL; ++r)
+          big = fmaxf(big, pm[r]);
+        float total = 0.0f;
+        float4 o = make_float4(0, 0, 0, 0);
+#pragma unroll
+        for (int r = 0; r < CL; ++r) {
+          const float f = expf(pm[r] - big);
+          total += f * pl[r];
+          o.x += f * pa[r].x; o.y += f * pa[r].y;
+          o.z += f * pa[r].z; o.w += f * pa[r].w;
+        }
+        if (active) {
+          float *dst = a.out + ((int64_t)b * a.q_heads + h0 + h) * hd + lane * 4;
+          *reinterpret_cast<float4 *>(dst) =
+              make_float4(o.x / total, o.y / total, o.z / total, o.w / total);
+        }
+      }
+    }
+    cluster.sync(); /* nobody leaves while block 0 may still read its part */
+    return;
+  }
   if (warp == 0) {
     for (int h = 0; h < nh; ++h) {
       float big = -3.0e38f;
@@ -962,6 +1036,19 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
           make_float4(o.x / total, o.y / total, o.z / total, o.w / total);
     }
   }
+}
+
+/* The same arithmetic with the parts of a head merged inside a cluster of
+   ATT_CLUSTER blocks (distributed shared memory) instead of through global
+   memory, a fence, an atomic and a last block: three round trips shorter. */
+constexpr int ATT_CLUSTER = 8;
+template <int GH>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attention_cluster_kernel(const AttnArgs a) {
+  __shared__ AttnShared<GH> sh;
+  chain_release();
+  attention_unit<GH, true, ATT_CLUSTER>(a, blockIdx.x, blockIdx.y, blockIdx.z,
+                                        threadIdx.x >> 5, threadIdx.x & 31, sh, 0);
 }
 
 template <int GH>
@@ -1239,6 +1326,24 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
   const int group = a.q_heads / a.kv_heads;
   const int gh = group >= 4 ? 4 : (group >= 2 ? 2 : 1);
   const int tiles = (group + gh - 1) / gh;
+  static const bool clustered = [] {
+    const char *e = getenv("VXB_ATTN_CLUSTER");
+    return !(e && e[0] == '0');
+  }();
+  if (clustered) {
+    const dim3 cgrid(ATT_CLUSTER, a.kv_heads * tiles, a.batch);
+    const dim3 block(ATT_WARPS * 32);
+    if (gh == 4)
+      launch_chained_cluster(attention_cluster_kernel<4>, cgrid, block,
+                             ATT_CLUSTER, stream, a);
+    else if (gh == 2)
+      launch_chained_cluster(attention_cluster_kernel<2>, cgrid, block,
+                             ATT_CLUSTER, stream, a);
+    else
+      launch_chained_cluster(attention_cluster_kernel<1>, cgrid, block,
+                             ATT_CLUSTER, stream, a);
+    return check_launch("the attention launch");
+  }
   const dim3 grid(a.max_pos / a.split + 1, a.kv_heads * tiles, a.batch);
   if (gh == 4)
     launch_chained(attention_decode_kernel<4>, grid, dim3(ATT_WARPS * 32), 0,
