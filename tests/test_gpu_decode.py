@@ -130,11 +130,16 @@ WIDE_NN = dict(dim=2048, hidden=2816, n_layers=2, q_heads=16, kv_heads=4,
                head_dim=128, vocab=2048)
 
 
-def test_nn_decoder_batch16_unfused_norm(oracle):
-    """Sixteen sequences of 2048-wide activations exceed the shared memory the
-    projection kernels give the fused RMSNorm, so the decoder normalises with
-    a kernel of its own; the tokens must still be the oracle's."""
-    batch, max_seq, steps = 16, 48, 10
+@pytest.mark.parametrize("batch,tensor_cores", [(16, True), (8, True), (16, False)])
+def test_nn_decoder_many_sequences(oracle, monkeypatch, batch, tensor_cores):
+    """8 and 16 sequences of 2048-wide activations. With head_dim 128 the
+    projections run on the tensor cores (activations as three bf16 terms);
+    VXB_BATCH_MMA=0 keeps them on the FMA kernels, where sixteen such
+    sequences exceed the shared memory of the fused RMSNorm and the decoder
+    normalises with a kernel of its own. Either way the tokens must be the
+    oracle's."""
+    monkeypatch.setenv("VXB_BATCH_MMA", "1" if tensor_cores else "0")
+    max_seq, steps = 48, 10
     dec, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=batch, **WIDE_NN)
     hm = nn_host_model(oracle, tensors, WIDE_NN, max_seq)
     rng = np.random.default_rng(21)
@@ -147,6 +152,8 @@ def test_nn_decoder_batch16_unfused_norm(oracle):
             got[b].append(toks[b])
         toks = dec.step(None)
     dec.close()
-    for b in (0, 7, 15):
+    from vx_b200 import ops
+    assert ops.kernel_status() == 0
+    for b in (0, batch // 2, batch - 1):
         want = oracle_generate(oracle, hm, list(prompts[b]), steps, max_seq)
         assert got[b] == want, "sequence %d: %s" % (b, report(got[b], want))

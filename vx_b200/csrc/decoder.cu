@@ -115,6 +115,12 @@ struct vx_decoder {
   /* the pushed partials are added by the next projection's prologue instead
      of a kernel of their own */
   bool fold;
+  /* 8 or 16 sequences: the projections run on the tensor cores */
+  bool mma;
+  void *mma_xs;
+  float *mma_scratch;
+  int32_t *mma_counters;
+  int mma_max_tiles;
   int64_t cache_layer_stride, cache_batch_stride;
   int split;
   int host_pos;
@@ -272,7 +278,72 @@ void record_step(vx_decoder *d, int max_pos) {
     else
       launches += add_partials(d);
   };
+  /* 8 or 16 sequences: every projection on the tensor cores */
+  auto batched = [&](int mode, const void *w0, const void *w1, const void *w2,
+                     int rows, int cols, const float *x, const void *norm_w,
+                     float *y, int64_t y_stride, const void *bias, int layer,
+                     const char *what) {
+    vxb::BatchedProj bp{};
+    bp.mode = mode;
+    bp.w0 = w0;
+    bp.w1 = w1;
+    bp.w2 = w2;
+    bp.rows = rows;
+    bp.cols = cols;
+    bp.batch = B;
+    bp.x = x;
+    bp.x_stride = cols;
+    bp.norm_w = norm_w;
+    bp.eps = c.eps;
+    bp.y = y;
+    bp.y_stride = y_stride;
+    bp.bias = bias;
+    bp.q_heads = d->q_local;
+    bp.kv_heads = d->kv_local;
+    bp.head_dim = hd;
+    bp.cos_t = d->cos_t;
+    bp.sin_t = d->sin_t;
+    bp.positions = d->positions;
+    bp.k_cache = d->k_cache + layer * d->cache_layer_stride;
+    bp.v_cache = d->v_cache + layer * d->cache_layer_stride;
+    bp.cache_batch_stride = d->cache_batch_stride;
+    bp.xs = d->mma_xs;
+    bp.scratch = d->mma_scratch;
+    bp.counters = d->mma_counters;
+    bp.max_tiles = d->mma_max_tiles;
+    need(vxb::batched_proj(bp, s), what);
+    launches += 2;
+  };
   for (int l = 0; l < c.n_layers; ++l) {
+    if (d->mma) {
+      batched(4, d->wq[l], d->wk[l], d->wv[l], (d->q_local + 2 * d->kv_local) * hd,
+              c.dim, d->x, d->attn_norm[l], d->q, (int64_t)d->q_local * hd,
+              d->bqkv[l], l, "q/k/v");
+      vxb::AttnArgs ab{};
+      ab.q = d->q;
+      ab.k_cache = d->k_cache + l * d->cache_layer_stride;
+      ab.v_cache = d->v_cache + l * d->cache_layer_stride;
+      ab.cache_batch_stride = d->cache_batch_stride;
+      ab.out = d->att;
+      ab.q_heads = d->q_local;
+      ab.kv_heads = d->kv_local;
+      ab.head_dim = hd;
+      ab.batch = B;
+      ab.positions = d->positions;
+      ab.max_pos = max_pos;
+      ab.scratch = d->scratch;
+      ab.counters = d->counters;
+      ab.split = d->split;
+      need(vxb::attention_decode(ab, s), "attention");
+      ++launches;
+      batched(1, d->wo[l], nullptr, nullptr, c.dim, d->q_local * hd, d->att,
+              nullptr, d->x, c.dim, nullptr, l, "the output projection");
+      batched(3, d->w_gate[l], d->w_up[l], nullptr, d->hidden_local, c.dim, d->x,
+              d->ffn_norm[l], d->h, d->hidden_local, nullptr, l, "gate/up");
+      batched(1, d->w_down[l], nullptr, nullptr, c.dim, d->hidden_local, d->h,
+              nullptr, d->x, c.dim, nullptr, l, "the down projection");
+      continue;
+    }
     vxb::QkvArgs qa{};
     qa.wq = d->wq[l];
     qa.wk = d->wk[l];
@@ -372,6 +443,10 @@ void record_step(vx_decoder *d, int max_pos) {
     after_push();
   }
 
+  if (d->mma) {
+    batched(0, d->lm_head, nullptr, nullptr, d->vocab_local, c.dim, d->x,
+            d->final_norm, d->logits, d->vocab_local, nullptr, 0, "the logits");
+  } else {
   vxb::MatvecArgs la{};
   la.w = d->lm_head;
   la.wbf16 = bf;
@@ -389,10 +464,12 @@ void record_step(vx_decoder *d, int max_pos) {
   la.mode = 0;
   need(vxb::matvec(la, s), "the logits");
   partials_taken();
+  ++launches;
+  }
   if (d->ranks == 1) {
     need(vxb::argmax(d->tokens, d->logits, d->vocab_local, B, d->vocab_local, s),
          "argmax");
-    launches += 2;
+    launches += 1;
   } else {
     need(vxb::argmax(d->local_best, d->logits, d->vocab_local, B,
                      d->vocab_local, s),
@@ -406,7 +483,7 @@ void record_step(vx_decoder *d, int max_pos) {
       stop("vx_decoder: ncclAllGather failed: %s",
            job->api()->GetErrorString(r));
     pick_pair_kernel<<<1, 32, 0, s>>>(d->tokens, d->pairs_all, d->ranks, B);
-    launches += 5;
+    launches += 4;
   }
   advance_kernel<<<1, 32, 0, s>>>(d->positions, B);
   ++launches;
@@ -532,6 +609,27 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
     open_peer_buffers(d, rank);
     d->push = true;
   }
+  d->mma = false;
+  d->mma_xs = nullptr;
+  d->mma_scratch = nullptr;
+  d->mma_counters = nullptr;
+  const char *nomma = getenv("VXB_BATCH_MMA");
+  if (c.weights_bf16 && d->ranks == 1 && (B == 8 || B == 16) && c.head_dim == 128 &&
+      c.dim % 64 == 0 && d->hidden_local % 64 == 0 && !(nomma && nomma[0] == '0')) {
+    int widest = c.dim > d->hidden_local ? c.dim : d->hidden_local;
+    if (d->q_local * c.head_dim > widest)
+      widest = d->q_local * c.head_dim;
+    int rows_max = 2 * d->hidden_local;
+    if ((d->q_local + 2 * d->kv_local) * c.head_dim > rows_max)
+      rows_max = (d->q_local + 2 * d->kv_local) * c.head_dim;
+    if (d->vocab_local > rows_max)
+      rows_max = d->vocab_local;
+    d->mma_max_tiles = rows_max / 64 + 2;
+    d->mma_xs = dev_alloc<uint16_t>((size_t)48 * widest);
+    d->mma_scratch = dev_alloc<float>(vxb::batched_proj_scratch_floats(rows_max, B));
+    d->mma_counters = dev_alloc<int32_t>(d->mma_max_tiles);
+    d->mma = true;
+  }
   const char *nofold = getenv("VXB_TP_FOLD");
   d->fold = d->push && d->fused_norm && !(nofold && nofold[0] == '0');
   CUDA_OK(cudaDeviceSynchronize());
@@ -559,7 +657,8 @@ void vx_decoder_destroy(vx_decoder *d) {
                   (void *)d->v_cache, (void *)d->scratch, (void *)d->counters,
                   (void *)d->tokens, (void *)d->positions,
                   (void *)d->local_best, (void *)d->pair,
-                  (void *)d->pairs_all})
+                  (void *)d->pairs_all, d->mma_xs, (void *)d->mma_scratch,
+                  (void *)d->mma_counters})
     cudaFree(p);
   cudaStreamDestroy(d->stream);
   delete d;

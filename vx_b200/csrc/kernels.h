@@ -181,6 +181,39 @@ size_t attn_scratch_floats(int batch, int q_heads, int head_dim, int max_seq,
                            int split);
 const char *attention_decode(const AttnArgs &a, cudaStream_t stream);
 
+/* ---- the projections for 8 or 16 sequences, on the tensor cores -------------
+ * y = W x with bf16 W [rows, cols] and f32 x [batch][cols] taken as three bf16
+ * terms (rowdot_umma.cu). mode: 0 y = s, 1 y += s, 3 SwiGLU (rows = units; w0
+ * gate rows, w1 up rows or NULL: up rows follow in w0), 4 q/k/v + bias + RoPE +
+ * KV store (head_dim 128; w1/w2 k and v matrices or NULL: rows follow in w0).
+ * xs: bf16 [48 or 32][cols] work space for the terms; scratch and counters:
+ * batched_proj_scratch_floats() floats and max_tiles zeroed int32. */
+struct BatchedProj {
+  int mode;
+  const void *w0, *w1, *w2;
+  int rows, cols, batch;
+  const float *x;
+  int64_t x_stride;
+  const void *norm_w; /* bf16, or NULL */
+  float eps;
+  float *y;
+  int64_t y_stride;
+  const void *bias;
+  int q_heads, kv_heads, head_dim;
+  const float *cos_t, *sin_t;
+  const int32_t *positions;
+  float *k_cache, *v_cache;
+  int64_t cache_batch_stride;
+  void *xs;
+  float *scratch;
+  int32_t *counters;
+  int max_tiles;
+};
+const char *batched_proj_refusal(const BatchedProj &a);
+size_t batched_proj_scratch_floats(int rows_max, int batch);
+const char *batched_proj(const BatchedProj &a, cudaStream_t stream);
+int batched_proj_status(cudaStream_t stream);
+
 const char *argmax(int32_t *out, const float *logits, int n, int batch,
                    int64_t stride, cudaStream_t stream);
 const char *embed(float *x, const void *table, bool tbf16, const int32_t *token,

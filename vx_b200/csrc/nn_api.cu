@@ -420,7 +420,8 @@ int32_t vx_b200_kernel_status(void) {
   const int g = vxb::gemm_status(vxb::caller_stream());
   const int f = vxb::flash_status(vxb::caller_stream());
   const int t = vxb::tp_status(vxb::caller_stream());
-  return g ? g : (f ? f : t);
+  const int m = vxb::batched_proj_status(vxb::caller_stream());
+  return g ? g : (f ? f : (t ? t : m));
 }
 
 int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,
