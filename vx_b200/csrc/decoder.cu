@@ -119,8 +119,6 @@ struct vx_decoder {
   bool mma;
   void *mma_xs;
   float *mma_scratch;
-  int32_t *mma_counters;
-  int mma_max_tiles;
   int64_t cache_layer_stride, cache_batch_stride;
   int split;
   int host_pos;
@@ -309,10 +307,8 @@ void record_step(vx_decoder *d, int max_pos) {
     bp.cache_batch_stride = d->cache_batch_stride;
     bp.xs = d->mma_xs;
     bp.scratch = d->mma_scratch;
-    bp.counters = d->mma_counters;
-    bp.max_tiles = d->mma_max_tiles;
     need(vxb::batched_proj(bp, s), what);
-    launches += 2;
+    launches += 3;
   };
   for (int l = 0; l < c.n_layers; ++l) {
     if (d->mma) {
@@ -612,7 +608,6 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
   d->mma = false;
   d->mma_xs = nullptr;
   d->mma_scratch = nullptr;
-  d->mma_counters = nullptr;
   const char *nomma = getenv("VXB_BATCH_MMA");
   if (c.weights_bf16 && d->ranks == 1 && (B == 8 || B == 16) && c.head_dim == 128 &&
       c.dim % 64 == 0 && d->hidden_local % 64 == 0 && !(nomma && nomma[0] == '0')) {
@@ -624,10 +619,8 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
       rows_max = (d->q_local + 2 * d->kv_local) * c.head_dim;
     if (d->vocab_local > rows_max)
       rows_max = d->vocab_local;
-    d->mma_max_tiles = rows_max / 64 + 2;
     d->mma_xs = dev_alloc<uint16_t>((size_t)48 * widest);
     d->mma_scratch = dev_alloc<float>(vxb::batched_proj_scratch_floats(rows_max, B));
-    d->mma_counters = dev_alloc<int32_t>(d->mma_max_tiles);
     d->mma = true;
   }
   const char *nofold = getenv("VXB_TP_FOLD");
@@ -657,8 +650,7 @@ void vx_decoder_destroy(vx_decoder *d) {
                   (void *)d->v_cache, (void *)d->scratch, (void *)d->counters,
                   (void *)d->tokens, (void *)d->positions,
                   (void *)d->local_best, (void *)d->pair,
-                  (void *)d->pairs_all, d->mma_xs, (void *)d->mma_scratch,
-                  (void *)d->mma_counters})
+                  (void *)d->pairs_all, d->mma_xs, (void *)d->mma_scratch})
     cudaFree(p);
   cudaStreamDestroy(d->stream);
   delete d;

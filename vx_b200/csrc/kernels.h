@@ -186,8 +186,8 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream);
  * terms (rowdot_umma.cu). mode: 0 y = s, 1 y += s, 3 SwiGLU (rows = units; w0
  * gate rows, w1 up rows or NULL: up rows follow in w0), 4 q/k/v + bias + RoPE +
  * KV store (head_dim 128; w1/w2 k and v matrices or NULL: rows follow in w0).
- * xs: bf16 [48 or 32][cols] work space for the terms; scratch and counters:
- * batched_proj_scratch_floats() floats and max_tiles zeroed int32. */
+ * xs: bf16 [48 or 32][cols] work space for the terms; scratch:
+ * batched_proj_scratch_floats() floats for the partial sums of the K runs. */
 struct BatchedProj {
   int mode;
   const void *w0, *w1, *w2;
@@ -206,8 +206,6 @@ struct BatchedProj {
   int64_t cache_batch_stride;
   void *xs;
   float *scratch;
-  int32_t *counters;
-  int max_tiles;
 };
 const char *batched_proj_refusal(const BatchedProj &a);
 size_t batched_proj_scratch_floats(int rows_max, int batch);

@@ -17,12 +17,15 @@
  * (W: two boxes of 64 rows, so that a tile can take its two halves from
  * different places: gate and up rows, or q/k/v matrices; x terms: one box of
  * N rows) into an 8-stage ring; warp 1 one thread of MMAs into one of four
- * 64-column TMEM accumulators; warps 2-5 the epilogue.  With S > 1 an item
- * stores its partial sums and the CTA that finishes a tile last adds them in
- * run order (so the result does not depend on timing) and applies the
- * projection's epilogue: store, residual add, SwiGLU, or bias + RoPE + KV-cache
- * store (head_dim 128: a tile is one head, and the rotation partners i and
- * i + 64 sit in the two halves of the tile).
+ * 64-column TMEM accumulators; warps 2-5 the epilogue, which adds the three
+ * terms and stores the item's partial sums.  A second, small kernel adds the
+ * runs of a tile in run order (so the result does not depend on timing) and
+ * applies the projection's epilogue: store, residual add, SwiGLU, or bias +
+ * RoPE + KV-cache store (head_dim 128: a tile is one head, and the rotation
+ * partners i and i + 64 sit in the two halves of the tile).  (Doing that in
+ * the main kernel, by whichever CTA finished a tile last, cost a fence and an
+ * atomic round trip per item and made the epilogue warps the bottleneck:
+ * 42.8 us per projection on average against 23.1 + 5.7 us this way.)
  */
 #include "kernels.h"
 #include "launch.cuh"
@@ -31,6 +34,7 @@
 #include <cuda_bf16.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace vxb {
@@ -56,7 +60,6 @@ struct Bars {
   uint64_t tmem_full[ACCS], tmem_empty[ACCS];
   uint32_t tmem_base;
   int stop;
-  int last; /* epilogue: this CTA finishes the tile */
 };
 
 /* Device-side view of one projection. */
@@ -77,7 +80,6 @@ struct MmaParams {
   float *k_cache, *v_cache;
   int64_t cache_batch_stride;
   float *partials;     /* [splits][batch][tiles * 128] */
-  int32_t *counters;   /* [tiles], zero between launches */
 };
 
 __device__ __forceinline__ void half_source(const MmaParams &p, int tile, int half,
@@ -121,7 +123,6 @@ rowdot_mma_kernel(const __grid_constant__ CUtensorMap map_w0,
   const int b_bytes = p.n * BK * 2;
   const int stage_bytes = A_BYTES + ((b_bytes + 1023) & ~1023);
   Bars *bars = reinterpret_cast<Bars *>(smem + STAGES * stage_bytes);
-  float *vals = reinterpret_cast<float *>(bars + 1); /* [128][batch], epilogue */
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   chain_release();
@@ -283,96 +284,13 @@ rowdot_mma_kernel(const __grid_constant__ CUtensorMap map_w0,
       if (lane == 0)
         ptx::mbar_arrive(&bars->tmem_empty[acc]);
 
+      /* this run's part of the tile; proj_finish_kernel adds the runs */
       const int64_t padded_rows = (int64_t)p.tiles * TM;
-      bool finish = true;
-      if (p.splits > 1) {
-        /* store this run's part; the CTA that brings the last part of the tile
-           adds all of them in run order */
-        float *mine = p.partials + ((int64_t)split * B) * padded_rows + tile * TM + r;
-        for (int b = 0; b < B; ++b)
+      float *mine = p.partials + ((int64_t)split * B) * padded_rows + tile * TM + r;
+#pragma unroll
+      for (int b = 0; b < 16; ++b)
+        if (b < B)
           mine[b * padded_rows] = sum[b];
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          const int seen = atomicAdd(&p.counters[tile], 1);
-          bars->last = seen == p.splits - 1;
-          if (bars->last)
-            p.counters[tile] = 0;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        finish = bars->last != 0;
-        if (finish) {
-          __threadfence();
-          for (int b = 0; b < B; ++b) {
-            float acc_b = 0.0f;
-            for (int s = 0; s < p.splits; ++s)
-              acc_b += __ldcg(p.partials + ((int64_t)s * B + b) * padded_rows +
-                              tile * TM + r);
-            sum[b] = acc_b;
-          }
-        }
-      }
-      if (!finish)
-        continue;
-
-      /* ---- the projection's own epilogue ---- */
-      if (p.mode == 0 || p.mode == 1) {
-        const int row = tile * TM + r;
-        if (row < p.rows)
-          for (int b = 0; b < B; ++b) {
-            float *y = p.y + b * p.y_stride + row;
-            *y = p.mode == 1 ? __ldcg(y) + sum[b] : sum[b];
-          }
-        continue;
-      }
-      /* SwiGLU and q/k/v need the value of the row 64 further on */
-      asm volatile("bar.sync 1, 128;" ::: "memory"); /* vals is free again */
-      for (int b = 0; b < B; ++b)
-        vals[r * B + b] = sum[b];
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (p.mode == 3) {
-        if (r < 64) {
-          const int unit = tile * 64 + r;
-          if (unit < p.rows)
-            for (int b = 0; b < B; ++b) {
-              const float g = sum[b], u = vals[(r + 64) * B + b];
-              /* nn_swiglu (nn.vx:169-209): g / (1 + e^-g) * u */
-              p.y[b * p.y_stride + unit] = g / (1.0f + expf(0.0f - g)) * u;
-            }
-        }
-        continue;
-      }
-      /* q/k/v: tile = head; pairs (i, i + 64), nn_rope_and_store (nn.vx:245-280) */
-      {
-        const int head = tile;
-        const int kind = head < p.q_heads ? 0 : (head < p.q_heads + p.kv_heads ? 1 : 2);
-        const int local = kind == 0 ? head
-                          : kind == 1 ? head - p.q_heads
-                                      : head - p.q_heads - p.kv_heads;
-        const int i = r & 63;
-        const float bias = p.bias ? bf16_val(p.bias, (int64_t)head * 128 + r) : 0.0f;
-        for (int b = 0; b < B; ++b) {
-          const int pos = p.positions[b];
-          const float mine_v = sum[b] + bias;
-          if (kind == 2) {
-            p.v_cache[b * p.cache_batch_stride +
-                      ((int64_t)pos * p.kv_heads + local) * 128 + r] = mine_v;
-            continue;
-          }
-          const float other =
-              vals[(r ^ 64) * B + b] +
-              (p.bias ? bf16_val(p.bias, (int64_t)head * 128 + (r ^ 64)) : 0.0f);
-          const float c = p.cos_t[(int64_t)pos * 64 + i];
-          const float s = p.sin_t[(int64_t)pos * 64 + i];
-          /* lower half: a c - b s; upper half: b c + a s (a lower, b upper) */
-          const float out = r < 64 ? __fsub_rn(__fmul_rn(mine_v, c), __fmul_rn(other, s))
-                                   : __fadd_rn(__fmul_rn(mine_v, c), __fmul_rn(other, s));
-          float *dst = kind == 0 ? p.y + b * p.y_stride + (int64_t)local * 128
-                                 : p.k_cache + b * p.cache_batch_stride +
-                                       ((int64_t)pos * p.kv_heads + local) * 128;
-          dst[r] = out;
-        }
-      }
     }
   }
 
@@ -384,9 +302,80 @@ rowdot_mma_kernel(const __grid_constant__ CUtensorMap map_w0,
   }
 }
 
+/* The runs of K added in run order (so the result does not depend on
+   timing), then the projection's own epilogue. One thread per sequence and
+   per output row (modes 0, 1), SwiGLU unit (mode 3) or rotation pair (mode 4). */
+__global__ void __launch_bounds__(256)
+proj_finish_kernel(const MmaParams p) {
+  chain_release();
+  chain_wait();
+  const int B = p.batch;
+  const int64_t padded_rows = (int64_t)p.tiles * TM;
+  const int per_seq = p.mode == 0 || p.mode == 1 ? p.rows : p.tiles * 64;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)per_seq * B)
+    return;
+  const int b = (int)(idx / per_seq), e = (int)(idx - (int64_t)b * per_seq);
+  /* the value of padded row `row`, all runs */
+  auto total = [&](int64_t row) {
+    const float *at = p.partials + (int64_t)b * padded_rows + row;
+    float v[16];
+#pragma unroll
+    for (int s = 0; s < 16; ++s)
+      v[s] = s < p.splits ? __ldcg(at + (int64_t)s * B * padded_rows) : 0.0f;
+    float t = 0.0f;
+#pragma unroll
+    for (int s = 0; s < 16; ++s)
+      if (s < p.splits)
+        t += v[s];
+    return t;
+  };
+  if (p.mode == 0 || p.mode == 1) {
+    float *y = p.y + b * p.y_stride + e;
+    const float t = total(e);
+    *y = p.mode == 1 ? *y + t : t;
+    return;
+  }
+  const int tile = e / 64, r = e - tile * 64;
+  const float lo = total((int64_t)tile * TM + r), hi = total((int64_t)tile * TM + r + 64);
+  if (p.mode == 3) {
+    if (e < p.rows) /* nn_swiglu (nn.vx:169-209): g / (1 + e^-g) * u */
+      p.y[b * p.y_stride + e] = lo / (1.0f + expf(0.0f - lo)) * hi;
+    return;
+  }
+  /* q/k/v: tile = head; pairs (r, r + 64), nn_rope_and_store (nn.vx:245-280) */
+  const int head = tile;
+  const int kind = head < p.q_heads ? 0 : (head < p.q_heads + p.kv_heads ? 1 : 2);
+  const int local = kind == 0 ? head
+                    : kind == 1 ? head - p.q_heads
+                                : head - p.q_heads - p.kv_heads;
+  float va = lo, vb = hi;
+  if (p.bias) {
+    va += bf16_val(p.bias, (int64_t)head * 128 + r);
+    vb += bf16_val(p.bias, (int64_t)head * 128 + r + 64);
+  }
+  const int pos = p.positions[b];
+  if (kind == 2) {
+    float *vrow = p.v_cache + b * p.cache_batch_stride +
+                  ((int64_t)pos * p.kv_heads + local) * 128;
+    vrow[r] = va;
+    vrow[r + 64] = vb;
+    return;
+  }
+  const float c = p.cos_t[(int64_t)pos * 64 + r];
+  const float sn = p.sin_t[(int64_t)pos * 64 + r];
+  float *dst = kind == 0 ? p.y + b * p.y_stride + (int64_t)local * 128
+                         : p.k_cache + b * p.cache_batch_stride +
+                               ((int64_t)pos * p.kv_heads + local) * 128;
+  dst[r] = __fsub_rn(__fmul_rn(va, c), __fmul_rn(vb, sn));
+  dst[r + 64] = __fadd_rn(__fmul_rn(vb, c), __fmul_rn(va, sn));
+}
+
 /* x (f32, optionally RMS-normalised first: nn_rms_norm, nn.vx:212-239) as three
    bf16 terms: row p * batch + b of xs holds term p of sequence b; rows from
-   3 * batch up to n are zero. One block per sequence. */
+   3 * batch up to n are zero. Block (b, chunk) writes 1024 columns of sequence
+   b (blockIdx.x >= batch: of the zero rows); each block of a normalised row
+   takes the row's sum of squares itself, in the same order. */
 __global__ void __launch_bounds__(1024)
 split3_kernel(__nv_bfloat16 *xs, const float *x, int64_t x_stride, int cols,
               int batch, int n, const void *norm_w, float eps) {
@@ -394,9 +383,10 @@ split3_kernel(__nv_bfloat16 *xs, const float *x, int64_t x_stride, int cols,
   chain_release();
   chain_wait();
   const int b = blockIdx.x;
+  const int i = blockIdx.y * 1024 + threadIdx.x;
   if (b >= batch) { /* padding rows */
-    for (int i = threadIdx.x; i < cols; i += blockDim.x)
-      for (int row = 3 * batch + (b - batch); row < n; row += gridDim.x - batch)
+    if (i < cols)
+      for (int row = 3 * batch; row < n; ++row)
         xs[(int64_t)row * cols + i] = __float2bfloat16(0.0f);
     return;
   }
@@ -404,8 +394,8 @@ split3_kernel(__nv_bfloat16 *xs, const float *x, int64_t x_stride, int cols,
   float inv = 1.0f;
   if (norm_w) {
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < cols; i += blockDim.x)
-      ss = fmaf(xr[i], xr[i], ss);
+    for (int j = threadIdx.x; j < cols; j += blockDim.x)
+      ss = fmaf(xr[j], xr[j], ss);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
@@ -418,7 +408,7 @@ split3_kernel(__nv_bfloat16 *xs, const float *x, int64_t x_stride, int cols,
       t += red[w];
     inv = 1.0f / sqrtf(t / (float)cols + eps);
   }
-  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+  if (i < cols) {
     float v = xr[i];
     if (norm_w)
       v = v * inv * bf16_val(norm_w, i);
@@ -487,8 +477,9 @@ const char *batched_proj(const BatchedProj &a, cudaStream_t stream) {
     return why;
   const int n = (3 * a.batch + 15) / 16 * 16;
   /* the activations' three terms */
-  launch_chained(split3_kernel, dim3(a.batch + (n > 3 * a.batch ? 1 : 0)), dim3(1024),
-                 0, stream, (__nv_bfloat16 *)a.xs, a.x, a.x_stride, a.cols, a.batch,
+  launch_chained(split3_kernel,
+                 dim3(a.batch + (n > 3 * a.batch ? 1 : 0), (a.cols + 1023) / 1024),
+                 dim3(1024), 0, stream, (__nv_bfloat16 *)a.xs, a.x, a.x_stride, a.cols, a.batch,
                  n, a.norm_w, a.eps);
   MmaParams p{};
   p.mode = a.mode;
@@ -509,7 +500,6 @@ const char *batched_proj(const BatchedProj &a, cudaStream_t stream) {
   p.v_cache = a.v_cache;
   p.cache_batch_stride = a.cache_batch_stride;
   p.partials = a.scratch;
-  p.counters = a.counters;
   int64_t rows0 = a.rows, rows1 = 0, rows2 = 0; /* rows of the three matrices */
   if (a.mode == 3) {
     p.tiles = a.rows / 64;
@@ -525,8 +515,6 @@ const char *batched_proj(const BatchedProj &a, cudaStream_t stream) {
   } else {
     p.tiles = (a.rows + TM - 1) / TM;
   }
-  if (p.tiles > a.max_tiles)
-    return "more row tiles than the counters provide for";
   p.splits = pick_splits(p.tiles, p.k_blocks, sm_count());
   CUtensorMap m0, m1, m2, mx;
   if (!make_map_16(&m0, a.w0, a.cols, rows0, a.cols, 64, 64, true))
@@ -540,15 +528,14 @@ const char *batched_proj(const BatchedProj &a, cudaStream_t stream) {
     return "cuTensorMapEncodeTiled refused the activations";
   const int b_bytes = n * BK * 2;
   const int stage_bytes = A_BYTES + ((b_bytes + 1023) & ~1023);
-  const size_t smem = (size_t)STAGES * stage_bytes + 1024 + sizeof(Bars) +
-                      TM * 16 * sizeof(float) + 64;
+  const size_t smem = (size_t)STAGES * stage_bytes + 1024 + sizeof(Bars) + 64;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
     attr_err = cudaFuncSetAttribute(rowdot_mma_kernel,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     STAGES * (A_BYTES + 8192) + 1024 +
-                                        (int)sizeof(Bars) + TM * 16 * 4 + 64);
+                                        (int)sizeof(Bars) + 64);
   });
   if (attr_err != cudaSuccess)
     return "the batched projection could not get its shared memory";
@@ -556,6 +543,10 @@ const char *batched_proj(const BatchedProj &a, cudaStream_t stream) {
   const int ctas = items < sm_count() ? items : sm_count();
   launch_chained(rowdot_mma_kernel, dim3(ctas), dim3(THREADS), smem, stream, m0, m1,
                  m2, mx, p);
+  const int64_t outputs =
+      (int64_t)a.batch * (p.mode == 0 || p.mode == 1 ? p.rows : p.tiles * 64);
+  launch_chained(proj_finish_kernel, dim3((unsigned)((outputs + 255) / 256)),
+                 dim3(256), 0, stream, p);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     static thread_local char msg[160];
