@@ -66,8 +66,7 @@ __device__ __forceinline__ float ex2(float x) {
    p = 2^(s * scale_log2 + neg_m), rounded to bf16 pairs into `packed`; `sum`
    gets the f32 row sum and `rel_max` the largest exponent met. The body is
    long (everything is unrolled so that P stays in registers) and the kernel
-   holds two copies of it, which is why masking is not a third and fourth:
-   the instruction cache is a resource here. */
+   holds one copy of it: the instruction cache is a resource here. */
 __device__ __forceinline__ void
 probabilities(uint32_t s_tmem, float scale_log2, float neg_m,
               uint32_t (&packed)[BKV / 2], float &rel_max, float &sum) {
@@ -93,6 +92,31 @@ probabilities(uint32_t s_tmem, float scale_log2, float neg_m,
   }
   rel_max = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
   sum = (part4[0] + part4[1]) + (part4[2] + part4[3]);
+}
+
+/* The same arithmetic when the maximum is known to hold (the pass after
+   row_max): P can go to tensor memory chunk by chunk, over score columns
+   that have been read already, so this form is a short loop instead of a
+   second copy of the long body above. Returns the row sum. */
+__device__ __forceinline__ float
+probabilities_stored(uint32_t s_tmem, float scale_log2, float neg_m) {
+  float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+  for (int c = 0; c < BKV / 32; ++c) {
+    uint32_t raw[32], packed[16];
+    ptx::tmem_ld_32x32b_x32(s_tmem + c * 32, raw);
+    ptx::tmem_ld_wait_for(raw);
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      const float p0 = ex2(fmaf(__uint_as_float(raw[e]), scale_log2, neg_m));
+      const float p1 = ex2(fmaf(__uint_as_float(raw[e + 1]), scale_log2, neg_m));
+      part4[(e >> 1) & 3] += p0 + p1;
+      const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+      packed[e >> 1] = *reinterpret_cast<const uint32_t *>(&pr);
+    }
+    ptx::tmem_st_32x32b_x16(s_tmem + c * 16, packed);
+  }
+  return (part4[0] + part4[1]) + (part4[2] + part4[3]);
 }
 
 /* The largest of a row's 128 scores (as stored, before scaling). */
@@ -394,13 +418,15 @@ flash2_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         l_sum *= fix;
         m_used = m_new;
-        probabilities(s_tmem, scale_log2, -m_used, packed, rel_max, sum);
+        sum = probabilities_stored(s_tmem, scale_log2, -m_used);
+      } else {
+        /* P, two bf16 per column, over the first half of the score columns. */
+        ptx::tmem_st_32x32b_x32(s_tmem,
+                                *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
+        ptx::tmem_st_32x32b_x32(s_tmem + 32,
+                                *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
       }
       l_sum += sum;
-      /* P, two bf16 per column, over the first half of the score columns. */
-      ptx::tmem_st_32x32b_x32(s_tmem, *reinterpret_cast<uint32_t(*)[32]>(&packed[0]));
-      ptx::tmem_st_32x32b_x32(s_tmem + 32,
-                              *reinterpret_cast<uint32_t(*)[32]>(&packed[32]));
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
       __syncwarp();
