@@ -280,7 +280,8 @@ void record_step(vx_decoder *d, int max_pos) {
   auto batched = [&](int mode, const void *w0, const void *w1, const void *w2,
                      int rows, int cols, const float *x, const void *norm_w,
                      float *y, int64_t y_stride, const void *bias, int layer,
-                     const char *what) {
+                     const char *what, bool terms_ready = false,
+                     bool leave_terms = false) {
     vxb::BatchedProj bp{};
     bp.mode = mode;
     bp.w0 = w0;
@@ -307,8 +308,10 @@ void record_step(vx_decoder *d, int max_pos) {
     bp.cache_batch_stride = d->cache_batch_stride;
     bp.xs = d->mma_xs;
     bp.scratch = d->mma_scratch;
+    bp.x_terms_ready = terms_ready;
+    bp.next_terms = leave_terms;
     need(vxb::batched_proj(bp, s), what);
-    launches += 3;
+    launches += terms_ready ? 2 : 3;
   };
   for (int l = 0; l < c.n_layers; ++l) {
     if (d->mma) {
@@ -334,10 +337,12 @@ void record_step(vx_decoder *d, int max_pos) {
       ++launches;
       batched(1, d->wo[l], nullptr, nullptr, c.dim, d->q_local * hd, d->att,
               nullptr, d->x, c.dim, nullptr, l, "the output projection");
+      /* SwiGLU's finishing kernel leaves the down projection's input as terms */
       batched(3, d->w_gate[l], d->w_up[l], nullptr, d->hidden_local, c.dim, d->x,
-              d->ffn_norm[l], d->h, d->hidden_local, nullptr, l, "gate/up");
+              d->ffn_norm[l], d->h, d->hidden_local, nullptr, l, "gate/up", false,
+              true);
       batched(1, d->w_down[l], nullptr, nullptr, c.dim, d->hidden_local, d->h,
-              nullptr, d->x, c.dim, nullptr, l, "the down projection");
+              nullptr, d->x, c.dim, nullptr, l, "the down projection", true);
       continue;
     }
     vxb::QkvArgs qa{};

@@ -206,6 +206,12 @@ struct BatchedProj {
   int64_t cache_batch_stride;
   void *xs;
   float *scratch;
+  /* chaining: x's terms are in xs already (left by the projection before);
+     leave this projection's output there as terms for the next one (mode 3:
+     SwiGLU's output is the down projection's input). A residual projection
+     followed by an RMSNorm cannot: the norm needs the whole row, and one block
+     per sequence doing both was no faster than the two kernels. */
+  int x_terms_ready, next_terms;
 };
 const char *batched_proj_refusal(const BatchedProj &a);
 size_t batched_proj_scratch_floats(int rows_max, int batch);

@@ -80,7 +80,23 @@ struct MmaParams {
   float *k_cache, *v_cache;
   int64_t cache_batch_stride;
   float *partials;     /* [splits][batch][tiles * 128] */
+  /* the finishing kernel may also leave its output as the three bf16 terms
+     that the next projection reads (NULL: no) */
+  __nv_bfloat16 *terms;
+  int terms_n; /* rows of the term matrix (48 or 32) */
 };
+
+/* v as three bf16 terms into rows b, batch + b, 2 batch + b of xs, column i. */
+__device__ __forceinline__ void store_terms(__nv_bfloat16 *xs, int cols, int batch,
+                                            int b, int i, float v) {
+  const __nv_bfloat16 t1 = __float2bfloat16(v);
+  const float r1 = v - __bfloat162float(t1);
+  const __nv_bfloat16 t2 = __float2bfloat16(r1);
+  const float r2 = r1 - __bfloat162float(t2);
+  xs[(int64_t)(0 * batch + b) * cols + i] = t1;
+  xs[(int64_t)(1 * batch + b) * cols + i] = t2;
+  xs[(int64_t)(2 * batch + b) * cols + i] = __float2bfloat16(r2);
+}
 
 __device__ __forceinline__ void half_source(const MmaParams &p, int tile, int half,
                                             int &which, int &row0) {
@@ -339,8 +355,16 @@ proj_finish_kernel(const MmaParams p) {
   const int tile = e / 64, r = e - tile * 64;
   const float lo = total((int64_t)tile * TM + r), hi = total((int64_t)tile * TM + r + 64);
   if (p.mode == 3) {
-    if (e < p.rows) /* nn_swiglu (nn.vx:169-209): g / (1 + e^-g) * u */
-      p.y[b * p.y_stride + e] = lo / (1.0f + expf(0.0f - lo)) * hi;
+    if (e < p.rows) { /* nn_swiglu (nn.vx:169-209): g / (1 + e^-g) * u */
+      const float h = lo / (1.0f + expf(0.0f - lo)) * hi;
+      p.y[b * p.y_stride + e] = h;
+      if (p.terms) {
+        store_terms(p.terms, p.rows, B, b, e, h);
+        if (b == 0)
+          for (int row = 3 * B; row < p.terms_n; ++row)
+            p.terms[(int64_t)row * p.rows + e] = __float2bfloat16(0.0f);
+      }
+    }
     return;
   }
   /* q/k/v: tile = head; pairs (r, r + 64), nn_rope_and_store (nn.vx:245-280) */
@@ -476,8 +500,9 @@ const char *batched_proj(const BatchedProj &a, cudaStream_t stream) {
   if (const char *why = batched_proj_refusal(a))
     return why;
   const int n = (3 * a.batch + 15) / 16 * 16;
-  /* the activations' three terms */
-  launch_chained(split3_kernel,
+  /* the activations' three terms, unless the projection before left them */
+  if (!a.x_terms_ready)
+    launch_chained(split3_kernel,
                  dim3(a.batch + (n > 3 * a.batch ? 1 : 0), (a.cols + 1023) / 1024),
                  dim3(1024), 0, stream, (__nv_bfloat16 *)a.xs, a.x, a.x_stride, a.cols, a.batch,
                  n, a.norm_w, a.eps);
@@ -500,6 +525,10 @@ const char *batched_proj(const BatchedProj &a, cudaStream_t stream) {
   p.v_cache = a.v_cache;
   p.cache_batch_stride = a.cache_batch_stride;
   p.partials = a.scratch;
+  p.terms = a.next_terms ? (__nv_bfloat16 *)a.xs : nullptr;
+  p.terms_n = a.next_terms ? (3 * a.batch + 15) / 16 * 16 : 0;
+  if (a.next_terms && a.mode != 3)
+    return "only the SwiGLU projection can leave terms";
   int64_t rows0 = a.rows, rows1 = 0, rows2 = 0; /* rows of the three matrices */
   if (a.mode == 3) {
     p.tiles = a.rows / 64;
