@@ -102,10 +102,31 @@ def attn(torch, args):
                 bytes=nbytes, gbs=nbytes / ms / 1e6)
 
 
+def decode16(torch, args):
+    """A few layers of the 7B shape decoding `--batch` (8 or 16) sequences per
+    step after `--pos` prompt positions: the tensor-core projections
+    (rowdot_mma_kernel), attention and their small companions, for profiling."""
+    from . import llama
+    shape = dict(llama.LLAMA2_7B)
+    shape["n_layers"] = args.layers
+    batch = args.batch if args.batch in (8, 16) else 16
+    dec, tensors = llama.nn_bf16_model(max_seq=1024, batch=batch, **shape)
+    rng = np.random.default_rng(1)
+    for _ in range(args.pos):
+        dec.step([int(t) for t in rng.integers(0, shape["vocab"], batch)],
+                 fetch=False)
+    ms = _timed(torch, torch.cuda.ExternalStream(dec.stream),
+                lambda: dec.step(None, fetch=False), args.iters)
+    dec.close()
+    return dict(kernel="decode step, %d layers of the 7B shape, %d sequences, "
+                       "position %d" % (args.layers, batch, args.pos),
+                us=ms * 1e3, status=ops.kernel_status())
+
+
 def main():
     import torch
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["rowdot", "gemm", "flash", "attn"])
+    ap.add_argument("case", choices=["rowdot", "gemm", "flash", "attn", "decode16"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--n", type=int, default=4096)
@@ -115,8 +136,8 @@ def main():
     ap.add_argument("--pos", type=int, default=600)
     args = ap.parse_args()
     torch.cuda.set_device(0)
-    print(json.dumps(dict(rowdot=rowdot, gemm=gemm, flash=flash,
-                          attn=attn)[args.case](torch, args)))
+    print(json.dumps(dict(rowdot=rowdot, gemm=gemm, flash=flash, attn=attn,
+                          decode16=decode16)[args.case](torch, args)))
 
 
 if __name__ == "__main__":
