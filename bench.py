@@ -413,6 +413,10 @@ def run_ours(args):
         try:
             line["decode_batch16"] = bench_decode_batch(torch, llama, shape, peaks, 16)
             line["gemm"] = bench_gemm(torch, peaks)
+            # the other sizes of the GEMM configuration (2048 fits L2: noted)
+            line["gemm_sweep"] = {
+                str(n): round(bench_gemm(torch, peaks, n=n, iters=it)["tflops"], 1)
+                for n, it in ((2048, 50), (4096, 30), (16384, 5))}
             line["flash_attention"] = bench_flash(torch, peaks)
         except RuntimeError as e:        # reported, never hidden
             line["extras_error"] = str(e)
