@@ -149,6 +149,15 @@ void vx_decoder_reset(vx_decoder *d);
 int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
                         int32_t *tokens_out);
 /* The logits of the last step: device memory, [batch, vocab] f32. */
+/* A run of prompt tokens of a one-sequence decoder, sixteen positions per
+   pass through the layers (the reference's multi-row kernels, nn.vx:2317-3066:
+   its llama programs feed a prompt one decode step at a time). Fills the KV
+   cache and advances the position; computes no logits, so the caller gives
+   the last prompt token to vx_decoder_step. Returns how many tokens it took
+   (a multiple of 16, the rest is the caller's to step through), or -1 with
+   vx_b200_last_error() for a decoder that cannot (needs batch 1, one rank,
+   bf16 weights, head_dim 128, widths in multiples of 64). */
+int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count);
 const float *vx_decoder_logits(const vx_decoder *d);
 /* The CUDA stream (a CUstream) that the decoder's steps run on, for a host
    that wants to record events around them. */

@@ -1,5 +1,7 @@
 """Whole-token decoding on a B200 against the CPU oracle: identical greedy
 tokens."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -157,3 +159,29 @@ def test_nn_decoder_many_sequences(oracle, monkeypatch, batch, tensor_cores):
     for b in (0, batch // 2, batch - 1):
         want = oracle_generate(oracle, hm, list(prompts[b]), steps, max_seq)
         assert got[b] == want, "sequence %d: %s" % (b, report(got[b], want))
+
+
+def test_prefill_sixteen_positions_at_a_time(oracle):
+    """A 40-token prompt fed through vx_decoder_prefill (two passes of sixteen
+    positions as rows of the tensor-core projections, the rest single steps),
+    then greedy steps: the tokens are the oracle's, which feeds the prompt one
+    token at a time."""
+    max_seq, steps = 64, 10
+    dec, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=1, **WIDE_NN)
+    hm = nn_host_model(oracle, tensors, WIDE_NN, max_seq)
+    prompt = [int(t) for t in
+              np.random.default_rng(33).integers(0, WIDE_NN["vocab"], 40)]
+    arr = (C.c_int32 * 39)(*prompt[:-1])
+    from vx_b200.lib import lib
+    assert lib().vx_decoder_prefill(dec.handle, arr, 39) == 32
+    dec.reset()
+    tok = dec.prefill(prompt)
+    got = []
+    for _ in range(steps):
+        got.append(tok)
+        tok = dec.step(None)[0]
+    dec.close()
+    from vx_b200 import ops
+    assert ops.kernel_status() == 0
+    want = oracle_generate(oracle, hm, prompt, steps, max_seq)
+    assert got == want, report(got, want)

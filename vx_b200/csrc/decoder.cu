@@ -31,6 +31,7 @@
 
 namespace vxb {
 cudaStream_t caller_stream();
+void set_last_error(const char *why);
 void note_kernel(const char *name);
 vx::NcclCollective *nccl_job();
 } // namespace vxb
@@ -52,6 +53,16 @@ namespace {
     if (e_ != cudaSuccess)                                                     \
       stop("%s failed: %s", #expr, cudaGetErrorString(e_));                    \
   } while (0)
+
+/* pos[i] = first[0] + i: the positions of a run of prompt tokens. */
+__global__ void run_positions_kernel(int32_t *pos, const int32_t *first, int n) {
+  if ((int)threadIdx.x < n)
+    pos[threadIdx.x] = first[0] + threadIdx.x;
+}
+__global__ void advance_by_kernel(int32_t *pos, int by) {
+  if (threadIdx.x == 0)
+    pos[0] += by;
+}
 
 __global__ void advance_kernel(int32_t *positions, int batch) {
   if (threadIdx.x < batch)
@@ -119,6 +130,10 @@ struct vx_decoder {
   bool mma;
   void *mma_xs;
   float *mma_scratch;
+  /* a one-sequence decoder reading its prompt sixteen positions at a time:
+     the same tensor-core projections with the positions as rows */
+  float *rows_x, *rows_q, *rows_att, *rows_h;
+  int32_t *rows_tokens, *rows_pos;
   int64_t cache_layer_stride, cache_batch_stride;
   int split;
   int host_pos;
@@ -610,6 +625,8 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
     open_peer_buffers(d, rank);
     d->push = true;
   }
+  d->rows_x = d->rows_q = d->rows_att = d->rows_h = nullptr;
+  d->rows_tokens = d->rows_pos = nullptr;
   d->mma = false;
   d->mma_xs = nullptr;
   d->mma_scratch = nullptr;
@@ -655,7 +672,9 @@ void vx_decoder_destroy(vx_decoder *d) {
                   (void *)d->v_cache, (void *)d->scratch, (void *)d->counters,
                   (void *)d->tokens, (void *)d->positions,
                   (void *)d->local_best, (void *)d->pair,
-                  (void *)d->pairs_all, d->mma_xs, (void *)d->mma_scratch})
+                  (void *)d->pairs_all, d->mma_xs, (void *)d->mma_scratch,
+                  (void *)d->rows_x, (void *)d->rows_q, (void *)d->rows_att,
+                  (void *)d->rows_h, (void *)d->rows_tokens, (void *)d->rows_pos})
     cudaFree(p);
   cudaStreamDestroy(d->stream);
   delete d;
@@ -687,6 +706,128 @@ int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
       stop("a kernel of the decoder faulted: %s", cudaGetErrorString(e));
   }
   return pos;
+}
+
+/* A run of prompt tokens of a one-sequence decoder, sixteen positions per
+   pass: the projections see the positions as the rows of rowdot_umma.cu (the
+   multi-row kernels of nn.vx:2317-3066 are the reference's form of this), every
+   row writes its K and V into the one cache at its own position, and row i
+   attends positions 0 .. first + i, which are all in the cache by then. No
+   logits: the caller feeds the last prompt token through vx_decoder_step.
+   Returns the number of tokens taken (a multiple of 16, possibly 0: what is
+   left goes through vx_decoder_step), or -1 with vx_b200_last_error() when
+   this decoder cannot do it. */
+int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) {
+  const vx_decoder_config &c = d->c;
+  constexpr int R = 16;
+  if (c.batch != 1 || !c.weights_bf16 || d->ranks != 1 || c.head_dim != 128 ||
+      c.dim % 64 != 0 || d->hidden_local % 64 != 0) {
+    vxb::set_last_error("vx_decoder_prefill: needs one sequence, one rank, bf16 "
+                        "weights, head_dim 128 and widths in multiples of 64");
+    return -1;
+  }
+  if (count < 0 || d->host_pos + count > c.max_seq) {
+    vxb::set_last_error("vx_decoder_prefill: the prompt does not fit max_seq");
+    return -1;
+  }
+  if (!d->rows_x) {
+    int widest = c.dim > d->hidden_local ? c.dim : d->hidden_local;
+    if (d->q_local * c.head_dim > widest)
+      widest = d->q_local * c.head_dim;
+    int rows_max = 2 * d->hidden_local;
+    if ((d->q_local + 2 * d->kv_local) * c.head_dim > rows_max)
+      rows_max = (d->q_local + 2 * d->kv_local) * c.head_dim;
+    d->rows_x = dev_alloc<float>((size_t)R * c.dim);
+    d->rows_q = dev_alloc<float>((size_t)R * d->q_local * c.head_dim);
+    d->rows_att = dev_alloc<float>((size_t)R * d->q_local * c.head_dim);
+    d->rows_h = dev_alloc<float>((size_t)R * d->hidden_local);
+    d->rows_tokens = dev_alloc<int32_t>(R);
+    d->rows_pos = dev_alloc<int32_t>(R);
+    if (!d->mma_xs) {
+      d->mma_xs = dev_alloc<uint16_t>((size_t)48 * widest);
+      d->mma_scratch = dev_alloc<float>(vxb::batched_proj_scratch_floats(rows_max, R));
+    }
+  }
+  cudaStream_t s = d->stream;
+  const int hd = c.head_dim;
+  int taken = 0;
+  while (count - taken >= R) {
+    CUDA_OK(cudaMemcpyAsync(d->rows_tokens, tokens + taken, R * sizeof(int32_t),
+                            cudaMemcpyHostToDevice, s));
+    run_positions_kernel<<<1, 32, 0, s>>>(d->rows_pos, d->positions, R);
+    need(vxb::embed(d->rows_x, d->embed, true, d->rows_tokens, c.dim, c.vocab, R,
+                    c.dim, s),
+         "embed");
+    auto proj = [&](int mode, const void *w0, const void *w1, const void *w2,
+                    int rows, int cols, const float *x, const void *norm_w,
+                    float *y, int64_t y_stride, const void *bias, int layer,
+                    const char *what, bool terms_ready, bool leave_terms) {
+      vxb::BatchedProj bp{};
+      bp.mode = mode;
+      bp.w0 = w0;
+      bp.w1 = w1;
+      bp.w2 = w2;
+      bp.rows = rows;
+      bp.cols = cols;
+      bp.batch = R;
+      bp.x = x;
+      bp.x_stride = cols;
+      bp.norm_w = norm_w;
+      bp.eps = c.eps;
+      bp.y = y;
+      bp.y_stride = y_stride;
+      bp.bias = bias;
+      bp.q_heads = d->q_local;
+      bp.kv_heads = d->kv_local;
+      bp.head_dim = hd;
+      bp.cos_t = d->cos_t;
+      bp.sin_t = d->sin_t;
+      bp.positions = d->rows_pos;
+      bp.k_cache = d->k_cache + layer * d->cache_layer_stride;
+      bp.v_cache = d->v_cache + layer * d->cache_layer_stride;
+      bp.cache_batch_stride = 0; /* every row writes into the one cache */
+      bp.xs = d->mma_xs;
+      bp.scratch = d->mma_scratch;
+      bp.x_terms_ready = terms_ready;
+      bp.next_terms = leave_terms;
+      need(vxb::batched_proj(bp, s), what);
+    };
+    for (int l = 0; l < c.n_layers; ++l) {
+      proj(4, d->wq[l], d->wk[l], d->wv[l], (d->q_local + 2 * d->kv_local) * hd,
+           c.dim, d->rows_x, d->attn_norm[l], d->rows_q, (int64_t)d->q_local * hd,
+           d->bqkv[l], l, "q/k/v", false, false);
+      vxb::AttnArgs aa{};
+      aa.q = d->rows_q;
+      aa.k_cache = d->k_cache + l * d->cache_layer_stride;
+      aa.v_cache = d->v_cache + l * d->cache_layer_stride;
+      aa.cache_batch_stride = 0;
+      aa.out = d->rows_att;
+      aa.q_heads = d->q_local;
+      aa.kv_heads = d->kv_local;
+      aa.head_dim = hd;
+      aa.batch = R;
+      aa.positions = d->rows_pos;
+      aa.max_pos = d->host_pos + taken + R - 1;
+      aa.fresh_from = d->positions; /* this pass's rows are new */
+      aa.scratch = nullptr; /* the cluster form needs none */
+      aa.counters = nullptr;
+      aa.split = d->split;
+      need(vxb::attention_decode_clustered(aa, s), "attention");
+      proj(1, d->wo[l], nullptr, nullptr, c.dim, d->q_local * hd, d->rows_att,
+           nullptr, d->rows_x, c.dim, nullptr, l, "the output projection", false,
+           false);
+      proj(3, d->w_gate[l], d->w_up[l], nullptr, d->hidden_local, c.dim, d->rows_x,
+           d->ffn_norm[l], d->rows_h, d->hidden_local, nullptr, l, "gate/up", false,
+           true);
+      proj(1, d->w_down[l], nullptr, nullptr, c.dim, d->hidden_local, d->rows_h,
+           nullptr, d->rows_x, c.dim, nullptr, l, "the down projection", true,
+           false);
+    }
+    advance_by_kernel<<<1, 32, 0, s>>>(d->positions, R);
+    taken += R;
+  }
+  d->host_pos += taken;
+  return taken;
 }
 
 const float *vx_decoder_logits(const vx_decoder *d) { return d->logits; }

@@ -176,10 +176,18 @@ struct AttnArgs {
   float *scratch;
   int32_t *counters;
   int split; /* positions per block */
+  /* device, or NULL: rows from fresh_from[0] on were written by the kernel
+     just before (a run of prompt positions sharing one cache); NULL: only row
+     `position` of each sequence was */
+  const int32_t *fresh_from;
 };
 size_t attn_scratch_floats(int batch, int q_heads, int head_dim, int max_seq,
                            int split);
 const char *attention_decode(const AttnArgs &a, cudaStream_t stream);
+/* The form that merges the parts of a head inside a cluster: needs neither
+   scratch nor counters, and the sequences may share one cache
+   (cache_batch_stride 0, as for a run of prompt positions). */
+const char *attention_decode_clustered(const AttnArgs &a, cudaStream_t stream);
 
 /* ---- the projections for 8 or 16 sequences, on the tensor cores -------------
  * y = W x with bf16 W [rows, cols] and f32 x [batch][cols] taken as three bf16

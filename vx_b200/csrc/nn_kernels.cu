@@ -798,6 +798,9 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
   const float *vc = a.v_cache + b * a.cache_batch_stride;
   const float *qb = a.q + (int64_t)b * a.q_heads * hd;
 
+  /* Cache rows below `settled` were written by earlier steps and may be read
+     before the kernels of this step have finished; the rest only after. */
+  const int settled = a.fresh_from ? min(pos, a.fresh_from[0]) : pos;
   /* A warp takes every fourth position, NB of them at a time so that their
      loads are in flight together: with 32 positions per block that is one
      round trip to memory per warp. */
@@ -808,8 +811,8 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
     for (int j = 0; j < NB; ++j) {
       const int t = t0 + j * ATT_WARPS;
       const bool take = active && t < t_end &&
-                        (old_rows_only ? t < pos
-                                       : t == pos || t0 != t_begin + warp || !CHAINED);
+                        (old_rows_only ? t < settled
+                                       : t >= settled || t0 != t_begin + warp || !CHAINED);
       if (take) {
         const int64_t row = ((int64_t)t * a.kv_heads + g) * hd + lane * 4;
         kv[j] = *reinterpret_cast<const float4 *>(kc + row);
@@ -1330,7 +1333,7 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
     const char *e = getenv("VXB_ATTN_CLUSTER");
     return !(e && e[0] == '0');
   }();
-  if (clustered) {
+  if (clustered || !a.scratch) {
     const dim3 cgrid(ATT_CLUSTER, a.kv_heads * tiles, a.batch);
     const dim3 block(ATT_WARPS * 32);
     if (gh == 4)
@@ -1355,6 +1358,13 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
     launch_chained(attention_decode_kernel<1>, grid, dim3(ATT_WARPS * 32), 0,
                    stream, a);
   return check_launch("the attention launch");
+}
+
+const char *attention_decode_clustered(const AttnArgs &a, cudaStream_t stream) {
+  AttnArgs b = a;
+  b.scratch = nullptr;
+  b.counters = nullptr;
+  return attention_decode(b, stream);
 }
 
 const char *argmax(int32_t *out, const float *logits, int n, int batch,

@@ -33,7 +33,8 @@ EXTRA_SYMBOLS = [
     "vx_nn_swiglu", "vx_nn_rms_norm", "vx_nn_rope_and_store",
     "vx_nn_attention", "vx_nn_argmax", "vx_nn_embed",
     "vx_decoder_create", "vx_decoder_destroy", "vx_decoder_reset",
-    "vx_decoder_step", "vx_decoder_logits", "vx_decoder_kernels_per_step",
+    "vx_decoder_step", "vx_decoder_prefill", "vx_decoder_logits",
+    "vx_decoder_kernels_per_step",
     "vx_decoder_stream",
     "vx_b200_last_error", "vx_b200_gemm", "vx_b200_kernel_status",
     "vx_b200_flash_attention", "vx_b200_gemm_column_split",
@@ -113,6 +114,8 @@ def lib():
     L.vx_decoder_reset.argtypes = [vp]
     L.vx_decoder_step.restype = i32
     L.vx_decoder_step.argtypes = [vp, vp, vp]
+    L.vx_decoder_prefill.restype = i32
+    L.vx_decoder_prefill.argtypes = [vp, vp, i32]
     L.vx_decoder_logits.restype = vp
     L.vx_decoder_logits.argtypes = [vp]
     L.vx_decoder_kernels_per_step.restype = i32

@@ -58,6 +58,22 @@ class Decoder:
                               C.addressof(self._out) if fetch else None)
         return [self._out[i] for i in range(self.cfg.batch)] if fetch else None
 
+    def prefill(self, tokens):
+        """Feed a prompt (one sequence): sixteen positions per pass where the
+        decoder can, single steps for the rest. Returns the argmax after the
+        last prompt token."""
+        tokens = [int(t) for t in tokens]
+        head = tokens[:-1]
+        taken = 0
+        if len(head) >= 16:
+            arr = (C.c_int32 * len(head))(*head)
+            taken = lib().vx_decoder_prefill(self.handle, arr, len(head))
+            if taken < 0:
+                taken = 0
+        for t in head[taken:]:
+            self.step([t], fetch=False)
+        return self.step([tokens[-1]])[0]
+
     def logits(self):
         """[batch, local vocab] f32 from the last step."""
         n = self.cfg.batch * (self.cfg.vocab // max(self.cfg.tp_ranks, 1))
