@@ -376,6 +376,26 @@ def run_ours(args):
     e2e_ms = event_ms(torch, stream, e2e_steps)
     barrier()
 
+    # -- the prompt itself: one decode step per token, and sixteen positions per
+    #    pass (vx_decoder_prefill); one GPU only
+    prefill = None
+    if not multi and not args.no_extras:
+        def timed_prompt(fn):
+            dec.reset()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            tok = fn()
+            torch.cuda.synchronize()
+            return (time.perf_counter() - t0) * 1e3, tok
+        step_ms, tok_a = timed_prompt(run_prompt)
+        rows_ms, tok_b = timed_prompt(lambda: dec.prefill(prompt))
+        prefill = dict(prompt_tokens=PROMPT, one_step_per_token_ms=step_ms,
+                       sixteen_positions_per_pass_ms=rows_ms,
+                       tokens_per_s=PROMPT / (rows_ms / 1e3),
+                       same_next_token=bool(tok_a == tok_b),
+                       timing="host clock around the whole prompt, "
+                              "synchronised on both sides")
+
     times = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
     if multi:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -405,6 +425,8 @@ def run_ours(args):
                 frac=step_gbs / peaks["hbm_gbs"], peak_source=peaks["source"]))
         if not multi:
             line["roofline"] = bench_dominant_kernel(torch, tensors, peaks, shape)
+        if prefill:
+            line["prefill"] = prefill
     dec.close()
     del tensors
     torch.cuda.empty_cache()
