@@ -12,10 +12,15 @@
  * a graph is recorded per block of 256 positions.
  *
  * Tensor parallel (tp_ranks > 1): every rank holds a slice of the heads and of
- * the MLP rows; the output and down projections produce partial sums that the
- * job of vx_collective_init adds (an all-reduce inside the graph), and the
- * logits are split by vocabulary with an exchange of each rank's best
- * (value, index).
+ * the MLP rows; the output and down projections produce partial sums that meet
+ * either in an NCCL all-reduce inside the graph (tp_reduce 0) or as (value,
+ * call) pairs that the projection kernel stores into every rank's memory and
+ * the next projection adds in its prologue (tp_reduce 1); the logits are split
+ * by vocabulary with an exchange of each rank's best (value, index).
+ *
+ * 8 or 16 sequences per step (head_dim 128): the projections go to the tensor
+ * cores (rowdot_umma.cu).  vx_decoder_prefill uses the same kernels to read a
+ * one-sequence prompt sixteen positions per pass.
  */
 #include "kernels.h"
 #include "vx_b200.h"

@@ -11,7 +11,8 @@
  * what follows a projection into it: RMSNorm in front of the q/k/v and the
  * gate/up projections, bias + RoPE + KV-cache store behind q/k/v, SwiGLU
  * behind gate/up, the residual add behind the output and down projections, and
- * the merge of the split-KV attention parts into the attention kernel itself.
+ * the merge of the attention parts into the attention kernel itself (inside a
+ * thread-block cluster, through distributed shared memory).
  *
  * No float atomics and a fixed order in every reduction: the same inputs give
  * the same bits on every run.
