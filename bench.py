@@ -278,7 +278,7 @@ def bench_dominant_kernel(torch, tensors, peaks, shape, iters=3):
                 launches_timed=launches,
                 # dram__bytes_read.sum of one launch under ncu (180 405 248 B) plus the
                 # 44 KB it writes; the profiler's own save/restore writes are left out
-                # (profiles/rowdot_swiglu_llama7b.md)
+                # (the capture is summarised under profiles/)
                 traffic=180405248 + 4 * shape["hidden"],
                 traffic_source="ncu capture of this kernel on 4 of these matrices")
 
