@@ -228,8 +228,11 @@ constexpr int RING_BYTES = WARPS * RING_STAGES * 2 * CHUNK_BYTES;
 __device__ int g_rowdot_status; /* non-zero: a ring wait gave up */
 __device__ int g_tp_status;     /* non-zero: a peer's flag never arrived */
 
+/* 96 registers for one sequence: 512 threads then leave a quarter of the
+   register file, so that the blocks of the attention kernel that follows
+   q/k/v can start (and fetch their old cache rows) beside these. */
 template <typename W, int B, int EPI>
-__global__ void __launch_bounds__(WARPS * 32, 1)
+__global__ void __maxnreg__(B == 1 ? 96 : 128)
 rowdot_kernel(const RowDotParams p) {
   extern __shared__ __align__(128) unsigned char smem_dyn[];
   unsigned char *ring = smem_dyn;                    /* [warp][stage][2][chunk] */
