@@ -97,9 +97,11 @@ struct TpGather {
   float *x_out;
 };
 /* The same sum as a kernel of its own: x[i] += the ranks' partials in rank
-   order; then epoch += 1. One block. */
+   order, one value per thread; the block that finishes last (counted in
+   `done`, zero between launches) advances epoch. */
 const char *tp_reduce_add(float *x, const TpPair *my_slots, int32_t *epoch,
-                          int ranks, int64_t count, cudaStream_t stream);
+                          int32_t *done, int ranks, int64_t count,
+                          cudaStream_t stream);
 int tp_status(cudaStream_t stream);
 const char *matvec(const MatvecArgs &a, cudaStream_t stream);
 

@@ -712,26 +712,41 @@ const char *launch_rowdot(RowDotParams &p, bool wbf16, cudaStream_t stream) {
  * each pair waited for (bounded) until it carries this call's number -- every
  * rank adds the same values in the same order, so x stays identical on all
  * ranks. */
-__global__ void __launch_bounds__(1024)
-tp_reduce_add_kernel(float *x, const TpPair *slots, int32_t *epoch, int ranks,
-                     int64_t count) {
+__global__ void __launch_bounds__(256)
+tp_reduce_add_kernel(float *x, const TpPair *slots, int32_t *epoch, int32_t *done,
+                     int ranks, int64_t count) {
   chain_release();
   chain_wait();
   const int call = *epoch + 1;
   const TpPair *mine = slots + (int64_t)(call & 1) * ranks * count;
-  for (int64_t i = threadIdx.x; i < count; i += blockDim.x) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) {
+    /* one value per thread, every rank's pair asked for at once */
+    float part[kMaxTpRanks];
+    bool in[kMaxTpRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxTpRanks; ++r)
+      in[r] = r >= ranks || pair_load(mine + r * count + i, call, part[r]);
     float v = x[i];
-    for (int r = 0; r < ranks; ++r) {
-      float part;
-      if (!pair_load(mine + r * count + i, call, part))
-        part = pair_wait(mine + r * count + i, call, &g_tp_status);
-      v += part;
-    }
+#pragma unroll
+    for (int r = 0; r < kMaxTpRanks; ++r)
+      if (r < ranks) {
+        if (!in[r])
+          part[r] = pair_wait(mine + r * count + i, call, &g_tp_status);
+        v += part[r];
+      }
     x[i] = v;
   }
+  /* the block that finishes last advances the call count: every block has
+     read it by then */
   __syncthreads();
-  if (threadIdx.x == 0)
-    *epoch = call;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done, 1) == (int)gridDim.x - 1) {
+      *done = 0;
+      *epoch = call;
+    }
+  }
 }
 
 /* ------------------------------------------------------------- rms_norm
@@ -1304,11 +1319,12 @@ const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream) {
 }
 
 const char *tp_reduce_add(float *x, const TpPair *my_slots, int32_t *epoch,
-                          int ranks, int64_t count, cudaStream_t stream) {
+                          int32_t *done, int ranks, int64_t count,
+                          cudaStream_t stream) {
   if (ranks < 1 || ranks > kMaxTpRanks)
     return "1 to 8 ranks";
-  launch_chained(tp_reduce_add_kernel, dim3(1), dim3(1024), 0, stream, x,
-                 my_slots, epoch, ranks, count);
+  launch_chained(tp_reduce_add_kernel, dim3((unsigned)((count + 255) / 256)),
+                 dim3(256), 0, stream, x, my_slots, epoch, done, ranks, count);
   return check_launch("the partial-sum launch");
 }
 
