@@ -100,11 +100,8 @@ typedef struct {
      0 = an NCCL all-reduce after the projection kernel; 1 = the projection
      kernel itself stores its results into every rank's receive buffer over
      NVLink (peer memory mapped through CUDA IPC) as (value, call number)
-     pairs that are their own arrival flags; the next projection (the
-     one with the RMSNorm in front) waits for every rank's flag and adds the
-     partials in its own prologue, in rank order. Where that projection cannot
-     take the norm (batch too large for its shared memory) a small kernel of
-     its own adds them instead. */
+     pairs that are their own arrival flags, and a small kernel adds them to
+     the residual in rank order (the same order on every rank). */
   int32_t tp_reduce;
 } vx_decoder_config;
 
