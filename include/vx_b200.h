@@ -145,7 +145,6 @@ void vx_decoder_reset(vx_decoder *d);
    the call then waits for the GPU. Returns the position the step ran at. */
 int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
                         int32_t *tokens_out);
-/* The logits of the last step: device memory, [batch, vocab] f32. */
 /* A run of prompt tokens of a one-sequence decoder, sixteen positions per
    pass through the layers (the reference's multi-row kernels, nn.vx:2317-3066:
    its llama programs feed a prompt one decode step at a time). Fills the KV
@@ -155,6 +154,7 @@ int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
    vx_b200_last_error() for a decoder that cannot (needs batch 1, one rank,
    bf16 weights, head_dim 128, widths in multiples of 64). */
 int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count);
+/* The logits of the last step: device memory, [batch, vocab] f32. */
 const float *vx_decoder_logits(const vx_decoder *d);
 /* The CUDA stream (a CUstream) that the decoder's steps run on, for a host
    that wants to record events around them. */
@@ -182,18 +182,29 @@ int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,
                                 void *out, int32_t B, int32_t H, int32_t S,
                                 int32_t D, float scale, int32_t causal);
 
+/* Which kernel vx_nn_attention and the decoder's attention run from now on:
+   1 = the parts of a head merged inside a thread-block cluster (no scratch
+   used; the default), 2 = the reference's scheme (nn.vx:343-368, 823-866):
+   one block per 32 or 64 positions, partial results in `part`, merged by the
+   block that finishes last; 0 = back to the default. Returns the choice
+   before. A decoder takes the choice when it records a token graph. This
+   entry point has no counterpart in the reference (which has one kernel). */
+int32_t vx_b200_attention_kernel(int32_t which);
+
 /* Decode attention with no allocation of any kind, for hosts that cannot call
    cudaMalloc: processes that handed all device memory to their own pool at
    start-up, and loops that cannot take the device-wide wait an allocation
    implies. The computation of vx_nn_attention on plain device pointers (q, out
-   [q_heads, head_dim]; caches [max_seq, kv_heads, head_dim]; f32); its scratch
-   is a fixed array inside the library image (2 MiB + 4 KiB per GPU, held until
-   the process exits). Limit: q_heads <= 256 and
+   [q_heads, head_dim]; caches [max_seq, kv_heads, head_dim]; f32), always by
+   the split kernel, whose partial results and counters live in a fixed array
+   inside the library image (68 KiB + 2 MiB per GPU, held until the process
+   exits). Limit: pos < 16384, q_heads <= 256 and
    q_heads * (pos / n + 1) * (head_dim + 2) <= 2^19 with n = 32 below position
    640, else 64; beyond it: -1 and a message. All calls on a GPU share the
    array, so calls that overlap on the GPU race: keep them in stream order. The
-   first call on a GPU sets the array up and should come before any stream
-   capture. This entry point has no counterpart in the reference. */
+   first call on a GPU looks up the array's address and fills it in, and should
+   come before any stream capture. This entry point has no counterpart in the
+   reference. */
 int32_t vx_b200_attention_decode_static(float *out, const float *q,
                                         const float *k_cache,
                                         const float *v_cache, int32_t pos,

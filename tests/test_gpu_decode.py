@@ -128,6 +128,32 @@ def test_nn_decoder_tokens_match_oracle(oracle, batch):
         assert got[b] == want, "sequence %d: %s" % (b, report(got[b], want))
 
 
+def test_nn_decoder_with_the_split_attention_kernel(oracle):
+    """The decoder recorded while the split kernel is chosen: the partial
+    results go through the decoder's scratch and counters instead of a
+    cluster's shared memory, and the tokens are still the oracle's."""
+    from vx_b200.lib import lib
+    max_seq, steps = 96, 16
+    before = lib().vx_b200_attention_kernel(2)
+    try:
+        dec, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=2, **SMALL_NN)
+        hm = nn_host_model(oracle, tensors, SMALL_NN, max_seq)
+        prompts = np.random.default_rng(9).integers(0, SMALL_NN["vocab"], (2, 40))
+        got = [[], []]
+        for p in range(prompts.shape[1]):
+            toks = dec.step(list(prompts[:, p]))
+        for _ in range(steps):
+            for b in range(2):
+                got[b].append(toks[b])
+            toks = dec.step(None)
+        dec.close()
+    finally:
+        lib().vx_b200_attention_kernel(before)
+    for b in range(2):
+        want = oracle_generate(oracle, hm, list(prompts[b]), steps, max_seq)
+        assert got[b] == want, "sequence %d: %s" % (b, report(got[b], want))
+
+
 WIDE_NN = dict(dim=2048, hidden=2816, n_layers=2, q_heads=16, kv_heads=4,
                head_dim=128, vocab=2048)
 

@@ -119,18 +119,60 @@ ATTENTION_CASES = [  # q_heads, kv_heads, head_dim, pos, max_seq
     (32, 2, 64, 655, 704), (32, 32, 128, 639, 640), (6, 6, 96, 31, 32)]
 
 
+@pytest.fixture(params=[1, 2], ids=["cluster", "split"])
+def attention_kernel(request):
+    """Both attention kernels: the cluster merge (the default) and the
+    reference's split scheme with partial results in `part` and a counter per
+    head tile (nn.vx:343-368, 823-866)."""
+    from vx_b200.lib import lib
+    before = lib().vx_b200_attention_kernel(request.param)
+    yield request.param
+    lib().vx_b200_attention_kernel(before)
+
+
 @pytest.mark.parametrize("qh,kvh,hd,pos,max_seq", ATTENTION_CASES)
-def test_attention(oracle, qh, kvh, hd, pos, max_seq):
+def test_attention(oracle, attention_kernel, qh, kvh, hd, pos, max_seq):
     q = oracle.random_f32(qh * hd, 61, 2.0).reshape(qh, hd)
     kc = oracle.random_f32(max_seq * kvh * hd, 62, 2.0).reshape(max_seq, kvh, hd)
     vc = oracle.random_f32(max_seq * kvh * hd, 63, 1.0).reshape(max_seq, kvh, hd)
     shape = ops.nn_attention_scratch_shape(max_seq, qh, kvh, hd)
     part = dev(np.full(shape, np.nan, np.float32))   # scratch content is free
     out = abi.DeviceTensor.empty((qh, hd), abi.F32)
-    for _ in range(2):                                # twice: the counters reset
-        ops.nn_attention(out, part, dev(q), dev(kc), dev(vc), pos, qh, kvh, hd)
-    close(out.to_host(), oracle.attention_f64(q, kc, vc, pos))
+    tq, tk, tv = dev(q), dev(kc), dev(vc)
+    # twice at this position and once at an earlier one in between: the split
+    # kernel's counters must be back at zero after every launch, whatever the
+    # number of parts was
+    for p in (pos, pos // 3, pos):
+        ops.nn_attention(out, part, tq, tk, tv, p, qh, kvh, hd)
+        close(out.to_host(), oracle.attention_f64(q, kc, vc, p))
     close(out.to_host(), oracle.nn_attention(q, kc, vc, pos), 2e-5)
+
+
+def test_attention_after_a_run_of_cache_writes(oracle, attention_kernel):
+    """The cache filled by back-to-back nn_rope_and_store calls (short kernels
+    that each let their successor start early) and attended at once: every row
+    must be the written one."""
+    qh, kvh, hd, max_seq = 8, 2, 64, 48
+    cos, sin = oracle.rope_tables(max_seq, hd, 10000.0)
+    kc = np.zeros((max_seq, kvh, hd), np.float32)
+    vc = np.zeros_like(kc)
+    tkc, tvc = dev(np.full_like(kc, np.nan)), dev(np.full_like(vc, np.nan))
+    tcos, tsin = dev(cos), dev(sin)
+    tq = abi.DeviceTensor.empty((qh, hd), abi.F32)
+    part = abi.DeviceTensor.empty(
+        ops.nn_attention_scratch_shape(max_seq, qh, kvh, hd), abi.F32)
+    out = abi.DeviceTensor.empty((qh, hd), abi.F32)
+    steps = []
+    for pos in range(40):
+        q = oracle.random_f32(qh * hd, 500 + pos, 1.0).reshape(qh, hd)
+        k = oracle.random_f32(kvh * hd, 600 + pos, 1.0).reshape(kvh, hd)
+        v = oracle.random_f32(kvh * hd, 700 + pos, 1.0).reshape(kvh, hd)
+        steps.append((dev(q), dev(k), dev(v)))
+        want_q = oracle.nn_rope_and_store(kc, vc, q, k, v, cos, sin, pos)
+    for pos, (dq, dk, dv) in enumerate(steps):
+        ops.nn_rope_and_store(tq, tkc, tvc, dq, dk, dv, tcos, tsin, pos, qh, kvh, hd)
+    ops.nn_attention(out, part, tq, tkc, tvc, 39, qh, kvh, hd)
+    close(out.to_host(), oracle.attention_f64(want_q, kc, vc, 39))
 
 
 def test_argmax_known_answer(oracle):

@@ -353,6 +353,7 @@ void record_step(vx_decoder *d, int max_pos) {
       ab.scratch = d->scratch;
       ab.counters = d->counters;
       ab.split = d->split;
+      ab.rows_settled = 1; /* earlier tokens are earlier graph launches */
       need(vxb::attention_decode(ab, s), "attention");
       ++launches;
       batched(1, d->wo[l], nullptr, nullptr, c.dim, d->q_local * hd, d->att,
@@ -411,6 +412,7 @@ void record_step(vx_decoder *d, int max_pos) {
     aa.scratch = d->scratch;
     aa.counters = d->counters;
     aa.split = d->split;
+    aa.rows_settled = 1; /* earlier tokens are earlier graph launches */
     need(vxb::attention_decode(aa, s), "attention");
 
     vxb::MatvecArgs oa{};
@@ -821,6 +823,7 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
       aa.scratch = nullptr; /* the cluster form needs none */
       aa.counters = nullptr;
       aa.split = d->split;
+      aa.rows_settled = 1; /* rows below fresh_from: earlier passes and steps */
       need(vxb::attention_decode_clustered(aa, s), "attention");
       proj(1, d->wo[l], nullptr, nullptr, c.dim, d->q_local * hd, d->rows_att,
            nullptr, d->rows_x, c.dim, nullptr, l, "the output projection", false,

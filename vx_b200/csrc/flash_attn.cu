@@ -28,6 +28,7 @@
  * most of the softmax time, and K/V tiles are read once for 256 query rows.
  */
 #include "kernels.h"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 #include <cuda_bf16.h>
@@ -427,14 +428,8 @@ template <int NQ>
 const char *launch_flash(const CUtensorMap &mq, const CUtensorMap &mk,
                          const CUtensorMap &mv, void *out, int B, int H, int S,
                          float scale, bool causal, cudaStream_t stream) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(flash_fwd_kernel<NQ>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    flash_smem_bytes<NQ>());
-  });
-  if (attr_err != cudaSuccess)
+  if (allow_dynamic_smem((const void *)flash_fwd_kernel<NQ>,
+                         flash_smem_bytes<NQ>()) != cudaSuccess)
     return "flash attention could not get its shared memory";
   const dim3 grid(S / (BQ * NQ), B * H);
   flash_fwd_kernel<NQ><<<grid, 64 + NQ * 256, flash_smem_bytes<NQ>(), stream>>>(

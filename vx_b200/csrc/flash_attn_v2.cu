@@ -19,6 +19,7 @@
  * other's products.
  */
 #include "kernels.h"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 #include <cuda_bf16.h>
@@ -523,13 +524,7 @@ const char *flash_attention_fwd_v2(const void *q, const void *k, const void *v,
       !make_map_16(&mk, k, HD, rows, HD, 64, BKV, true) ||
       !make_map_16(&mv, v, HD, rows, HD, 64, BKV, true))
     return "cuTensorMapEncodeTiled refused q, k or v";
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(
-        flash2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  });
-  if (attr_err != cudaSuccess)
+  if (allow_dynamic_smem((const void *)flash2_kernel, SMEM_BYTES) != cudaSuccess)
     return "flash attention could not get its shared memory";
   const dim3 grid(S / (BQ * NQ), B * H);
   flash2_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(

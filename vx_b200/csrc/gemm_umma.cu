@@ -28,6 +28,7 @@
  * row strides are multiples of 8 elements.
  */
 #include "kernels.h"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 #include <cuda_bf16.h>
@@ -334,14 +335,8 @@ int sm_count() {
 template <typename T, bool kBNMajor>
 const char *launch_umma(const CUtensorMap &ma, const CUtensorMap &mb, void *c,
                         int64_t ldc, int m, int n, int k, cudaStream_t stream) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(umma_gemm_kernel<T, kBNMajor>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_BYTES);
-  });
-  if (attr_err != cudaSuccess)
+  if (allow_dynamic_smem((const void *)umma_gemm_kernel<T, kBNMajor>,
+                         SMEM_BYTES) != cudaSuccess)
     return "the tcgen05 GEMM could not get its shared memory";
   const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();

@@ -163,10 +163,21 @@ const char *rope_and_store(float *q_out, float *k_cache, float *v_cache,
                            int pos, int q_heads, int kv_heads, int head_dim,
                            cudaStream_t stream);
 
-/* Split-KV attention of one new token per sequence over rows 0..pos of the
-   cache, with the merge done by the last block of each head.
-   scratch: f32 [batch][q_heads][splits][head_dim + 2] plus int32 counters
-   [batch][q_heads] that are zero before the launch and zero after it. */
+/* Attention of one new token per sequence over rows 0..pos of its KV cache
+   (nn_attention with its parts and merge, stdlib/std/nn.vx:343-368, 823-866).
+   The positions are cut into runs, each run gives a partial (max, sum,
+   weighted V) per head, and the partials are merged in run order. Two kernels
+   do the same arithmetic and differ in where the partials meet:
+     kAttnCluster  a cluster of 8 blocks per head tile, merged through
+                   distributed shared memory; needs no scratch, and sequences
+                   may share one cache (cache_batch_stride 0);
+     kAttnSplit    one block per `split` positions (the reference's 32 below
+                   position 640 and 64 from there on, or what the caller
+                   says), partials in `scratch`, merged by whichever block of
+                   a head tile finishes last, counted in `counters`.
+   scratch: f32 [batch][q_heads][max_pos / split + 1][head_dim + 2];
+   counters: int32 [batch][head tiles], zero before the launch, zero after. */
+enum { kAttnAuto = 0, kAttnCluster = 1, kAttnSplit = 2 };
 struct AttnArgs {
   const float *q; /* [batch][q_heads*hd] */
   const float *k_cache, *v_cache;
@@ -177,18 +188,27 @@ struct AttnArgs {
   int max_pos;              /* host bound on positions: sizes the grid */
   float *scratch;
   int32_t *counters;
-  int split; /* positions per block */
+  int split; /* positions per block (kAttnSplit) */
   /* device, or NULL: rows from fresh_from[0] on were written by the kernel
      just before (a run of prompt positions sharing one cache); NULL: only row
      `position` of each sequence was */
   const int32_t *fresh_from;
+  int kernel; /* kAttnAuto: the process-wide choice, which starts as cluster */
+  /* 1: the caller vouches that every cache row below the position was written
+     before the chain of dependent launches this kernel is part of began (a
+     decoder: earlier tokens are earlier graph launches), so those rows may be
+     fetched before the wait for the kernel in front. 0: everything is read
+     after that wait (the stand-alone operator: the rows may come from a run
+     of short kernels launched just before, each of which lets its successor
+     start early). */
+  int rows_settled;
 };
 size_t attn_scratch_floats(int batch, int q_heads, int head_dim, int max_seq,
                            int split);
 const char *attention_decode(const AttnArgs &a, cudaStream_t stream);
-/* The form that merges the parts of a head inside a cluster: needs neither
-   scratch nor counters, and the sequences may share one cache
-   (cache_batch_stride 0, as for a run of prompt positions). */
+/* The process-wide choice that kAttnAuto stands for; returns the one before. */
+int attention_kernel_choice(int which);
+/* Shorthand for kernel = kAttnCluster with no scratch. */
 const char *attention_decode_clustered(const AttnArgs &a, cudaStream_t stream);
 
 /* ---- the projections for 8 or 16 sequences, on the tensor cores -------------

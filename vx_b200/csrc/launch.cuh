@@ -19,6 +19,8 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <utility>
 
 namespace vxb {
@@ -31,6 +33,29 @@ __device__ __forceinline__ void chain_wait() {
 /* The next kernel of the chain may start its independent part. */
 __device__ __forceinline__ void chain_release() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+/* A kernel that wants more than 48 KiB of dynamic shared memory has to opt in,
+   and the opt-in belongs to the (kernel, device) pair: a process that places
+   regions on several GPUs (spawn on(Topology::GPU[i]) switches the current
+   device) needs it on each of them. Asked once per pair, for the current
+   device; the answer of that one call is what every later call returns. */
+inline cudaError_t allow_dynamic_smem(const void *kernel, int bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void *, int>, cudaError_t> asked;
+  int dev = 0;
+  const cudaError_t which = cudaGetDevice(&dev);
+  if (which != cudaSuccess)
+    return which;
+  std::lock_guard<std::mutex> lock(mu);
+  const auto key = std::make_pair(kernel, dev);
+  const auto hit = asked.find(key);
+  if (hit != asked.end())
+    return hit->second;
+  const cudaError_t e = cudaFuncSetAttribute(
+      kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  asked[key] = e;
+  return e;
 }
 
 inline bool chain_enabled() {

@@ -424,6 +424,10 @@ int32_t vx_b200_kernel_status(void) {
   return g ? g : (f ? f : (t ? t : m));
 }
 
+int32_t vx_b200_attention_kernel(int32_t which) {
+  return vxb::attention_kernel_choice(which);
+}
+
 int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,
                                 void *out, int32_t B, int32_t H, int32_t S,
                                 int32_t D, float scale, int32_t causal) {

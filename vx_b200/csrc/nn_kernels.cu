@@ -664,12 +664,9 @@ const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
     return "a fused RMSNorm needs the activations of all sequences to fit in "
            "96 KiB of shared memory";
   const size_t smem = RING_BYTES + (p.x_in_smem ? xbytes : 0);
-  static std::once_flag once;
-  std::call_once(once, [] {
-    cudaFuncSetAttribute(rowdot_kernel<W, B, EPI>,
-                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         RING_BYTES + MAX_SMEM_X);
-  });
+  if (allow_dynamic_smem((const void *)rowdot_kernel<W, B, EPI>,
+                         RING_BYTES + MAX_SMEM_X) != cudaSuccess)
+    return "a projection could not get its shared memory on this GPU";
   /* One block of 16 warps per SM with a 128 KiB ring (measured faster than
      two blocks of 8 warps with 64 KiB each: 31.7 vs 34.3 us on the 7B gate/up
      projection). Fewer blocks when there are fewer items than warps. */
@@ -858,7 +855,9 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
 
   /* Cache rows below `settled` were written by earlier steps and may be read
      before the kernels of this step have finished; the rest only after. */
-  const int settled = a.fresh_from ? min(pos, a.fresh_from[0]) : pos;
+  const int settled = !a.rows_settled ? 0
+                      : a.fresh_from  ? min(pos, a.fresh_from[0])
+                                      : pos;
   /* A warp takes every fourth position, NB of them at a time so that their
      loads are in flight together: with 32 positions per block that is one
      round trip to memory per warp. */
@@ -1101,7 +1100,8 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
 
 /* The same arithmetic with the parts of a head merged inside a cluster of
    ATT_CLUSTER blocks (distributed shared memory) instead of through global
-   memory, a fence, an atomic and a last block: three round trips shorter. */
+   memory, a fence, an atomic and a last block: three round trips shorter.
+   This is what kAttnAuto runs unless the process chose otherwise. */
 constexpr int ATT_CLUSTER = 8;
 template <int GH>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
@@ -1388,11 +1388,14 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
   const int group = a.q_heads / a.kv_heads;
   const int gh = group >= 4 ? 4 : (group >= 2 ? 2 : 1);
   const int tiles = (group + gh - 1) / gh;
-  static const bool clustered = [] {
-    const char *e = getenv("VXB_ATTN_CLUSTER");
-    return !(e && e[0] == '0');
-  }();
-  if (clustered || !a.scratch) {
+  int which = a.kernel == kAttnAuto ? attention_kernel_choice(-1) : a.kernel;
+  if (which == kAttnAuto)
+    which = kAttnCluster;
+  if (which == kAttnSplit && (!a.scratch || !a.counters))
+    return "the split attention kernel needs scratch memory and counters";
+  if (which != kAttnCluster && which != kAttnSplit)
+    return "unknown attention kernel";
+  if (which == kAttnCluster) {
     const dim3 cgrid(ATT_CLUSTER, a.kv_heads * tiles, a.batch);
     const dim3 block(ATT_WARPS * 32);
     if (gh == 4)
@@ -1419,10 +1422,21 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
   return check_launch("the attention launch");
 }
 
+int attention_kernel_choice(int which) {
+  static std::mutex mu;
+  static int choice = kAttnAuto;
+  std::lock_guard<std::mutex> lock(mu);
+  const int before = choice;
+  if (which == kAttnAuto || which == kAttnCluster || which == kAttnSplit)
+    choice = which;
+  return before;
+}
+
 const char *attention_decode_clustered(const AttnArgs &a, cudaStream_t stream) {
   AttnArgs b = a;
   b.scratch = nullptr;
   b.counters = nullptr;
+  b.kernel = kAttnCluster;
   return attention_decode(b, stream);
 }
 

@@ -558,15 +558,9 @@ const char *batched_proj(const BatchedProj &a, cudaStream_t stream) {
   const int b_bytes = n * BK * 2;
   const int stage_bytes = A_BYTES + ((b_bytes + 1023) & ~1023);
   const size_t smem = (size_t)STAGES * stage_bytes + 1024 + sizeof(Bars) + 64;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(rowdot_mma_kernel,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    STAGES * (A_BYTES + 8192) + 1024 +
-                                        (int)sizeof(Bars) + 64);
-  });
-  if (attr_err != cudaSuccess)
+  if (allow_dynamic_smem((const void *)rowdot_mma_kernel,
+                         STAGES * (A_BYTES + 8192) + 1024 + (int)sizeof(Bars) +
+                             64) != cudaSuccess)
     return "the batched projection could not get its shared memory";
   const int items = p.tiles * p.splits;
   const int ctas = items < sm_count() ? items : sm_count();

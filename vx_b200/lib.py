@@ -39,7 +39,7 @@ EXTRA_SYMBOLS = [
     "vx_b200_last_error", "vx_b200_gemm", "vx_b200_kernel_status",
     "vx_b200_flash_attention", "vx_b200_gemm_column_split",
     "vx_b200_fill_normal", "vx_b200_fill_uniform",
-    "vx_b200_attention_decode_static",
+    "vx_b200_attention_decode_static", "vx_b200_attention_kernel",
 ]
 
 _lib = None
@@ -140,6 +140,8 @@ def lib():
     L.vx_b200_attention_decode_static.restype = i32
     L.vx_b200_attention_decode_static.argtypes = [vp, vp, vp, vp, i32, i32, i32,
                                                   i32]
+    L.vx_b200_attention_kernel.restype = i32
+    L.vx_b200_attention_kernel.argtypes = [i32]
     _lib = L
     return L
 
