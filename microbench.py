@@ -2,20 +2,27 @@
 that ends quickly (a few launches, at most a few GB on the device, inputs
 larger than the 126 MB L2 where DRAM figures matter).
 
-  python -m vx_b200.microbench rowdot  [--layers 4] [--iters 3]
-  python -m vx_b200.microbench gemm    [--n 4096] [--iters 3]
-  python -m vx_b200.microbench flash   [--batch 1] [--heads 8] [--seq 4096]
-  python -m vx_b200.microbench attn    [--pos 600]
+  python microbench.py rowdot  [--layers 4] [--iters 3]
+  python microbench.py gemm    [--n 4096] [--iters 3]
+  python microbench.py flash   [--batch 1] [--heads 8] [--seq 4096]
+  python microbench.py attn    [--pos 600]
 Each prints one JSON line with the CUDA-event time per launch.
 """
 import argparse
 import ctypes as C
 import json
 
+import os
+import sys
+
 import numpy as np
 
-from . import abi, ops
-from .lib import lib
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from vx_b200 import abi, ops  # noqa: E402
+from vx_b200.lib import lib  # noqa: E402
 
 
 def _timed(torch, stream, fn, iters):
@@ -106,7 +113,7 @@ def decode16(torch, args):
     """A few layers of the 7B shape decoding `--batch` (8 or 16) sequences per
     step after `--pos` prompt positions: the tensor-core projections
     (rowdot_mma_kernel), attention and their small companions, for profiling."""
-    from . import llama
+    from vx_b200 import llama
     shape = dict(llama.LLAMA2_7B)
     shape["n_layers"] = args.layers
     batch = args.batch if args.batch in (8, 16) else 16

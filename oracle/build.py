@@ -15,6 +15,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_build")
 LIB = os.path.join(OUT_DIR, "libvx_oracle.so")
 SRC = os.path.join(HERE, "vx_oracle.cpp")
+TWIN_LIB = os.path.join(OUT_DIR, "libvx_llama_twin.so")
+TWIN_SRC = os.path.join(HERE, "llama_twin.c")
 
 
 def build(force: bool = False) -> str:
@@ -29,5 +31,21 @@ def build(force: bool = False) -> str:
     return LIB
 
 
+def build_twin(force: bool = False) -> str:
+    """The second, independent restatement of the f32 Llama decode
+    (llama_twin.c), a library of its own so that it shares nothing with the
+    first."""
+    os.makedirs(OUT_DIR, exist_ok=True)
+    if (not force and os.path.exists(TWIN_LIB)
+            and os.path.getmtime(TWIN_LIB) >= os.path.getmtime(TWIN_SRC)):
+        return TWIN_LIB
+    cmd = ["gcc", "-std=c99", "-O2", "-ffp-contract=off", "-shared", "-fPIC",
+           "-Wall", TWIN_SRC, "-o", TWIN_LIB + ".tmp", "-lm"]
+    subprocess.run(cmd, check=True)
+    os.replace(TWIN_LIB + ".tmp", TWIN_LIB)
+    return TWIN_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv))
+    print(build_twin(force="--force" in sys.argv))

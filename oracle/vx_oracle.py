@@ -177,6 +177,22 @@ def llama_forward(cfg, weights, kc, vc, token, pos):
     return logits
 
 
+def llama_twin_generate(cfg, weights, first_token, steps):
+    """The same greedy decode by the second restatement (llama_twin.c, after
+    benchmarks/llama2_100.vx with its online softmax), one thread."""
+    twin = C.CDLL(_build.build_twin())
+    twin.twin_generate.argtypes = [C.POINTER(LlamaConfig), C.c_void_p,
+                                   C.c_void_p, C.c_int32]
+    twin.twin_generate.restype = C.c_int
+    weights = np.ascontiguousarray(weights, dtype=np.float32)
+    assert weights.size == llama_weight_count(cfg)
+    tokens = np.zeros(steps + 1, dtype=np.int32)
+    tokens[0] = first_token
+    rc = twin.twin_generate(C.byref(cfg), _p(weights), _p(tokens), steps)
+    assert rc == 0, "the twin needs n_kv_heads == n_heads (and memory)"
+    return tokens
+
+
 # ---- std::nn operators -----------------------------------------------------------
 def nn_matvec(w16, x, rows, cols, y=None):
     add = y is not None

@@ -61,43 +61,57 @@ def nn_host_model(oracle, tensors, cfgd, max_seq):
 
     L = cfgd["n_layers"]
     qkv_rows = (cfgd["q_heads"] + 2 * cfgd["kv_heads"]) * cfgd["head_dim"]
-    layers = []
-    for l in range(L):
-        layers += [u16(tensors["attn_norm"][l]).reshape(-1),
-                   u16(tensors["wq"][l]).reshape(-1),
-                   np.zeros(qkv_rows, np.uint16),
-                   u16(tensors["wo"][l]).reshape(-1),
-                   u16(tensors["ffn_norm"][l]).reshape(-1),
-                   u16(tensors["w_gate"][l]).reshape(-1),
-                   u16(tensors["w_down"][l]).reshape(-1)]
-    flat = np.concatenate(layers)
     cfg = oracle.NnConfig(cfgd["dim"], cfgd["hidden"], L, cfgd["q_heads"],
                           cfgd["kv_heads"], cfgd["head_dim"], cfgd["vocab"],
                           max_seq, 1e-5, 10000.0)
-    assert flat.size == L * oracle.nn_layer_params(cfg)
+    per_layer = oracle.nn_layer_params(cfg)
+    flat = np.empty(L * per_layer, np.uint16)   # filled in place: 13 GB at 7B
+    at = 0
+    for l in range(L):
+        for part in (tensors["attn_norm"][l], tensors["wq"][l], None,
+                     tensors["wo"][l], tensors["ffn_norm"][l],
+                     tensors["w_gate"][l], tensors["w_down"][l]):
+            if part is None:                    # the q/k/v bias: zero
+                flat[at:at + qkv_rows] = 0
+                at += qkv_rows
+            else:
+                n = part.numel()
+                flat[at:at + n] = u16(part).reshape(-1)
+                at += n
+    assert at == flat.size
     return dict(cfg=cfg, layers=flat, embed=u16(tensors["embed"]),
                 final_norm=u16(tensors["final_norm"]),
                 lm_head=u16(tensors["lm_head"]), cos=tensors["cos"],
                 sin=tensors["sin"])
 
 
-def oracle_generate(oracle, hm, prompt, steps, max_seq):
+def oracle_generate(oracle, hm, prompt, steps, max_seq, want_gaps=False):
     cfg = hm["cfg"]
     shape = (cfg.n_layers, max_seq, cfg.kv_heads, cfg.head_dim)
     kc, vc = np.zeros(shape, np.float32), np.zeros(shape, np.float32)
-    out, pos, tok = [], 0, None
+    out, gaps, pos, tok = [], [], 0, None
+
+    def step(t):
+        if not want_gaps:
+            return oracle.nn_decode_step(cfg, hm["embed"], hm["layers"],
+                                         hm["final_norm"], hm["lm_head"],
+                                         hm["cos"], hm["sin"], kc, vc, t, pos), 0.0
+        tok, logits = oracle.nn_decode_step(
+            cfg, hm["embed"], hm["layers"], hm["final_norm"], hm["lm_head"],
+            hm["cos"], hm["sin"], kc, vc, t, pos, want_logits=True)
+        top2 = np.partition(logits, -2)[-2:]
+        return tok, float(top2[1] - top2[0])
+
+    gap = 0.0
     for t in prompt:
-        tok = oracle.nn_decode_step(cfg, hm["embed"], hm["layers"],
-                                    hm["final_norm"], hm["lm_head"], hm["cos"],
-                                    hm["sin"], kc, vc, t, pos)
+        tok, gap = step(t)
         pos += 1
     for _ in range(steps):
         out.append(tok)
-        tok = oracle.nn_decode_step(cfg, hm["embed"], hm["layers"],
-                                    hm["final_norm"], hm["lm_head"], hm["cos"],
-                                    hm["sin"], kc, vc, tok, pos)
+        gaps.append(gap)        # the gap of the step that chose this token
+        tok, gap = step(tok)
         pos += 1
-    return out
+    return (out, gaps) if want_gaps else out
 
 
 SMALL_NN = dict(dim=512, hidden=1408, n_layers=4, q_heads=8, kv_heads=4,
@@ -211,3 +225,32 @@ def test_prefill_sixteen_positions_at_a_time(oracle):
     assert ops.kernel_status() == 0
     want = oracle_generate(oracle, hm, prompt, steps, max_seq)
     assert got == want, report(got, want)
+
+
+def test_config5_llama7b_shape_100_tokens(oracle):
+    """The benchmarked configuration at its own shape: dim 4096, 32 layers, 32
+    heads of 128, hidden 11008, vocab 32000, bf16 weights N(0, 0.02^2) from
+    seed 7; a 16-token prompt (uniform ids, seed 8) and 100 greedy steps.
+    The tokens must equal the CPU restatement's, step for step (identical
+    token text across placements is the reference's own check,
+    scripts/campaigns/llama/run_perf_matrix.sh:273-292). The oracle runs 116
+    steps of 13 GFLOP on the host cores: about a minute."""
+    max_seq, steps = 160, 100
+    dec, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=1, **llama.LLAMA2_7B)
+    prompt = [int(t) for t in
+              np.random.default_rng(8).integers(0, llama.LLAMA2_7B["vocab"], 16)]
+    tok = None
+    for t in prompt:
+        tok = dec.step([t])[0]
+    got = []
+    for _ in range(steps):
+        got.append(tok)
+        tok = dec.step(None)[0]
+    dec.close()
+    from vx_b200 import ops
+    assert ops.kernel_status() == 0
+    hm = nn_host_model(oracle, tensors, llama.LLAMA2_7B, max_seq)
+    del tensors
+    want, gaps = oracle_generate(oracle, hm, prompt, steps, max_seq,
+                                 want_gaps=True)
+    assert got == want, report(got, want, gaps)

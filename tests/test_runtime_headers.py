@@ -3,8 +3,9 @@ repository's headers (vx_b200/runtime/*.h, include/vx_hardware_runtime.h).
 
 The test sources stay where they are under the reference tree; a scratch
 directory mirrors the reference's layout with links, so their relative includes
-(`../../runtime/x.h`) land on our headers. Needs the reference tree, so this
-runs where that is mounted and skips elsewhere.
+(`../../runtime/x.h`) land on our headers. Needs the reference tree (its path
+comes from VX_REFERENCE_ROOT, default /root/reference), so this runs where
+that is mounted and skips elsewhere.
 """
 import os
 import subprocess
@@ -12,7 +13,8 @@ import subprocess
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF_TESTS = "/root/reference/tests/runtime"
+REF_TESTS = os.path.join(os.environ.get("VX_REFERENCE_ROOT", "/root/reference"),
+                         "tests", "runtime")
 CASES = ["gemm_plan", "kernel_launch", "payload", "device_pool",
          "arrival_counts", "collective"]
 
