@@ -3,14 +3,18 @@
 Headline (the JSON line's metric/value): greedy decode of a Llama-2-7B-shaped
 bf16 model, batch 1, through the whole-token entry point -- tokens/s after a
 512-token prompt, tensor-parallel over --gpus ranks of one box.  A "step" is
-one decoded token.  The same line carries the bf16 GEMM and flash-attention
-figures of the other configurations (N=1 only), the roofline of the dominant
-kernel, and the CPU baseline.
+one decoded token.  The same line carries, at every N, a digest of the tokens
+the model generates from a fixed prompt (so that every tensor-parallel degree
+shows the tokens of one GPU), and at N=1 the figures of the other
+configurations (f32 1024^3, the bf16 GEMM sweep, flash attention, 16
+sequences per step), each with its error against the CPU oracle on sampled
+rows, the roofline of the dominant kernel, and the CPU baseline.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 """
 import argparse
 import ctypes as C
+import hashlib
 import json
 import os
 import subprocess
@@ -25,7 +29,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 PROMPT = 512
-MAX_SEQ = 1024
+MAX_SEQ = 4096                   # the configuration's context length
+DIGEST_PROMPT, DIGEST_STEPS = 16, 64
+CPU_CHECK_STEPS = 8              # oracle steps compared with the GPU's tokens
+CPU_TIMED_STEPS = 8              # oracle steps timed at positions >= 512
 
 
 def measured_peaks():
@@ -56,9 +63,13 @@ class ClockSampler:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index),
                  "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=subprocess.PIPE, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            deadline = time.time() + 2.0     # the first sample takes a moment
+            while not self.lines and time.time() < deadline:
+                time.sleep(0.01)
+            self.lines.clear()               # what follows is under load
         except OSError:
             self.proc = None
         return self
@@ -94,76 +105,100 @@ class ClockSampler:
                     reasons=sorted(reasons), samples=len(sm))
 
 
+def digest_prompt(vocab):
+    return [int(t) for t in np.random.default_rng(8).integers(0, vocab, PROMPT)
+            [:DIGEST_PROMPT]]
+
+
+def tokens_sha(tokens):
+    return hashlib.sha256(np.asarray(tokens, np.int32).tobytes()).hexdigest()[:16]
+
+
 # ---- the CPU arm -----------------------------------------------------------------
-def cpu_decode_baseline(threads):
-    """The oracle's std::nn decode step at Llama-2-7B shapes on the host cores.
-    A bounded sample: one full layer (all five operators) at position 512 plus
-    the classifier, timed, and scaled to 32 layers."""
-    from oracle import vx_oracle as oracle
+def random_kv_rows(kc, vc, first, last, seed=5):
+    """Rows first..last-1 of every layer's cache get N(0,1) values: the rows a
+    512-token prompt would have left (their values do not change the time)."""
+    rng = np.random.default_rng(seed)
+    for l in range(kc.shape[0]):
+        kc[l, first:last] = rng.standard_normal(kc[l, first:last].shape,
+                                                dtype=np.float32)
+        vc[l, first:last] = rng.standard_normal(vc[l, first:last].shape,
+                                                dtype=np.float32)
+
+
+def cpu_timed_steps(oracle, hm, kv, first_pos, steps):
+    """Whole decode steps of the oracle (all 32 layers + classifier + argmax)
+    at positions first_pos, first_pos + 1, ...: seconds per step, each."""
+    cfg, (kc, vc) = hm["cfg"], kv
+    tok, times = 1, []
+    for i in range(steps):
+        t0 = time.perf_counter()
+        tok = oracle.nn_decode_step(cfg, hm["embed"], hm["layers"],
+                                    hm["final_norm"], hm["lm_head"], hm["cos"],
+                                    hm["sin"], kc, vc, tok, first_pos + i)
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def synthetic_host_model(oracle, shape, max_seq):
+    """A 7B-shaped model for the CPU arm alone (no GPU involved): one layer of
+    random bf16 weights, laid down 32 times (32 distinct 400 MB blocks of
+    memory with the same contents: the time of a step does not depend on the
+    values, only on streaming 13 GB)."""
     from vx_b200 import llama
-    oracle.set_threads(threads)
-    s = llama.LLAMA2_7B
-    dim, hid, hd, qh, kvh = s["dim"], s["hidden"], s["head_dim"], s["q_heads"], s["kv_heads"]
-    pos = PROMPT
+    cfg = oracle.NnConfig(shape["dim"], shape["hidden"], shape["n_layers"],
+                          shape["q_heads"], shape["kv_heads"], shape["head_dim"],
+                          shape["vocab"], max_seq, 1e-5, 10000.0)
+    per_layer = oracle.nn_layer_params(cfg)
     rng = np.random.default_rng(7)
-
-    def w16(n):
-        return rng.integers(0x3000, 0x3C00, n, dtype=np.uint16)  # small positive bf16
-
-    wqkv, bq = w16((qh + 2 * kvh) * hd * dim), np.zeros((qh + 2 * kvh) * hd, np.uint16)
-    wo, wgu, wd = w16(dim * dim), w16(2 * hid * dim), w16(dim * hid)
-    norm = w16(dim)
-    head = w16(s["vocab"] * dim)
-    x = rng.standard_normal(dim).astype(np.float32)
-    kc = rng.standard_normal((pos + 1, kvh, hd)).astype(np.float32)
-    vc = rng.standard_normal((pos + 1, kvh, hd)).astype(np.float32)
-    cos, sin = oracle.rope_tables(pos + 1, hd, 10000.0)
-
-    def layer():
-        xb = oracle.nn_rms_norm(x, norm, dim, 1e-5)
-        q, k, v = oracle.nn_qkv(wqkv, bq, xb, qh, kvh, hd, dim)
-        qr = oracle.nn_rope_and_store(kc, vc, q, k, v, cos, sin, pos)
-        att = oracle.nn_attention(qr, kc, vc, pos)
-        y = oracle.nn_matvec(wo, att.reshape(-1), dim, dim, y=x)
-        xb = oracle.nn_rms_norm(y, norm, dim, 1e-5)
-        h = oracle.nn_swiglu(wgu, xb, hid, dim)
-        return oracle.nn_matvec(wd, h, dim, hid, y=y)
-
-    layer()
-    t0 = time.perf_counter()
-    reps = 3
-    for _ in range(reps):
-        layer()
-    t_layer = (time.perf_counter() - t0) / reps
-    t0 = time.perf_counter()
-    oracle.nn_matvec(head, x, s["vocab"], dim)
-    t_head = time.perf_counter() - t0
-    per_token = t_layer * s["n_layers"] + t_head
-    return dict(value=1.0 / per_token, unit="tokens/s", cores=threads,
-                kind="port",
-                sample="1 of 32 layers at position %d (mean of %d runs) + the "
-                       "classifier, scaled to 32 layers: %.1f ms/layer, %.1f ms "
-                       "classifier" % (pos, reps, t_layer * 1e3, t_head * 1e3))
+    one = oracle.f32_to_bf16(rng.standard_normal(per_layer, dtype=np.float32)
+                             * np.float32(0.02))
+    layers = np.tile(one, shape["n_layers"])
+    table = oracle.f32_to_bf16(
+        rng.standard_normal(shape["vocab"] * shape["dim"], dtype=np.float32)
+        * np.float32(0.02))
+    cos, sin = llama.rope_tables(max_seq, shape["head_dim"], 10000.0)
+    ones = oracle.f32_to_bf16(np.ones(shape["dim"], np.float32))
+    return dict(cfg=cfg, layers=layers, embed=table, final_norm=ones,
+                lm_head=table, cos=cos, sin=sin)
 
 
 def run_reference(args):
+    """The reference's CPU path (its port: the reference itself needs Rust and
+    LLVM to build) on all host cores: K whole decode steps of the 7B-shaped
+    model at positions 512.., after W untimed ones."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from oracle import vx_oracle as oracle
+    from vx_b200 import llama
     threads = os.cpu_count() or 1
-    runs = []
-    for _ in range(max(1, min(args.steps, 3))):
-        runs.append(cpu_decode_baseline(threads))
-    best = max(runs, key=lambda r: r["value"])
-    line = dict(metric="llama2_7b_decode_tokens_per_s", value=best["value"],
+    oracle.set_threads(threads)
+    shape = llama.LLAMA2_7B
+    max_seq = PROMPT + args.warmup + args.steps + 8
+    hm = synthetic_host_model(oracle, shape, max_seq)
+    kv_shape = (shape["n_layers"], max_seq, shape["kv_heads"], shape["head_dim"])
+    kv = (np.zeros(kv_shape, np.float32), np.zeros(kv_shape, np.float32))
+    random_kv_rows(kv[0], kv[1], 0, PROMPT)
+    cpu_timed_steps(oracle, hm, kv, PROMPT, args.warmup)
+    times = cpu_timed_steps(oracle, hm, kv, PROMPT + args.warmup, args.steps)
+    total = float(sum(times))
+    value = args.steps / total
+    base = dict(value=value, unit="tokens/s", cores=threads, kind="port",
+                sample="%d whole decode steps (32 layers, classifier, argmax) "
+                       "at positions %d..%d after %d untimed ones; KV rows "
+                       "below 512 random" % (args.steps, PROMPT + args.warmup,
+                                             PROMPT + args.warmup + args.steps - 1,
+                                             args.warmup))
+    line = dict(metric="llama2_7b_decode_tokens_per_s", value=value,
                 unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
-                warmup=args.warmup, ms_per_step=1e3 / best["value"],
+                warmup=args.warmup, ms_per_step=1e3 * total / args.steps,
                 higher_is_better=True, scaling="strong", vs_baseline=None,
-                dtype="bf16 weights, f32 accumulate", data="synthetic",
-                impl="reference", config=workload_config(1, args.gpus),
-                cpu_baseline=best,
-                e2e=dict(value=best["value"], unit="tokens/s",
-                         h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+                dtype="bf16 weights, f32 activations and accumulate",
+                data="synthetic", impl="reference",
+                config=workload_config(1, args.gpus), cpu_baseline=base,
+                e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0,
+                         d2h_bytes_per_step=0))
     print(json.dumps(line))
 
 
@@ -188,43 +223,113 @@ def event_ms(torch, stream, fn):
     return start.elapsed_time(stop)
 
 
-def bench_gemm(torch, peaks, n=8192, iters=20):
-    """bf16 n^3 through the dispatch entry point, device-resident operands."""
+class on_stream:
+    """The library's work goes to `stream` inside the block."""
+
+    def __init__(self, stream):
+        self.stream = stream
+
+    def __enter__(self):
+        from vx_b200.lib import lib
+        lib().vx_cuda_set_stream(C.c_void_p(self.stream.cuda_stream))
+
+    def __exit__(self, *exc):
+        from vx_b200.lib import lib
+        lib().vx_cuda_set_stream(None)
+
+
+def bench_gemm_f32(torch, oracle, n=1024, iters=50):
+    """Configuration 1: f32 n^3 with A, B uniform[-1,1) from seeds 0 and 1,
+    through the dispatch entry point with device-resident operands and with
+    host operands (staged both ways inside the call); the whole C against the
+    CPU loop nest, which is also timed on one thread (the reference's host
+    GEMM is one thread) and on all cores."""
     from vx_b200 import abi, ops
-    from vx_b200.lib import lib
+    a = np.random.default_rng(0).uniform(-1, 1, (n, n)).astype(np.float32)
+    b = np.random.default_rng(1).uniform(-1, 1, (n, n)).astype(np.float32)
+    ta, tb = abi.DeviceTensor.from_host(a), abi.DeviceTensor.from_host(b)
+    tc = abi.DeviceTensor.empty((n, n), abi.F32)
+    stream = torch.cuda.Stream()
+    with on_stream(stream):
+        for _ in range(3):
+            ops.matmul_into(tc, ta, tb)
+        stream.synchronize()
+        ms = event_ms(torch, stream, lambda: [ops.matmul_into(tc, ta, tb)
+                                              for _ in range(iters)]) / iters
+    got = tc.to_host()
+    t0 = time.perf_counter()
+    host = ops.matmul_host(a, b, slot=False)
+    host_ms = (time.perf_counter() - t0) * 1e3
+    threads = os.cpu_count() or 1
+    oracle.set_threads(1)
+    t0 = time.perf_counter()
+    want = oracle.gemm(a, b)
+    cpu1 = time.perf_counter() - t0
+    oracle.set_threads(threads)
+    t0 = time.perf_counter()
+    oracle.gemm(a, b)
+    cpun = time.perf_counter() - t0
+    for t in (ta, tb, tc):
+        t.free()
+    flop = 2.0 * n ** 3
+    return dict(workload="f32 %d^3, uniform[-1,1) seeds 0/1, true FP32" % n,
+                tflops=flop / ms / 1e9, ms=ms, iters=iters,
+                rel_frobenius_err=float(np.linalg.norm(got - want) /
+                                        np.linalg.norm(want)),
+                host_operands_ms=host_ms,
+                host_operands_rel_err=float(np.linalg.norm(host - want) /
+                                            np.linalg.norm(want)),
+                cpu_one_thread_s=cpu1, cpu_all_cores_s=cpun, cpu_cores=threads,
+                tolerance=1e-4)
+
+
+def bench_gemm(torch, oracle, peaks, n=8192, iters=20, check_rows=8):
+    """bf16 n^3 through the dispatch entry point, device-resident operands;
+    `check_rows` sampled rows of C against the oracle's f32-accumulate loop."""
+    from vx_b200 import abi, ops
     ta, tb, tc = (abi.DeviceTensor.empty((n, n), abi.BF16) for _ in range(3))
     ops.fill_uniform(ta, 3, -1.0, 1.0)
     ops.fill_uniform(tb, 1003, -1.0, 1.0)
     stream = torch.cuda.Stream()
-    lib().vx_cuda_set_stream(C.c_void_p(stream.cuda_stream))
-    try:
+    with on_stream(stream):
         for _ in range(3):
             ops.matmul_into(tc, ta, tb)
         stream.synchronize()
         ms = event_ms(torch, stream, lambda: [ops.matmul_into(tc, ta, tb)
                                               for _ in range(iters)]) / iters
         status = ops.kernel_status()
-    finally:
-        lib().vx_cuda_set_stream(None)
+    out = dict(workload="bf16 %d^3, f32 accumulate, bf16 out" % n,
+               tflops=2.0 * n ** 3 / ms / 1e9, ms=ms, kernel_status=status,
+               iters=iters)
+    out["frac_of_measured_cublas"] = out["tflops"] / peaks["bf16_tflops"]
+    out["frac_of_nominal_2250"] = out["tflops"] / 2250.0
+    if check_rows:
+        rows = (np.arange(check_rows, dtype=np.int64) * 7919 + 13) % n
+        a16, b16, c16 = ta.to_host(), tb.to_host(), tc.to_host()
+        t0 = time.perf_counter()
+        want = oracle.bf16_to_f32(oracle.gemm_bf16_rows(a16, b16, rows))
+        cpu_s = time.perf_counter() - t0
+        got = oracle.bf16_to_f32(c16[rows])
+        out["rel_err_sampled_rows"] = float(np.linalg.norm(got - want) /
+                                            np.linalg.norm(want))
+        out["rows_checked"] = int(check_rows)
+        out["tolerance"] = 2e-2
+        out["cpu_all_cores_s_extrapolated"] = cpu_s * n / check_rows
     for t in (ta, tb, tc):
         t.free()
-    tflops = 2.0 * n ** 3 / ms / 1e9
-    return dict(workload="bf16 %d^3, f32 accumulate, bf16 out" % n,
-                tflops=tflops, ms=ms, frac_of_measured_cublas=tflops / peaks["bf16_tflops"],
-                frac_of_nominal_2250=tflops / 2250.0, kernel_status=status,
-                iters=iters)
+    return out
 
 
-def bench_flash(torch, peaks, B=8, H=32, S=4096, D=128, iters=5):
+def bench_flash(torch, oracle, peaks, B=8, H=32, S=4096, D=128, iters=5):
+    """Configuration 3, and sampled rows of a few (batch, head) pairs against
+    the oracle's f32 attention over the same bf16 inputs."""
     from vx_b200 import abi, ops
-    from vx_b200.lib import lib
     ts = [abi.DeviceTensor.empty((B, H, S, D), abi.BF16) for _ in range(4)]
     for t, seed in zip(ts[:3], (10, 11, 12)):
         ops.fill_normal(t, seed, 1.0)
     stream = torch.cuda.Stream()
-    lib().vx_cuda_set_stream(C.c_void_p(stream.cuda_stream))
     scale = 1.0 / np.sqrt(D)
-    try:
+    with on_stream(stream):
         for _ in range(2):
             ops.flash_attention(ts[0], ts[1], ts[2], ts[3], scale, True)
         stream.synchronize()
@@ -232,8 +337,16 @@ def bench_flash(torch, peaks, B=8, H=32, S=4096, D=128, iters=5):
             ops.flash_attention(ts[0], ts[1], ts[2], ts[3], scale, True)
             for _ in range(iters)]) / iters
         status = ops.kernel_status()
-    finally:
-        lib().vx_cuda_set_stream(None)
+    rows = np.unique(np.concatenate([np.arange(5, S, 509), [0, 127, 128, S - 1]]))
+    worst, cpu_s = 0.0, 0.0
+    pairs = [(0, 0), (B // 2, H // 3), (B - 1, H - 1)]
+    for b, h in pairs:
+        at = (b * H + h) * S * D
+        q, k, v, o = (t.view(at, (S, D)).to_host() for t in ts)
+        t0 = time.perf_counter()
+        want = oracle.attention_rows(q, k, v, scale, True, rows)
+        cpu_s += time.perf_counter() - t0
+        worst = max(worst, float(np.abs(oracle.bf16_to_f32(o)[rows] - want).max()))
     for t in ts:
         t.free()
     flops = 4.0 * B * H * D * S * (S + 1) / 2
@@ -241,7 +354,13 @@ def bench_flash(torch, peaks, B=8, H=32, S=4096, D=128, iters=5):
     return dict(workload="bf16 causal forward [%d,%d,%d,%d]" % (B, H, S, D),
                 tflops=tflops, ms=ms, flops_counted="causal: 4*B*H*D*S*(S+1)/2",
                 frac_of_measured_cublas=tflops / peaks["bf16_tflops"],
-                kernel_status=status, iters=iters)
+                frac_of_nominal_2250=tflops / 2250.0,
+                target="0.60 of tensor peak; both denominators are given",
+                kernel_status=status, iters=iters, max_abs_err=worst,
+                rows_checked=int(rows.size) * len(pairs), tolerance=2e-2,
+                # the sampled rows average S/2 keys like all rows do
+                cpu_all_cores_s_extrapolated=cpu_s * B * H * S /
+                (rows.size * len(pairs)))
 
 
 def bench_dominant_kernel(torch, tensors, peaks, shape, iters=3):
@@ -249,7 +368,6 @@ def bench_dominant_kernel(torch, tensors, peaks, shape, iters=3):
     180 MB matrices, so nothing is left in L2), timed with CUDA events on the
     stream it is launched on."""
     from vx_b200 import abi, ops
-    from vx_b200.lib import lib
     dim, hid = shape["dim"], shape["hidden"]
     x = abi.DeviceTensor.empty((dim,), abi.F32)
     ops.fill_normal(x, 99, 1.0)
@@ -257,16 +375,13 @@ def bench_dominant_kernel(torch, tensors, peaks, shape, iters=3):
     ws = [abi.DeviceTensor(t.data_ptr(), (2 * hid * dim,), abi.BF16, abi.home_gpu())
           for t in tensors["w_gate"]]
     stream = torch.cuda.Stream()
-    lib().vx_cuda_set_stream(C.c_void_p(stream.cuda_stream))
-    try:
+    with on_stream(stream):
         for w in ws[:3]:
             ops.nn_swiglu(out, w, x, hid, dim)
         stream.synchronize()
         launches = iters * len(ws)
         ms = event_ms(torch, stream, lambda: [ops.nn_swiglu(out, w, x, hid, dim)
                                               for _ in range(iters) for w in ws])
-    finally:
-        lib().vx_cuda_set_stream(None)
     per_launch_ms = ms / launches
     bytes_per_launch = 2 * hid * dim * 2 + dim * 4 + hid * 4
     achieved = bytes_per_launch / per_launch_ms / 1e6
@@ -312,6 +427,105 @@ def bench_decode_batch(torch, llama, shape, peaks, batch):
                 steps=steps, hbm_gbs=gbs, frac_of_measured_hbm=gbs / peaks["hbm_gbs"])
 
 
+def bench_skinny_layers(torch, llama, rank, world):
+    """The per-layer cost that is not weight streaming: a model with the 7B
+    width but almost no weights (one head per rank, 64 MLP rows per rank),
+    32 layers. At N > 1 the difference from N = 1 is two exchanges per layer."""
+    skinny = dict(dim=4096, hidden=64 * world, n_layers=32, q_heads=world,
+                  kv_heads=world, head_dim=128, vocab=64 * world)
+    dec, tensors = llama.nn_bf16_model(max_seq=64, batch=1, tp_rank=rank,
+                                       tp_ranks=world, **skinny)
+    stream = torch.cuda.ExternalStream(dec.stream)
+    dec.step([1], fetch=False)
+    for _ in range(8):
+        dec.step(None, fetch=False)
+    torch.cuda.synchronize()
+    steps = 24
+    ms = event_ms(torch, stream,
+                  lambda: [dec.step(None, fetch=False) for _ in range(steps)])
+    dec.close()
+    del tensors
+    return ms * 1e3 / steps / skinny["n_layers"]
+
+
+def bench_column_split(torch, dist, rank, world, n=16384, iters=3):
+    """Configuration 4's multi-GPU half: C = A B with B column-split over the
+    ranks; every rank computes its column block, the blocks are all-gathered
+    (vx_collective_all_gather_bf16's NCCL call) and interleaved into the
+    row-major C, all inside the timed region. The local GEMM is also timed
+    alone, so the line says what the gather and the interleave cost."""
+    from vx_b200 import abi, ops
+    from vx_b200.lib import check, lib
+    nl = n // world
+    ta = abi.DeviceTensor.empty((n, n), abi.BF16)
+    tb = abi.DeviceTensor.empty((n, nl), abi.BF16)
+    tcl = abi.DeviceTensor.empty((n, nl), abi.BF16)
+    tg = abi.DeviceTensor.empty((world, n, nl), abi.BF16)
+    tc = abi.DeviceTensor.empty((n, n), abi.BF16)
+    ops.fill_uniform(ta, 3, -1.0, 1.0)
+    ops.fill_uniform(tb, 2003 + rank, -1.0, 1.0)
+    stream = torch.cuda.Stream()
+
+    def whole():
+        check(lib().vx_b200_gemm_column_split(abi.BF16, n, nl, n, ta.ptr, tb.ptr,
+                                              tcl.ptr, tg.ptr, tc.ptr))
+
+    def local():
+        check(lib().vx_b200_gemm(abi.BF16, 0, n, nl, n, ta.ptr, n, tb.ptr, nl,
+                                 tcl.ptr, nl, None))
+
+    with on_stream(stream):
+        whole()
+        local()
+        stream.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = event_ms(torch, stream, lambda: [whole() for _ in range(iters)]) / iters
+        dist.barrier()
+        torch.cuda.synchronize()
+        local_ms = event_ms(torch, stream,
+                            lambda: [local() for _ in range(iters)]) / iters
+        status = ops.kernel_status()
+    times = torch.tensor([ms, local_ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, local_ms = (float(v) for v in times.cpu())
+    for t in (ta, tb, tcl, tg, tc):
+        t.free()
+    flop = 2.0 * n ** 3
+    return dict(workload="bf16 %d^3, B column-split over %d ranks, all-gather "
+                         "of C + interleave inside the timed region" % (n, world),
+                ms=ms, tflops_aggregate=flop / ms / 1e9,
+                tflops_per_gpu=flop / world / ms / 1e9, local_gemm_ms=local_ms,
+                gather_and_interleave_share=(ms - local_ms) / ms,
+                kernel_status=status, iters=iters)
+
+
+def cpu_baseline_with_the_model(oracle, hm, got_tokens, threads):
+    """The CPU arm on the model the GPU decoded: the first CPU_CHECK_STEPS
+    tokens after the digest prompt must be the GPU's (the oracle as checker),
+    then whole steps are timed at positions >= 512 over random KV rows."""
+    oracle.set_threads(threads)
+    cfg = hm["cfg"]
+    max_seq = PROMPT + CPU_TIMED_STEPS + 8
+    shape = (cfg.n_layers, max_seq, cfg.kv_heads, cfg.head_dim)
+    kv = (np.zeros(shape, np.float32), np.zeros(shape, np.float32))
+    hm = dict(hm, cos=hm["cos"][:max_seq], sin=hm["sin"][:max_seq])
+    cfg.max_seq = max_seq
+    want = oracle.nn_generate(hm, digest_prompt(cfg.vocab), CPU_CHECK_STEPS,
+                              max_seq, kv=kv)
+    random_kv_rows(kv[0], kv[1], DIGEST_PROMPT + CPU_CHECK_STEPS, PROMPT)
+    times = cpu_timed_steps(oracle, hm, kv, PROMPT, 1 + CPU_TIMED_STEPS)[1:]
+    value = len(times) / float(sum(times))
+    return dict(value=value, unit="tokens/s", cores=threads, kind="port",
+                sample="%d whole decode steps (32 layers, classifier, argmax) of "
+                       "this model at positions %d..%d after one untimed; KV "
+                       "rows below 512 random" % (len(times), PROMPT + 1,
+                                                  PROMPT + len(times)),
+                tokens_checked=CPU_CHECK_STEPS,
+                tokens_match_gpu=bool(list(want) ==
+                                      list(got_tokens[:CPU_CHECK_STEPS])))
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -325,7 +539,6 @@ def run_ours(args):
     if multi:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     from vx_b200 import collective, llama
-    from vx_b200.lib import lib
     peaks = measured_peaks()
     shape = llama.LLAMA2_7B
 
@@ -353,16 +566,23 @@ def run_ours(args):
             dec.step([int(t)], fetch=False)
         return dec.step([int(prompt[-1])])[0]
 
-    # -- device-resident: the argmax feeds the next step on the GPU ------------
+    # -- device-resident: the argmax feeds the next step on the GPU. Exactly
+    #    `steps` steps per measurement; a short region is measured several
+    #    times (the median counts) so that the clock record has samples.
     run_prompt()
     for _ in range(args.warmup):
         dec.step(None, fetch=False)
     barrier()
+    repeats = 1 if args.steps >= 400 else 5
+    measured = []
     with ClockSampler(local) as clocks:
-        ms = event_ms(torch, stream,
-                      lambda: [dec.step(None, fetch=False) for _ in range(args.steps)])
-        time.sleep(0.25)
-    barrier()
+        for _ in range(repeats):
+            measured.append(event_ms(
+                torch, stream,
+                lambda: [dec.step(None, fetch=False) for _ in range(args.steps)]))
+            barrier()
+        time.sleep(0.1)
+    ms = float(np.median(measured))
     # -- end to end: a host token in, the argmax token out, every step ---------
     tok = run_prompt()
     for _ in range(args.warmup):
@@ -373,10 +593,22 @@ def run_ours(args):
     def e2e_steps():
         for _ in range(args.steps):
             holder["tok"] = dec.step([holder["tok"]])[0]
-    e2e_ms = event_ms(torch, stream, e2e_steps)
+    e2e_ms = float(np.median([event_ms(torch, stream, e2e_steps)
+                              for _ in range(repeats)]))
     barrier()
 
-    # -- the prompt itself: one decode step per token, and sixteen positions per
+    # -- what the model says: the tokens after a fixed 16-token prompt, the
+    #    same at every tensor-parallel degree
+    dec.reset()
+    tok = None
+    for t in digest_prompt(shape["vocab"]):
+        tok = dec.step([t])[0]
+    said = []
+    for _ in range(DIGEST_STEPS):
+        said.append(tok)
+        tok = dec.step(None)[0]
+
+    # -- the prompt itself: one decode step per token, and many positions per
     #    pass (vx_decoder_prefill); one GPU only
     prefill = None
     if not multi and not args.no_extras:
@@ -388,11 +620,21 @@ def run_ours(args):
             torch.cuda.synchronize()
             return (time.perf_counter() - t0) * 1e3, tok
         step_ms, tok_a = timed_prompt(run_prompt)
+        timed_prompt(lambda: dec.prefill(prompt))            # warm
         rows_ms, tok_b = timed_prompt(lambda: dec.prefill(prompt))
+        after = [tok_b]
+        for _ in range(15):
+            after.append(dec.step(None)[0])
+        dec.reset()
+        tok = run_prompt()
+        after_steps = [tok]
+        for _ in range(15):
+            after_steps.append(dec.step(None)[0])
         prefill = dict(prompt_tokens=PROMPT, one_step_per_token_ms=step_ms,
-                       sixteen_positions_per_pass_ms=rows_ms,
+                       prefill_ms=rows_ms,
                        tokens_per_s=PROMPT / (rows_ms / 1e3),
                        same_next_token=bool(tok_a == tok_b),
+                       same_16_following_tokens=bool(after == after_steps),
                        timing="host clock around the whole prompt, "
                               "synchronised on both sides")
 
@@ -401,11 +643,14 @@ def run_ours(args):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, e2e_ms = (float(v) for v in times.cpu())
     launches = dec.kernels_per_step * args.steps
+    from vx_b200 import ops
+    status = ops.kernel_status()
 
+    line = None
     if rank == 0:
         tokens_per_s = args.steps / (ms / 1e3)
         per_token_bytes = llama.weight_bytes_per_token(**shape)
-        mean_pos = PROMPT + args.warmup + args.steps / 2.0
+        mean_pos = PROMPT + args.warmup + args.steps * repeats / 2.0
         kv_bytes = 2 * shape["n_layers"] * shape["kv_heads"] * shape["head_dim"] * 4 * (mean_pos + 1)
         step_gbs = (per_token_bytes + kv_bytes) / world / (ms / args.steps) / 1e6
         line = dict(
@@ -418,6 +663,10 @@ def run_ours(args):
             e2e=dict(value=args.steps / (e2e_ms / 1e3), unit="tokens/s",
                      h2d_bytes_per_step=4, d2h_bytes_per_step=4),
             gpu_launches=launches, kernels_per_step=dec.kernels_per_step,
+            timed_repeats=repeats, kernel_status=status,
+            tokens_sha=tokens_sha(said), tokens_head=said[:8],
+            tokens_of="%d greedy tokens after the first %d ids of the prompt"
+                      % (DIGEST_STEPS, DIGEST_PROMPT),
             clocks=clocks.summary(),
             step_roofline=dict(
                 bound="hbm", bytes_per_step_per_gpu=(per_token_bytes + kv_bytes) / world,
@@ -428,25 +677,51 @@ def run_ours(args):
         if prefill:
             line["prefill"] = prefill
     dec.close()
+
+    host_model = None
+    if rank == 0 and not multi:
+        from oracle import vx_oracle as oracle
+        host_model = oracle.nn_model_from_tensors(tensors, shape, MAX_SEQ)
     del tensors
     torch.cuda.empty_cache()
 
+    try:
+        line_extra = {}
+        line_extra["skinny_us_per_layer"] = bench_skinny_layers(torch, llama, rank,
+                                                                world)
+        if multi and not args.no_extras:
+            line_extra["gemm_column_split"] = bench_column_split(torch, dist, rank,
+                                                                 world)
+        if rank == 0:
+            line.update(line_extra)
+    except RuntimeError as e:            # reported, never hidden
+        if rank == 0:
+            line["extras_error"] = str(e)
+
     if rank == 0 and not multi and not args.no_extras:
+        from oracle import vx_oracle as oracle
         try:
             line["decode_batch16"] = bench_decode_batch(torch, llama, shape, peaks, 16)
-            # attention before the GEMMs: seconds of dense GEMM leave the GPU at
-            # its power cap, and what runs next is measured at lower clocks
-            line["flash_attention"] = bench_flash(torch, peaks)
-            line["gemm"] = bench_gemm(torch, peaks)
+            line["gemm_f32_1024"] = bench_gemm_f32(torch, oracle)
+            # attention before the big GEMMs: seconds of dense GEMM leave the GPU
+            # at its power cap, and what runs next is measured at lower clocks
+            line["flash_attention"] = bench_flash(torch, oracle, peaks)
+            line["gemm"] = bench_gemm(torch, oracle, peaks)
             # the other sizes of the GEMM configuration (2048 fits L2: noted)
-            line["gemm_sweep"] = {
-                str(n): round(bench_gemm(torch, peaks, n=n, iters=it)["tflops"], 1)
-                for n, it in ((2048, 50), (4096, 30), (16384, 5))}
+            line["gemm_sweep"] = {}
+            for n, it in ((2048, 50), (4096, 30), (16384, 5)):
+                r = bench_gemm(torch, oracle, peaks, n=n, iters=it, check_rows=4)
+                line["gemm_sweep"][str(n)] = dict(
+                    tflops=round(r["tflops"], 1),
+                    rel_err_sampled_rows=r["rel_err_sampled_rows"],
+                    kernel_status=r["kernel_status"])
         except RuntimeError as e:        # reported, never hidden
             line["extras_error"] = str(e)
     if rank == 0:
-        if not multi:
-            line["cpu_baseline"] = cpu_decode_baseline(os.cpu_count() or 1)
+        if host_model is not None:
+            from oracle import vx_oracle as oracle
+            line["cpu_baseline"] = cpu_baseline_with_the_model(
+                oracle, host_model, said, os.cpu_count() or 1)
         print(json.dumps(line))
     if multi:
         collective.leave_job()
@@ -461,7 +736,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true",
-                    help="skip the GEMM and flash-attention figures")
+                    help="skip the GEMM, flash-attention and batch-16 figures")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -53,65 +53,11 @@ def test_small_llama_logits_close(oracle):
 
 
 def nn_host_model(oracle, tensors, cfgd, max_seq):
-    """The oracle's view of a model that nn_bf16_model built on the GPU."""
-    import torch
-
-    def u16(t):
-        return t.view(torch.int16).cpu().numpy().view(np.uint16)
-
-    L = cfgd["n_layers"]
-    qkv_rows = (cfgd["q_heads"] + 2 * cfgd["kv_heads"]) * cfgd["head_dim"]
-    cfg = oracle.NnConfig(cfgd["dim"], cfgd["hidden"], L, cfgd["q_heads"],
-                          cfgd["kv_heads"], cfgd["head_dim"], cfgd["vocab"],
-                          max_seq, 1e-5, 10000.0)
-    per_layer = oracle.nn_layer_params(cfg)
-    flat = np.empty(L * per_layer, np.uint16)   # filled in place: 13 GB at 7B
-    at = 0
-    for l in range(L):
-        for part in (tensors["attn_norm"][l], tensors["wq"][l], None,
-                     tensors["wo"][l], tensors["ffn_norm"][l],
-                     tensors["w_gate"][l], tensors["w_down"][l]):
-            if part is None:                    # the q/k/v bias: zero
-                flat[at:at + qkv_rows] = 0
-                at += qkv_rows
-            else:
-                n = part.numel()
-                flat[at:at + n] = u16(part).reshape(-1)
-                at += n
-    assert at == flat.size
-    return dict(cfg=cfg, layers=flat, embed=u16(tensors["embed"]),
-                final_norm=u16(tensors["final_norm"]),
-                lm_head=u16(tensors["lm_head"]), cos=tensors["cos"],
-                sin=tensors["sin"])
+    return oracle.nn_model_from_tensors(tensors, cfgd, max_seq)
 
 
 def oracle_generate(oracle, hm, prompt, steps, max_seq, want_gaps=False):
-    cfg = hm["cfg"]
-    shape = (cfg.n_layers, max_seq, cfg.kv_heads, cfg.head_dim)
-    kc, vc = np.zeros(shape, np.float32), np.zeros(shape, np.float32)
-    out, gaps, pos, tok = [], [], 0, None
-
-    def step(t):
-        if not want_gaps:
-            return oracle.nn_decode_step(cfg, hm["embed"], hm["layers"],
-                                         hm["final_norm"], hm["lm_head"],
-                                         hm["cos"], hm["sin"], kc, vc, t, pos), 0.0
-        tok, logits = oracle.nn_decode_step(
-            cfg, hm["embed"], hm["layers"], hm["final_norm"], hm["lm_head"],
-            hm["cos"], hm["sin"], kc, vc, t, pos, want_logits=True)
-        top2 = np.partition(logits, -2)[-2:]
-        return tok, float(top2[1] - top2[0])
-
-    gap = 0.0
-    for t in prompt:
-        tok, gap = step(t)
-        pos += 1
-    for _ in range(steps):
-        out.append(tok)
-        gaps.append(gap)        # the gap of the step that chose this token
-        tok, gap = step(tok)
-        pos += 1
-    return (out, gaps) if want_gaps else out
+    return oracle.nn_generate(hm, prompt, steps, max_seq, want_gaps=want_gaps)
 
 
 SMALL_NN = dict(dim=512, hidden=1408, n_layers=4, q_heads=8, kv_heads=4,

@@ -15,6 +15,7 @@ DTYPE_BYTES = {I1: 1, I8: 1, I16: 2, I32: 4, I64: 8, F32: 4, F64: 8, F16: 2,
                BF16: 2}
 NUMPY_OF = {F32: np.float32, F64: np.float64, F16: np.float16, BF16: np.uint16,
             I32: np.int32, I64: np.int64}
+I32_KIND, I64_KIND, F32_KIND = 4, 5, 6   # scalar argument kinds (VX_ABI_KIND_*)
 TOPO_CPU = 0
 TOPO_GPU_BASE = 500
 SLOT_BIT = 1 << 24
@@ -139,13 +140,18 @@ class DeviceTensor:
                [C.c_int64(v) for v in vals[2:]]
 
 
-def dispatch(blob, args, tags):
+def dispatch(blob, args, tags, launch_values=()):
     """vx_plugin_dispatch_async(payload, size, device_args, arg_tags, n).
     args: ctypes objects; for a memref, the descriptor array. Memref arguments
     are passed as pointer-to-pointer-to-descriptor, scalars as pointer-to-value,
-    as LaunchOpLowering builds them."""
+    as LaunchOpLowering builds them. launch_values: the i32 values that `$j`
+    in `grid=`, `block=` and `launch=` names; they sit after the n kernel
+    arguments and are not counted in n."""
     n = len(args)
-    holders, slots = [], (C.c_void_p * n)()
+    extra = [C.c_int32(int(v)) for v in launch_values]
+    args = list(args) + extra
+    tags = list(tags) + [I32_KIND] * len(extra)
+    holders, slots = [], (C.c_void_p * len(args))()
     for i, (a, tag) in enumerate(zip(args, tags)):
         if (tag & 0xFF) == 0:
             p = C.c_void_p(C.addressof(a))
@@ -153,7 +159,7 @@ def dispatch(blob, args, tags):
             slots[i] = C.addressof(p)
         else:
             slots[i] = C.addressof(a)
-    tag_arr = (C.c_int32 * n)(*tags)
+    tag_arr = (C.c_int32 * len(args))(*tags)
     buf = C.create_string_buffer(blob, len(blob))
     rc = lib().vx_plugin_dispatch_async(buf, len(blob), slots, tag_arr, n)
     holders.clear()

@@ -13,10 +13,12 @@
  *
  * Tensor parallel (tp_ranks > 1): every rank holds a slice of the heads and of
  * the MLP rows; the output and down projections produce partial sums that meet
- * either in an NCCL all-reduce inside the graph (tp_reduce 0) or as (value,
- * call) pairs that the projection kernel stores into every rank's memory and
- * the next projection adds in its prologue (tp_reduce 1); the logits are split
- * by vocabulary with an exchange of each rank's best (value, index).
+ * either in an NCCL all-reduce inside the graph (tp_reduce 0) or inside the
+ * projection kernel itself (tp_reduce 1): each warp stores its finished values
+ * into every other rank's memory as (value, call) pairs, waits for the other
+ * ranks' pairs of the same rows and adds them to the residual, so a layer is
+ * the same five kernels as on one GPU; the logits are split by vocabulary with
+ * an exchange of each rank's best (value, index).
  *
  * 8 or 16 sequences per step (head_dim 128): the projections go to the tensor
  * cores (rowdot_umma.cu).  vx_decoder_prefill uses the same kernels to read a
@@ -118,7 +120,7 @@ struct vx_decoder {
   const void *embed, *final_norm, *lm_head;
   const float *cos_t, *sin_t;
   /* device state */
-  float *x, *x2, *xn, *q, *att, *h, *tmp, *logits, *k_cache, *v_cache, *scratch;
+  float *x, *xn, *q, *att, *h, *tmp, *logits, *k_cache, *v_cache, *scratch;
   bool fused_norm; /* the activations of all sequences fit the projections' shared memory */
   int32_t *tokens, *positions, *counters, *local_best;
   float2 *pair, *pairs_all;
@@ -127,10 +129,7 @@ struct vx_decoder {
   vxb::TpPush tp;
   void *recv;                       /* this rank's slots + flags (IPC-shared) */
   void *peer_recv[vxb::kMaxTpRanks];
-  int32_t *tp_epoch, *tp_done, *tp_gather_done;
-  /* the pushed partials are added by the next projection's prologue instead
-     of a kernel of their own */
-  bool fold;
+  int32_t *tp_epoch, *tp_done;
   /* 8 or 16 sequences: the projections run on the tensor cores */
   bool mma;
   void *mma_xs;
@@ -170,20 +169,13 @@ void all_reduce(vx_decoder *d, float *buf, int64_t count) {
     stop("vx_decoder: ncclAllReduce failed: %s", job->api()->GetErrorString(r));
 }
 
-/* x += the sum over ranks of the partial projection just computed: either the
-   partials were pushed into every rank's receive slots by the projection
-   kernel itself and one small kernel adds them, or NCCL sums d->tmp and a
-   second kernel adds it. Returns the number of launches. */
+/* x += the sum over ranks of the partial projection just computed. With the
+   pushed exchange the projection kernel has done it already; else NCCL sums
+   d->tmp and a second kernel adds it. Returns the number of launches. */
 int add_partials(vx_decoder *d) {
-  if (d->ranks == 1)
+  if (d->ranks == 1 || d->push)
     return 0;
   const int64_t n = (int64_t)d->c.batch * d->c.dim;
-  if (d->push) {
-    need(vxb::tp_reduce_add(d->x, d->tp.slots[d->tp.rank], d->tp_epoch,
-                            d->tp_gather_done, d->ranks, n, d->stream),
-         "adding the partial sums");
-    return 1;
-  }
   all_reduce(d, d->tmp, n);
   add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, d->stream>>>(d->x, d->tmp, n);
   return 2;
@@ -199,7 +191,6 @@ void open_peer_buffers(vx_decoder *d, int rank) {
   CUDA_OK(cudaMemset(d->recv, 0, bytes));
   d->tp_epoch = dev_alloc<int32_t>(4);
   d->tp_done = d->tp_epoch + 1;
-  d->tp_gather_done = d->tp_epoch + 2;
   cudaIpcMemHandle_t mine;
   CUDA_OK(cudaIpcGetMemHandle(&mine, d->recv));
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
@@ -231,6 +222,7 @@ void open_peer_buffers(vx_decoder *d, int rank) {
   d->tp.rank = rank;
   d->tp.count = n;
   d->tp.epoch = d->tp_epoch;
+  d->tp.done = d->tp_done;
   cudaFree(one);
   cudaFree(all);
   /* Nobody writes into a buffer before everybody has mapped it. */
@@ -262,40 +254,6 @@ void record_step(vx_decoder *d, int max_pos) {
   need(vxb::embed(d->x, d->embed, bf, d->tokens, c.dim, c.vocab, B, c.dim, s),
        "embed");
   ++launches;
-  /* Folded exchange: the residual stream alternates between x and x2. A
-     projection whose input still lacks the partials of the one before reads
-     x_cur, adds them in its prologue and leaves the sum in the other buffer.
-     A step has 2 * n_layers such hand-overs, so it ends where it began. */
-  float *x_cur = d->x, *x_other = d->x2;
-  bool owed = false;
-  vxb::TpGather fold{};
-  if (d->fold) {
-    fold.slots = d->tp.slots[d->tp.rank];
-    fold.epoch = d->tp_epoch;
-    fold.done = d->tp_gather_done;
-    fold.ranks = d->ranks;
-    fold.count = (int64_t)B * c.dim;
-  }
-  auto take_partials = [&]() -> const vxb::TpGather * {
-    if (!owed)
-      return nullptr;
-    fold.x_out = x_other;
-    return &fold;
-  };
-  auto partials_taken = [&]() {
-    if (owed) {
-      std::swap(x_cur, x_other);
-      owed = false;
-    }
-  };
-  /* after a pushed projection: either the next prologue adds the partials,
-     or a kernel of its own does, now */
-  auto after_push = [&]() {
-    if (d->fold)
-      owed = true;
-    else
-      launches += add_partials(d);
-  };
   /* 8 or 16 sequences: every projection on the tensor cores */
   auto batched = [&](int mode, const void *w0, const void *w1, const void *w2,
                      int rows, int cols, const float *x, const void *norm_w,
@@ -376,8 +334,7 @@ void record_step(vx_decoder *d, int max_pos) {
     qa.kv_heads = d->kv_local;
     qa.head_dim = hd;
     qa.cols = c.dim;
-    qa.x = d->fold ? x_cur : normed(d, d->attn_norm[l], launches);
-    qa.gather = take_partials();
+    qa.x = normed(d, d->attn_norm[l], launches);
     qa.x_stride = c.dim;
     qa.batch = B;
     qa.norm_w = d->fused_norm ? d->attn_norm[l] : nullptr;
@@ -395,7 +352,6 @@ void record_step(vx_decoder *d, int max_pos) {
     qa.cache_batch_stride = d->cache_batch_stride;
     qa.max_seq = c.max_seq;
     need(vxb::qkv_rope_store(qa, s), "q/k/v");
-    partials_taken();
 
     vxb::AttnArgs aa{};
     aa.q = d->q;
@@ -423,13 +379,13 @@ void record_step(vx_decoder *d, int max_pos) {
     oa.x = d->att;
     oa.x_stride = oa.cols;
     oa.batch = B;
-    oa.y = d->ranks > 1 ? d->tmp : d->x;
+    oa.y = d->ranks > 1 && !d->push ? d->tmp : d->x;
     oa.y_stride = c.dim;
     oa.mode = d->push ? 3 : (d->ranks > 1 ? 0 : 1);
     oa.push = &d->tp;
     need(vxb::matvec(oa, s), "the output projection");
     launches += 3;
-    after_push();
+    launches += add_partials(d);
 
     vxb::SwigluArgs sa{};
     sa.w = d->w_gate[l];
@@ -437,8 +393,7 @@ void record_step(vx_decoder *d, int max_pos) {
     sa.wbf16 = bf;
     sa.rows = d->hidden_local;
     sa.cols = c.dim;
-    sa.x = d->fold ? x_cur : normed(d, d->ffn_norm[l], launches);
-    sa.gather = take_partials();
+    sa.x = normed(d, d->ffn_norm[l], launches);
     sa.x_stride = c.dim;
     sa.out = d->h;
     sa.out_stride = d->hidden_local;
@@ -447,7 +402,6 @@ void record_step(vx_decoder *d, int max_pos) {
     sa.norm_bf16 = bf;
     sa.eps = c.eps;
     need(vxb::swiglu(sa, s), "gate/up");
-    partials_taken();
 
     vxb::MatvecArgs da{};
     da.w = d->w_down[l];
@@ -457,13 +411,13 @@ void record_step(vx_decoder *d, int max_pos) {
     da.x = d->h;
     da.x_stride = d->hidden_local;
     da.batch = B;
-    da.y = d->ranks > 1 ? d->tmp : d->x;
+    da.y = d->ranks > 1 && !d->push ? d->tmp : d->x;
     da.y_stride = c.dim;
     da.mode = d->push ? 3 : (d->ranks > 1 ? 0 : 1);
     da.push = &d->tp;
     need(vxb::matvec(da, s), "the down projection");
     launches += 2;
-    after_push();
+    launches += add_partials(d);
   }
 
   if (d->mma) {
@@ -475,8 +429,7 @@ void record_step(vx_decoder *d, int max_pos) {
   la.wbf16 = bf;
   la.rows = d->vocab_local;
   la.cols = c.dim;
-  la.x = d->fold ? x_cur : normed(d, d->final_norm, launches);
-  la.gather = take_partials();
+  la.x = normed(d, d->final_norm, launches);
   la.x_stride = c.dim;
   la.batch = B;
   la.norm_w = d->fused_norm ? d->final_norm : nullptr;
@@ -486,7 +439,6 @@ void record_step(vx_decoder *d, int max_pos) {
   la.y_stride = d->vocab_local;
   la.mode = 0;
   need(vxb::matvec(la, s), "the logits");
-  partials_taken();
   ++launches;
   }
   if (d->ranks == 1) {
@@ -606,7 +558,6 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
   d->cache_layer_stride = d->cache_batch_stride * B;
   d->x = dev_alloc<float>((size_t)B * c.dim);
   d->tmp = dev_alloc<float>((size_t)B * c.dim);
-  d->x2 = dev_alloc<float>((size_t)B * c.dim);
   d->xn = dev_alloc<float>((size_t)B * c.dim);
   d->fused_norm = (size_t)B * ((c.dim + 255) / 256 * 256) * sizeof(float) <= 96 * 1024;
   d->q = dev_alloc<float>((size_t)B * d->q_local * c.head_dim);
@@ -652,12 +603,6 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
     d->mma_scratch = dev_alloc<float>(vxb::batched_proj_scratch_floats(rows_max, B));
     d->mma = true;
   }
-  /* Folding the sum into the next projection's prologue (VXB_TP_FOLD=1) makes
-     every block read every rank's partials; a kernel of its own with one value
-     per thread is cheaper: 539 against 519 tokens/s on two GPUs, and folded
-     four GPUs gave 464. */
-  const char *fold_env = getenv("VXB_TP_FOLD");
-  d->fold = d->push && d->fused_norm && fold_env && fold_env[0] == '1';
   CUDA_OK(cudaDeviceSynchronize());
   return d;
 }
@@ -678,7 +623,7 @@ void vx_decoder_destroy(vx_decoder *d) {
   }
   for (auto &g : d->graphs)
     cudaGraphExecDestroy(g.second);
-  for (void *p : {(void *)d->x, (void *)d->x2, (void *)d->xn, (void *)d->tmp, (void *)d->q, (void *)d->att,
+  for (void *p : {(void *)d->x, (void *)d->xn, (void *)d->tmp, (void *)d->q, (void *)d->att,
                   (void *)d->h, (void *)d->logits, (void *)d->k_cache,
                   (void *)d->v_cache, (void *)d->scratch, (void *)d->counters,
                   (void *)d->tokens, (void *)d->positions,

@@ -820,6 +820,34 @@ bool run_device_image(const void *payload, size_t size, void **args,
   if (!vx_launch_build_params(args, tags, num_args, &params))
     return false; /* a publication slot: no device form exists for it */
 
+  /* `assert_flag=1` (reference runtime/vx_kernel_launch.h:379-393): the kernel
+     takes one parameter more than the dispatch carries, a pointer to a 4-byte
+     integer in device memory that a failed `assert` sets; the kernel then
+     runs on to its end. The integer is cleared on the stream before the
+     launch and read after it; a value other than 0 stops the program, as a
+     failed assert on the host does. One integer per GPU, kept for the life of
+     the process. Reading it waits for the kernel, which a recording graph
+     cannot hold. */
+  int32_t *assert_word = nullptr;
+  void *assert_param = nullptr;
+  if (vx_launch_takes_assert_flag(payload, size)) {
+    if (recording())
+      refuse_in_recording("A kernel built with asserts is checked after it ran",
+                          "Build the kernel without asserts for a recording.");
+    static std::mutex mu;
+    static std::unordered_map<int, int32_t *> words;
+    std::lock_guard<std::mutex> lock(mu);
+    int32_t *&word = words[device];
+    if (!word)
+      CUDA_OK(cudaMalloc((void **)&word, sizeof(int32_t)));
+    assert_word = word;
+    if (params.count >= VX_LAUNCH_MAX_PARAMS)
+      fatal("%s has more parameters than a launch can carry", name);
+    assert_param = assert_word;
+    params.params[params.count++] = &assert_param;
+    CUDA_OK(cudaMemsetAsync(assert_word, 0, sizeof(int32_t), t_stream));
+  }
+
   if (k.params != params.count)
     fatal("%s declares %d parameters and its arguments produced %d.\n"
           "          Launching would read past what was supplied. The compiler's "
@@ -900,6 +928,17 @@ bool run_device_image(const void *payload, size_t size, void **args,
     fatal("launching %s failed: %s", name, err ? err : "?");
   }
   started_kernel(name);
+  if (assert_word) {
+    int32_t failed = 0;
+    const cudaError_t e = cudaMemcpyAsync(&failed, assert_word, sizeof failed,
+                                          cudaMemcpyDeviceToHost, t_stream);
+    const cudaError_t w =
+        e == cudaSuccess ? cudaStreamSynchronize(t_stream) : e;
+    if (w != cudaSuccess)
+      fatal("%s faulted on GPU %d: %s", name, device, cudaGetErrorString(w));
+    if (failed != 0)
+      fatal("an assert failed in %s", name);
+  }
   if (timed) {
     float ms = 0;
     cudaEventRecord(t1, t_stream);

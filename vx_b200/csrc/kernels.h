@@ -56,21 +56,26 @@ struct MatvecArgs {
   bool norm_bf16;
   float eps;
   /* epilogue */
-  int mode;            /* 0 y = s, 1 y += s, 2 y = s + bias, 3 push to peers */
+  int mode;            /* 0 y = s, 1 y += s, 2 y = s + bias,
+                          3 y += the sum of all ranks' s (see TpPush) */
   const void *bias;    /* mode 2, bf16 */
   const struct TpPush *push; /* mode 3 */
-  const struct TpGather *gather; /* NULL, or: x is x + the ranks' partials */
 };
 
-/* Mode 3: the projection is one rank's partial of a row-split product. Every
-   finished value goes straight into slot `rank` of EVERY rank's receive buffer
-   (stores over NVLink into peer memory; no y is written) as an 8-byte pair
-   (value, call number): an aligned 8-byte store arrives whole, so the pair is
-   its own flag and the exchange needs no fence, no counter and no separate
-   signal. Receive buffers: pairs [2 sets][ranks][count]; call c (1, 2, ...)
-   uses set c & 1, so that a rank that is one call ahead does not overwrite
-   what a slower rank still reads. `epoch` (device int32) holds the number of
-   calls completed so far. */
+/* Mode 3: the projection is one rank's partial of a row-split product, and
+   y += the sum over ranks of the partials, in one kernel. A warp that finishes
+   two rows stores its two values straight into slot `rank` of every OTHER
+   rank's receive buffer (stores over NVLink into peer memory) as (value, call
+   number) pairs -- an aligned 8-byte store arrives whole, so a pair is its own
+   arrival flag and the exchange needs no fence, no counter and no separate
+   signal -- then waits (bounded) for the other ranks' pairs of the same two
+   rows in its own buffer and adds all partials to y in rank order: every rank
+   adds the same values in the same order, so y stays identical on all ranks.
+   Receive buffers: pairs [2 sets][ranks][count]; call c (1, 2, ...) uses set
+   c & 1: a rank cannot be two calls ahead of another, because it needs that
+   rank's values of the call between. `epoch` (device int32) holds the number
+   of calls completed so far; the block that finishes last (counted in `done`,
+   zero between launches) advances it. */
 constexpr int kMaxTpRanks = 8;
 struct TpPair {
   float value;
@@ -79,29 +84,10 @@ struct TpPair {
 struct TpPush {
   TpPair *slots[kMaxTpRanks]; /* per rank: its receive slots */
   int ranks, rank;
-  int64_t count;              /* values per slot: batch * rows */
-  const int32_t *epoch;       /* this rank's, device memory */
+  int64_t count;              /* values per slot: batch * rows (even) */
+  int32_t *epoch;             /* this rank's, device memory */
+  int32_t *done;
 };
-/* The receiving side folded into the NEXT projection's prologue: its input is
-   x_in + the ranks' partials, in rank order, each taken when its pair carries
-   call epoch + 1 (a bounded wait: on expiry the status word is set and the
-   value is used as it is). Block 0 also stores the sum to x_out, a buffer
-   other than x_in (the residual stream for what follows); the block that
-   finishes last advances epoch. For projections with a fused RMSNorm. */
-struct TpGather {
-  const TpPair *slots; /* this rank's receive slots */
-  int32_t *epoch;      /* calls completed so far */
-  int32_t *done;       /* block counter, zero between launches */
-  int ranks;
-  int64_t count;       /* values per slot: batch * cols */
-  float *x_out;
-};
-/* The same sum as a kernel of its own: x[i] += the ranks' partials in rank
-   order, one value per thread; the block that finishes last (counted in
-   `done`, zero between launches) advances epoch. */
-const char *tp_reduce_add(float *x, const TpPair *my_slots, int32_t *epoch,
-                          int32_t *done, int ranks, int64_t count,
-                          cudaStream_t stream);
 int tp_status(cudaStream_t stream);
 const char *matvec(const MatvecArgs &a, cudaStream_t stream);
 
@@ -119,7 +105,6 @@ struct SwigluArgs {
   const void *norm_w;
   bool norm_bf16;
   float eps;
-  const struct TpGather *gather;
 };
 const char *swiglu(const SwigluArgs &a, cudaStream_t stream);
 
@@ -152,7 +137,6 @@ struct QkvArgs {
   float *k_cache, *v_cache;
   int64_t cache_batch_stride;
   int max_seq;
-  const struct TpGather *gather;
 };
 const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream);
 

@@ -114,8 +114,6 @@ struct RowDotParams {
   int max_seq;
   /* EPI_PUSH */
   TpPush tp;
-  /* x = x + the ranks' partials of the projection before (ranks 0: no) */
-  TpGather gather;
 };
 
 /* acc[b] += sum over the E weights of one 16-byte word (8 bf16 or 4 f32) of
@@ -141,11 +139,21 @@ fma16(const uint4 &wv, const float (&xv)[B][16 / sizeof(W)], float (&acc)[B]) {
       acc[b] = fmaf(wf[e], xv[b][e], acc[b]);
 }
 
-/* A (value, call) pair of the pushed exchange: stored and loaded as one 8-byte
-   access that bypasses L1, so it arrives whole and is seen when it arrives. */
+/* The pushed exchange moves (value, call) pairs: an aligned 8-byte store
+   arrives whole, so a pair that carries the expected call number is complete
+   and is its own arrival flag. An item's two rows travel as two pairs in one
+   16-byte store; each half is still checked by its own call number. Stores
+   and loads bypass L1 (volatile): a pair is seen when it arrives. */
 __device__ __forceinline__ void pair_store(TpPair *at, float v, int call) {
   asm volatile("st.volatile.global.v2.b32 [%0], {%1, %2};" ::"l"(at),
                "r"(__float_as_uint(v)), "r"(call)
+               : "memory");
+}
+__device__ __forceinline__ void pair2_store(TpPair *at, float v0, float v1,
+                                            int call) {
+  asm volatile("st.volatile.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(at),
+               "r"(__float_as_uint(v0)), "r"(call), "r"(__float_as_uint(v1)),
+               "r"(call)
                : "memory");
 }
 __device__ __forceinline__ bool pair_load(const TpPair *at, int call, float &v) {
@@ -158,17 +166,17 @@ __device__ __forceinline__ bool pair_load(const TpPair *at, int call, float &v) 
   v = __uint_as_float(bits);
   return seen == call;
 }
-/* Spin (bounded) until the pair carries `call`. */
-__device__ __noinline__ float pair_wait(const TpPair *at, int call, int *status) {
-  float v;
-  const long long t0 = clock64();
-  while (!pair_load(at, call, v)) {
-    if (clock64() - t0 > ptx::kWaitCycles) {
-      atomicCAS(status, 0, 0x53);
-      break;
-    }
-  }
-  return v;
+__device__ __forceinline__ bool pair2_load(const TpPair *at, int call, float &v0,
+                                           float &v1) {
+  uint32_t b0, b1;
+  int c0, c1;
+  asm volatile("ld.volatile.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(b0), "=r"(c0), "=r"(b1), "=r"(c1)
+               : "l"(at)
+               : "memory");
+  v0 = __uint_as_float(b0);
+  v1 = __uint_as_float(b1);
+  return c0 == call && c1 == call;
 }
 
 /* The two weight rows of an item, and for q/k/v which head and pair it is. */
@@ -310,13 +318,6 @@ rowdot_kernel(const RowDotParams p) {
   chain_wait(); /* from here on: x, y, positions of the kernels before */
   const int push_call = EPI == EPI_PUSH ? *p.tp.epoch + 1 : 0;
   const int64_t push_set = push_call & 1;
-  /* The partials of the projection before this one, if their sum is folded in
-     here: pairs of set (call & 1). */
-  const int gather_call = p.gather.ranks ? *p.gather.epoch + 1 : 0;
-  const TpPair *gslots =
-      p.gather.ranks ? p.gather.slots + (int64_t)(gather_call & 1) *
-                                            p.gather.ranks * p.gather.count
-                     : nullptr;
 
   /* ---- prologue: x (normalised if asked) into shared memory ---- */
   float inv[B];
@@ -333,94 +334,39 @@ rowdot_kernel(const RowDotParams p) {
     for (int b = 0; b < B; ++b) {
       float ss = 0.0f;
       const float *px = p.x + b * p.x_stride;
-      /* Several loads in flight per thread: x was written by the kernel before
-         and comes from L2, a microsecond away; one load at a time made this
-         loop the longest part of a short projection. Without partials to
-         add: four values per load. */
-      if (!gslots) {
-        const float4 *px4 = reinterpret_cast<const float4 *>(px);
-        const int quads = cols / 4;
-        for (int q0 = threadIdx.x; q0 < quads; q0 += 4 * blockDim.x) {
-          float4 v[4], wn[4];
+      /* Several loads in flight per thread, four values per load: x was
+         written by the kernel before and comes from L2, a microsecond away;
+         one load at a time made this loop the longest part of a short
+         projection. */
+      const float4 *px4 = reinterpret_cast<const float4 *>(px);
+      const int quads = cols / 4;
+      for (int q0 = threadIdx.x; q0 < quads; q0 += 4 * blockDim.x) {
+        float4 v[4], wn[4];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int q = q0 + k * blockDim.x;
-            v[k] = wn[k] = make_float4(0, 0, 0, 0);
-            if (q < quads) {
-              v[k] = px4[q];
-              if (p.norm_bf16) {
-                const uint2 w = reinterpret_cast<const uint2 *>(p.norm_w)[q];
-                wn[k] = make_float4(bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y));
-              } else {
-                wn[k] = reinterpret_cast<const float4 *>(p.norm_w)[q];
-              }
-            }
-          }
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int q = q0 + k * blockDim.x;
-            if (q < quads) {
-              *reinterpret_cast<float4 *>(&xs[b * xs_stride + xs_at(4 * q)]) =
-                  make_float4(v[k].x * wn[k].x, v[k].y * wn[k].y, v[k].z * wn[k].z,
-                              v[k].w * wn[k].w);
-              ss = fmaf(v[k].x, v[k].x, ss);
-              ss = fmaf(v[k].y, v[k].y, ss);
-              ss = fmaf(v[k].z, v[k].z, ss);
-              ss = fmaf(v[k].w, v[k].w, ss);
-            }
-          }
-        }
-      } else
-      for (int i0 = threadIdx.x; i0 < cols; i0 += 8 * blockDim.x) {
-        float v[8], wn[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int i = i0 + k * blockDim.x;
-          v[k] = i < cols ? px[i] : 0.0f;
-          wn[k] = i >= cols ? 0.0f
-                  : p.norm_bf16 ? bf16_at(p.norm_w, i)
-                                : ((const float *)p.norm_w)[i];
-        }
-        if (gslots) {
-          /* x + partials in rank order (each pair is waited for where it has
-             not arrived yet); block 0 keeps the sum for later */
-          for (int r = 0; r < p.gather.ranks; ++r) {
-            float part[8];
-            bool in[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const int i = i0 + k * blockDim.x;
-              in[k] = i >= cols ||
-                      pair_load(gslots + r * p.gather.count + b * p.x_stride + i,
-                                gather_call, part[k]);
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const int i = i0 + k * blockDim.x;
-              if (i < cols) {
-                if (!in[k])
-                  part[k] = pair_wait(gslots + r * p.gather.count +
-                                          b * p.x_stride + i,
-                                      gather_call, &g_tp_status);
-                v[k] += part[k];
-              }
-            }
-          }
-          if (blockIdx.x == 0) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const int i = i0 + k * blockDim.x;
-              if (i < cols)
-                p.gather.x_out[b * p.x_stride + i] = v[k];
+        for (int k = 0; k < 4; ++k) {
+          const int q = q0 + k * blockDim.x;
+          v[k] = wn[k] = make_float4(0, 0, 0, 0);
+          if (q < quads) {
+            v[k] = px4[q];
+            if (p.norm_bf16) {
+              const uint2 w = reinterpret_cast<const uint2 *>(p.norm_w)[q];
+              wn[k] = make_float4(bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y));
+            } else {
+              wn[k] = reinterpret_cast<const float4 *>(p.norm_w)[q];
             }
           }
         }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int i = i0 + k * blockDim.x;
-          if (i < cols) {
-            xs[b * xs_stride + xs_at(i)] = v[k] * wn[k];
-            ss = fmaf(v[k], v[k], ss);
+        for (int k = 0; k < 4; ++k) {
+          const int q = q0 + k * blockDim.x;
+          if (q < quads) {
+            *reinterpret_cast<float4 *>(&xs[b * xs_stride + xs_at(4 * q)]) =
+                make_float4(v[k].x * wn[k].x, v[k].y * wn[k].y, v[k].z * wn[k].z,
+                            v[k].w * wn[k].w);
+            ss = fmaf(v[k].x, v[k].x, ss);
+            ss = fmaf(v[k].y, v[k].y, ss);
+            ss = fmaf(v[k].z, v[k].z, ss);
+            ss = fmaf(v[k].w, v[k].w, ss);
           }
         }
       }
@@ -538,24 +484,65 @@ rowdot_kernel(const RowDotParams p) {
       t1[b] = warp_sum(s1[b]) * inv[b];
       s0[b] = s1[b] = 0.0f;
     }
+    if (EPI == EPI_PUSH) {
+      /* This rank's partial of a row-split product. Lane r sends both values
+         of the item to rank r (slot `rank` of r's receive buffer, peer memory
+         over NVLink, one 16-byte store), then waits for rank r's partial of
+         the same two rows in this rank's own buffer (a bounded wait on
+         exactly that pair of pairs: every rank runs the same rows at about
+         the same time). The partials are added to the residual in rank
+         order, the same order on every rank, so y stays identical on all of
+         them. The exchange has no kernel of its own, no fence, no counter. */
+      const int ra = 2 * item;
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const int64_t in_set = b * p.y_stride + ra;
+        float v0 = t0[b], v1 = t1[b]; /* every lane holds the warp's sums */
+        if (lane < p.tp.ranks && lane != p.tp.rank) {
+          TpPair *to = p.tp.slots[lane] +
+                       (push_set * p.tp.ranks + p.tp.rank) * p.tp.count + in_set;
+          if (r1)
+            pair2_store(to, v0, v1, push_call);
+          else
+            pair_store(to, v0, push_call);
+          const TpPair *from = p.tp.slots[p.tp.rank] +
+                               (push_set * p.tp.ranks + lane) * p.tp.count + in_set;
+          const long long began = clock64();
+          for (;;) {
+            const bool here = r1 ? pair2_load(from, push_call, v0, v1)
+                                 : pair_load(from, push_call, v0);
+            if (here)
+              break;
+            /* a wait that ran out anywhere ends every later wait at once */
+            if (*(volatile int *)&g_tp_status != 0 ||
+                clock64() - began > ptx::kWaitCycles) {
+              atomicCAS(&g_tp_status, 0, 0x53);
+              break;
+            }
+          }
+        }
+        float *y = p.y + b * p.y_stride;
+        float s0v = lane == 0 ? y[ra] : 0.0f;
+        float s1v = (lane == 0 && r1) ? y[ra + 1] : 0.0f;
+        for (int r = 0; r < p.tp.ranks; ++r) {
+          s0v += __shfl_sync(0xffffffffu, v0, r);
+          s1v += __shfl_sync(0xffffffffu, v1, r);
+        }
+        if (lane == 0) {
+          y[ra] = s0v;
+          if (r1)
+            y[ra + 1] = s1v;
+        }
+      }
+      continue;
+    }
     if (lane != 0)
       continue;
 
     /* ---- epilogue, lane 0 ---- */
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      if (EPI == EPI_PUSH) {
-        /* This rank's partial of a row-split product, stored into slot
-           `rank` of every rank's receive buffer (peer memory over NVLink). */
-        const int ra = 2 * item;
-        const int64_t at =
-            (push_set * p.tp.ranks + p.tp.rank) * p.tp.count + b * p.y_stride + ra;
-        for (int r = 0; r < p.tp.ranks; ++r) {
-          pair_store(p.tp.slots[r] + at, t0[b], push_call);
-          if (r1)
-            pair_store(p.tp.slots[r] + at + 1, t1[b], push_call);
-        }
-      } else if (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_BIAS) {
+      if (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_BIAS) {
         float *y = p.y + b * p.y_stride;
         const int ra = 2 * item, rb = 2 * item + 1;
         float v0 = t0[b], v1 = t1[b];
@@ -623,15 +610,15 @@ rowdot_kernel(const RowDotParams p) {
     }
   }
 
-  if (p.gather.ranks) {
-    /* Every block has read the epoch and the slots once the last one is here. */
+  if (EPI == EPI_PUSH) {
+    /* The block that finishes last advances the call count: every block read
+       it when it began. */
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence();
-      const int arrived = atomicAdd(p.gather.done, 1);
-      if (arrived == (int)gridDim.x - 1) {
-        *p.gather.done = 0;
-        *p.gather.epoch = gather_call;
+      if (atomicAdd(p.tp.done, 1) == (int)gridDim.x - 1) {
+        *p.tp.done = 0;
+        *p.tp.epoch = push_call;
       }
     }
   }
@@ -703,49 +690,6 @@ const char *launch_rowdot(RowDotParams &p, bool wbf16, cudaStream_t stream) {
                : launch_rowdot_w<float, EPI>(p, stream);
 }
 
-/* ---------------------------------------------------- the receiving side
- * of a pushed projection as a kernel of its own (for projections that cannot
- * take the sum in their prologue): x += the ranks' partials in rank order,
- * each pair waited for (bounded) until it carries this call's number -- every
- * rank adds the same values in the same order, so x stays identical on all
- * ranks. */
-__global__ void __launch_bounds__(256)
-tp_reduce_add_kernel(float *x, const TpPair *slots, int32_t *epoch, int32_t *done,
-                     int ranks, int64_t count) {
-  chain_release();
-  chain_wait();
-  const int call = *epoch + 1;
-  const TpPair *mine = slots + (int64_t)(call & 1) * ranks * count;
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < count) {
-    /* one value per thread, every rank's pair asked for at once */
-    float part[kMaxTpRanks];
-    bool in[kMaxTpRanks];
-#pragma unroll
-    for (int r = 0; r < kMaxTpRanks; ++r)
-      in[r] = r >= ranks || pair_load(mine + r * count + i, call, part[r]);
-    float v = x[i];
-#pragma unroll
-    for (int r = 0; r < kMaxTpRanks; ++r)
-      if (r < ranks) {
-        if (!in[r])
-          part[r] = pair_wait(mine + r * count + i, call, &g_tp_status);
-        v += part[r];
-      }
-    x[i] = v;
-  }
-  /* the block that finishes last advances the call count: every block has
-     read it by then */
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(done, 1) == (int)gridDim.x - 1) {
-      *done = 0;
-      *epoch = call;
-    }
-  }
-}
-
 /* ------------------------------------------------------------- rms_norm
  * nn_rms_norm (nn.vx:212-239); one block per sequence. */
 __global__ void __launch_bounds__(1024)
@@ -808,25 +752,24 @@ __global__ void rope_store_kernel(float *q_out, float *k_cache, float *v_cache,
  * running (max, sum, weighted V) per query head, and the four warps are merged
  * in warp order.  The block that finishes last for a (sequence, head tile)
  * merges the parts of all splits in split order. */
-constexpr int ATT_WARPS = 4;
-
-/* What the four warps of one unit share. */
-template <int GH> struct AttnShared {
+/* What the ATT_WARPS warps of one unit share. */
+template <int GH, int ATT_WARPS> struct AttnShared {
   float m[ATT_WARPS][GH], l[ATT_WARPS][GH];
   __align__(16) float acc[ATT_WARPS][GH][128];
   int is_last;
 };
-__device__ __forceinline__ void sync_four_warps(int bar_id) {
+template <int ATT_WARPS> __device__ __forceinline__ void sync_unit_warps(int bar_id) {
   asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(ATT_WARPS * 32) : "memory");
 }
 
 /* One unit of work: (split, KV head and head tile `y`, sequence b), done by the
-   four warps that meet at named barrier `bar_id`. CHAINED: the caller is a
+   ATT_WARPS warps (4, 8 or 16: as many as fill the GPU for the number of heads
+   there are) that meet at named barrier `bar_id`. CHAINED: the caller is a
    kernel of its own in a chain of dependent launches. */
-template <int GH, bool CHAINED, int CL = 0>
+template <int GH, bool CHAINED, int CL, int ATT_WARPS>
 __device__ __forceinline__ void
 attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
-               int lane, AttnShared<GH> &sh, int bar_id) {
+               int lane, AttnShared<GH, ATT_WARPS> &sh, int bar_id) {
   /* The position was written by the step before this one, and every cache row
      below it by earlier steps: those may be read before the kernels of this
      step have finished. Row `pos` and q come from the kernel just before. */
@@ -858,9 +801,9 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
   const int settled = !a.rows_settled ? 0
                       : a.fresh_from  ? min(pos, a.fresh_from[0])
                                       : pos;
-  /* A warp takes every fourth position, NB of them at a time so that their
-     loads are in flight together: with 32 positions per block that is one
-     round trip to memory per warp. */
+  /* A warp takes every ATT_WARPS-th position, NB of them at a time so that
+     their loads are in flight together: with 32 positions per block of four
+     warps that is one round trip to memory per warp. */
   constexpr int NB = 8;
   float4 kv[NB], vv[NB];
   auto load_batch = [&](int t0, bool old_rows_only) {
@@ -940,7 +883,7 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
     }
   }
 
-  /* ---- merge the four warps, in warp order ---- */
+  /* ---- merge the warps, in warp order ---- */
   float (&sm_m)[ATT_WARPS][GH] = sh.m;
   float (&sm_l)[ATT_WARPS][GH] = sh.l;
   float (&sm_acc)[ATT_WARPS][GH][128] = sh.acc;
@@ -954,7 +897,7 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
     if (active)
       *reinterpret_cast<float4 *>(&sm_acc[warp][h][lane * 4]) = acc[h];
   }
-  sync_four_warps(bar_id);
+  sync_unit_warps<ATT_WARPS>(bar_id);
   const int row_floats = hd + 2;
   float *part = a.scratch;
   auto part_at = [&](int head, int sp) {
@@ -999,7 +942,7 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
         float4 pa[NP];
 #pragma unroll
         for (int r = 0; r < CL; ++r) {
-          const AttnShared<GH> *peer = cluster.map_shared_rank(&sh, r);
+          const AttnShared<GH, ATT_WARPS> *peer = cluster.map_shared_rank(&sh, r);
           pm[r] = peer->m[0][h];
           pl[r] = peer->l[0][h];
           pa[r] = active
@@ -1065,7 +1008,7 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
         *counter = 0; /* ready for the next launch */
     }
   }
-  sync_four_warps(bar_id);
+  sync_unit_warps<ATT_WARPS>(bar_id);
   if (!is_last)
     return;
   __threadfence();
@@ -1103,22 +1046,23 @@ attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
    memory, a fence, an atomic and a last block: three round trips shorter.
    This is what kAttnAuto runs unless the process chose otherwise. */
 constexpr int ATT_CLUSTER = 8;
-template <int GH>
+template <int GH, int ATT_WARPS>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_cluster_kernel(const AttnArgs a) {
-  __shared__ AttnShared<GH> sh;
+  __shared__ AttnShared<GH, ATT_WARPS> sh;
   chain_release();
-  attention_unit<GH, true, ATT_CLUSTER>(a, blockIdx.x, blockIdx.y, blockIdx.z,
-                                        threadIdx.x >> 5, threadIdx.x & 31, sh, 0);
+  attention_unit<GH, true, ATT_CLUSTER, ATT_WARPS>(
+      a, blockIdx.x, blockIdx.y, blockIdx.z, threadIdx.x >> 5, threadIdx.x & 31,
+      sh, 0);
 }
 
 template <int GH>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
+__global__ void __launch_bounds__(4 * 32)
 attention_decode_kernel(const AttnArgs a) {
-  __shared__ AttnShared<GH> sh;
+  __shared__ AttnShared<GH, 4> sh;
   chain_release();
-  attention_unit<GH, true>(a, blockIdx.x, blockIdx.y, blockIdx.z,
-                           threadIdx.x >> 5, threadIdx.x & 31, sh, 0);
+  attention_unit<GH, true, 0, 4>(a, blockIdx.x, blockIdx.y, blockIdx.z,
+                                 threadIdx.x >> 5, threadIdx.x & 31, sh, 0);
 }
 
 /* ---------------------------------------------------------------- argmax
@@ -1216,11 +1160,6 @@ const char *matvec(const MatvecArgs &a, cudaStream_t stream) {
   p.y = a.y;
   p.y_stride = a.y_stride;
   p.bias = a.bias;
-  if (a.gather) {
-    if (!a.norm_w)
-      return "partials are folded into a projection with a fused RMSNorm only";
-    p.gather = *a.gather;
-  }
   switch (a.mode) {
   case 0: return launch_rowdot<EPI_STORE>(p, a.wbf16, stream);
   case 1: return launch_rowdot<EPI_ADD>(p, a.wbf16, stream);
@@ -1228,6 +1167,8 @@ const char *matvec(const MatvecArgs &a, cudaStream_t stream) {
   case 3:
     if (!a.push || a.push->ranks < 1 || a.push->ranks > kMaxTpRanks)
       return "a pushed projection needs the receive buffers of 1 to 8 ranks";
+    if (a.push->count % 2 != 0 || a.y_stride % 2 != 0)
+      return "a pushed projection needs an even number of rows";
     p.tp = *a.push;
     return launch_rowdot<EPI_PUSH>(p, a.wbf16, stream);
   default: return "unknown matvec mode";
@@ -1270,11 +1211,6 @@ const char *swiglu(const SwigluArgs &a, cudaStream_t stream) {
   p.eps = a.eps;
   p.y = a.out;
   p.y_stride = a.out_stride;
-  if (a.gather) {
-    if (!a.norm_w)
-      return "partials are folded into a projection with a fused RMSNorm only";
-    p.gather = *a.gather;
-  }
   return launch_rowdot<EPI_SWIGLU>(p, a.wbf16, stream);
 }
 
@@ -1310,22 +1246,7 @@ const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream) {
   p.v_cache = a.v_cache;
   p.cache_batch_stride = a.cache_batch_stride;
   p.max_seq = a.max_seq;
-  if (a.gather) {
-    if (!a.norm_w)
-      return "partials are folded into a projection with a fused RMSNorm only";
-    p.gather = *a.gather;
-  }
   return launch_rowdot<EPI_QKV>(p, a.wbf16, stream);
-}
-
-const char *tp_reduce_add(float *x, const TpPair *my_slots, int32_t *epoch,
-                          int32_t *done, int ranks, int64_t count,
-                          cudaStream_t stream) {
-  if (ranks < 1 || ranks > kMaxTpRanks)
-    return "1 to 8 ranks";
-  launch_chained(tp_reduce_add_kernel, dim3((unsigned)((count + 255) / 256)),
-                 dim3(256), 0, stream, x, my_slots, epoch, done, ranks, count);
-  return check_launch("the partial-sum launch");
 }
 
 int tp_status(cudaStream_t stream) {
@@ -1397,28 +1318,37 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
     return "unknown attention kernel";
   if (which == kAttnCluster) {
     const dim3 cgrid(ATT_CLUSTER, a.kv_heads * tiles, a.batch);
-    const dim3 block(ATT_WARPS * 32);
-    if (gh == 4)
-      launch_chained_cluster(attention_cluster_kernel<4>, cgrid, block,
-                             ATT_CLUSTER, stream, a);
-    else if (gh == 2)
-      launch_chained_cluster(attention_cluster_kernel<2>, cgrid, block,
-                             ATT_CLUSTER, stream, a);
-    else
-      launch_chained_cluster(attention_cluster_kernel<1>, cgrid, block,
-                             ATT_CLUSTER, stream, a);
+    /* Warps per block by how many blocks there are: with few heads (a rank of
+       a tensor-parallel job holds 4 of 32) sixteen warps per block put the
+       positions of a head on 128 warps, one round trip to memory each; with
+       every SM already holding several blocks, four. */
+    const int64_t blocks = (int64_t)cgrid.x * cgrid.y * cgrid.z;
+    const int warps = blocks <= sm_count() ? 16 : (blocks <= 2 * sm_count() ? 8 : 4);
+    auto go = [&](auto kernel) {
+      launch_chained_cluster(kernel, cgrid, dim3(warps * 32), ATT_CLUSTER, stream, a);
+    };
+    if (gh == 4) {
+      if (warps == 16) go(attention_cluster_kernel<4, 16>);
+      else if (warps == 8) go(attention_cluster_kernel<4, 8>);
+      else go(attention_cluster_kernel<4, 4>);
+    } else if (gh == 2) {
+      if (warps == 16) go(attention_cluster_kernel<2, 16>);
+      else if (warps == 8) go(attention_cluster_kernel<2, 8>);
+      else go(attention_cluster_kernel<2, 4>);
+    } else {
+      if (warps == 16) go(attention_cluster_kernel<1, 16>);
+      else if (warps == 8) go(attention_cluster_kernel<1, 8>);
+      else go(attention_cluster_kernel<1, 4>);
+    }
     return check_launch("the attention launch");
   }
   const dim3 grid(a.max_pos / a.split + 1, a.kv_heads * tiles, a.batch);
   if (gh == 4)
-    launch_chained(attention_decode_kernel<4>, grid, dim3(ATT_WARPS * 32), 0,
-                   stream, a);
+    launch_chained(attention_decode_kernel<4>, grid, dim3(4 * 32), 0, stream, a);
   else if (gh == 2)
-    launch_chained(attention_decode_kernel<2>, grid, dim3(ATT_WARPS * 32), 0,
-                   stream, a);
+    launch_chained(attention_decode_kernel<2>, grid, dim3(4 * 32), 0, stream, a);
   else
-    launch_chained(attention_decode_kernel<1>, grid, dim3(ATT_WARPS * 32), 0,
-                   stream, a);
+    launch_chained(attention_decode_kernel<1>, grid, dim3(4 * 32), 0, stream, a);
   return check_launch("the attention launch");
 }
 
