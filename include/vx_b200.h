@@ -82,13 +82,53 @@ void vx_nn_argmax(VX_TENSOR1(out), VX_TENSOR1(logits), int32_t n);
 void vx_nn_embed(VX_TENSOR1(x), VX_TENSOR1(table), VX_TENSOR1(token),
                  int32_t dim);
 
+/* The same projections with quantised weights. fp8 (nn.vx:1296-1640): `w` is
+   f8e4m3 codes, 4 to a 32-bit word, `scales` one f32 per block of 128 x 128
+   weights, [ceil(rows / 128), cols / 128]; rows a multiple of 4, cols of 128.
+   Q4_0 (nn.vx:1645-2100): codes of 4 bits, 8 to a word, weight = (code - 8) *
+   scale with one f16 scale per 32 weights of a row, [rows, cols / 32]; rows a
+   multiple of 4, cols of 32. The bias of the q/k/v projections is bf16. */
+/* nn_matvec_fp8 nn.vx:1306, _add :1367, _heads_add :1427, nn_qkv_fp8 :1492,
+   nn_swiglu_fp8 :1577 */
+void vx_nn_matvec_fp8(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                      VX_TENSOR1(x), int32_t rows, int32_t cols);
+void vx_nn_matvec_fp8_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                          VX_TENSOR1(x), int32_t rows, int32_t cols);
+void vx_nn_matvec_fp8_heads_add(VX_TENSOR1(y), VX_TENSOR1(w),
+                                VX_TENSOR1(scales), VX_TENSOR2(x), int32_t rows,
+                                int32_t heads, int32_t head_dim);
+void vx_nn_qkv_fp8(VX_TENSOR2(q), VX_TENSOR2(k), VX_TENSOR2(v), VX_TENSOR1(w),
+                   VX_TENSOR1(scales), VX_TENSOR1(b), VX_TENSOR1(x),
+                   int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                   int32_t cols);
+void vx_nn_swiglu_fp8(VX_TENSOR1(out), VX_TENSOR1(w), VX_TENSOR1(scales),
+                      VX_TENSOR1(x), int32_t rows, int32_t cols);
+/* nn_matvec_q4 nn.vx:1666, _add :1748, _heads_add :1831, nn_qkv_q4 :1912,
+   nn_swiglu_q4 :2005 */
+void vx_nn_matvec_q4(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                     VX_TENSOR1(x), int32_t rows, int32_t cols);
+void vx_nn_matvec_q4_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                         VX_TENSOR1(x), int32_t rows, int32_t cols);
+void vx_nn_matvec_q4_heads_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                               VX_TENSOR2(x), int32_t rows, int32_t heads,
+                               int32_t head_dim);
+void vx_nn_qkv_q4(VX_TENSOR2(q), VX_TENSOR2(k), VX_TENSOR2(v), VX_TENSOR1(w),
+                  VX_TENSOR1(scales), VX_TENSOR1(b), VX_TENSOR1(x),
+                  int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                  int32_t cols);
+void vx_nn_swiglu_q4(VX_TENSOR1(out), VX_TENSOR1(w), VX_TENSOR1(scales),
+                     VX_TENSOR1(x), int32_t rows, int32_t cols);
+
 /* ---- a whole decoder token -------------------------------------------------- */
 typedef struct {
   int32_t dim, hidden, n_layers, q_heads, kv_heads, head_dim, vocab, max_seq;
   float eps;
   float rope_theta;
   /* 1: bf16 weights, half-split RoPE from tables (std::nn); 0: f32 weights,
-     interleaved RoPE computed from the position (llama2.vx). */
+     interleaved RoPE computed from the position (llama2.vx); 2 and 3: the
+     std::nn flavour with the four projections of every layer in fp8 or in
+     Q4_0 (their scales in vx_decoder_weights; norms, embedding and classifier
+     stay bf16; one sequence, one rank). */
   int32_t weights_bf16;
   int32_t batch; /* 1, 2, 4, 8 or 16 sequences */
   /* Tensor parallel: this process holds q_heads / tp_ranks query heads,
@@ -128,6 +168,14 @@ typedef struct {
   const void *lm_head;
   const float *cos;
   const float *sin;
+  /* weights_bf16 2 or 3: the scales of wq (q, k and v rows in one matrix), wo,
+     w_gate (gate rows then up rows) and w_down, one entry per layer: f32
+     [ceil(rows / 128), cols / 128] for fp8, f16 [rows, cols / 32] for Q4_0.
+     Not read otherwise. */
+  const void *const *s_qkv;
+  const void *const *s_o;
+  const void *const *s_gate_up;
+  const void *const *s_down;
 } vx_decoder_weights;
 
 typedef struct vx_decoder vx_decoder;
@@ -162,6 +210,23 @@ void *vx_decoder_stream(const vx_decoder *d);
 /* How many kernels one step launches (for accounting). */
 int32_t vx_decoder_kernels_per_step(const vx_decoder *d);
 
+/* A llama2.c checkpoint: the file the reference's llama programs read through
+   vx_load_config and vx_load_weights (stdlib/rust_core/src/ffi/llama.rs:11-47;
+   the order of the weights: stdlib/std/llama.vx:86-148). */
+typedef struct {
+  int32_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
+} vx_llama2c_config;
+/* Reads and checks the header (a negative vocab_size, llama2.c's mark of a
+   classifier of its own, comes back positive). 0, or -1 with the reason in
+   vx_b200_last_error(): no such file, a file shorter than its header says. */
+int32_t vx_b200_llama2c_config(const char *path, vx_llama2c_config *out);
+/* A decoder (f32 weights, interleaved RoPE: the llama2.vx flavour) over the
+   weights of the checkpoint, which are copied to the current GPU once and
+   belong to the decoder. max_seq 0: the file's seq_len. NULL with the reason in
+   vx_b200_last_error() when the file cannot be used. */
+vx_decoder *vx_decoder_from_llama2c(const char *path, int32_t batch,
+                                    int32_t max_seq);
+
 /* ---- direct calls -------------------------------------------------------------
  * All return 0, or -1 with the reason in vx_b200_last_error(). */
 const char *vx_b200_last_error(void);
@@ -169,7 +234,8 @@ const char *vx_b200_last_error(void);
 /* C[m,n] = A[m,k] * B[k,n], row-major device memory, strides in elements.
    dtype is a VX_DTYPE_* code (f32, f64, f16, bf16). route: 0 = as a dispatch
    would run it; for 16-bit types 1 = tcgen05 with B as stored, 2 = tcgen05
-   after transposing B into scratch ([n, k] elements), 3 = the plain kernel. */
+   after transposing B into scratch ([n, k] elements), 3 = the plain kernel,
+   4 and 5 = 1 and 2 on CTA pairs (256x256 tiles on the two SMs of a TPC). */
 int32_t vx_b200_gemm(int32_t dtype, int32_t route, int64_t m, int64_t n,
                      int64_t k, const void *a, int64_t lda, const void *b,
                      int64_t ldb, void *c, int64_t ldc, void *scratch);

@@ -623,6 +623,206 @@ void oracle_rope_tables(float *cos_t, float *sin_t, int max_seq, int head_dim,
     }
 }
 
+/* ---- fp8 and Q4_0 weights (nn.vx:1296-1303 and 1645-1663) ---------------------
+ * The restatements keep the reference kernels' order of sums; the *_f64
+ * functions are the plain loops of the reference's own tests
+ * (std_nn_fp8_kernels_match_loops_on_the_cpu.vx:82-103,
+ * std_nn_q4_kernels_match_loops_on_the_cpu.vx:119-131), against which those
+ * tests accept max |got - want| <= 1e-5 max |want|. */
+
+/* The value of an f8e4m3 code as the kernels' table has it (nn.vx:1316-1326):
+   e = 0 gives m * 2^-9; else the bits with 120 added to the exponent. */
+static inline float fp8_value(uint32_t code) {
+  const uint32_t mag = code & 127u;
+  float value;
+  if (mag < 8u) {
+    value = (float)mag * 0.001953125f;
+  } else {
+    const uint32_t bits = (mag << 20) + 1006632960u;
+    memcpy(&value, &bits, 4);
+  }
+  return code & 128u ? 0.0f - value : value;
+}
+static inline double fp8_value_f64(uint32_t code) {
+  const int e = (int)((code >> 3) & 15u);
+  const double m = (double)(code & 7u);
+  double v = e == 0 ? m / 8.0 * ldexp(1.0, -6) : (1.0 + m / 8.0) * ldexp(1.0, e - 7);
+  return code >= 128u ? 0.0 - v : v;
+}
+static inline uint32_t fp8_code(const uint32_t *w, int64_t at) {
+  return (w[at / 4] >> (8u * (uint32_t)(at % 4))) & 255u;
+}
+
+/* One row of nn_matvec_fp8 (nn.vx:1306-1363): 128 lanes, lane l takes the 8
+   columns l*8.. of every 1024; the 8 products are added left to right, the sum
+   times the block's scale joins the lane's total; the lanes are added in lane
+   order. srow: the row of the scales table (row / 128 of the whole matrix). */
+static float fp8_row(const uint32_t *w, int64_t first_code, const float *scales,
+                     int srow, const float *x, int cols) {
+  const int tiles = cols / 128;
+  float total = 0.0f;
+  for (int l = 0; l < 128; ++l) {
+    float acc = 0.0f;
+    for (int c = l * 8; c < cols; c += 1024) {
+      float sum = fp8_value(fp8_code(w, first_code + c)) * x[c];
+      for (int k = 1; k < 8; ++k)
+        sum = sum + fp8_value(fp8_code(w, first_code + c + k)) * x[c + k];
+      acc = acc + sum * scales[srow * tiles + c / 128];
+    }
+    total += acc;
+  }
+  return total;
+}
+
+/* nn_matvec_fp8 :1306, nn_matvec_fp8_add :1367, nn_matvec_fp8_heads_add :1427
+   (add = 1); row_base: the row of the whole matrix that row 0 here is. */
+void oracle_nn_matvec_fp8(float *y, const uint32_t *w, const float *scales,
+                          const float *x, int rows, int cols, int add,
+                          int row_base) {
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    const int whole = row_base + r;
+    const float s = fp8_row(w, (int64_t)whole * cols, scales, whole / 128, x, cols);
+    y[r] = add ? y[r] + s : s;
+  }
+}
+/* nn_swiglu_fp8 :1577-1640 */
+void oracle_nn_swiglu_fp8(float *out, const uint32_t *w, const float *scales,
+                          const float *x, int rows, int cols) {
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    const float g = fp8_row(w, (int64_t)r * cols, scales, r / 128, x, cols);
+    const float u = fp8_row(w, (int64_t)(rows + r) * cols, scales,
+                            (rows + r) / 128, x, cols);
+    out[r] = g / (1.0f + cr_expf(0.0f - g)) * u;
+  }
+}
+void oracle_fp8_dot_f64(double *want, const uint32_t *w, const float *scales,
+                        const float *x, int rows, int cols) {
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    double sum = 0.0;
+    for (int c = 0; c < cols; ++c)
+      sum = sum + fp8_value_f64(fp8_code(w, (int64_t)r * cols + c)) *
+                      (double)scales[(r / 128) * (cols / 128) + c / 128] *
+                      (double)x[c];
+    want[r] = sum;
+  }
+}
+
+/* IEEE half to float (the scales of Q4_0 are f16). */
+static inline float f16_to_f32(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  const uint32_t e = (h >> 10) & 31u, m = h & 1023u;
+  uint32_t bits;
+  if (e == 0) {
+    if (m == 0) {
+      bits = sign;
+    } else { /* subnormal: m * 2^-24 */
+      float v = (float)m * 5.9604644775390625e-8f;
+      memcpy(&bits, &v, 4);
+      bits |= sign;
+    }
+  } else if (e == 31) {
+    bits = sign | 0x7F800000u | (m << 13);
+  } else {
+    bits = sign | ((e + 112u) << 23) | (m << 13);
+  }
+  float out;
+  memcpy(&out, &bits, 4);
+  return out;
+}
+
+/* One row of nn_matvec_q4 (nn.vx:1666-1744): 32 lanes, lane l takes the two
+   words 2l, 2l+1 of every 64 (16 weights, one scale); a code in nibble t
+   enters as (word & mask_t) times x / 16^t, the 8 of every code comes off as
+   8 times the sum of the 16 values of x; the 16 products are added left to
+   right; (dot - sum8) times the scale joins the lane's total; the lanes are
+   added in lane order. w: this row's words; scales: this row's. */
+static float q4_row(const uint32_t *w, const uint16_t *scales, const float *x,
+                    int cols) {
+  const int words = cols / 8;
+  static const float inv16[8] = {1.0f, 0.0625f, 0.00390625f, 0.000244140625f,
+                                 0.0000152587890625f, 0.00000095367431640625f,
+                                 0.000000059604644775390625f,
+                                 0.0000000037252902984619140625f};
+  float total = 0.0f;
+  for (int l = 0; l < 32; ++l) {
+    float acc = 0.0f;
+    for (int i = l * 2; i < words; i += 64) {
+      const int c = i * 8;
+      float xp[16];
+      for (int t = 0; t < 16; ++t)
+        xp[t] = x[c + t];
+      float sum = xp[0];
+      for (int t = 1; t < 16; ++t)
+        sum = sum + xp[t];
+      const float sum8 = 8.0f * sum;
+      for (int t = 0; t < 16; ++t)
+        xp[t] = xp[t] * inv16[t & 7];
+      float dot = 0.0f;
+      for (int t = 0; t < 16; ++t) {
+        const uint32_t word = w[i + t / 8];
+        const float masked = (float)(word & (15u << (4 * (t & 7))));
+        dot = t == 0 ? masked * xp[0] : dot + masked * xp[t];
+      }
+      acc = acc + (dot - sum8) * f16_to_f32(scales[i / 4]);
+    }
+    total += acc;
+  }
+  return total;
+}
+/* nn_matvec_q4 :1666, _add :1748, _heads_add :1831 */
+void oracle_nn_matvec_q4(float *y, const uint32_t *w, const uint16_t *scales,
+                         const float *x, int rows, int cols, int add) {
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    const float s = q4_row(w + (int64_t)r * (cols / 8),
+                           scales + (int64_t)r * (cols / 32), x, cols);
+    y[r] = add ? y[r] + s : s;
+  }
+}
+/* nn_swiglu_q4 :2005-2100 */
+void oracle_nn_swiglu_q4(float *out, const uint32_t *w, const uint16_t *scales,
+                         const float *x, int rows, int cols) {
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    const float g = q4_row(w + (int64_t)r * (cols / 8),
+                           scales + (int64_t)r * (cols / 32), x, cols);
+    const float u = q4_row(w + (int64_t)(rows + r) * (cols / 8),
+                           scales + (int64_t)(rows + r) * (cols / 32), x, cols);
+    out[r] = g / (1.0f + cr_expf(0.0f - g)) * u;
+  }
+}
+void oracle_q4_dot_f64(double *want, const uint32_t *w, const uint16_t *scales,
+                       const float *x, int rows, int cols) {
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    double t = 0.0;
+    for (int c = 0; c < cols; ++c) {
+      const uint32_t word = w[(int64_t)r * (cols / 8) + c / 8];
+      const int code = (int)((word >> (4 * (c % 8))) & 15u);
+      t = t + (double)(code - 8) *
+                  (double)f16_to_f32(scales[(int64_t)r * (cols / 32) + c / 32]) *
+                  (double)x[c];
+    }
+    want[r] = t;
+  }
+}
+/* The tests' generators: word i of the random tensor `seed` is
+   mix(seed * 7919 + i); an fp8 word has no NaN code (0x7f, 0xff): such a byte
+   is lowered by one (std_nn_fp8_kernels_match_loops_on_the_cpu.vx:41-50). */
+void oracle_random_words(uint32_t *out, int64_t n, uint32_t seed, int fp8) {
+  for (int64_t i = 0; i < n; ++i) {
+    uint32_t word = mix32(seed * 7919u + (uint32_t)i);
+    if (fp8)
+      for (int k = 0; k < 4; ++k)
+        if (((word >> (8 * k)) & 127u) == 127u)
+          word = word - (1u << (8 * k));
+    out[i] = word;
+  }
+}
+
 /* ---- a decoder of std::nn operators (the 7B-shaped configuration) -----------
  * Per layer, in this order: attn_norm[dim], wqkv[(q+2kv)*hd, dim],
  * bqkv[(q+2kv)*hd], wo[dim, q*hd], ffn_norm[dim], w_gate_up[2*hidden, dim],

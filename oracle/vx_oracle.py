@@ -79,6 +79,14 @@ def _declare(L):
     L.oracle_attention_rows.argtypes = [vp, vp, vp, C.c_int, C.c_int, f32,
                                         C.c_int, vp, C.c_int, vp]
     L.oracle_all_reduce_sum_f32.argtypes = [vp, C.c_int, vp, i64]
+    L.oracle_nn_matvec_fp8.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int,
+                                       C.c_int]
+    L.oracle_nn_swiglu_fp8.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int]
+    L.oracle_fp8_dot_f64.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int]
+    L.oracle_nn_matvec_q4.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int]
+    L.oracle_nn_swiglu_q4.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int]
+    L.oracle_q4_dot_f64.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int]
+    L.oracle_random_words.argtypes = [vp, i64, C.c_uint32, C.c_int]
 
 
 def _p(a):
@@ -285,6 +293,64 @@ def nn_decode_step(cfg, embed, layers, final_norm, lm_head, cos, sin, kc, vc,
         _p(cos), _p(sin), _p(kc), _p(vc), int(token), int(pos),
         _p(logits) if want_logits else None)
     return (tok, logits) if want_logits else tok
+
+
+# ---- fp8 and Q4_0 weights -------------------------------------------------------------
+def random_words(n, seed, fp8=False):
+    """u32 words of the reference tests' generator; fp8: no NaN codes."""
+    out = np.empty(int(n), np.uint32)
+    lib().oracle_random_words(_p(out), out.size, seed, int(fp8))
+    return out
+
+
+def quant_matvec(quant, w, scales, x, rows, cols, y=None, row_base=0):
+    """nn_matvec_fp8 / nn_matvec_q4 (and their _add forms with y given)."""
+    add = y is not None
+    out = np.array(y, dtype=np.float32) if add else np.empty(rows, np.float32)
+    x = np.ascontiguousarray(x, np.float32)
+    if quant == "fp8":
+        lib().oracle_nn_matvec_fp8(_p(out), _p(w), _p(scales), _p(x), rows, cols,
+                                   int(add), row_base)
+    else:
+        w = w[row_base * (cols // 8):]
+        scales = scales[row_base * (cols // 32):]
+        lib().oracle_nn_matvec_q4(_p(out), _p(np.ascontiguousarray(w)),
+                                  _p(np.ascontiguousarray(scales)), _p(x), rows,
+                                  cols, int(add))
+    return out
+
+
+def quant_swiglu(quant, w, scales, x, rows, cols):
+    out = np.empty(rows, np.float32)
+    fn = lib().oracle_nn_swiglu_fp8 if quant == "fp8" else lib().oracle_nn_swiglu_q4
+    fn(_p(out), _p(w), _p(scales), _p(np.ascontiguousarray(x, np.float32)), rows,
+       cols)
+    return out
+
+
+def quant_dot_f64(quant, w, scales, x, rows, cols):
+    """Every row times x in f64 from the definition of the format."""
+    want = np.empty(rows, np.float64)
+    fn = lib().oracle_fp8_dot_f64 if quant == "fp8" else lib().oracle_q4_dot_f64
+    fn(_p(want), _p(w), _p(scales), _p(np.ascontiguousarray(x, np.float32)), rows,
+       cols)
+    return want
+
+
+def quant_inputs(quant, rows, cols, seed):
+    """Codes and scales of a rows x cols matrix as the reference's tests make
+    them: fp8 scales 0.002 + 0.001 * random (f32, one per 128 x 128 block),
+    Q4_0 scales 0.003 + random * 0.001 rounded to f16 (one per 32 weights)."""
+    if quant == "fp8":
+        w = random_words(rows * cols // 4, seed, fp8=True)
+        n = ((rows + 127) // 128) * (cols // 128)
+        s = (np.float32(0.002) + np.float32(0.001) * random_f32(n, seed + 1, 1.0)) \
+            .astype(np.float32)
+    else:
+        w = random_words(rows * (cols // 8), seed)
+        n = rows * (cols // 32)
+        s = (np.float32(0.003) + random_f32(n, seed + 1, 0.001)).astype(np.float16)
+    return w, s
 
 
 # ---- a whole std::nn model on the host ------------------------------------------

@@ -160,3 +160,32 @@ def test_payload_and_descriptor_builders_match_the_wire_format():
     assert abi.memref_tag(abi.BF16, 2) == (2 << 16) | (9 << 8)
     assert abi.memref_tag(abi.F32, 2, slot=True) == (1 << 24) | (2 << 16) | (6 << 8)
     assert abi.gpu(3) == 503
+
+
+def test_llama2c_header_is_read_and_checked(tmp_path):
+    """vx_b200_llama2c_config (the reference's vx_load_config,
+    stdlib/rust_core/src/ffi/llama.rs:11-27): no GPU involved."""
+    import ctypes as C
+    import numpy as np
+    from vx_b200 import llama
+    from vx_b200.lib import Llama2cConfig, lib
+    L = lib()
+    shape = dict(dim=64, hidden=176, n_layers=2, n_heads=4, n_kv_heads=4,
+                 vocab=512, seq_len=32)
+    flat, _ = llama.small_f32_weights(**shape)
+    good = tmp_path / "model.bin"
+    llama.write_llama2c(str(good), flat, **shape)
+    head = Llama2cConfig()
+    assert L.vx_b200_llama2c_config(str(good).encode(), C.byref(head)) == 0
+    assert (head.dim, head.hidden_dim, head.n_layers, head.n_heads,
+            head.n_kv_heads, head.vocab_size, head.seq_len) == (64, 176, 2, 4, 4, 512, 32)
+    assert L.vx_b200_llama2c_config(str(tmp_path / "none.bin").encode(), None) == -1
+    assert b"cannot open" in L.vx_b200_last_error()
+    short = tmp_path / "short.bin"
+    short.write_bytes(good.read_bytes()[:4096])
+    assert L.vx_b200_llama2c_config(str(short).encode(), None) == -1
+    assert b"cut short" in L.vx_b200_last_error()
+    junk = tmp_path / "junk.bin"
+    junk.write_bytes(np.zeros(64, np.int32).tobytes())
+    assert L.vx_b200_llama2c_config(str(junk).encode(), None) == -1
+    assert b"does not begin with a llama2.c header" in L.vx_b200_last_error()

@@ -147,29 +147,48 @@ def test_nn_decoder_many_sequences(oracle, monkeypatch, batch, tensor_cores):
         assert got[b] == want, "sequence %d: %s" % (b, report(got[b], want))
 
 
-def test_prefill_sixteen_positions_at_a_time(oracle):
-    """A 40-token prompt fed through vx_decoder_prefill (two passes of sixteen
-    positions as rows of the tensor-core projections, the rest single steps),
-    then greedy steps: the tokens are the oracle's, which feeds the prompt one
-    token at a time."""
-    max_seq, steps = 64, 10
+def test_prefill_a_whole_prompt_at_once(oracle):
+    """A 100-token prompt through vx_decoder_prefill (the positions as the rows
+    of tensor-core GEMMs, f32 attention over the prompt), then greedy steps:
+    the tokens are the oracle's, which feeds the prompt one token at a time.
+    Then the same split in two: 40 single steps, and the next 59 positions as
+    one pass that starts at position 40."""
+    from vx_b200 import ops
+    from vx_b200.lib import lib
+    max_seq, steps = 128, 12
     dec, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=1, **WIDE_NN)
     hm = nn_host_model(oracle, tensors, WIDE_NN, max_seq)
     prompt = [int(t) for t in
-              np.random.default_rng(33).integers(0, WIDE_NN["vocab"], 40)]
-    arr = (C.c_int32 * 39)(*prompt[:-1])
-    from vx_b200.lib import lib
-    assert lib().vx_decoder_prefill(dec.handle, arr, 39) == 32
-    dec.reset()
-    tok = dec.prefill(prompt)
-    got = []
-    for _ in range(steps):
-        got.append(tok)
-        tok = dec.step(None)[0]
-    dec.close()
-    from vx_b200 import ops
-    assert ops.kernel_status() == 0
+              np.random.default_rng(33).integers(0, WIDE_NN["vocab"], 100)]
     want = oracle_generate(oracle, hm, prompt, steps, max_seq)
+
+    def greedy(tok):
+        got = []
+        for _ in range(steps):
+            got.append(tok)
+            tok = dec.step(None)[0]
+        return got
+
+    short = (C.c_int32 * 20)(*prompt[:20])
+    assert lib().vx_decoder_prefill(dec.handle, short, 20) == 0   # too few: steps
+    arr = (C.c_int32 * 99)(*prompt[:-1])
+    assert lib().vx_decoder_prefill(dec.handle, arr, 99) == 99
+    got = greedy(dec.step([prompt[-1]])[0])
+    assert ops.kernel_status() == 0
+    assert got == want, report(got, want)
+
+    dec.reset()
+    for t in prompt[:40]:
+        dec.step([t], fetch=False)
+    rest = (C.c_int32 * 59)(*prompt[40:99])
+    assert lib().vx_decoder_prefill(dec.handle, rest, 59) == 59
+    got = greedy(dec.step([prompt[-1]])[0])
+    assert ops.kernel_status() == 0
+    assert got == want, report(got, want)
+
+    dec.reset()
+    got = greedy(dec.prefill(prompt))
+    dec.close()
     assert got == want, report(got, want)
 
 
@@ -200,3 +219,25 @@ def test_config5_llama7b_shape_100_tokens(oracle):
     want, gaps = oracle_generate(oracle, hm, prompt, steps, max_seq,
                                  want_gaps=True)
     assert got == want, report(got, want, gaps)
+
+
+def test_a_llama2c_checkpoint_file_decodes_like_the_oracle(oracle, tmp_path):
+    """The file format the reference's llama programs load (7 int32, then f32
+    weights in llama2.c order): written here from seeded weights, read by
+    vx_decoder_from_llama2c, and decoded greedily; the tokens are the CPU
+    program's."""
+    shape = dict(dim=128, hidden=352, n_layers=3, n_heads=4, n_kv_heads=4,
+                 vocab=1000, seq_len=64)
+    flat, _ = llama.small_f32_weights(seed=77, **shape)
+    path = str(tmp_path / "model.bin")
+    llama.write_llama2c(path, flat, **shape)
+    cfg = oracle.LlamaConfig(128, 352, 3, 4, 4, 1000, 64)
+    want = list(oracle.llama_generate(cfg, flat, 1, 40))
+    dec = llama.Decoder.from_llama2c(path)
+    got, tok = [1], dec.step([1])[0]
+    got.append(tok)
+    for _ in range(39):
+        tok = dec.step(None)[0]
+        got.append(tok)
+    dec.close()
+    assert got == want, report(got, want)

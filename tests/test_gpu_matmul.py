@@ -135,7 +135,7 @@ def run_route(a16, b16, route):
     ta = abi.DeviceTensor.from_host(a16, bf16=True)
     tb = abi.DeviceTensor.from_host(b16, bf16=True)
     tc = abi.DeviceTensor.empty((m, n), abi.BF16)
-    ts = abi.DeviceTensor.empty((n, k), abi.BF16) if route == 2 else None
+    ts = abi.DeviceTensor.empty((n, k), abi.BF16) if route in (2, 5) else None
     ops.gemm(ta, tb, tc, route=route, scratch=ts)
     status = ops.kernel_status()
     out = tc.to_host()
@@ -145,13 +145,15 @@ def run_route(a16, b16, route):
     return out, status
 
 
-ROUTES = [int(r) for r in os.environ.get("VX_TEST_ROUTES", "3,2,1").split(",")]
+# 1, 2: one CTA per 128x256 tile (B as stored / transposed first); 3: the plain
+# kernel; 4, 5: the same two forms on CTA pairs (256x256 tiles)
+ROUTES = [int(r) for r in os.environ.get("VX_TEST_ROUTES", "3,2,1,4,5").split(",")]
 
 
 @pytest.mark.parametrize("route", ROUTES)
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 256),
                                    (384, 768, 1024), (200, 264, 136),
-                                   (2048, 2048, 2048)])
+                                   (2048, 2048, 2048), (2304, 1280, 512)])
 def test_bf16_gemm_routes(oracle, route, m, n, k):
     a16, b16 = bf16_inputs(oracle, m, n, k)
     got, status = run_route(a16, b16, route)
@@ -180,6 +182,21 @@ def test_bf16_dispatch_route_is_exact_on_small_integers(oracle):
         want = oracle.gemm_bf16_entry(a16, b16, r, c)
         # the bf16 result is the exact f32 sum rounded once
         assert got[r, c] == oracle.bf16_to_f32(oracle.f32_to_bf16(np.float32(want)))
+
+
+def test_bf16_pair_route_is_exact_on_small_integers(oracle):
+    """The CTA-pair kernel on exact inputs: every one of the 4608 x 3072
+    results must be the exact sum rounded once (which half of which tile a
+    value came from cannot hide in a tolerance)."""
+    m, n, k = 4608, 3072, 640       # 18 x 12 pair tiles: more than one per pair
+    i = np.arange(m)[:, None]
+    a = ((i * 3 + np.arange(k)[None, :] * 5) % 7 - 3).astype(np.float32)
+    b = ((np.arange(k)[:, None] * 2 + np.arange(n)[None, :]) % 5 - 2).astype(np.float32)
+    a16, b16 = oracle.f32_to_bf16(a), oracle.f32_to_bf16(b)
+    got, status = run_route(a16, b16, 4)
+    assert status == 0, "a wait in the paired kernel gave up: 0x%x" % status
+    exact = (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    assert np.array_equal(got, oracle.f32_to_bf16(exact))
 
 
 def test_f16_gemm(oracle):

@@ -1,6 +1,7 @@
 """The CPU oracle against every known answer the reference's own tests hold for
 this path (no GPU)."""
 import numpy as np
+import pytest
 
 
 def test_gpu_matmul_roles_known_answer(oracle):
@@ -200,3 +201,38 @@ def test_the_two_restatements_of_the_llama_decode_give_the_same_100_tokens(oracl
     # a random model with a shared embedding/classifier mostly repeats itself;
     # the sequence still changes token several times
     assert len(set(first.tolist())) >= 3
+
+
+@pytest.mark.parametrize("quant,rows,cols", [("fp8", 296, 896), ("fp8", 64, 4864),
+                                             ("q4", 296, 896), ("q4", 64, 4864)])
+def test_quantised_matvec_meets_the_reference_criterion(oracle, quant, rows, cols):
+    """The restatements of nn_matvec_fp8 / nn_matvec_q4 on the shapes, codes and
+    scales of the reference's tests
+    (std_nn_{fp8,q4}_kernels_match_loops_on_the_cpu.vx), against the plain f64
+    loops of those tests, with their criterion."""
+    w, s = oracle.quant_inputs(quant, rows, cols, 1)
+    x = oracle.random_f32(cols, 3, 1.0)
+    want = oracle.quant_dot_f64(quant, w, s, x, rows, cols)
+    got = oracle.quant_matvec(quant, w, s, x, rows, cols)
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    y0 = oracle.random_f32(rows, 4, 1.0)
+    got = oracle.quant_matvec(quant, w, s, x, rows, cols, y=y0)
+    assert np.abs(got - (y0 + want)).max() <= 1e-5 * np.abs(y0 + want).max()
+
+
+def test_fp8_code_values_follow_the_definition(oracle):
+    """Each of the 254 non-NaN codes alone in a row: the table the kernels use
+    (nn.vx:1316-1326) gives the value of the f8e4m3 definition exactly."""
+    codes = [c for c in range(256) if (c & 127) != 127]
+    rows, cols = len(codes) + (-len(codes)) % 4, 128
+    w = np.zeros(rows * cols // 4, np.uint32)
+    for r, c in enumerate(codes):
+        w[r * cols // 4] = c                      # column 0 of row r
+    s = np.ones(((rows + 127) // 128) * (cols // 128), np.float32)
+    x = np.zeros(cols, np.float32)
+    x[0] = 1.0
+    got = oracle.quant_matvec("fp8", w, s, x, rows, cols)
+    want = oracle.quant_dot_f64("fp8", w, s, x, rows, cols)
+    assert np.array_equal(got.astype(np.float64), want)
+    assert want[codes.index(0x38)] == 1.0 and want[codes.index(0x01)] == 2.0 ** -9
+    assert want[codes.index(0x7e)] == 448.0 and want[codes.index(0xc0)] == -2.0

@@ -48,6 +48,8 @@ def memref_tag(elem, rank, slot=False):
 def code_of(dtype, bf16=False):
     if bf16:
         return BF16
+    if np.dtype(dtype) == np.dtype(np.uint32):   # words of packed codes: u32 is
+        return I32                               # a 32-bit integer on the wire
     for code, np_t in NUMPY_OF.items():
         if code != BF16 and np.dtype(dtype) == np.dtype(np_t):
             return code

@@ -28,9 +28,15 @@
 #include "vx_b200.h"
 #include "vx_collective.h"
 
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <utility>
 #include <string>
@@ -61,11 +67,6 @@ namespace {
       stop("%s failed: %s", #expr, cudaGetErrorString(e_));                    \
   } while (0)
 
-/* pos[i] = first[0] + i: the positions of a run of prompt tokens. */
-__global__ void run_positions_kernel(int32_t *pos, const int32_t *first, int n) {
-  if ((int)threadIdx.x < n)
-    pos[threadIdx.x] = first[0] + threadIdx.x;
-}
 __global__ void advance_by_kernel(int32_t *pos, int by) {
   if (threadIdx.x == 0)
     pos[0] += by;
@@ -82,7 +83,78 @@ __global__ void add_kernel(float *x, const float *t, int64_t n) {
     x[i] = x[i] + t[i];
 }
 
-/* pair[b] = (best local logit, its GLOBAL index as float bits). */
+/* The token of a vocabulary-split model: every rank has the best logit of its
+   slice (local_best) and all ranks must agree on the best of all. Thread
+   (b, r) stores this rank's (value, global index) of sequence b into rank r's
+   slots as one 16-byte (value, index, call, call) record -- the two call
+   numbers make it its own arrival flag, as in the exchange of the partial
+   sums -- and waits (bounded) for rank r's record of sequence b; then the
+   largest value wins, the lowest index on a tie (rank order is index order, so
+   the first rank with that value). One block; slots: [2 sets][ranks][batch]. */
+struct PickSlot {
+  float value;
+  int32_t index, call, call_again;
+};
+struct PickPeers {
+  PickSlot *slots[vxb::kMaxTpRanks];
+};
+__global__ void __launch_bounds__(vxb::kMaxTpRanks * 32)
+tp_pick_kernel(int32_t *token, const int32_t *local_best, const float *logits,
+               int64_t stride, int vocab_offset, PickPeers peers, int ranks,
+               int rank, int batch, int32_t *epoch, int32_t *gave_up) {
+  __shared__ float values[32][vxb::kMaxTpRanks];
+  __shared__ int32_t indices[32][vxb::kMaxTpRanks];
+  const int call = *epoch + 1, set = call & 1;
+  const int b = threadIdx.x / ranks, r = threadIdx.x % ranks;
+  if (b < batch) {
+    const int best = local_best[b];
+    float v = logits[b * stride + best];
+    int32_t idx = best + vocab_offset;
+    if (r != rank) {
+      PickSlot *to = peers.slots[r] + ((int64_t)set * ranks + rank) * batch + b;
+      asm volatile("st.volatile.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(to),
+                   "r"(__float_as_uint(v)), "r"(idx), "r"(call), "r"(call)
+                   : "memory");
+      const PickSlot *from =
+          peers.slots[rank] + ((int64_t)set * ranks + r) * batch + b;
+      const long long began = clock64();
+      for (;;) {
+        uint32_t bits;
+        int32_t c0, c1;
+        asm volatile("ld.volatile.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(bits), "=r"(idx), "=r"(c0), "=r"(c1)
+                     : "l"(from)
+                     : "memory");
+        v = __uint_as_float(bits);
+        if (c0 == call && c1 == call)
+          break;
+        if (clock64() - began > (1ll << 31)) { /* about a second */
+          atomicCAS(gave_up, 0, 0x54);
+          break;
+        }
+      }
+    }
+    values[b][r] = v;
+    indices[b][r] = idx;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < batch) {
+    float best = values[threadIdx.x][0];
+    int32_t at = indices[threadIdx.x][0];
+    for (int k = 1; k < ranks; ++k)
+      if (values[threadIdx.x][k] > best) {
+        best = values[threadIdx.x][k];
+        at = indices[threadIdx.x][k];
+      }
+    token[threadIdx.x] = at;
+  }
+  if (threadIdx.x == 0)
+    *epoch = call;
+}
+
+/* The same agreement from an all-gather of (value, index bits) pairs (the
+   NCCL form): pair[b] of this rank, then the pick over gathered
+   [ranks][batch]. */
 __global__ void best_pair_kernel(float2 *pair, const int32_t *local_best,
                                  const float *logits, int64_t stride,
                                  int vocab_offset) {
@@ -91,8 +163,6 @@ __global__ void best_pair_kernel(float2 *pair, const int32_t *local_best,
   pair[b] = make_float2(logits[b * stride + i],
                         __int_as_float(i + vocab_offset));
 }
-/* gathered: [ranks][batch] pairs; the largest value wins, the lowest index on
-   a tie (rank order is index order, so the first rank with the value). */
 __global__ void pick_pair_kernel(int32_t *token, const float2 *gathered,
                                  int ranks, int batch) {
   const int b = threadIdx.x;
@@ -116,7 +186,8 @@ struct vx_decoder {
   vx_decoder_config c;
   int ranks, q_local, kv_local, hidden_local, vocab_local, vocab_offset;
   std::vector<const void *> attn_norm, wq, wk, wv, bqkv, wo, ffn_norm, w_gate,
-      w_up, w_down;
+      w_up, w_down, s_qkv, s_o, s_gate_up, s_down;
+  int wfmt; /* 0, or kFmtFp8 / kFmtQ4 for the layers' projections */
   const void *embed, *final_norm, *lm_head;
   const float *cos_t, *sin_t;
   /* device state */
@@ -129,21 +200,26 @@ struct vx_decoder {
   vxb::TpPush tp;
   void *recv;                       /* this rank's slots + flags (IPC-shared) */
   void *peer_recv[vxb::kMaxTpRanks];
-  int32_t *tp_epoch, *tp_done;
+  int32_t *tp_epoch, *tp_done, *pick_epoch, *pick_gave_up;
+  PickPeers pick;
   /* 8 or 16 sequences: the projections run on the tensor cores */
   bool mma;
   void *mma_xs;
   float *mma_scratch;
-  /* a one-sequence decoder reading its prompt sixteen positions at a time:
-     the same tensor-core projections with the positions as rows */
-  float *rows_x, *rows_q, *rows_att, *rows_h;
-  int32_t *rows_tokens, *rows_pos;
+  /* a one-sequence decoder reading a whole prompt at once (prefill.cu):
+     activations of rows_cap positions, their bf16 terms, the GEMMs' partial
+     sums */
+  float *rows_x, *rows_q, *rows_partials;
+  void *rows_terms;
+  int32_t *rows_tokens;
+  int rows_cap;
   int64_t cache_layer_stride, cache_batch_stride;
   int split;
   int host_pos;
   cudaStream_t stream;
   std::map<int, cudaGraphExec_t> graphs;
   int kernels_per_step;
+  void *owned_weights; /* a checkpoint this decoder loaded itself, or NULL */
 };
 
 namespace {
@@ -186,11 +262,15 @@ int add_partials(vx_decoder *d) {
    all-gather), and maps every other rank's. */
 void open_peer_buffers(vx_decoder *d, int rank) {
   const int64_t n = (int64_t)d->c.batch * d->c.dim;
-  const size_t bytes = (size_t)2 * d->ranks * n * sizeof(vxb::TpPair);
+  /* the pairs of the partial sums, then the records of the token agreement */
+  const size_t pair_bytes = (size_t)2 * d->ranks * n * sizeof(vxb::TpPair);
+  const size_t bytes = pair_bytes + (size_t)2 * d->ranks * 32 * sizeof(PickSlot);
   CUDA_OK(cudaMalloc(&d->recv, bytes));
   CUDA_OK(cudaMemset(d->recv, 0, bytes));
   d->tp_epoch = dev_alloc<int32_t>(4);
   d->tp_done = d->tp_epoch + 1;
+  d->pick_epoch = d->tp_epoch + 2;
+  d->pick_gave_up = d->tp_epoch + 3;
   cudaIpcMemHandle_t mine;
   CUDA_OK(cudaIpcGetMemHandle(&mine, d->recv));
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
@@ -217,6 +297,7 @@ void open_peer_buffers(vx_decoder *d, int rank) {
              p, cudaGetErrorString(e));
     }
     d->tp.slots[p] = (vxb::TpPair *)d->peer_recv[p];
+    d->pick.slots[p] = (PickSlot *)((char *)d->peer_recv[p] + pair_bytes);
   }
   d->tp.ranks = d->ranks;
   d->tp.rank = rank;
@@ -329,6 +410,8 @@ void record_step(vx_decoder *d, int max_pos) {
     qa.wk = d->wk[l];
     qa.wv = d->wv[l];
     qa.wbf16 = bf;
+    qa.wfmt = d->wfmt;
+    qa.sq = d->s_qkv[l];
     qa.bias = d->bqkv[l];
     qa.q_heads = d->q_local;
     qa.kv_heads = d->kv_local;
@@ -374,6 +457,8 @@ void record_step(vx_decoder *d, int max_pos) {
     vxb::MatvecArgs oa{};
     oa.w = d->wo[l];
     oa.wbf16 = bf;
+    oa.wfmt = d->wfmt;
+    oa.scales = d->s_o[l];
     oa.rows = c.dim;
     oa.cols = d->q_local * hd;
     oa.x = d->att;
@@ -391,6 +476,8 @@ void record_step(vx_decoder *d, int max_pos) {
     sa.w = d->w_gate[l];
     sa.w_up = d->w_up[l];
     sa.wbf16 = bf;
+    sa.wfmt = d->wfmt;
+    sa.scales = d->s_gate_up[l];
     sa.rows = d->hidden_local;
     sa.cols = c.dim;
     sa.x = normed(d, d->ffn_norm[l], launches);
@@ -406,6 +493,8 @@ void record_step(vx_decoder *d, int max_pos) {
     vxb::MatvecArgs da{};
     da.w = d->w_down[l];
     da.wbf16 = bf;
+    da.wfmt = d->wfmt;
+    da.scales = d->s_down[l];
     da.rows = c.dim;
     da.cols = d->hidden_local;
     da.x = d->h;
@@ -449,6 +538,12 @@ void record_step(vx_decoder *d, int max_pos) {
     need(vxb::argmax(d->local_best, d->logits, d->vocab_local, B,
                      d->vocab_local, s),
          "argmax");
+    if (d->push) {
+      tp_pick_kernel<<<1, d->ranks * 32, 0, s>>>(
+          d->tokens, d->local_best, d->logits, d->vocab_local, d->vocab_offset,
+          d->pick, d->ranks, d->tp.rank, B, d->pick_epoch, d->pick_gave_up);
+      launches += 2;
+    } else {
     best_pair_kernel<<<1, B, 0, s>>>(d->pair, d->local_best, d->logits,
                                      d->vocab_local, d->vocab_offset);
     vx::NcclCollective *job = vxb::nccl_job();
@@ -459,6 +554,7 @@ void record_step(vx_decoder *d, int max_pos) {
            job->api()->GetErrorString(r));
     pick_pair_kernel<<<1, 32, 0, s>>>(d->tokens, d->pairs_all, d->ranks, B);
     launches += 4;
+    }
   }
   advance_kernel<<<1, 32, 0, s>>>(d->positions, B);
   ++launches;
@@ -543,6 +639,22 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
   copy(d->w_gate, w->w_gate, true, "w_gate");
   copy(d->w_up, w->w_up, false, "w_up");
   copy(d->w_down, w->w_down, true, "w_down");
+  d->wfmt = c.weights_bf16 == 2 ? vxb::kFmtFp8 : c.weights_bf16 == 3 ? vxb::kFmtQ4 : 0;
+  copy(d->s_qkv, d->wfmt ? w->s_qkv : nullptr, d->wfmt != 0, "s_qkv");
+  copy(d->s_o, d->wfmt ? w->s_o : nullptr, d->wfmt != 0, "s_o");
+  copy(d->s_gate_up, d->wfmt ? w->s_gate_up : nullptr, d->wfmt != 0, "s_gate_up");
+  copy(d->s_down, d->wfmt ? w->s_down : nullptr, d->wfmt != 0, "s_down");
+  if (d->wfmt) {
+    if (c.batch != 1 || d->ranks != 1)
+      stop("vx_decoder_create: fp8 and Q4_0 weights take one sequence on one rank");
+    for (int l = 0; l < c.n_layers; ++l)
+      if (d->wk[l] || d->wv[l] || d->w_up[l])
+        stop("vx_decoder_create: fp8 and Q4_0 weights need the q, k and v rows in "
+             "one matrix (wk, wv NULL) and the gate and up rows in one (w_up NULL)");
+    if (c.dim % (d->wfmt == vxb::kFmtFp8 ? 128 : 32) || c.hidden % (d->wfmt == vxb::kFmtFp8 ? 128 : 32))
+      stop("vx_decoder_create: fp8 needs dim and hidden in multiples of 128, Q4_0 "
+           "of 32");
+  }
   d->embed = w->embed;
   d->final_norm = w->final_norm;
   d->lm_head = w->lm_head;
@@ -576,6 +688,7 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
   d->pairs_all = (float2 *)dev_alloc<float>(2 * 32 * (size_t)d->ranks);
   d->host_pos = 0;
   d->kernels_per_step = 0;
+  d->owned_weights = nullptr;
   CUDA_OK(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
   d->push = false;
   d->recv = nullptr;
@@ -583,13 +696,15 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
     open_peer_buffers(d, rank);
     d->push = true;
   }
-  d->rows_x = d->rows_q = d->rows_att = d->rows_h = nullptr;
-  d->rows_tokens = d->rows_pos = nullptr;
+  d->rows_x = d->rows_q = d->rows_partials = nullptr;
+  d->rows_terms = nullptr;
+  d->rows_tokens = nullptr;
+  d->rows_cap = 0;
   d->mma = false;
   d->mma_xs = nullptr;
   d->mma_scratch = nullptr;
   const char *nomma = getenv("VXB_BATCH_MMA");
-  if (c.weights_bf16 && d->ranks == 1 && (B == 8 || B == 16) && c.head_dim == 128 &&
+  if (c.weights_bf16 == 1 && d->ranks == 1 && (B == 8 || B == 16) && c.head_dim == 128 &&
       c.dim % 64 == 0 && d->hidden_local % 64 == 0 && !(nomma && nomma[0] == '0')) {
     int widest = c.dim > d->hidden_local ? c.dim : d->hidden_local;
     if (d->q_local * c.head_dim > widest)
@@ -629,15 +744,28 @@ void vx_decoder_destroy(vx_decoder *d) {
                   (void *)d->tokens, (void *)d->positions,
                   (void *)d->local_best, (void *)d->pair,
                   (void *)d->pairs_all, d->mma_xs, (void *)d->mma_scratch,
-                  (void *)d->rows_x, (void *)d->rows_q, (void *)d->rows_att,
-                  (void *)d->rows_h, (void *)d->rows_tokens, (void *)d->rows_pos})
+                  (void *)d->rows_x, (void *)d->rows_q, (void *)d->rows_partials,
+                  d->rows_terms, (void *)d->rows_tokens})
     cudaFree(p);
+  cudaFree(d->owned_weights);
   cudaStreamDestroy(d->stream);
   delete d;
 }
 
 void vx_decoder_reset(vx_decoder *d) {
   CUDA_OK(cudaStreamSynchronize(d->stream));
+  if (d->push) {
+    /* a wait for another rank's record that ran out is worth a line: the
+       tokens since then are not the model's */
+    int32_t gave_up = 0;
+    CUDA_OK(cudaMemcpy(&gave_up, d->pick_gave_up, sizeof gave_up,
+                       cudaMemcpyDeviceToHost));
+    if (gave_up) {
+      fprintf(stderr, "[Vx CUDA] vx_decoder: a rank's best token did not arrive "
+                      "within a second; the ranks no longer agree\n");
+      CUDA_OK(cudaMemset(d->pick_gave_up, 0, sizeof gave_up));
+    }
+  }
   CUDA_OK(cudaMemsetAsync(d->positions, 0, 32 * sizeof(int32_t), d->stream));
   CUDA_OK(cudaStreamSynchronize(d->stream));
   d->host_pos = 0;
@@ -664,127 +792,314 @@ int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
   return pos;
 }
 
-/* A run of prompt tokens of a one-sequence decoder, sixteen positions per
-   pass: the projections see the positions as the rows of rowdot_umma.cu (the
-   multi-row kernels of nn.vx:2317-3066 are the reference's form of this), every
-   row writes its K and V into the one cache at its own position, and row i
-   attends positions 0 .. first + i, which are all in the cache by then. No
-   logits: the caller feeds the last prompt token through vx_decoder_step.
-   Returns the number of tokens taken (a multiple of 16, possibly 0: what is
-   left goes through vx_decoder_step), or -1 with vx_b200_last_error() when
-   this decoder cannot do it. */
+/* A run of prompt tokens of a one-sequence decoder, all positions at once: the
+   positions are the rows of tensor-core GEMMs (prefill.cu; the reference's form
+   of this are the multi-row kernels of nn.vx:2317-3066), every position writes
+   its K and V into the cache at its own row, and position t attends rows
+   0 .. first + t. No logits: the caller feeds the last prompt token through
+   vx_decoder_step. Returns the number of tokens taken (all of them, or 0 when
+   there are fewer than 32: single steps are as fast then), or -1 with
+   vx_b200_last_error() when this decoder cannot do it. */
 int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) {
   const vx_decoder_config &c = d->c;
-  constexpr int R = 16;
-  if (c.batch != 1 || !c.weights_bf16 || d->ranks != 1 || c.head_dim != 128 ||
-      c.dim % 64 != 0 || d->hidden_local % 64 != 0) {
+  const int hd = c.head_dim;
+  const int qkv_rows = (d->q_local + 2 * d->kv_local) * hd, att_cols = d->q_local * hd;
+  bool fused = true;
+  for (int l = 0; l < c.n_layers; ++l)
+    fused = fused && !d->wk[l] && !d->wv[l] && !d->w_up[l];
+  if (c.batch != 1 || c.weights_bf16 != 1 || d->ranks != 1 || hd != 128 ||
+      c.dim % 64 != 0 || d->hidden_local % 64 != 0 || !fused) {
     vxb::set_last_error("vx_decoder_prefill: needs one sequence, one rank, bf16 "
-                        "weights, head_dim 128 and widths in multiples of 64");
+                        "weights with q/k/v rows in one matrix and gate/up rows "
+                        "in one matrix, head_dim 128 and widths in multiples "
+                        "of 64");
     return -1;
   }
   if (count < 0 || d->host_pos + count > c.max_seq) {
     vxb::set_last_error("vx_decoder_prefill: the prompt does not fit max_seq");
     return -1;
   }
-  if (!d->rows_x) {
+  if (count < 32)
+    return 0;
+  const int T = count;
+  if (T > d->rows_cap) {
+    for (void *p : {(void *)d->rows_x, (void *)d->rows_q, d->rows_terms,
+                    (void *)d->rows_partials, (void *)d->rows_tokens})
+      cudaFree(p);
     int widest = c.dim > d->hidden_local ? c.dim : d->hidden_local;
-    if (d->q_local * c.head_dim > widest)
-      widest = d->q_local * c.head_dim;
-    int rows_max = 2 * d->hidden_local;
-    if ((d->q_local + 2 * d->kv_local) * c.head_dim > rows_max)
-      rows_max = (d->q_local + 2 * d->kv_local) * c.head_dim;
-    d->rows_x = dev_alloc<float>((size_t)R * c.dim);
-    d->rows_q = dev_alloc<float>((size_t)R * d->q_local * c.head_dim);
-    d->rows_att = dev_alloc<float>((size_t)R * d->q_local * c.head_dim);
-    d->rows_h = dev_alloc<float>((size_t)R * d->hidden_local);
-    d->rows_tokens = dev_alloc<int32_t>(R);
-    d->rows_pos = dev_alloc<int32_t>(R);
-    if (!d->mma_xs) {
-      d->mma_xs = dev_alloc<uint16_t>((size_t)48 * widest);
-      d->mma_scratch = dev_alloc<float>(vxb::batched_proj_scratch_floats(rows_max, R));
-    }
+    if (att_cols > widest)
+      widest = att_cols;
+    size_t partial = vxb::rows_gemm_partial_floats(T, qkv_rows, c.dim);
+    for (size_t other : {vxb::rows_gemm_partial_floats(T, c.dim, att_cols),
+                         vxb::rows_gemm_partial_floats(T, 2 * d->hidden_local, c.dim),
+                         vxb::rows_gemm_partial_floats(T, c.dim, d->hidden_local)})
+      if (other > partial)
+        partial = other;
+    d->rows_x = dev_alloc<float>((size_t)T * c.dim);
+    d->rows_q = dev_alloc<float>((size_t)T * att_cols);
+    d->rows_terms = dev_alloc<uint16_t>((size_t)T * 3 * widest);
+    d->rows_partials = dev_alloc<float>(partial);
+    d->rows_tokens = dev_alloc<int32_t>(T);
+    d->rows_cap = T;
   }
   cudaStream_t s = d->stream;
-  const int hd = c.head_dim;
-  int taken = 0;
-  while (count - taken >= R) {
-    CUDA_OK(cudaMemcpyAsync(d->rows_tokens, tokens + taken, R * sizeof(int32_t),
-                            cudaMemcpyHostToDevice, s));
-    run_positions_kernel<<<1, 32, 0, s>>>(d->rows_pos, d->positions, R);
-    need(vxb::embed(d->rows_x, d->embed, true, d->rows_tokens, c.dim, c.vocab, R,
-                    c.dim, s),
-         "embed");
-    auto proj = [&](int mode, const void *w0, const void *w1, const void *w2,
-                    int rows, int cols, const float *x, const void *norm_w,
-                    float *y, int64_t y_stride, const void *bias, int layer,
-                    const char *what, bool terms_ready, bool leave_terms) {
-      vxb::BatchedProj bp{};
-      bp.mode = mode;
-      bp.w0 = w0;
-      bp.w1 = w1;
-      bp.w2 = w2;
-      bp.rows = rows;
-      bp.cols = cols;
-      bp.batch = R;
-      bp.x = x;
-      bp.x_stride = cols;
-      bp.norm_w = norm_w;
-      bp.eps = c.eps;
-      bp.y = y;
-      bp.y_stride = y_stride;
-      bp.bias = bias;
-      bp.q_heads = d->q_local;
-      bp.kv_heads = d->kv_local;
-      bp.head_dim = hd;
-      bp.cos_t = d->cos_t;
-      bp.sin_t = d->sin_t;
-      bp.positions = d->rows_pos;
-      bp.k_cache = d->k_cache + layer * d->cache_layer_stride;
-      bp.v_cache = d->v_cache + layer * d->cache_layer_stride;
-      bp.cache_batch_stride = 0; /* every row writes into the one cache */
-      bp.xs = d->mma_xs;
-      bp.scratch = d->mma_scratch;
-      bp.x_terms_ready = terms_ready;
-      bp.next_terms = leave_terms;
-      need(vxb::batched_proj(bp, s), what);
-    };
-    for (int l = 0; l < c.n_layers; ++l) {
-      proj(4, d->wq[l], d->wk[l], d->wv[l], (d->q_local + 2 * d->kv_local) * hd,
-           c.dim, d->rows_x, d->attn_norm[l], d->rows_q, (int64_t)d->q_local * hd,
-           d->bqkv[l], l, "q/k/v", false, false);
-      vxb::AttnArgs aa{};
-      aa.q = d->rows_q;
-      aa.k_cache = d->k_cache + l * d->cache_layer_stride;
-      aa.v_cache = d->v_cache + l * d->cache_layer_stride;
-      aa.cache_batch_stride = 0;
-      aa.out = d->rows_att;
-      aa.q_heads = d->q_local;
-      aa.kv_heads = d->kv_local;
-      aa.head_dim = hd;
-      aa.batch = R;
-      aa.positions = d->rows_pos;
-      aa.max_pos = d->host_pos + taken + R - 1;
-      aa.fresh_from = d->positions; /* this pass's rows are new */
-      aa.scratch = nullptr; /* the cluster form needs none */
-      aa.counters = nullptr;
-      aa.split = d->split;
-      aa.rows_settled = 1; /* rows below fresh_from: earlier passes and steps */
-      need(vxb::attention_decode_clustered(aa, s), "attention");
-      proj(1, d->wo[l], nullptr, nullptr, c.dim, d->q_local * hd, d->rows_att,
-           nullptr, d->rows_x, c.dim, nullptr, l, "the output projection", false,
-           false);
-      proj(3, d->w_gate[l], d->w_up[l], nullptr, d->hidden_local, c.dim, d->rows_x,
-           d->ffn_norm[l], d->rows_h, d->hidden_local, nullptr, l, "gate/up", false,
-           true);
-      proj(1, d->w_down[l], nullptr, nullptr, c.dim, d->hidden_local, d->rows_h,
-           nullptr, d->rows_x, c.dim, nullptr, l, "the down projection", true,
-           false);
-    }
-    advance_by_kernel<<<1, 32, 0, s>>>(d->positions, R);
-    taken += R;
+  CUDA_OK(cudaMemcpyAsync(d->rows_tokens, tokens, (size_t)T * sizeof(int32_t),
+                          cudaMemcpyHostToDevice, s));
+  need(vxb::embed(d->rows_x, d->embed, true, d->rows_tokens, c.dim, c.vocab, T,
+                  c.dim, s),
+       "embed");
+  int splits = 1;
+  for (int l = 0; l < c.n_layers; ++l) {
+    float *kc = d->k_cache + l * d->cache_layer_stride;
+    float *vc = d->v_cache + l * d->cache_layer_stride;
+    need(vxb::rows_norm_terms(d->rows_terms, d->rows_x, d->attn_norm[l], T, c.dim,
+                              c.eps, s),
+         "RMSNorm");
+    need(vxb::rows_gemm(d->rows_terms, d->wq[l], T, qkv_rows, c.dim,
+                        d->rows_partials, &splits, s),
+         "q/k/v");
+    need(vxb::rows_qkv_finish(d->rows_partials, splits, T, d->q_local, d->kv_local,
+                              hd, d->bqkv[l], d->cos_t, d->sin_t, d->positions,
+                              d->rows_q, kc, vc, s),
+         "RoPE and the cache store");
+    need(vxb::rows_attention(d->rows_terms, d->rows_q, kc, vc, d->positions, T,
+                             d->q_local, d->kv_local, hd, s),
+         "attention");
+    need(vxb::rows_gemm(d->rows_terms, d->wo[l], T, c.dim, att_cols,
+                        d->rows_partials, &splits, s),
+         "the output projection");
+    need(vxb::rows_residual_finish(d->rows_x, d->rows_partials, splits, T, c.dim, s),
+         "the residual add");
+    need(vxb::rows_norm_terms(d->rows_terms, d->rows_x, d->ffn_norm[l], T, c.dim,
+                              c.eps, s),
+         "RMSNorm");
+    need(vxb::rows_gemm(d->rows_terms, d->w_gate[l], T, 2 * d->hidden_local, c.dim,
+                        d->rows_partials, &splits, s),
+         "gate/up");
+    need(vxb::rows_swiglu_finish(d->rows_terms, d->rows_partials, splits, T,
+                                 d->hidden_local, s),
+         "SwiGLU");
+    need(vxb::rows_gemm(d->rows_terms, d->w_down[l], T, c.dim, d->hidden_local,
+                        d->rows_partials, &splits, s),
+         "the down projection");
+    need(vxb::rows_residual_finish(d->rows_x, d->rows_partials, splits, T, c.dim, s),
+         "the residual add");
   }
-  d->host_pos += taken;
-  return taken;
+  advance_by_kernel<<<1, 32, 0, s>>>(d->positions, T);
+  d->host_pos += T;
+  return T;
+}
+
+/* ---- llama2.c checkpoints ------------------------------------------------------
+ * The file the reference's llama programs read (stdlib/rust_core/src/ffi/
+ * llama.rs:11-47: vx_load_config takes the first 7 int32, vx_load_weights the
+ * f32 values after them; stdlib/std/llama.vx:86-148 gives the order): dim,
+ * hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len, then
+ * token_embedding_table [vocab, dim], rms_att [L, dim], wq [L, dim, dim],
+ * wk, wv [L, kv_dim, dim], wo [L, dim, dim], rms_ffn [L, dim],
+ * w1 [L, hidden, dim], w2 [L, dim, hidden], w3 [L, hidden, dim],
+ * rms_final [dim]. llama2.c writes a negative vocab_size when the classifier
+ * is not the embedding table; it then follows two legacy RoPE tables of
+ * seq_len * head_size / 2 values each. */
+namespace {
+struct MappedFile {
+  const unsigned char *data = nullptr;
+  size_t bytes = 0;
+  int fd = -1;
+  ~MappedFile() {
+    if (data)
+      munmap((void *)data, bytes);
+    if (fd >= 0)
+      close(fd);
+  }
+};
+const char *map_file(const char *path, MappedFile *f) {
+  static thread_local char msg[512];
+  f->fd = path ? open(path, O_RDONLY) : -1;
+  struct stat st;
+  if (f->fd < 0 || fstat(f->fd, &st) != 0) {
+    snprintf(msg, sizeof msg, "cannot open the checkpoint %s",
+             path ? path : "(null)");
+    return msg;
+  }
+  f->bytes = (size_t)st.st_size;
+  if (f->bytes < 28) {
+    snprintf(msg, sizeof msg,
+             "%s is %zu bytes: shorter than the 7 int32 of a llama2.c header",
+             path, f->bytes);
+    return msg;
+  }
+  void *p = mmap(nullptr, f->bytes, PROT_READ, MAP_PRIVATE, f->fd, 0);
+  if (p == MAP_FAILED) {
+    snprintf(msg, sizeof msg, "cannot map the checkpoint %s", path);
+    return msg;
+  }
+  f->data = (const unsigned char *)p;
+  return nullptr;
+}
+/* The header, checked; `floats` gets how many f32 values the weights take. */
+const char *read_llama2c_header(const MappedFile &f, const char *path,
+                                vx_llama2c_config *c, bool *shared,
+                                int64_t *floats) {
+  static thread_local char msg[512];
+  memcpy(c, f.data, 28);
+  *shared = c->vocab_size > 0;
+  if (!*shared)
+    c->vocab_size = -c->vocab_size;
+  if (c->dim <= 0 || c->hidden_dim <= 0 || c->n_layers <= 0 || c->n_heads <= 0 ||
+      c->n_kv_heads <= 0 || c->vocab_size <= 0 || c->seq_len <= 0 ||
+      c->dim % c->n_heads != 0 || c->n_heads % c->n_kv_heads != 0) {
+    snprintf(msg, sizeof msg,
+             "%s does not begin with a llama2.c header (dim %d, hidden_dim %d, "
+             "n_layers %d, n_heads %d, n_kv_heads %d, vocab_size %d, seq_len %d)",
+             path, c->dim, c->hidden_dim, c->n_layers, c->n_heads, c->n_kv_heads,
+             c->vocab_size, c->seq_len);
+    return msg;
+  }
+  const int64_t dim = c->dim, L = c->n_layers, hs = c->dim / c->n_heads;
+  const int64_t kv = c->n_kv_heads * hs, hid = c->hidden_dim, vocab = c->vocab_size;
+  int64_t n = vocab * dim + L * dim + L * dim * dim + 2 * L * dim * kv +
+              L * dim * dim + L * dim + 3 * L * dim * hid + dim;
+  if (!*shared)
+    n += c->seq_len * hs + vocab * dim; /* two tables of seq_len*hs/2, wcls */
+  *floats = n;
+  if ((int64_t)f.bytes < 28 + 4 * n) {
+    snprintf(msg, sizeof msg,
+             "%s holds %zu bytes, and its header describes %lld bytes of "
+             "weights after the 28 of the header: the file is cut short or the "
+             "header is not this file's",
+             path, f.bytes, (long long)(4 * n));
+    return msg;
+  }
+  return nullptr;
+}
+} // namespace
+
+int32_t vx_b200_llama2c_config(const char *path, vx_llama2c_config *out) {
+  MappedFile f;
+  bool shared;
+  int64_t floats;
+  vx_llama2c_config c;
+  const char *why = map_file(path, &f);
+  if (!why)
+    why = read_llama2c_header(f, path, &c, &shared, &floats);
+  if (why) {
+    vxb::set_last_error(why);
+    return -1;
+  }
+  if (out)
+    *out = c;
+  return 0;
+}
+
+vx_decoder *vx_decoder_from_llama2c(const char *path, int32_t batch,
+                                    int32_t max_seq) {
+  MappedFile f;
+  bool shared;
+  int64_t floats;
+  vx_llama2c_config c;
+  const char *why = map_file(path, &f);
+  if (!why)
+    why = read_llama2c_header(f, path, &c, &shared, &floats);
+  if (why) {
+    vxb::set_last_error(why);
+    return nullptr;
+  }
+  /* One device buffer for all weights, filled through a pinned staging buffer
+     in pieces, so that neither a second host copy of the model nor a pageable
+     copy of it is made. */
+  float *dev = nullptr;
+  if (cudaMalloc((void **)&dev, (size_t)floats * 4) != cudaSuccess) {
+    cudaGetLastError();
+    vxb::set_last_error("out of device memory for the checkpoint's weights");
+    return nullptr;
+  }
+  const size_t piece = (size_t)32 << 20;
+  void *pinned[2] = {nullptr, nullptr};
+  cudaEvent_t landed[2];
+  cudaStream_t copy_stream;
+  CUDA_OK(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
+  for (int i = 0; i < 2; ++i) {
+    CUDA_OK(cudaMallocHost(&pinned[i], piece));
+    CUDA_OK(cudaEventCreateWithFlags(&landed[i], cudaEventDisableTiming));
+  }
+  const unsigned char *src = f.data + 28;
+  const size_t total = (size_t)floats * 4;
+  int turn = 0;
+  for (size_t at = 0; at < total; at += piece, turn ^= 1) {
+    const size_t n = total - at < piece ? total - at : piece;
+    CUDA_OK(cudaEventSynchronize(landed[turn])); /* the buffer is free again */
+    memcpy(pinned[turn], src + at, n);
+    CUDA_OK(cudaMemcpyAsync((char *)dev + at, pinned[turn], n,
+                            cudaMemcpyHostToDevice, copy_stream));
+    CUDA_OK(cudaEventRecord(landed[turn], copy_stream));
+  }
+  CUDA_OK(cudaStreamSynchronize(copy_stream));
+  for (int i = 0; i < 2; ++i) {
+    cudaFreeHost(pinned[i]);
+    cudaEventDestroy(landed[i]);
+  }
+  cudaStreamDestroy(copy_stream);
+
+  const int64_t dim = c.dim, L = c.n_layers, hs = c.dim / c.n_heads;
+  const int64_t kv = c.n_kv_heads * hs, hid = c.hidden_dim, vocab = c.vocab_size;
+  const float *p = dev;
+  const float *tok = p;          p += vocab * dim;
+  const float *rms_att = p;      p += L * dim;
+  const float *wq = p;           p += L * dim * dim;
+  const float *wk = p;           p += L * dim * kv;
+  const float *wv = p;           p += L * dim * kv;
+  const float *wo = p;           p += L * dim * dim;
+  const float *rms_ffn = p;      p += L * dim;
+  const float *w1 = p;           p += L * dim * hid;
+  const float *w2 = p;           p += L * hid * dim;
+  const float *w3 = p;           p += L * dim * hid;
+  const float *rms_final = p;    p += dim;
+  const float *wcls = shared ? tok : p + (int64_t)c.seq_len * hs;
+  std::vector<const void *> a_norm(L), a_wq(L), a_wk(L), a_wv(L), a_wo(L),
+      f_norm(L), a_w1(L), a_w2(L), a_w3(L);
+  for (int64_t l = 0; l < L; ++l) {
+    a_norm[l] = rms_att + l * dim;
+    a_wq[l] = wq + l * dim * dim;
+    a_wk[l] = wk + l * dim * kv;
+    a_wv[l] = wv + l * dim * kv;
+    a_wo[l] = wo + l * dim * dim;
+    f_norm[l] = rms_ffn + l * dim;
+    a_w1[l] = w1 + l * dim * hid;
+    a_w2[l] = w2 + l * hid * dim;
+    a_w3[l] = w3 + l * dim * hid;
+  }
+  vx_decoder_weights w{};
+  w.embed = tok;
+  w.attn_norm = a_norm.data();
+  w.wq = a_wq.data();
+  w.wk = a_wk.data();
+  w.wv = a_wv.data();
+  w.wo = a_wo.data();
+  w.ffn_norm = f_norm.data();
+  w.w_gate = a_w1.data();
+  w.w_up = a_w3.data();
+  w.w_down = a_w2.data();
+  w.final_norm = rms_final;
+  w.lm_head = wcls;
+  vx_decoder_config cfg{};
+  cfg.dim = c.dim;
+  cfg.hidden = c.hidden_dim;
+  cfg.n_layers = c.n_layers;
+  cfg.q_heads = c.n_heads;
+  cfg.kv_heads = c.n_kv_heads;
+  cfg.head_dim = (int32_t)hs;
+  cfg.vocab = c.vocab_size;
+  cfg.max_seq = max_seq > 0 ? max_seq : c.seq_len;
+  cfg.eps = 1e-5f;
+  cfg.rope_theta = 10000.0f;
+  cfg.weights_bf16 = 0;
+  cfg.batch = batch > 0 ? batch : 1;
+  cfg.tp_ranks = 1;
+  cfg.tp_reduce = 0;
+  vx_decoder *d = vx_decoder_create(&cfg, &w);
+  d->owned_weights = dev;
+  return d;
 }
 
 const float *vx_decoder_logits(const vx_decoder *d) { return d->logits; }

@@ -34,6 +34,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -42,6 +43,11 @@ namespace vxb {
 const char *gemm_16_plain(bool is_bf16, const void *a, int64_t lda,
                           const void *b, int64_t ldb, void *c, int64_t ldc,
                           int64_t m, int64_t n, int64_t k, cudaStream_t stream);
+/* gemm_umma_pair.cu: the same product on CTA pairs (256x256 tiles). */
+const char *gemm_16_pair(int route, bool is_bf16, const void *a, int64_t lda,
+                         const void *b, int64_t ldb, void *c, int64_t ldc,
+                         int64_t m, int64_t n, int64_t k, cudaStream_t stream);
+int gemm_pair_status();
 
 namespace {
 
@@ -367,6 +373,16 @@ const char *gemm_16_route(int route, bool is_bf16, const void *a, int64_t lda,
   if (!umma_shape_ok(a, lda, b, ldb, c, ldc, m, n, k))
     return "the tcgen05 GEMM needs 16-byte aligned bases and row strides that "
            "are multiples of 8 elements";
+  if (route == 4)
+    return gemm_16_pair(4, is_bf16, a, lda, b, ldb, c, ldc, m, n, k, stream);
+  if (route == 5) {
+    if (!scratch || ((uintptr_t)scratch & 15) || k % 8 != 0)
+      return "the transposed-B route needs a 16-byte aligned scratch matrix "
+             "and k a multiple of 8";
+    if (const char *why = transpose_16(b, ldb, scratch, k, k, n, stream))
+      return why;
+    return gemm_16_pair(5, is_bf16, a, lda, scratch, k, c, ldc, m, n, k, stream);
+  }
   CUtensorMap ma, mb;
   if (!make_map_16(&ma, a, k, m, lda, BK, BM, is_bf16))
     return "cuTensorMapEncodeTiled refused the A matrix";
@@ -399,7 +415,21 @@ const char *gemm_16(bool is_bf16, const void *a, int64_t lda, const void *b,
   const bool small = m * n < 128 * 256 || k < 64;
   if (small || !umma_shape_ok(a, lda, b, ldb, c, ldc, m, n, k) || !encoder())
     return gemm_16_plain(is_bf16, a, lda, b, ldb, c, ldc, m, n, k, stream);
-  return gemm_16_route(1, is_bf16, a, lda, b, ldb, c, ldc, m, n, k, nullptr,
+  /* One CTA per 128x256 tile, or a CTA pair per 256x256 tile: the pair's MMA
+     runs near the tensor pipe's full rate where the single CTA's is limited
+     to 77 % by its operand fetch, but its tile is twice as large, so it pays
+     only from about a wave of tiles on. Cost in units of a one-CTA tile. */
+  const int64_t t1 = ((m + 127) / 128) * ((n + 255) / 256);
+  const int64_t t2 = ((m + 255) / 256) * ((n + 255) / 256);
+  const int sms = sm_count();
+  const double cost1 = (double)((t1 + sms - 1) / sms);
+  const double cost2 = (double)((t2 + sms / 2 - 1) / (sms / 2)) * 1.64;
+  /* VXB_GEMM_ROUTE=1 or 4 pins the choice (for measurements). */
+  const char *force = getenv("VXB_GEMM_ROUTE");
+  const int route = force && (force[0] == '1' || force[0] == '4')
+                        ? force[0] - '0'
+                        : (cost2 < cost1 ? 4 : 1);
+  return gemm_16_route(route, is_bf16, a, lda, b, ldb, c, ldc, m, n, k, nullptr,
                        stream);
 }
 
@@ -411,7 +441,8 @@ int gemm_status(cudaStream_t stream) {
     return -1;
   if (v)
     cudaMemcpyToSymbol(g_status, &zero, sizeof zero);
-  return v;
+  const int pair = gemm_pair_status();
+  return v ? v : pair;
 }
 
 } // namespace vxb

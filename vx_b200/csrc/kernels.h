@@ -26,7 +26,8 @@ const char *gemm_16(bool is_bf16, const void *a, int64_t lda, const void *b,
                     int64_t k, cudaStream_t stream);
 /* Forced routes, for tests and benchmarks. route: 0 = pick, 1 = tcgen05 with
    B read as stored (N-major operand), 2 = tcgen05 after transposing B into
-   `scratch` ([n,k], caller-owned), 3 = the plain tiled kernel. */
+   `scratch` ([n,k], caller-owned), 3 = the plain tiled kernel, 4 and 5 = 1
+   and 2 on CTA pairs (tcgen05.mma.cta_group::2, 256x256 tiles). */
 const char *gemm_16_route(int route, bool is_bf16, const void *a, int64_t lda,
                           const void *b, int64_t ldb, void *c, int64_t ldc,
                           int64_t m, int64_t n, int64_t k, void *scratch,
@@ -40,11 +41,19 @@ const char *matvec_f32(float *y, const float *x, const float *w, int n, int d,
                        cudaStream_t stream);
 
 /* ---- decode operators ------------------------------------------------------
- * W is bf16 (wbf16) or f32, row-major [rows, cols]; x and y are f32 with
- * `batch` vectors, row b of x at x + b*x_stride.                            */
+ * W is row-major [rows, cols] in one of four formats; x and y are f32 with
+ * `batch` vectors, row b of x at x + b*x_stride. wfmt 0: bf16 (wbf16) or f32.
+ * kFmtFp8: f8e4m3 codes, one byte each, with f32 scales [ceil(rows/128),
+ * cols/128] (stdlib/std/nn.vx:1296-1303); kFmtQ4: Q4_0, two codes a byte,
+ * weight = (code - 8) * an f16 scale per 32 weights of a row
+ * (nn.vx:1645-1663). The quantised formats take one sequence.               */
+enum { kFmtF32 = 1, kFmtBf16 = 2, kFmtFp8 = 3, kFmtQ4 = 4 };
 struct MatvecArgs {
   const void *w;
   bool wbf16;
+  int wfmt;            /* 0: as wbf16 says */
+  const void *scales;  /* kFmtFp8, kFmtQ4 */
+  int row_base;        /* w is rows row_base.. of the matrix `scales` is for */
   int rows, cols;
   const float *x;
   int64_t x_stride;
@@ -95,6 +104,9 @@ const char *matvec(const MatvecArgs &a, cudaStream_t stream);
 struct SwigluArgs {
   const void *w;
   bool wbf16;
+  int wfmt;
+  const void *scales, *scales_up; /* of w, and of w_up when that is given */
+  int row_base;
   int rows, cols;
   const void *w_up; /* NULL: up rows follow the gate rows in w */
   const float *x;
@@ -120,6 +132,8 @@ const char *rms_norm(float *y, const float *x, const void *w, bool wbf16, int n,
 struct QkvArgs {
   const void *wq, *wk, *wv; /* wk == NULL: fused rows in wq */
   bool wbf16;
+  int wfmt;
+  const void *sq, *sk, *sv; /* the scales of wq, wk, wv */
   const void *bias; /* bf16 or NULL */
   int q_heads, kv_heads, head_dim, cols;
   const float *x;
@@ -231,6 +245,41 @@ const char *batched_proj_refusal(const BatchedProj &a);
 size_t batched_proj_scratch_floats(int rows_max, int batch);
 const char *batched_proj(const BatchedProj &a, cudaStream_t stream);
 int batched_proj_status(cudaStream_t stream);
+
+/* ---- a whole prompt at once (prefill.cu) ---------------------------------------
+ * T positions as the rows of GEMMs on CTA pairs. Activations travel between
+ * the GEMMs as "terms": a bf16 matrix [T, 3 cols] holding x as x1 | x2 | x3
+ * with x = x1 + x2 + x3 exactly. rows_gemm leaves partials[run][t][r], the sums
+ * of `*splits_out` runs of the K dimension; the *_finish calls add the runs in
+ * run order and apply the projection's epilogue. */
+int rows_gemm_splits(int t, int n, int cols);
+size_t rows_gemm_partial_floats(int t, int n, int cols);
+/* partials[run][t][r] = sum over the run's part of c of W[r, c] x[t, c];
+   w bf16 [n, cols], cols a multiple of 64. */
+const char *rows_gemm(const void *terms, const void *w, int t, int n, int cols,
+                      float *partials, int *splits_out, cudaStream_t stream);
+/* terms of RMSNorm(x[t]) * w for every position (nn_rms_norm_rows). */
+const char *rows_norm_terms(void *terms, const float *x, const void *w, int t,
+                            int dim, float eps, cudaStream_t stream);
+/* bias + half-split RoPE; q to q_out [t][q_heads*hd], k and v to cache rows
+   first_pos[0] + t. */
+const char *rows_qkv_finish(const float *partials, int splits, int t, int q_heads,
+                            int kv_heads, int hd, const void *bias,
+                            const float *cos_t, const float *sin_t,
+                            const int32_t *first_pos, float *q_out, float *k_cache,
+                            float *v_cache, cudaStream_t stream);
+/* x[t][r] += the product, r below n. */
+const char *rows_residual_finish(float *x, const float *partials, int splits, int t,
+                                 int n, cudaStream_t stream);
+/* terms of silu(gate) * up; partials have 2 hidden rows: gate, then up. */
+const char *rows_swiglu_finish(void *terms, const float *partials, int splits, int t,
+                               int hidden, cudaStream_t stream);
+/* Causal attention of the T prompt positions over cache rows 0 ..
+   first_pos[0] + t, f32; the output as terms [T, 3 q_heads hd]. head_dim 128. */
+const char *rows_attention(void *terms, const float *q, const float *k_cache,
+                           const float *v_cache, const int32_t *first_pos, int t,
+                           int q_heads, int kv_heads, int hd, cudaStream_t stream);
+int rows_status();
 
 const char *argmax(int32_t *out, const float *logits, int n, int batch,
                    int64_t stride, cudaStream_t stream);

@@ -389,6 +389,168 @@ void vx_nn_embed(VX_TENSOR1(x), VX_TENSOR1(table), VX_TENSOR1(token),
 }
 #undef FN
 
+} /* extern "C" */
+
+/* ------------------------------------------------ fp8 and Q4_0 projections
+ * (nn.vx:1296-1640 and 1645-2100). One body for both formats: `quant` is
+ * kFmtFp8 (codes 4 to a u32 word, f32 scales per 128 x 128 block) or kFmtQ4
+ * (codes 8 to a word, an f16 scale per 32 weights of a row). The checks are
+ * nn_check_fp8 and nn_check_q4 (nn.vx:2267-2284). */
+namespace {
+void check_quant(const char *fn, int quant, int64_t w_len, int64_t s_len,
+                 int64_t x_len, int rows, int cols) {
+  if (quant == vxb::kFmtFp8) {
+    if (rows <= 0 || rows % 4 != 0 || cols <= 0 || cols % 128 != 0)
+      stop("%s: rows must be a multiple of 4, and cols a multiple of 128", fn);
+    if (x_len < cols)
+      stop("%s: the input has fewer values than cols", fn);
+    if (rows > w_len / (cols / 4) ||
+        s_len < (int64_t)((rows + 127) / 128) * (cols / 128))
+      stop("%s: the codes or the scales are too few for rows x cols", fn);
+  } else {
+    if (rows <= 0 || rows % 4 != 0 || cols <= 0 || cols % 32 != 0)
+      stop("%s: rows must be a multiple of 4, and cols a multiple of 32", fn);
+    if (x_len < cols)
+      stop("%s: the input has fewer values than cols", fn);
+    if (rows > w_len / (cols / 8) || rows > s_len / (cols / 32))
+      stop("%s: the codes or the scales are too few for rows x cols", fn);
+  }
+}
+void quant_matvec(const char *fn, int quant, float *y, int64_t y_len,
+                  const void *w, int64_t w_len, const void *scales,
+                  int64_t s_len, const float *x, int64_t x_len, int rows,
+                  int cols, int mode) {
+  check_quant(fn, quant, w_len, s_len, x_len, rows, cols);
+  if (y_len < rows)
+    stop("%s: the output has fewer values than rows", fn);
+  vxb::MatvecArgs a{};
+  a.w = w;
+  a.wfmt = quant;
+  a.scales = scales;
+  a.rows = rows;
+  a.cols = cols;
+  a.x = x;
+  a.x_stride = cols;
+  a.y = y;
+  a.y_stride = rows;
+  a.batch = 1;
+  a.mode = mode;
+  must(vxb::matvec(a, vxb::caller_stream()), fn);
+}
+void quant_qkv(const char *fn, int quant, float *q, float *k, float *v,
+               const void *w, int64_t w_len, const void *scales, int64_t s_len,
+               const uint16_t *bias, int64_t b_len, const float *x,
+               int64_t x_len, int q_heads, int kv_heads, int head_dim, int cols) {
+  const int rows_all = (q_heads + 2 * kv_heads) * head_dim;
+  check_quant(fn, quant, w_len, s_len, x_len, rows_all, cols);
+  if (b_len < rows_all)
+    stop("%s: the bias has fewer values than rows", fn);
+  float *outs[3] = {q, k, v};
+  const int counts[3] = {q_heads, kv_heads, kv_heads};
+  const int64_t row_bytes = quant == vxb::kFmtFp8 ? cols : cols / 2;
+  int row = 0;
+  for (int part = 0; part < 3; ++part) {
+    vxb::MatvecArgs a{};
+    a.w = (const char *)w + row * row_bytes;
+    a.wfmt = quant;
+    a.scales = scales; /* of the whole matrix: row_base says where we are */
+    a.row_base = row;
+    a.rows = counts[part] * head_dim;
+    a.cols = cols;
+    a.x = x;
+    a.x_stride = cols;
+    a.y = outs[part];
+    a.y_stride = a.rows;
+    a.batch = 1;
+    a.mode = 2;
+    a.bias = bias + row;
+    must(vxb::matvec(a, vxb::caller_stream()), fn);
+    row += a.rows;
+  }
+}
+void quant_swiglu(const char *fn, int quant, float *out, int64_t out_len,
+                  const void *w, int64_t w_len, const void *scales,
+                  int64_t s_len, const float *x, int64_t x_len, int rows,
+                  int cols) {
+  check_quant(fn, quant, w_len, s_len, x_len, 2 * rows, cols);
+  if (out_len < rows)
+    stop("%s: the output has fewer values than rows", fn);
+  vxb::SwigluArgs a{};
+  a.w = w;
+  a.wfmt = quant;
+  a.scales = scales;
+  a.rows = rows;
+  a.cols = cols;
+  a.x = x;
+  a.x_stride = cols;
+  a.out = out;
+  a.out_stride = rows;
+  a.batch = 1;
+  must(vxb::swiglu(a, vxb::caller_stream()), fn);
+}
+} // namespace
+
+#define QUANT_EXPORTS(SUFFIX, QUANT, SCALE_T, TAG)                             \
+  void vx_nn_matvec_##SUFFIX(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(scales), \
+                             VX_TENSOR1(x), int32_t rows, int32_t cols) {      \
+    static const char FN[] = "nn_matvec_" TAG;                                 \
+    UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(x);   \
+    quant_matvec(FN, QUANT, T1(float, y), y_n0, T1(uint32_t, w), w_n0,         \
+                 T1(SCALE_T, scales), scales_n0, T1(float, x), x_n0, rows,     \
+                 cols, 0);                                                     \
+  }                                                                            \
+  void vx_nn_matvec_##SUFFIX##_add(VX_TENSOR1(y), VX_TENSOR1(w),               \
+                                   VX_TENSOR1(scales), VX_TENSOR1(x),          \
+                                   int32_t rows, int32_t cols) {               \
+    static const char FN[] = "nn_matvec_" TAG "_add";                          \
+    UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(x);   \
+    quant_matvec(FN, QUANT, T1(float, y), y_n0, T1(uint32_t, w), w_n0,         \
+                 T1(SCALE_T, scales), scales_n0, T1(float, x), x_n0, rows,     \
+                 cols, 1);                                                     \
+  }                                                                            \
+  void vx_nn_matvec_##SUFFIX##_heads_add(                                      \
+      VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(scales), VX_TENSOR2(x),         \
+      int32_t rows, int32_t heads, int32_t head_dim) {                         \
+    static const char FN[] = "nn_matvec_" TAG "_heads_add";                    \
+    UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(x);   \
+    check_heads(FN, x_n0, x_n1, heads, head_dim);                              \
+    quant_matvec(FN, QUANT, T1(float, y), y_n0, T1(uint32_t, w), w_n0,         \
+                 T1(SCALE_T, scales), scales_n0, T2(float, x),                 \
+                 (int64_t)heads * head_dim, rows, heads * head_dim, 1);        \
+  }                                                                            \
+  void vx_nn_qkv_##SUFFIX(VX_TENSOR2(q), VX_TENSOR2(k), VX_TENSOR2(v),         \
+                          VX_TENSOR1(w), VX_TENSOR1(scales), VX_TENSOR1(b),    \
+                          VX_TENSOR1(x), int32_t q_heads, int32_t kv_heads,    \
+                          int32_t head_dim, int32_t cols) {                    \
+    static const char FN[] = "nn_qkv_" TAG;                                    \
+    UNUSED_ALLOC(q); UNUSED_ALLOC(k); UNUSED_ALLOC(v); UNUSED_ALLOC(w);        \
+    UNUSED_ALLOC(scales); UNUSED_ALLOC(b); UNUSED_ALLOC(x);                    \
+    check_heads(FN, q_n0, q_n1, q_heads, head_dim);                            \
+    check_heads(FN, k_n0, k_n1, kv_heads, head_dim);                           \
+    check_heads(FN, v_n0, v_n1, kv_heads, head_dim);                           \
+    quant_qkv(FN, QUANT, T2(float, q), T2(float, k), T2(float, v),             \
+              T1(uint32_t, w), w_n0, T1(SCALE_T, scales), scales_n0,           \
+              T1(uint16_t, b), b_n0, T1(float, x), x_n0, q_heads, kv_heads,    \
+              head_dim, cols);                                                 \
+  }                                                                            \
+  void vx_nn_swiglu_##SUFFIX(VX_TENSOR1(out), VX_TENSOR1(w),                   \
+                             VX_TENSOR1(scales), VX_TENSOR1(x), int32_t rows,  \
+                             int32_t cols) {                                   \
+    static const char FN[] = "nn_swiglu_" TAG;                                 \
+    UNUSED_ALLOC(out); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(x); \
+    quant_swiglu(FN, QUANT, T1(float, out), out_n0, T1(uint32_t, w), w_n0,     \
+                 T1(SCALE_T, scales), scales_n0, T1(float, x), x_n0, rows,     \
+                 cols);                                                        \
+  }
+
+extern "C" {
+QUANT_EXPORTS(fp8, vxb::kFmtFp8, float, "fp8")
+QUANT_EXPORTS(q4, vxb::kFmtQ4, uint16_t, "q4")
+}
+#undef QUANT_EXPORTS
+
+extern "C" {
+
 /* --------------------------------------------------------------- direct calls */
 int32_t vx_b200_gemm(int32_t dtype, int32_t route, int64_t m, int64_t n,
                      int64_t k, const void *a, int64_t lda, const void *b,
@@ -421,7 +583,8 @@ int32_t vx_b200_kernel_status(void) {
   const int f = vxb::flash_status(vxb::caller_stream());
   const int t = vxb::tp_status(vxb::caller_stream());
   const int m = vxb::batched_proj_status(vxb::caller_stream());
-  return g ? g : (f ? f : (t ? t : m));
+  const int r = vxb::rows_status();
+  return g ? g : (f ? f : (t ? t : (m ? m : r)));
 }
 
 int32_t vx_b200_attention_kernel(int32_t which) {

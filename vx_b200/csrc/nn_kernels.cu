@@ -23,6 +23,8 @@
 
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include <algorithm>
 #include <cstdio>
@@ -35,13 +37,6 @@ namespace {
 constexpr int WARPS = 16;            /* per block, projection kernels */
 constexpr int MAX_SMEM_X = 96 * 1024; /* x (all batch rows) staged per block */
 
-__device__ __forceinline__ uint4 ld_stream(const void *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
 __device__ __forceinline__ float bf_lo(uint32_t u) {
   return __uint_as_float(u << 16);
 }
@@ -89,6 +84,11 @@ enum { EPI_STORE = 0, EPI_ADD = 1, EPI_BIAS = 2, EPI_SWIGLU = 3, EPI_QKV = 4,
 struct RowDotParams {
   /* weights */
   const void *w0, *w1, *w2; /* matvec: w0; swiglu: gate w0, up w1; qkv: q,k,v */
+  /* the scales of w0, w1, w2 (fp8: f32 [ceil(rows/128), cols/128]; Q4_0: f16
+     [rows, cols/32]); row_base: the row of the whole matrix that row 0 of w0
+     is, when w0 is a run of rows inside a matrix with one table of scales */
+  const void *s0, *s1, *s2;
+  int row_base;
   int rows, cols;
   int items;
   /* activations */
@@ -116,14 +116,70 @@ struct RowDotParams {
   TpPush tp;
 };
 
-/* acc[b] += sum over the E weights of one 16-byte word (8 bf16 or 4 f32) of
-   w * x[b]. */
+/* Weight formats. A row is a run of 16-byte words; a word holds E weights:
+   4 f32, 8 bf16, 16 fp8 (f8e4m3 codes with an f32 scale per block of 128 x 128
+   weights, nn.vx:1296-1303) or 32 Q4_0 codes (4 bits, weight = (code - 8) *
+   an f16 scale per 32 weights of a row, nn.vx:1645-1663). */
+struct Fp8W {};
+struct Q4W {};
+template <typename W> struct PerWord { static constexpr int n = 16 / (int)sizeof(W); };
+template <> struct PerWord<Fp8W> { static constexpr int n = 16; };
+template <> struct PerWord<Q4W> { static constexpr int n = 32; };
+template <typename W> struct Scaled { static constexpr bool yes = false; };
+template <> struct Scaled<Fp8W> { static constexpr bool yes = true; };
+template <> struct Scaled<Q4W> { static constexpr bool yes = true; };
+
+/* The 16 weights of an fp8 word, and the 32 of a Q4_0 word less 8 each, as
+   f32 (both exact). */
+__device__ __forceinline__ void unpack_fp8(const uint4 &wv, float (&wf)[16]) {
+  const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __half2_raw two = __nv_cvt_fp8x2_to_halfraw2(
+          (__nv_fp8x2_storage_t)(u[j] >> (16 * h)), __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&two));
+      wf[4 * j + 2 * h] = f.x;
+      wf[4 * j + 2 * h + 1] = f.y;
+    }
+  }
+}
+__device__ __forceinline__ void unpack_q4(const uint4 &wv, float (&wf)[32]) {
+  /* 0x4B000000 | c is the float 2^23 + c for c below 2^23, so a nibble left
+     in place t (t below 4) gives 2^23 + 16^t c, and subtracting
+     2^23 + 8 * 16^t leaves 16^t (c - 8), exactly: wf[8j + 4h + t] is the
+     weight times 16^t, and fma16 takes the factor off the sums (the
+     reference takes it off x, nn.vx:1659-1661). The upper four nibbles of a
+     32-bit word are shifted down first. */
+  const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t lo = u[j], hi = u[j] >> 16;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const uint32_t mask = 15u << (4 * t);
+      const float off = 8388608.0f + 8.0f * (float)(1 << (4 * t));
+      wf[8 * j + t] = __uint_as_float((lo & mask) | 0x4B000000u) - off;
+      wf[8 * j + 4 + t] = __uint_as_float((hi & mask) | 0x4B000000u) - off;
+    }
+  }
+}
+
+/* acc[b] += sum over the E weights of one 16-byte word of w * x[b]; for the
+   scaled formats the word's sum is taken first and enters acc[b] times the
+   word's scale. */
 template <typename W, int B>
 __device__ __forceinline__ void
-fma16(const uint4 &wv, const float (&xv)[B][16 / sizeof(W)], float (&acc)[B]) {
-  constexpr int E = 16 / (int)sizeof(W);
+fma16(const uint4 &wv, const float (&xv)[B][PerWord<W>::n], float (&acc)[B],
+      float scale) {
+  constexpr int E = PerWord<W>::n;
   float wf[E];
-  if (E == 8) {
+  if constexpr (E == 16) {
+    unpack_fp8(wv, wf);
+  } else if constexpr (E == 32) {
+    unpack_q4(wv, wf);
+  } else if constexpr (E == 8) {
     wf[0] = bf_lo(wv.x); wf[1] = bf_hi(wv.x);
     wf[2] = bf_lo(wv.y); wf[3] = bf_hi(wv.y);
     wf[E - 4] = bf_lo(wv.z); wf[E - 3] = bf_hi(wv.z);
@@ -132,11 +188,34 @@ fma16(const uint4 &wv, const float (&xv)[B][16 / sizeof(W)], float (&acc)[B]) {
     wf[0] = __uint_as_float(wv.x); wf[1] = __uint_as_float(wv.y);
     wf[2] = __uint_as_float(wv.z); wf[3] = __uint_as_float(wv.w);
   }
+  if constexpr (E == 32) {
 #pragma unroll
-  for (int b = 0; b < B; ++b)
+    for (int b = 0; b < B; ++b) {
+      float part[4] = {0.0f, 0.0f, 0.0f, 0.0f}; /* by nibble place */
 #pragma unroll
-    for (int e = 0; e < E; ++e)
-      acc[b] = fmaf(wf[e], xv[b][e], acc[b]);
+      for (int e = 0; e < E; ++e)
+        part[e & 3] = fmaf(wf[e], xv[b][e], part[e & 3]);
+      const float dot = fmaf(part[3], 1.0f / 4096.0f,
+                             fmaf(part[2], 1.0f / 256.0f,
+                                  fmaf(part[1], 1.0f / 16.0f, part[0])));
+      acc[b] = fmaf(dot, scale, acc[b]);
+    }
+  } else if constexpr (Scaled<W>::yes) {
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      float dot = 0.0f;
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        dot = fmaf(wf[e], xv[b][e], dot);
+      acc[b] = fmaf(dot, scale, acc[b]);
+    }
+  } else {
+#pragma unroll
+    for (int b = 0; b < B; ++b)
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        acc[b] = fmaf(wf[e], xv[b][e], acc[b]);
+  }
 }
 
 /* The pushed exchange moves (value, call) pairs: an aligned 8-byte store
@@ -179,48 +258,84 @@ __device__ __forceinline__ bool pair2_load(const TpPair *at, int call, float &v0
   return c0 == call && c1 == call;
 }
 
-/* The two weight rows of an item, and for q/k/v which head and pair it is. */
-template <typename W, int EPI> struct ItemRows {
-  const W *r0, *r1; /* r1 == nullptr: an odd last row */
+/* The two weight rows of an item (byte addresses), where their scales are,
+   and for q/k/v which head and pair it is. */
+struct ItemRows {
+  const char *r0, *r1; /* r1 == nullptr: an odd last row */
+  const char *sc0, *sc1; /* scaled formats: the scales of the rows' first column */
   int head, idx, kind; /* qkv: kind 0 q, 1 k, 2 v */
 };
+template <typename W>
+__device__ __forceinline__ const char *scale_row(const void *scales, int row,
+                                                 int cols) {
+  if (PerWord<W>::n == 16) /* fp8: one row of scales per 128 rows */
+    return (const char *)scales + (int64_t)(row / 128) * (cols / 128) * 4;
+  return (const char *)scales + (int64_t)row * (cols / 32) * 2; /* Q4_0 */
+}
 template <typename W, int EPI>
-__device__ __forceinline__ ItemRows<W, EPI> item_rows(const RowDotParams &p,
-                                                     int item) {
-  ItemRows<W, EPI> it;
+__device__ __forceinline__ ItemRows item_rows(const RowDotParams &p, int item) {
+  ItemRows it;
   const int cols = p.cols;
+  const int64_t row_bytes = (int64_t)cols * 16 / PerWord<W>::n;
   it.head = it.idx = it.kind = 0;
+  it.sc0 = it.sc1 = nullptr;
   if (EPI == EPI_SWIGLU) {
-    it.r0 = (const W *)p.w0 + (int64_t)item * cols;
-    it.r1 = p.w1 ? (const W *)p.w1 + (int64_t)item * cols
-                 : (const W *)p.w0 + (int64_t)(p.rows + item) * cols;
+    it.r0 = (const char *)p.w0 + item * row_bytes;
+    it.r1 = p.w1 ? (const char *)p.w1 + item * row_bytes
+                 : (const char *)p.w0 + (p.rows + item) * row_bytes;
+    if (Scaled<W>::yes) {
+      it.sc0 = scale_row<W>(p.s0, p.row_base + item, cols);
+      it.sc1 = p.w1 ? scale_row<W>(p.s1, item, cols)
+                    : scale_row<W>(p.s0, p.row_base + p.rows + item, cols);
+    }
   } else if (EPI == EPI_QKV) {
     const int half = p.head_dim / 2;
     it.head = item / half;
     it.idx = item - it.head * half;
     const int a = p.rope_mode == 0 ? it.idx : 2 * it.idx;
     const int b = p.rope_mode == 0 ? it.idx + half : 2 * it.idx + 1;
-    const W *base;
-    int local = it.head;
+    const char *base;
+    const void *sbase = p.s0;
+    int local = it.head, srow = p.row_base;
     if (it.head < p.q_heads) {
-      base = (const W *)p.w0;
+      base = (const char *)p.w0;
     } else if (it.head < p.q_heads + p.kv_heads) {
       it.kind = 1;
       local = it.head - p.q_heads;
-      base = p.w1 ? (const W *)p.w1
-                  : (const W *)p.w0 + (int64_t)p.q_heads * p.head_dim * cols;
+      if (p.w1) {
+        base = (const char *)p.w1;
+        sbase = p.s1;
+        srow = 0;
+      } else {
+        base = (const char *)p.w0 + p.q_heads * p.head_dim * row_bytes;
+        srow += p.q_heads * p.head_dim;
+      }
     } else {
       it.kind = 2;
       local = it.head - p.q_heads - p.kv_heads;
-      base = p.w2 ? (const W *)p.w2
-                  : (const W *)p.w0 + (int64_t)(p.q_heads + p.kv_heads) *
-                                          p.head_dim * cols;
+      if (p.w2) {
+        base = (const char *)p.w2;
+        sbase = p.s2;
+        srow = 0;
+      } else {
+        base = (const char *)p.w0 +
+               (p.q_heads + p.kv_heads) * p.head_dim * row_bytes;
+        srow += (p.q_heads + p.kv_heads) * p.head_dim;
+      }
     }
-    it.r0 = base + ((int64_t)local * p.head_dim + a) * cols;
-    it.r1 = base + ((int64_t)local * p.head_dim + b) * cols;
+    it.r0 = base + ((int64_t)local * p.head_dim + a) * row_bytes;
+    it.r1 = base + ((int64_t)local * p.head_dim + b) * row_bytes;
+    if (Scaled<W>::yes) {
+      it.sc0 = scale_row<W>(sbase, srow + local * p.head_dim + a, cols);
+      it.sc1 = scale_row<W>(sbase, srow + local * p.head_dim + b, cols);
+    }
   } else {
-    it.r0 = (const W *)p.w0 + (int64_t)(2 * item) * cols;
-    it.r1 = 2 * item + 1 < p.rows ? it.r0 + cols : nullptr;
+    it.r0 = (const char *)p.w0 + (int64_t)(2 * item) * row_bytes;
+    it.r1 = 2 * item + 1 < p.rows ? it.r0 + row_bytes : nullptr;
+    if (Scaled<W>::yes) {
+      it.sc0 = scale_row<W>(p.s0, p.row_base + 2 * item, cols);
+      it.sc1 = scale_row<W>(p.s0, p.row_base + 2 * item + 1, cols);
+    }
   }
   return it;
 }
@@ -240,25 +355,28 @@ __device__ int g_tp_status;     /* non-zero: a peer's flag never arrived */
    register file, so that the blocks of the attention kernel that follows
    q/k/v can start (and fetch their old cache rows) beside these. */
 template <typename W, int B, int EPI>
-__global__ void __maxnreg__(B == 1 ? 96 : 128)
+__global__ void __maxnreg__(B == 1 && !Scaled<W>::yes ? 96 : 128)
 rowdot_kernel(const RowDotParams p) {
   extern __shared__ __align__(128) unsigned char smem_dyn[];
   unsigned char *ring = smem_dyn;                    /* [warp][stage][2][chunk] */
   float *xs = (float *)(smem_dyn + RING_BYTES);      /* [B][cols] when x_in_smem */
   __shared__ float ssq[B][WARPS]; /* per-warp sums of squares of x */
   __shared__ __align__(8) uint64_t bars[WARPS][RING_STAGES];
-  constexpr int E = 16 / (int)sizeof(W);             /* elements per 16 bytes */
-  constexpr int CHUNK_COLS = CHUNK_BYTES / (int)sizeof(W);
+  constexpr int E = PerWord<W>::n;                   /* weights per 16 bytes */
+  constexpr int CHUNK_COLS = CHUNK_BYTES / 16 * E;
+  constexpr int GROUP = 32 * E; /* the weights of one word of each lane */
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int cols = p.cols;
-  /* x in shared memory: for bf16 weights a lane needs 8 consecutive values per
-     word; they are stored as two float4 halves 128 floats apart within each
-     group of 256, so that the 32 lanes of a warp read consecutive float4s. */
-  const int xs_stride = (cols + 255) / 256 * 256;
+  /* x in shared memory: a lane needs the E consecutive values of its word as
+     E / 4 float4s. Within each group of 32 E values they are stored quarter by
+     quarter, 128 floats apart (value i of the group: which float4 of its lane,
+     then the lane, then the place in the float4), so that the 32 lanes of a
+     warp read consecutive float4s. */
+  const int xs_stride = (cols + GROUP - 1) / GROUP * GROUP;
   auto xs_at = [](int i) {
-    return E == 8 ? (i & ~255) | (((i >> 2) & 1) << 7) | (((i >> 3) & 31) << 2) |
-                        (i & 3)
-                  : i;
+    return E > 4 ? (i & ~(GROUP - 1)) | (((i % E) >> 2) << 7) |
+                       (((i / E) & 31) << 2) | (i & 3)
+                 : i;
   };
 
   /* ---- this warp's items, as a stream of (item, chunk) units ---- */
@@ -266,7 +384,7 @@ rowdot_kernel(const RowDotParams p) {
   const int64_t gw = (int64_t)blockIdx.x * WARPS + warp;
   const int first = (int)(gw * p.items / total_warps);
   const int last = (int)((gw + 1) * p.items / total_warps);
-  const int row_bytes = cols * (int)sizeof(W);
+  const int row_bytes = cols / E * 16;
   const int nch = (row_bytes + CHUNK_BYTES - 1) / CHUNK_BYTES;
   const int units = (last - first) * nch;
   unsigned char *my_ring = ring + warp * (RING_STAGES * 2 * CHUNK_BYTES);
@@ -284,9 +402,9 @@ rowdot_kernel(const RowDotParams p) {
   int ld_u = 0, ld_item = first, ld_ch = 0, ld_stage = 0;
   const char *ld_r0 = nullptr, *ld_r1 = nullptr;
   if (units > 0) {
-    const ItemRows<W, EPI> it = item_rows<W, EPI>(p, first);
-    ld_r0 = (const char *)it.r0;
-    ld_r1 = (const char *)(it.r1 ? it.r1 : it.r0);
+    const ItemRows it = item_rows<W, EPI>(p, first);
+    ld_r0 = it.r0;
+    ld_r1 = it.r1 ? it.r1 : it.r0;
   }
   auto issue_next = [&]() {
     if (ld_u >= units)
@@ -305,9 +423,9 @@ rowdot_kernel(const RowDotParams p) {
       ld_ch = 0;
       ++ld_item;
       if (ld_u < units) {
-        const ItemRows<W, EPI> it = item_rows<W, EPI>(p, ld_item);
-        ld_r0 = (const char *)it.r0;
-        ld_r1 = (const char *)(it.r1 ? it.r1 : it.r0);
+        const ItemRows it = item_rows<W, EPI>(p, ld_item);
+        ld_r0 = it.r0;
+        ld_r1 = it.r1 ? it.r1 : it.r0;
       }
     }
   };
@@ -408,8 +526,8 @@ rowdot_kernel(const RowDotParams p) {
   }
   const float *xbase = p.x_in_smem ? xs : p.x;
   const int64_t xstr = p.x_in_smem ? xs_stride : p.x_stride;
-  /* where a lane finds the x of its 16-byte word, and its second half */
-  const bool x_perm = E == 8 && p.x_in_smem;
+  /* where a lane finds the x of its 16-byte word, and its further quarters */
+  const bool x_perm = E > 4 && p.x_in_smem;
   const int lane_x = x_perm ? lane * 4 : lane * E;
   const int hi_off = x_perm ? 128 : 4;
 
@@ -418,25 +536,34 @@ rowdot_kernel(const RowDotParams p) {
   for (int b = 0; b < B; ++b)
     s0[b] = s1[b] = 0.0f;
 
-  /* One 16-byte word of both rows at byte `off` of the stage, times x. */
-  auto word = [&](const unsigned char *src, const float *xcol, int off) {
+  /* One 16-byte word of both rows at byte `off` of the stage, times x. `col`:
+     the column of the word's first weight; sc0, sc1: the rows' scales. */
+  auto word = [&](const unsigned char *src, const float *xcol, int off, int col,
+                  const char *sc0, const char *sc1) {
     const uint4 wa = *reinterpret_cast<const uint4 *>(src + off);
     const uint4 wb = *reinterpret_cast<const uint4 *>(src + CHUNK_BYTES + off);
-    const float *xw = xcol + off / (int)sizeof(W);
+    float scale_a = 1.0f, scale_b = 1.0f;
+    if (E == 16) {
+      scale_a = __ldg(reinterpret_cast<const float *>(sc0) + col / 128);
+      scale_b = __ldg(reinterpret_cast<const float *>(sc1) + col / 128);
+    } else if (E == 32) {
+      scale_a = __half2float(__ldg(reinterpret_cast<const __half *>(sc0) + col / 32));
+      scale_b = __half2float(__ldg(reinterpret_cast<const __half *>(sc1) + col / 32));
+    }
+    const float *xw = xcol + off / 16 * E;
     float xv[B][E];
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      const float4 lo = *reinterpret_cast<const float4 *>(xw + b * xstr);
-      xv[b][0] = lo.x; xv[b][1] = lo.y; xv[b][2] = lo.z; xv[b][3] = lo.w;
-      if (E == 8) {
-        const float4 hi =
-            *reinterpret_cast<const float4 *>(xw + b * xstr + hi_off);
-        xv[b][E - 4] = hi.x; xv[b][E - 3] = hi.y;
-        xv[b][E - 2] = hi.z; xv[b][E - 1] = hi.w;
+#pragma unroll
+      for (int q = 0; q < (E + 3) / 4; ++q) {
+        const float4 v =
+            *reinterpret_cast<const float4 *>(xw + b * xstr + q * hi_off);
+        xv[b][(4 * q) % E] = v.x; xv[b][(4 * q + 1) % E] = v.y;
+        xv[b][(4 * q + 2) % E] = v.z; xv[b][(4 * q + 3) % E] = v.w;
       }
     }
-    fma16<W, B>(wa, xv, s0);
-    fma16<W, B>(wb, xv, s1);
+    fma16<W, B>(wa, xv, s0, scale_a);
+    fma16<W, B>(wb, xv, s1, scale_b);
   };
 
   int next_item = first, next_ch = 0, next_stage = 0;
@@ -459,13 +586,20 @@ rowdot_kernel(const RowDotParams p) {
     }
     const unsigned char *src = my_ring + s * (2 * CHUNK_BYTES) + lane * 16;
     const float *xcol = xbase + ch * CHUNK_COLS + lane_x;
+    const char *sc0 = nullptr, *sc1 = nullptr;
+    if (Scaled<W>::yes) {
+      const ItemRows here = item_rows<W, EPI>(p, item);
+      sc0 = here.sc0;
+      sc1 = here.r1 ? here.sc1 : here.sc0;
+    }
+    const int col0 = ch * CHUNK_COLS + lane * E;
     if (ch != nch - 1 || last_bytes == CHUNK_BYTES) {
 #pragma unroll
       for (int i = 0; i < CHUNK_BYTES / 512; ++i)
-        word(src, xcol, i * 512);
+        word(src, xcol, i * 512, col0 + i * GROUP, sc0, sc1);
     } else {
       for (int off = 0; off + lane * 16 < last_bytes; off += 512)
-        word(src, xcol, off);
+        word(src, xcol, off, col0 + off / 512 * GROUP, sc0, sc1);
     }
     /* Every lane has read the stage: it may be filled again. */
     __syncwarp();
@@ -474,8 +608,8 @@ rowdot_kernel(const RowDotParams p) {
       continue;
 
     /* ---- the item is complete: reduce, then the epilogue on lane 0 ---- */
-    const ItemRows<W, EPI> it = item_rows<W, EPI>(p, item);
-    const W *r1 = it.r1;
+    const ItemRows it = item_rows<W, EPI>(p, item);
+    const char *r1 = it.r1;
     const int head = it.head, idx = it.idx, kind = it.kind;
     float t0[B], t1[B];
 #pragma unroll
@@ -645,7 +779,9 @@ const char *check_launch(const char *what) {
 
 template <typename W, int B, int EPI>
 const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
-  const size_t xbytes = (size_t)B * ((p.cols + 255) / 256 * 256) * sizeof(float);
+  constexpr int GROUP = 32 * PerWord<W>::n;
+  const size_t xbytes =
+      (size_t)B * ((p.cols + GROUP - 1) / GROUP * GROUP) * sizeof(float);
   p.x_in_smem = xbytes <= (size_t)MAX_SMEM_X;
   if (p.norm_w && !p.x_in_smem)
     return "a fused RMSNorm needs the activations of all sequences to fit in "
@@ -678,16 +814,33 @@ const char *launch_rowdot_w(RowDotParams &p, cudaStream_t stream) {
   }
 }
 
+/* fmt: a kFmt* code of kernels.h. */
 template <int EPI>
-const char *launch_rowdot(RowDotParams &p, bool wbf16, cudaStream_t stream) {
-  if (p.cols % 8 != 0)
-    return "the number of columns must be a multiple of 8";
+const char *launch_rowdot(RowDotParams &p, int fmt, cudaStream_t stream) {
+  const int per_word = fmt == kFmtF32 ? 4 : fmt == kFmtBf16 ? 8 : fmt == kFmtFp8 ? 16 : 32;
+  if (p.cols % 8 != 0 || p.cols % per_word != 0)
+    return "the number of columns must be a multiple of 8 (f32, bf16), of 128 "
+           "(fp8) or of 32 (Q4_0)";
   if (((uintptr_t)p.w0 | (uintptr_t)p.w1 | (uintptr_t)p.w2 | (uintptr_t)p.x) & 15)
     return "weights and activations must be 16-byte aligned";
   if (p.x_stride % 4 != 0 && p.batch > 1)
     return "the stride between sequences must be a multiple of 4 values";
-  return wbf16 ? launch_rowdot_w<__nv_bfloat16, EPI>(p, stream)
-               : launch_rowdot_w<float, EPI>(p, stream);
+  if (fmt == kFmtFp8 || fmt == kFmtQ4) {
+    if (fmt == kFmtFp8 && p.cols % 128 != 0)
+      return "an fp8 matrix has a multiple of 128 columns";
+    if (!p.s0 || (p.w1 && !p.s1) || (p.w2 && !p.s2))
+      return "a quantised matrix needs its scales";
+    if (p.batch != 1)
+      return "the quantised projections take one sequence";
+    if (EPI == EPI_PUSH)
+      return "the quantised projections are not sharded";
+    /* the switch is on a constant: only the instantiations below exist */
+    if (EPI != EPI_PUSH)
+      return fmt == kFmtFp8 ? launch_rowdot_b<Fp8W, 1, EPI == EPI_PUSH ? EPI_STORE : EPI>(p, stream)
+                            : launch_rowdot_b<Q4W, 1, EPI == EPI_PUSH ? EPI_STORE : EPI>(p, stream);
+  }
+  return fmt == kFmtBf16 ? launch_rowdot_w<__nv_bfloat16, EPI>(p, stream)
+                         : launch_rowdot_w<float, EPI>(p, stream);
 }
 
 /* ------------------------------------------------------------- rms_norm
@@ -1160,17 +1313,20 @@ const char *matvec(const MatvecArgs &a, cudaStream_t stream) {
   p.y = a.y;
   p.y_stride = a.y_stride;
   p.bias = a.bias;
+  p.s0 = a.scales;
+  p.row_base = a.row_base;
+  const int fmt = a.wfmt ? a.wfmt : (a.wbf16 ? kFmtBf16 : kFmtF32);
   switch (a.mode) {
-  case 0: return launch_rowdot<EPI_STORE>(p, a.wbf16, stream);
-  case 1: return launch_rowdot<EPI_ADD>(p, a.wbf16, stream);
-  case 2: return launch_rowdot<EPI_BIAS>(p, a.wbf16, stream);
+  case 0: return launch_rowdot<EPI_STORE>(p, fmt, stream);
+  case 1: return launch_rowdot<EPI_ADD>(p, fmt, stream);
+  case 2: return launch_rowdot<EPI_BIAS>(p, fmt, stream);
   case 3:
     if (!a.push || a.push->ranks < 1 || a.push->ranks > kMaxTpRanks)
       return "a pushed projection needs the receive buffers of 1 to 8 ranks";
     if (a.push->count % 2 != 0 || a.y_stride % 2 != 0)
       return "a pushed projection needs an even number of rows";
     p.tp = *a.push;
-    return launch_rowdot<EPI_PUSH>(p, a.wbf16, stream);
+    return launch_rowdot<EPI_PUSH>(p, fmt, stream);
   default: return "unknown matvec mode";
   }
 }
@@ -1211,7 +1367,11 @@ const char *swiglu(const SwigluArgs &a, cudaStream_t stream) {
   p.eps = a.eps;
   p.y = a.out;
   p.y_stride = a.out_stride;
-  return launch_rowdot<EPI_SWIGLU>(p, a.wbf16, stream);
+  p.s0 = a.scales;
+  p.s1 = a.scales_up;
+  p.row_base = a.row_base;
+  return launch_rowdot<EPI_SWIGLU>(p, a.wfmt ? a.wfmt : (a.wbf16 ? kFmtBf16 : kFmtF32),
+                                   stream);
 }
 
 const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream) {
@@ -1246,7 +1406,11 @@ const char *qkv_rope_store(const QkvArgs &a, cudaStream_t stream) {
   p.v_cache = a.v_cache;
   p.cache_batch_stride = a.cache_batch_stride;
   p.max_seq = a.max_seq;
-  return launch_rowdot<EPI_QKV>(p, a.wbf16, stream);
+  p.s0 = a.sq;
+  p.s1 = a.sk;
+  p.s2 = a.sv;
+  return launch_rowdot<EPI_QKV>(p, a.wfmt ? a.wfmt : (a.wbf16 ? kFmtBf16 : kFmtF32),
+                                stream);
 }
 
 int tp_status(cudaStream_t stream) {
@@ -1323,7 +1487,13 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
        positions of a head on 128 warps, one round trip to memory each; with
        every SM already holding several blocks, four. */
     const int64_t blocks = (int64_t)cgrid.x * cgrid.y * cgrid.z;
-    const int warps = blocks <= sm_count() ? 16 : (blocks <= 2 * sm_count() ? 8 : 4);
+    int warps = blocks <= sm_count() ? 16 : (blocks <= 2 * sm_count() ? 8 : 4);
+    /* VXB_ATTN_WARPS=4, 8 or 16 pins it (for measurements) */
+    if (const char *pin = getenv("VXB_ATTN_WARPS")) {
+      const int v = atoi(pin);
+      if (v == 4 || v == 8 || v == 16)
+        warps = v;
+    }
     auto go = [&](auto kernel) {
       launch_chained_cluster(kernel, cgrid, dim3(warps * 32), ATT_CLUSTER, stream, a);
     };

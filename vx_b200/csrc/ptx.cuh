@@ -300,6 +300,108 @@ __device__ inline void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+/* ---- CTA pairs (cta_group::2) ------------------------------------------------
+ * Two CTAs of a cluster of two, on the two SMs of one TPC, act as one 256-row
+ * tensor-core unit: CTA 0 of the pair (the leader) issues the MMAs, which read
+ * the A rows and the B columns that each CTA holds in its OWN shared memory (at
+ * the same offsets) and write each CTA's half of the accumulator into that
+ * CTA's tensor memory. No load here carries a cluster multicast: each CTA
+ * fetches its own halves. */
+__device__ inline uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+/* The shared::cluster address of the same variable in CTA `rank` of the
+   cluster. */
+__device__ inline uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(saddr), "r"(rank));
+  return out;
+}
+/* All threads of all CTAs of the cluster meet. */
+__device__ inline void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\t"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+/* One arrival on an mbarrier that may be in another CTA of the cluster
+   (a shared::cluster address from map_to_cta). */
+__device__ inline void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
+                   cluster_addr)
+               : "memory");
+}
+/* try_wait that also sees what other CTAs of the cluster did before they
+   arrived. */
+__device__ inline bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(done)
+               : "r"(smem_addr(bar)), "r"(parity)
+               : "memory");
+  return done != 0;
+}
+__device__ inline bool mbar_wait_cluster(uint64_t *bar, uint32_t parity,
+                                         volatile int *stop) {
+  if (mbar_try_wait_cluster(bar, parity))
+    return true;
+  const long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_cluster(bar, parity))
+        return true;
+    if (*stop || clock64() - t0 > kWaitCycles)
+      return false;
+  }
+}
+/* A tiled load into THIS CTA's shared memory whose byte count is reported to
+   an mbarrier given as a shared::cluster address: the leader's. */
+__device__ inline void tma_load_2d_pair(void *dst, const CUtensorMap *map, int x,
+                                        int y, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global."
+               "mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                   smem_addr(dst)),
+               "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+               : "memory");
+}
+/* TMEM of both CTAs of the pair: one warp of EACH CTA executes these. */
+__device__ inline void tmem_alloc_pair(uint32_t *slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::
+                   "r"(smem_addr(slot)),
+               "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::
+                   : "memory");
+}
+__device__ inline void tmem_dealloc_pair(uint32_t base, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base),
+               "r"(cols)
+               : "memory");
+}
+/* D[tmem of both CTAs] (+)= A * B with M = 256: issued by one thread of the
+   leader CTA. */
+__device__ inline void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc,
+                                        uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::
+                   "r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+/* One arrival on the mbarrier at this offset in BOTH CTAs of the pair when
+   every MMA this thread issued so far has finished. */
+__device__ inline void umma_commit_pair(uint64_t *bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster."
+               "multicast::cluster.b64 [%0], %1;" ::"r"(smem_addr(bar)),
+               "h"(both)
+               : "memory");
+}
+
 __device__ inline bool elect_one() {
   uint32_t pred;
   asm volatile("{\n\t.reg .pred p;\n\t"

@@ -32,10 +32,14 @@ EXTRA_SYMBOLS = [
     "vx_nn_matvec", "vx_nn_matvec_add", "vx_nn_matvec_heads_add", "vx_nn_qkv",
     "vx_nn_swiglu", "vx_nn_rms_norm", "vx_nn_rope_and_store",
     "vx_nn_attention", "vx_nn_argmax", "vx_nn_embed",
+    "vx_nn_matvec_fp8", "vx_nn_matvec_fp8_add", "vx_nn_matvec_fp8_heads_add",
+    "vx_nn_qkv_fp8", "vx_nn_swiglu_fp8",
+    "vx_nn_matvec_q4", "vx_nn_matvec_q4_add", "vx_nn_matvec_q4_heads_add",
+    "vx_nn_qkv_q4", "vx_nn_swiglu_q4",
     "vx_decoder_create", "vx_decoder_destroy", "vx_decoder_reset",
     "vx_decoder_step", "vx_decoder_prefill", "vx_decoder_logits",
     "vx_decoder_kernels_per_step",
-    "vx_decoder_stream",
+    "vx_decoder_stream", "vx_b200_llama2c_config", "vx_decoder_from_llama2c",
     "vx_b200_last_error", "vx_b200_gemm", "vx_b200_kernel_status",
     "vx_b200_flash_attention", "vx_b200_gemm_column_split",
     "vx_b200_fill_normal", "vx_b200_fill_uniform",
@@ -60,7 +64,15 @@ class DecoderWeights(C.Structure):
                 ("attn_norm", "wq", "wk", "wv", "bqkv", "wo", "ffn_norm",
                  "w_gate", "w_up", "w_down")] + \
                [("final_norm", C.c_void_p), ("lm_head", C.c_void_p),
-                ("cos", C.c_void_p), ("sin", C.c_void_p)]
+                ("cos", C.c_void_p), ("sin", C.c_void_p)] + \
+               [(n, C.POINTER(C.c_void_p)) for n in
+                ("s_qkv", "s_o", "s_gate_up", "s_down")]
+
+
+class Llama2cConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in
+                ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads",
+                 "vocab_size", "seq_len")]
 
 
 def lib():
@@ -140,6 +152,10 @@ def lib():
     L.vx_b200_attention_decode_static.restype = i32
     L.vx_b200_attention_decode_static.argtypes = [vp, vp, vp, vp, i32, i32, i32,
                                                   i32]
+    L.vx_b200_llama2c_config.restype = i32
+    L.vx_b200_llama2c_config.argtypes = [C.c_char_p, vp]
+    L.vx_decoder_from_llama2c.restype = vp
+    L.vx_decoder_from_llama2c.argtypes = [C.c_char_p, i32, i32]
     L.vx_b200_attention_kernel.restype = i32
     L.vx_b200_attention_kernel.argtypes = [i32]
     _lib = L

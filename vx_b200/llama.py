@@ -14,7 +14,7 @@ import ctypes as C
 import numpy as np
 
 from . import abi
-from .lib import DecoderConfig, DecoderWeights, lib
+from .lib import DecoderConfig, DecoderWeights, Llama2cConfig, lib
 
 
 def _ptr_array(ptrs):
@@ -25,6 +25,30 @@ def _ptr_array(ptrs):
 class Decoder:
     """One vx_decoder. `weights` maps field -> list of device pointers (per
     layer) or a single pointer; `keep` holds whatever owns that memory."""
+
+    @classmethod
+    def from_llama2c(cls, path, batch=1, max_seq=0):
+        """A decoder over a llama2.c checkpoint file (the reference's
+        vx_load_config + vx_load_weights, stdlib/rust_core/src/ffi/llama.rs):
+        the library reads the file and owns the weights on the GPU."""
+        L = lib()
+        head = Llama2cConfig()
+        if L.vx_b200_llama2c_config(path.encode(), C.byref(head)) != 0:
+            raise RuntimeError(L.vx_b200_last_error().decode())
+        handle = L.vx_decoder_from_llama2c(path.encode(), batch, max_seq)
+        if not handle:
+            raise RuntimeError(L.vx_b200_last_error().decode())
+        self = cls.__new__(cls)
+        self.cfg = DecoderConfig(
+            dim=head.dim, hidden=head.hidden_dim, n_layers=head.n_layers,
+            q_heads=head.n_heads, kv_heads=head.n_kv_heads,
+            head_dim=head.dim // head.n_heads, vocab=head.vocab_size,
+            max_seq=max_seq or head.seq_len, eps=1e-5, rope_theta=10000.0,
+            weights_bf16=0, batch=batch, tp_ranks=1, tp_reduce=0)
+        self.keep, self._arrays, self._w, self.handle = None, {}, None, handle
+        self._in = (C.c_int32 * 32)()
+        self._out = (C.c_int32 * 32)()
+        return self
 
     def __init__(self, cfg, weights, keep=None):
         self.cfg = cfg
@@ -59,13 +83,13 @@ class Decoder:
         return [self._out[i] for i in range(self.cfg.batch)] if fetch else None
 
     def prefill(self, tokens):
-        """Feed a prompt (one sequence): sixteen positions per pass where the
-        decoder can, single steps for the rest. Returns the argmax after the
-        last prompt token."""
+        """Feed a prompt (one sequence): all positions but the last in one pass
+        where the decoder can (vx_decoder_prefill), single steps otherwise.
+        Returns the argmax after the last prompt token."""
         tokens = [int(t) for t in tokens]
         head = tokens[:-1]
         taken = 0
-        if len(head) >= 16:
+        if head:
             arr = (C.c_int32 * len(head))(*head)
             taken = lib().vx_decoder_prefill(self.handle, arr, len(head))
             if taken < 0:
@@ -95,6 +119,16 @@ class Decoder:
         if self.handle:
             lib().vx_decoder_destroy(self.handle)
             self.handle = None
+
+
+def write_llama2c(path, flat, dim, hidden, n_layers, n_heads, n_kv_heads, vocab,
+                  seq_len):
+    """A llama2.c checkpoint with a shared classifier: the 7 int32 of the header,
+    then the f32 weights in the order of small_f32_weights()."""
+    with open(path, "wb") as f:
+        f.write(np.array([dim, hidden, n_layers, n_heads, n_kv_heads, vocab,
+                          seq_len], np.int32).tobytes())
+        f.write(np.ascontiguousarray(flat, np.float32).tobytes())
 
 
 # ---- the f32 program's model ---------------------------------------------------

@@ -173,3 +173,25 @@ def nn_argmax(out, logits, n):
 
 def nn_embed(x, table, token, dim):
     _call("vx_nn_embed", x, table, token, C.c_int32(dim))
+
+
+# ---- fp8 and Q4_0 weights (quant: "fp8" or "q4") ------------------------------------
+def nn_matvec_quant(quant, y, w, scales, x, rows, cols, add=False):
+    _call("vx_nn_matvec_%s%s" % (quant, "_add" if add else ""), y, w, scales, x,
+          C.c_int32(rows), C.c_int32(cols))
+
+
+def nn_matvec_quant_heads_add(quant, y, w, scales, x, rows, heads, head_dim):
+    _call("vx_nn_matvec_%s_heads_add" % quant, y, w, scales, x, C.c_int32(rows),
+          C.c_int32(heads), C.c_int32(head_dim))
+
+
+def nn_qkv_quant(quant, q, k, v, w, scales, b, x, q_heads, kv_heads, head_dim,
+                 cols):
+    _call("vx_nn_qkv_%s" % quant, q, k, v, w, scales, b, x, C.c_int32(q_heads),
+          C.c_int32(kv_heads), C.c_int32(head_dim), C.c_int32(cols))
+
+
+def nn_swiglu_quant(quant, out, w, scales, x, rows, cols):
+    _call("vx_nn_swiglu_%s" % quant, out, w, scales, x, C.c_int32(rows),
+          C.c_int32(cols))
