@@ -119,6 +119,21 @@ void vx_nn_qkv_q4(VX_TENSOR2(q), VX_TENSOR2(k), VX_TENSOR2(v), VX_TENSOR1(w),
 void vx_nn_swiglu_q4(VX_TENSOR1(out), VX_TENSOR1(w), VX_TENSOR1(scales),
                      VX_TENSOR1(x), int32_t rows, int32_t cols);
 
+/* Kernels for n positions at once (nn.vx:2312-2950): each is the one-position
+   kernel for every row t of its [n, ...] tensors, with bit-identical rows.
+   nn_matvec_rows nn.vx:2802, nn_matvec_q4_rows :2317, nn_rms_norm_rows :2835,
+   nn_argmax_rows :2866, nn_embed_rows :2933. */
+void vx_nn_matvec_rows(VX_TENSOR2(y), VX_TENSOR1(w), VX_TENSOR2(x), int32_t n,
+                       int32_t rows, int32_t cols);
+void vx_nn_matvec_q4_rows(VX_TENSOR2(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                          VX_TENSOR2(x), int32_t n, int32_t rows, int32_t cols);
+void vx_nn_rms_norm_rows(VX_TENSOR2(y), VX_TENSOR2(x), VX_TENSOR1(w), int32_t n,
+                         int32_t dim, float eps);
+void vx_nn_argmax_rows(VX_TENSOR1(out), VX_TENSOR2(logits), int32_t n,
+                       int32_t count);
+void vx_nn_embed_rows(VX_TENSOR2(x), VX_TENSOR1(table), VX_TENSOR1(tokens),
+                      int32_t n, int32_t dim);
+
 /* ---- a whole decoder token -------------------------------------------------- */
 typedef struct {
   int32_t dim, hidden, n_layers, q_heads, kv_heads, head_dim, vocab, max_seq;
@@ -283,6 +298,17 @@ int32_t vx_b200_attention_decode_static(float *out, const float *q,
 int32_t vx_b200_gemm_column_split(int32_t dtype, int64_t m, int64_t n_local,
                                   int64_t k, const void *a, const void *b_local,
                                   void *c_local, void *gathered, void *c_full);
+
+/* A bf16 matrix [rows, cols] in device memory into one of the quantised
+   formats of std::nn, for hosts that make such a model out of bf16 weights
+   (the reference's programs load theirs already quantised). format 2: fp8,
+   `codes` rows * cols bytes, `scales` f32 [ceil(rows/128), cols/128] (the
+   block's largest magnitude / 448), cols a multiple of 128. format 3: Q4_0 as
+   llama.cpp makes it, `codes` rows * cols / 2 bytes, `scales` f16
+   [rows, cols/32], cols a multiple of 32. The numbers are vx_decoder_config's
+   weights_bf16 values. */
+int32_t vx_b200_quantize(int32_t format, const void *w_bf16, int32_t rows,
+                         int32_t cols, void *codes, void *scales);
 
 /* Seeded synthetic data made on the GPU: N(0, sigma^2) or U[lo, hi), written as
    f32 or as bf16 (round to nearest even). */

@@ -6,6 +6,8 @@ larger than the 126 MB L2 where DRAM figures matter).
   python microbench.py gemm    [--n 4096] [--iters 3]
   python microbench.py flash   [--batch 1] [--heads 8] [--seq 4096]
   python microbench.py attn    [--pos 600]
+  python microbench.py shard   [--ranks 8] [--pos 520]
+  python microbench.py prefill [--layers 4]
 Each prints one JSON line with the CUDA-event time per launch.
 """
 import argparse
@@ -44,20 +46,42 @@ def _timed(torch, stream, fn, iters):
 
 def rowdot(torch, args):
     """The gate/up projection + SwiGLU at Llama-2-7B shapes over `layers`
-    different matrices (180 MB each)."""
+    different matrices (180 MB each in bf16; --fmt fp8 or q4: the same matrix
+    quantised, 90 or 51 MB)."""
+    import torch as th
     dim, hid = 4096, 11008
-    ws = [abi.DeviceTensor.empty((2 * hid * dim,), abi.BF16)
-          for _ in range(args.layers)]
-    for i, w in enumerate(ws):
-        ops.fill_normal(w, 100 + i, 0.02)
     x = abi.DeviceTensor.empty((dim,), abi.F32)
     ops.fill_normal(x, 99, 1.0)
     out = abi.DeviceTensor.empty((hid,), abi.F32)
-    ms = _timed(torch, torch.cuda.Stream(),
-                lambda: [ops.nn_swiglu(out, w, x, hid, dim) for w in ws],
-                args.iters) / len(ws)
-    nbytes = 2 * hid * dim * 2 + dim * 4 + hid * 4
-    return dict(kernel="rowdot swiglu 22016x4096 bf16", us=ms * 1e3,
+    if args.fmt == "bf16":
+        ws = [abi.DeviceTensor.empty((2 * hid * dim,), abi.BF16)
+              for _ in range(args.layers)]
+        for i, w in enumerate(ws):
+            ops.fill_normal(w, 100 + i, 0.02)
+        run = lambda: [ops.nn_swiglu(out, w, x, hid, dim) for w in ws]
+        nbytes = 2 * hid * dim * 2 + dim * 4 + hid * 4
+    else:
+        code = 2 if args.fmt == "fp8" else 3
+        per = 2 * hid * dim
+        quantised = []
+        src = abi.DeviceTensor.empty((per,), abi.BF16)
+        for i in range(args.layers):
+            ops.fill_normal(src, 100 + i, 0.02)
+            codes = abi.DeviceTensor.empty((per // 4 if code == 2 else per // 8,),
+                                           abi.I32)
+            scales = (abi.DeviceTensor.empty((2 * hid // 128 * (dim // 128),), abi.F32)
+                      if code == 2 else
+                      abi.DeviceTensor.empty((2 * hid * (dim // 32),), abi.F16))
+            rc = lib().vx_b200_quantize(code, src.ptr, 2 * hid, dim, codes.ptr,
+                                        scales.ptr)
+            assert rc == 0
+            quantised.append((codes, scales))
+        run = lambda: [ops.nn_swiglu_quant(args.fmt, out, c, s, x, hid, dim)
+                       for c, s in quantised]
+        nbytes = (per + per // 16384 * 4 if code == 2 else per // 2 + per // 32 * 2) \
+            + dim * 4 + hid * 4
+    ms = _timed(torch, torch.cuda.Stream(), run, args.iters) / args.layers
+    return dict(kernel="rowdot swiglu 22016x4096 %s" % args.fmt, us=ms * 1e3,
                 bytes=nbytes, gbs=nbytes / ms / 1e6)
 
 
@@ -130,10 +154,59 @@ def decode16(torch, args):
                 us=ms * 1e3, status=ops.kernel_status())
 
 
+def shard(torch, args):
+    """One rank's share of the 7B shape at tensor-parallel degree `--ranks`, run
+    alone on one GPU (no exchange): heads, MLP rows and vocabulary divided by
+    the ranks, the width kept. The decode step at position `--pos`: what a
+    rank's chain of kernels costs apart from the exchange."""
+    from vx_b200 import llama
+    r = args.ranks
+    shape = dict(dim=4096, hidden=11008 // r, n_layers=32, q_heads=32 // r,
+                 kv_heads=32 // r, head_dim=128, vocab=32000 // r)
+    dec, tensors = llama.nn_bf16_model(max_seq=1024, batch=1, **shape)
+    rng = np.random.default_rng(1)
+    for t in rng.integers(0, shape["vocab"], args.pos):
+        dec.step([int(t)], fetch=False)
+    ms = _timed(torch, torch.cuda.ExternalStream(dec.stream),
+                lambda: dec.step(None, fetch=False), max(args.iters, 20))
+    dec.close()
+    nbytes = llama.weight_bytes_per_token(**shape)
+    return dict(kernel="decode step of 1/%d of the 7B shape, position %d" % (r, args.pos),
+                us=ms * 1e3, us_per_layer=ms * 1e3 / 32, tokens_per_s=1e3 / ms,
+                weight_gbs=nbytes / ms / 1e6, status=ops.kernel_status())
+
+
+def prefill(torch, args):
+    """A 512-token prompt through `--layers` layers of the 7B shape in one pass
+    (vx_decoder_prefill): the multi-position GEMMs, their finishing kernels and
+    the f32 attention over the prompt."""
+    import time
+    from vx_b200 import llama
+    shape = dict(llama.LLAMA2_7B)
+    shape["n_layers"] = args.layers
+    dec, tensors = llama.nn_bf16_model(max_seq=1024, batch=1, **shape)
+    prompt = np.random.default_rng(8).integers(0, shape["vocab"], 512)
+    best = None
+    for _ in range(max(2, args.iters)):
+        dec.reset()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        dec.prefill(prompt)
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3
+        best = ms if best is None else min(best, ms)
+    dec.close()
+    return dict(kernel="prefill of 512 tokens, %d layers of the 7B shape" % args.layers,
+                ms=best, ms_per_layer=best / args.layers, status=ops.kernel_status())
+
+
 def main():
     import torch
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["rowdot", "gemm", "flash", "attn", "decode16"])
+    ap.add_argument("case", choices=["rowdot", "gemm", "flash", "attn", "decode16",
+                                     "shard", "prefill"])
+    ap.add_argument("--ranks", type=int, default=8)
+    ap.add_argument("--fmt", default="bf16", choices=["bf16", "fp8", "q4"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--n", type=int, default=4096)
@@ -144,7 +217,8 @@ def main():
     args = ap.parse_args()
     torch.cuda.set_device(0)
     print(json.dumps(dict(rowdot=rowdot, gemm=gemm, flash=flash, attn=attn,
-                          decode16=decode16)[args.case](torch, args)))
+                          decode16=decode16, shard=shard,
+                          prefill=prefill)[args.case](torch, args)))
 
 
 if __name__ == "__main__":

@@ -891,6 +891,65 @@ int32_t oracle_nn_decode_step(const oracle_nn_config *c, const uint16_t *embed,
   return oracle_nn_argmax(logits.data(), c->vocab);
 }
 
+/* The same step with the four projections of every layer in fp8 (quant 2) or
+   Q4_0 (quant 3): nn_qkv_fp8 / nn_matvec_fp8_heads_add / nn_swiglu_fp8 /
+   nn_matvec_fp8_add, or their q4 twins, in place of the bf16 kernels. Norms,
+   bias, embedding and classifier stay bf16. layer[l * 11 + i]: attn_norm,
+   wqkv codes, wqkv scales, bqkv, wo codes, wo scales, ffn_norm, gate/up
+   codes, gate/up scales, down codes, down scales. */
+int32_t oracle_nn_decode_step_quant(const oracle_nn_config *c, int quant,
+                                    const uint16_t *embed,
+                                    const void *const *layer,
+                                    const uint16_t *final_norm,
+                                    const uint16_t *lm_head, const float *cos_t,
+                                    const float *sin_t, float *k_cache,
+                                    float *v_cache, int32_t token, int32_t pos,
+                                    float *logits_out) {
+  const int dim = c->dim, hd = c->head_dim, qh = c->q_heads, kvh = c->kv_heads;
+  const int qkv_rows = (qh + 2 * kvh) * hd;
+  std::vector<float> x(dim), xb(dim), qkv((size_t)qkv_rows), qr((size_t)qh * hd),
+      att((size_t)qh * hd), h((size_t)c->hidden), logits((size_t)c->vocab);
+  oracle_nn_embed(x.data(), embed, token, dim);
+  const int64_t cache_layer = (int64_t)c->max_seq * kvh * hd;
+  auto matvec = [&](float *y, const void *w, const void *s, const float *in,
+                    int rows, int cols, int add) {
+    if (quant == 2)
+      oracle_nn_matvec_fp8(y, (const uint32_t *)w, (const float *)s, in, rows,
+                           cols, add, 0);
+    else
+      oracle_nn_matvec_q4(y, (const uint32_t *)w, (const uint16_t *)s, in, rows,
+                          cols, add);
+  };
+  for (int l = 0; l < c->n_layers; ++l) {
+    const void *const *p = layer + (int64_t)l * 11;
+    float *kc = k_cache + l * cache_layer, *vc = v_cache + l * cache_layer;
+    oracle_nn_rms_norm(xb.data(), x.data(), (const uint16_t *)p[0], dim, c->eps);
+    matvec(qkv.data(), p[1], p[2], xb.data(), qkv_rows, dim, 0);
+    const uint16_t *bias = (const uint16_t *)p[3];
+    for (int r = 0; r < qkv_rows; ++r)
+      qkv[r] = qkv[r] + bf16_to_f32(bias[r]);
+    oracle_nn_rope_and_store(qr.data(), kc, vc, qkv.data(),
+                             qkv.data() + (size_t)qh * hd,
+                             qkv.data() + (size_t)(qh + kvh) * hd, cos_t, sin_t,
+                             hd / 2, pos, qh, kvh, hd);
+    oracle_nn_attention(att.data(), qr.data(), kc, vc, pos, qh, kvh, hd);
+    matvec(x.data(), p[4], p[5], att.data(), dim, qh * hd, 1);
+    oracle_nn_rms_norm(xb.data(), x.data(), (const uint16_t *)p[6], dim, c->eps);
+    if (quant == 2)
+      oracle_nn_swiglu_fp8(h.data(), (const uint32_t *)p[7], (const float *)p[8],
+                           xb.data(), c->hidden, dim);
+    else
+      oracle_nn_swiglu_q4(h.data(), (const uint32_t *)p[7],
+                          (const uint16_t *)p[8], xb.data(), c->hidden, dim);
+    matvec(x.data(), p[9], p[10], h.data(), dim, c->hidden, 1);
+  }
+  oracle_nn_rms_norm(xb.data(), x.data(), final_norm, dim, c->eps);
+  oracle_nn_matvec(logits.data(), lm_head, xb.data(), c->vocab, dim, 0);
+  if (logits_out)
+    memcpy(logits_out, logits.data(), sizeof(float) * (size_t)c->vocab);
+  return oracle_nn_argmax(logits.data(), c->vocab);
+}
+
 /* ---- attention over whole sequences (the flash-attention configuration) -----
  * softmax(q.k * scale) v with a causal mask, f32 from bf16-rounded inputs: the
  * loop of std_nn_kernels_match_loops_on_the_cpu.vx:347-390 for every query

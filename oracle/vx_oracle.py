@@ -87,6 +87,10 @@ def _declare(L):
     L.oracle_nn_swiglu_q4.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int]
     L.oracle_q4_dot_f64.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int]
     L.oracle_random_words.argtypes = [vp, i64, C.c_uint32, C.c_int]
+    L.oracle_nn_decode_step_quant.argtypes = [C.POINTER(NnConfig), C.c_int, vp,
+                                              vp, vp, vp, vp, vp, vp, vp, i32,
+                                              i32, vp]
+    L.oracle_nn_decode_step_quant.restype = i32
 
 
 def _p(a):
@@ -351,6 +355,71 @@ def quant_inputs(quant, rows, cols, seed):
         n = rows * (cols // 32)
         s = (np.float32(0.003) + random_f32(n, seed + 1, 0.001)).astype(np.float16)
     return w, s
+
+
+def quant_model_from_tensors(tensors, cfgd, max_seq, quant):
+    """The oracle's view of a model that vx_b200.llama.nn_quant_model built on
+    the GPU: per layer the 11 arrays oracle_nn_decode_step_quant reads."""
+    import torch
+
+    def host(t, dtype):
+        return np.ascontiguousarray(t.cpu().numpy()).view(dtype).reshape(-1)
+
+    L = cfgd["n_layers"]
+    qkv_rows = (cfgd["q_heads"] + 2 * cfgd["kv_heads"]) * cfgd["head_dim"]
+    scale_t = np.float32 if quant == "fp8" else np.uint16
+    arrays = []
+    for l in range(L):
+        arrays += [host(tensors["attn_norm"][l].view(torch.int16), np.uint16),
+                   host(tensors["wq"][l], np.uint32),
+                   host(tensors["s_qkv"][l].view(torch.int16)
+                        if quant == "q4" else tensors["s_qkv"][l], scale_t),
+                   np.zeros(qkv_rows, np.uint16),
+                   host(tensors["wo"][l], np.uint32),
+                   host(tensors["s_o"][l].view(torch.int16)
+                        if quant == "q4" else tensors["s_o"][l], scale_t),
+                   host(tensors["ffn_norm"][l].view(torch.int16), np.uint16),
+                   host(tensors["w_gate"][l], np.uint32),
+                   host(tensors["s_gate_up"][l].view(torch.int16)
+                        if quant == "q4" else tensors["s_gate_up"][l], scale_t),
+                   host(tensors["w_down"][l], np.uint32),
+                   host(tensors["s_down"][l].view(torch.int16)
+                        if quant == "q4" else tensors["s_down"][l], scale_t)]
+    cfg = NnConfig(cfgd["dim"], cfgd["hidden"], L, cfgd["q_heads"],
+                   cfgd["kv_heads"], cfgd["head_dim"], cfgd["vocab"], max_seq,
+                   1e-5, 10000.0)
+
+    def u16(t):
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+    return dict(cfg=cfg, quant=2 if quant == "fp8" else 3, arrays=arrays,
+                embed=u16(tensors["embed"]), final_norm=u16(tensors["final_norm"]),
+                lm_head=u16(tensors["lm_head"]), cos=tensors["cos"],
+                sin=tensors["sin"])
+
+
+def quant_generate(hm, prompt, steps, max_seq):
+    """nn_generate for a quantised model."""
+    cfg = hm["cfg"]
+    shape = (cfg.n_layers, max_seq, cfg.kv_heads, cfg.head_dim)
+    kc, vc = np.zeros(shape, np.float32), np.zeros(shape, np.float32)
+    ptrs = (C.c_void_p * len(hm["arrays"]))(*[a.ctypes.data for a in hm["arrays"]])
+    out, pos, tok = [], 0, None
+
+    def step(t):
+        return lib().oracle_nn_decode_step_quant(
+            C.byref(cfg), hm["quant"], _p(hm["embed"]), ptrs, _p(hm["final_norm"]),
+            _p(hm["lm_head"]), _p(hm["cos"]), _p(hm["sin"]), _p(kc), _p(vc),
+            int(t), int(pos), None)
+
+    for t in prompt:
+        tok = step(t)
+        pos += 1
+    for _ in range(steps):
+        out.append(tok)
+        tok = step(tok)
+        pos += 1
+    return out
 
 
 # ---- a whole std::nn model on the host ------------------------------------------

@@ -241,3 +241,82 @@ def test_a_llama2c_checkpoint_file_decodes_like_the_oracle(oracle, tmp_path):
         got.append(tok)
     dec.close()
     assert got == want, report(got, want)
+
+
+QUANT_NN = dict(dim=512, hidden=1408, n_layers=3, q_heads=8, kv_heads=4,
+                head_dim=64, vocab=4096)
+
+
+@pytest.mark.parametrize("quant", ["fp8", "q4"])
+def test_quantised_decoder_tokens_match_oracle(oracle, quant):
+    """The decoder with every layer's projections in fp8 or Q4_0 (quantised on
+    the GPU from seeded bf16 weights): a random prompt, then greedy steps; the
+    oracle decodes the same codes and scales with the restatements of the
+    reference's fp8 / q4 kernels."""
+    max_seq, steps = 96, 24
+    dec, tensors = llama.nn_quant_model(quant, max_seq=max_seq, **QUANT_NN)
+    hm = oracle.quant_model_from_tensors(tensors, QUANT_NN, max_seq, quant)
+    prompt = [int(t) for t in
+              np.random.default_rng(12).integers(0, QUANT_NN["vocab"], 40)]
+    tok = None
+    for t in prompt:
+        tok = dec.step([t])[0]
+    got = []
+    for _ in range(steps):
+        got.append(tok)
+        tok = dec.step(None)[0]
+    dec.close()
+    want = oracle.quant_generate(hm, prompt, steps, max_seq)
+    assert got == want, report(got, want)
+
+
+def test_quantisers_follow_their_definitions(oracle):
+    """vx_b200_quantize against numpy: fp8 scale = block amax / 448 and codes
+    that decode (by the definition of f8e4m3) to within half a step of w /
+    scale; Q4_0 as llama.cpp: d = the value of largest magnitude / -8, code =
+    min(15, floor(w / d + 8.5))."""
+    import torch
+    from vx_b200.lib import lib
+    rows, cols = 200, 256
+    w = (torch.randn(rows, cols, generator=torch.Generator().manual_seed(5)) * 0.02) \
+        .to(torch.bfloat16).cuda()
+    wf = w.float().cpu().numpy()
+    codes = torch.empty(rows * cols, dtype=torch.uint8, device="cuda")
+    scales = torch.empty(2 * 2, dtype=torch.float32, device="cuda")
+    assert lib().vx_b200_quantize(2, w.data_ptr(), rows, cols, codes.data_ptr(),
+                                  scales.data_ptr()) == 0
+    torch.cuda.synchronize()
+    s = scales.cpu().numpy().reshape(2, 2)
+    c = codes.cpu().numpy().reshape(rows, cols)
+    for br in range(2):
+        for bc in range(2):
+            blk = wf[br * 128:(br + 1) * 128, bc * 128:(bc + 1) * 128]
+            assert s[br, bc] == np.float32(np.abs(blk).max() / np.float32(448.0))
+    assert not ((c & 127) == 127).any()
+    words = np.ascontiguousarray(c).view(np.uint32).reshape(-1)
+    # decode every weight by the definition and compare with w: within half an
+    # e4m3 step (2^-4 relative) of the scaled value, and exact at the block amax
+    ident = np.eye(cols, dtype=np.float32)
+    back = np.stack([oracle.quant_dot_f64("fp8", words, s.reshape(-1), ident[j],
+                                          rows, cols) for j in range(0, cols, 37)], 1)
+    ref = wf[:, 0:cols:37]
+    assert np.abs(back - ref).max() <= np.abs(wf).max() / 448 * 16 + 1e-12
+    assert np.abs(back - ref).max() <= 0.07 * np.abs(ref).max()
+
+    codes4 = torch.empty(rows * cols // 2, dtype=torch.uint8, device="cuda")
+    scales4 = torch.empty(rows * cols // 32, dtype=torch.float16, device="cuda")
+    assert lib().vx_b200_quantize(3, w.data_ptr(), rows, cols, codes4.data_ptr(),
+                                  scales4.data_ptr()) == 0
+    torch.cuda.synchronize()
+    g = wf.reshape(-1, 32)
+    at = np.abs(g).argmax(1)
+    d = g[np.arange(g.shape[0]), at] / np.float32(-8.0)
+    assert np.array_equal(scales4.cpu().numpy(), d.astype(np.float16))
+    want = np.minimum(15, np.floor(g * (np.float32(1.0) / d)[:, None]
+                                   + np.float32(8.5))).astype(np.int64)
+    want = np.maximum(want, 0)
+    nib = codes4.cpu().numpy().reshape(-1, 16)
+    got = np.empty((g.shape[0], 32), np.int64)
+    got[:, 0::2] = nib & 15
+    got[:, 1::2] = nib >> 4
+    assert np.array_equal(got, want)

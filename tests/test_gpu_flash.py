@@ -18,7 +18,7 @@ def make_qkv(oracle, B, H, S, D):
 
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("B,H,S", [(1, 2, 128), (1, 3, 256), (2, 2, 384),
-                                   (1, 2, 1024)])
+                                   (1, 2, 1024), (1, 2, 4096)])
 def test_flash_matches_oracle(oracle, B, H, S, causal):
     D = 128
     q, k, v = make_qkv(oracle, B, H, S, D)
@@ -28,7 +28,10 @@ def test_flash_matches_oracle(oracle, B, H, S, causal):
     ops.flash_attention(tq, tk, tv, to, scale, causal)
     assert ops.kernel_status() == 0
     got = oracle.bf16_to_f32(to.to_host())
-    rows = np.unique(np.concatenate([np.arange(0, S, 37), [0, 63, 64, 127, S - 1]]))
+    # every 37th row, every 331st at the benchmark's sequence length (a row of
+    # the oracle costs S * D products), and the rows at tile edges
+    rows = np.unique(np.concatenate([np.arange(0, S, 37 if S <= 1024 else 331),
+                                     [0, 63, 64, 127, S - 1]]))
     for b in range(B):
         for h in range(H):
             want = oracle.attention_rows(q[b, h], k[b, h], v[b, h], scale,

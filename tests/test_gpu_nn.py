@@ -192,3 +192,56 @@ def test_embed(oracle):
     x = abi.DeviceTensor.empty((dim,), abi.F32)
     ops.nn_embed(x, dev(table, True), dev(np.array([token], np.int32)), dim)
     assert np.array_equal(x.to_host(), oracle.nn_embed(table, token, dim))
+
+
+# ---- kernels for n positions at once: every row bit for bit the one-position
+# ---- kernel's (the method and sizes of the reference's
+# ---- apple_gpu_kernels_for_n_positions_match_one_position.vx: 5 positions)
+def test_rows_kernels_match_one_position_bit_for_bit(oracle):
+    n = 5
+    # bf16 product: 16 rows of 1024
+    rows, cols = 16, 1024
+    w = rand_bf16(oracle, rows * cols, 91, 0.1)
+    x = oracle.random_f32(n * cols, 92, 1.0).reshape(n, cols)
+    tw = dev(w, True)
+    ty = abi.DeviceTensor.empty((n, rows), abi.F32)
+    ops.nn_matvec_rows(ty, tw, dev(x), n, rows, cols)
+    got = ty.to_host()
+    for t in range(n):
+        one = abi.DeviceTensor.empty((rows,), abi.F32)
+        ops.nn_matvec(one, tw, dev(x[t]), rows, cols)
+        assert np.array_equal(got[t], one.to_host()), t
+    # Q4_0 product: 64 rows of 512
+    rows, cols = 64, 512
+    wq, sq = oracle.quant_inputs("q4", rows, cols, 93)
+    xq = oracle.random_f32(n * cols, 94, 1.0).reshape(n, cols)
+    twq, tsq = dev(wq), dev(sq)
+    tyq = abi.DeviceTensor.empty((n, rows), abi.F32)
+    ops.nn_matvec_q4_rows(tyq, twq, tsq, dev(xq), n, rows, cols)
+    gotq = tyq.to_host()
+    for t in range(n):
+        one = abi.DeviceTensor.empty((rows,), abi.F32)
+        ops.nn_matvec_quant("q4", one, twq, tsq, dev(xq[t]), rows, cols)
+        assert np.array_equal(gotq[t], one.to_host()), t
+    # rms norm: 256 values a row
+    dim = 256
+    xn = oracle.random_f32(n * dim, 95, 3.0).reshape(n, dim)
+    wn = rand_bf16(oracle, dim, 96, 1.0)
+    tn = abi.DeviceTensor.empty((n, dim), abi.F32)
+    ops.nn_rms_norm_rows(tn, dev(xn), dev(wn, True), n, dim, 1e-6)
+    gotn = tn.to_host()
+    for t in range(n):
+        one = abi.DeviceTensor.empty((dim,), abi.F32)
+        ops.nn_rms_norm(one, dev(xn[t]), dev(wn, True), dim, 1e-6)
+        assert np.array_equal(gotn[t], one.to_host()), t
+    # embed and argmax
+    table = rand_bf16(oracle, 10 * dim, 97, 1.0)
+    tokens = np.array([7, 0, 9, 3, 3], np.int32)
+    te = abi.DeviceTensor.empty((n, dim), abi.F32)
+    ops.nn_embed_rows(te, dev(table, True), dev(tokens), n, dim)
+    assert np.array_equal(te.to_host(), oracle.bf16_to_f32(table).reshape(10, dim)[tokens])
+    logits = oracle.random_f32(n * 3000, 98, 1.0).reshape(n, 3000)
+    logits[2, 17] = logits[2, 2900] = 5.0                # a tie: the lower index
+    ta = abi.DeviceTensor.empty((n,), abi.I32)
+    ops.nn_argmax_rows(ta, dev(logits), n, 3000)
+    assert list(ta.to_host()) == [int(np.argmax(r)) for r in logits]

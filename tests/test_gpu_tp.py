@@ -56,3 +56,42 @@ def test_column_split_gemm_with_all_gather(tmp_path):
            os.path.join(ROOT, "tests", "gemm_tp_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-3000:]
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_one_process_uses_two_gpus_in_turn():
+    """`spawn on(Topology::GPU[i])` switches GPUs inside one process: kernels
+    that opt in to more than 48 KiB of shared memory (the projections' weight
+    ring, the tensor-core GEMMs) must get that opt-in on every GPU they run
+    on, not only on the first."""
+    code = r"""
+import sys
+import numpy as np
+import torch
+sys.path.insert(0, %r)
+from oracle import vx_oracle as oracle
+from vx_b200 import abi, ops
+rng = np.random.default_rng(0)
+a16 = oracle.f32_to_bf16(rng.uniform(-1, 1, (512, 256)).astype(np.float32))
+b16 = oracle.f32_to_bf16(rng.uniform(-1, 1, (256, 512)).astype(np.float32))
+w = oracle.f32_to_bf16(oracle.random_f32(2 * 200 * 896, 41, 0.1))
+x = oracle.random_f32(896, 42, 1.0)
+want_c = oracle.bf16_to_f32(oracle.gemm_bf16_rows(a16, b16, np.arange(512)))
+want_s = oracle.nn_swiglu(w, x, 200, 896)
+for g in (0, 1, 0):
+    torch.cuda.set_device(g)
+    abi.set_home_gpu(g)
+    ta = abi.DeviceTensor.from_host(a16, bf16=True)
+    tb = abi.DeviceTensor.from_host(b16, bf16=True)
+    got = oracle.bf16_to_f32(ops.matmul(ta, tb).to_host())
+    assert np.linalg.norm(got - want_c) <= 4e-3 * np.linalg.norm(want_c), g
+    out = abi.DeviceTensor.empty((200,), abi.F32)
+    ops.nn_swiglu(out, abi.DeviceTensor.from_host(w, bf16=True),
+                  abi.DeviceTensor.from_host(x), 200, 896)
+    assert np.abs(out.to_host() - want_s).max() <= 2e-5 * np.abs(want_s).max(), g
+    assert ops.kernel_status() == 0
+print("both GPUs ok")
+""" % ROOT
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0 and "both GPUs ok" in r.stdout, r.stderr[-3000:]

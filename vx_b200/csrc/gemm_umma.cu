@@ -415,20 +415,23 @@ const char *gemm_16(bool is_bf16, const void *a, int64_t lda, const void *b,
   const bool small = m * n < 128 * 256 || k < 64;
   if (small || !umma_shape_ok(a, lda, b, ldb, c, ldc, m, n, k) || !encoder())
     return gemm_16_plain(is_bf16, a, lda, b, ldb, c, ldc, m, n, k, stream);
-  /* One CTA per 128x256 tile, or a CTA pair per 256x256 tile: the pair's MMA
-     runs near the tensor pipe's full rate where the single CTA's is limited
-     to 77 % by its operand fetch, but its tile is twice as large, so it pays
-     only from about a wave of tiles on. Cost in units of a one-CTA tile. */
+  /* One CTA per 128x256 tile, or a CTA pair per 256x256 tile. The single CTA's
+     MMA is held to 77 % of the tensor pipe by its operand fetch and the pair's
+     runs near the full rate, so a pair finishes its tile (twice the work on
+     two SMs) in about 0.82 of the time one CTA needs for its own; but there
+     are half as many pair tiles, so for a small product the last wave decides,
+     and below two waves of pair tiles the cluster's start-up shows (2048^3:
+     823 against 912 TFLOP/s). Cost in units of a one-CTA tile time. */
   const int64_t t1 = ((m + 127) / 128) * ((n + 255) / 256);
   const int64_t t2 = ((m + 255) / 256) * ((n + 255) / 256);
   const int sms = sm_count();
   const double cost1 = (double)((t1 + sms - 1) / sms);
-  const double cost2 = (double)((t2 + sms / 2 - 1) / (sms / 2)) * 1.64;
+  const double cost2 = (double)((t2 + sms / 2 - 1) / (sms / 2)) * 0.82;
   /* VXB_GEMM_ROUTE=1 or 4 pins the choice (for measurements). */
   const char *force = getenv("VXB_GEMM_ROUTE");
   const int route = force && (force[0] == '1' || force[0] == '4')
                         ? force[0] - '0'
-                        : (cost2 < cost1 ? 4 : 1);
+                        : (cost2 < cost1 && t2 >= sms ? 4 : 1);
   return gemm_16_route(route, is_bf16, a, lda, b, ldb, c, ldc, m, n, k, nullptr,
                        stream);
 }

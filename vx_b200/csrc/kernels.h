@@ -303,6 +303,13 @@ const char *fill_normal(void *out, bool as_bf16, int64_t n, uint64_t seed,
                         float sigma, cudaStream_t stream);
 const char *fill_uniform(void *out, bool as_bf16, int64_t n, uint64_t seed,
                          float lo, float hi, cudaStream_t stream);
+/* A bf16 matrix [rows, cols] into fp8 codes (one byte each) with f32 scales
+   [ceil(rows/128), cols/128], or into Q4_0 codes (two a byte) with f16 scales
+   [rows, cols/32]: quantize.cu. */
+const char *quantize_fp8(const void *w_bf16, int rows, int cols, void *codes,
+                         float *scales, cudaStream_t stream);
+const char *quantize_q4(const void *w_bf16, int rows, int cols, void *codes,
+                        void *scales_f16, cudaStream_t stream);
 const char *interleave_gathered(const void *gathered, void *out, int ranks,
                                 int64_t m, int64_t n_local, int elem_bytes,
                                 cudaStream_t stream);

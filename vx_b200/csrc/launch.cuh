@@ -86,13 +86,26 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block,
    (grid.x a multiple of it): the blocks of a cluster run together and can read
    one another's shared memory. */
 template <typename... KArgs, typename... Args>
+cudaError_t launch_chained_cluster_smem(void (*kernel)(KArgs...), dim3 grid,
+                                        dim3 block, unsigned cluster_x, size_t smem,
+                                        cudaStream_t stream, Args &&...args);
+
+template <typename... KArgs, typename... Args>
 cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block,
                                    unsigned cluster_x, cudaStream_t stream,
                                    Args &&...args) {
+  return launch_chained_cluster_smem(kernel, grid, block, cluster_x, 0, stream,
+                                     std::forward<Args>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained_cluster_smem(void (*kernel)(KArgs...), dim3 grid,
+                                        dim3 block, unsigned cluster_x, size_t smem,
+                                        cudaStream_t stream, Args &&...args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;

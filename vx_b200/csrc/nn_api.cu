@@ -549,6 +549,121 @@ QUANT_EXPORTS(q4, vxb::kFmtQ4, uint16_t, "q4")
 }
 #undef QUANT_EXPORTS
 
+
+/* ---------------------------------------------- kernels for n positions
+ * (nn.vx:2312-2950: "the kernel of the same name without _rows ... for each
+ * position ... row t of the output is bit-identical to the one-position kernel
+ * on x[t]"). The projections take the positions 16, 8, 4, 2 or 1 at a time
+ * through the one-position kernel's own code (every sequence of a launch is
+ * summed in the order a single one is), so that property holds here too. */
+namespace {
+template <typename F> void in_chunks(int n, F &&run) {
+  int t = 0;
+  for (int chunk = 16; chunk >= 1; chunk /= 2)
+    while (n - t >= chunk) {
+      run(t, chunk);
+      t += chunk;
+    }
+}
+void check_rows(const char *fn, int n, int64_t x_rows, int64_t y_rows) {
+  if (n <= 0 || x_rows < n || y_rows < n)
+    stop("%s: the input and the output need n rows", fn);
+}
+} // namespace
+
+extern "C" {
+
+#define FN "nn_matvec_rows"
+void vx_nn_matvec_rows(VX_TENSOR2(y), VX_TENSOR1(w), VX_TENSOR2(x), int32_t n,
+                       int32_t rows, int32_t cols) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(x);
+  check_matrix(FN, y_n1, w_n0, x_n1, rows, cols);
+  check_rows(FN, n, x_n0, y_n0);
+  float *yp = T2(float, y);
+  const float *xp = T2(float, x);
+  const uint16_t *wp = T1(uint16_t, w);
+  in_chunks(n, [&](int t, int chunk) {
+    vxb::MatvecArgs a{};
+    a.w = wp;
+    a.wbf16 = true;
+    a.rows = rows;
+    a.cols = cols;
+    a.x = xp + (int64_t)t * x_n1;
+    a.x_stride = x_n1;
+    a.y = yp + (int64_t)t * y_n1;
+    a.y_stride = y_n1;
+    a.batch = chunk;
+    a.mode = 0;
+    must(vxb::matvec(a, vxb::caller_stream()), FN);
+  });
+}
+#undef FN
+
+#define FN "nn_matvec_q4_rows"
+void vx_nn_matvec_q4_rows(VX_TENSOR2(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                          VX_TENSOR2(x), int32_t n, int32_t rows, int32_t cols) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(x);
+  check_rows(FN, n, x_n0, y_n0);
+  float *yp = T2(float, y);
+  const float *xp = T2(float, x);
+  for (int t = 0; t < n; ++t)
+    quant_matvec(FN, vxb::kFmtQ4, yp + (int64_t)t * y_n1, y_n1, T1(uint32_t, w),
+                 w_n0, T1(uint16_t, scales), scales_n0, xp + (int64_t)t * x_n1,
+                 x_n1, rows, cols, 0);
+}
+#undef FN
+
+#define FN "nn_rms_norm_rows"
+void vx_nn_rms_norm_rows(VX_TENSOR2(y), VX_TENSOR2(x), VX_TENSOR1(w), int32_t n,
+                         int32_t dim, float eps) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(x); UNUSED_ALLOC(w);
+  if (dim <= 0 || y_n1 < dim || x_n1 < dim || w_n0 < dim)
+    stop("nn_rms_norm_rows: a row has fewer than dim values");
+  check_rows(FN, n, x_n0, y_n0);
+  float *yp = T2(float, y);
+  const float *xp = T2(float, x);
+  if (y_n1 == x_n1) {
+    must(vxb::rms_norm(yp, xp, T1(uint16_t, w), true, dim, eps, n, x_n1,
+                       vxb::caller_stream()),
+         FN);
+    return;
+  }
+  for (int t = 0; t < n; ++t)
+    must(vxb::rms_norm(yp + (int64_t)t * y_n1, xp + (int64_t)t * x_n1,
+                       T1(uint16_t, w), true, dim, eps, 1, dim,
+                       vxb::caller_stream()),
+         FN);
+}
+#undef FN
+
+#define FN "nn_argmax_rows"
+void vx_nn_argmax_rows(VX_TENSOR1(out), VX_TENSOR2(logits), int32_t n,
+                       int32_t count) {
+  UNUSED_ALLOC(out); UNUSED_ALLOC(logits);
+  if (count <= 0 || logits_n1 < count)
+    stop("nn_argmax_rows: a row of `logits` has fewer than count values");
+  if (n <= 0 || logits_n0 < n || out_n0 < n)
+    stop("nn_argmax_rows: `logits` needs n rows, and `out` n values");
+  must(vxb::argmax(T1(int32_t, out), T2(float, logits), count, n, logits_n1,
+                   vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+#define FN "nn_embed_rows"
+void vx_nn_embed_rows(VX_TENSOR2(x), VX_TENSOR1(table), VX_TENSOR1(tokens),
+                      int32_t n, int32_t dim) {
+  UNUSED_ALLOC(x); UNUSED_ALLOC(table); UNUSED_ALLOC(tokens);
+  if (dim <= 0 || x_n1 < dim || n <= 0 || x_n0 < n || tokens_n0 < n)
+    stop("nn_embed_rows: `x` needs n rows of dim values, and `tokens` n values");
+  must(vxb::embed(T2(float, x), T1(uint16_t, table), true, T1(int32_t, tokens),
+                  dim, (int)(table_n0 / dim), n, x_n1, vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+} /* extern "C" */
+
 extern "C" {
 
 /* --------------------------------------------------------------- direct calls */
@@ -619,6 +734,19 @@ int32_t vx_b200_gemm_column_split(int32_t dtype, int64_t m, int64_t n_local,
     return fail(why.c_str());
   return done(vxb::interleave_gathered(gathered, c_full, ranks, m, n_local, 2, s),
               "a column-split GEMM");
+}
+
+int32_t vx_b200_quantize(int32_t format, const void *w_bf16, int32_t rows,
+                         int32_t cols, void *codes, void *scales) {
+  if (format == 2)
+    return done(vxb::quantize_fp8(w_bf16, rows, cols, codes, (float *)scales,
+                                  vxb::caller_stream()),
+                "a quantisation");
+  if (format == 3)
+    return done(vxb::quantize_q4(w_bf16, rows, cols, codes, scales,
+                                 vxb::caller_stream()),
+                "a quantisation");
+  return fail("vx_b200_quantize takes format 2 (fp8) or 3 (Q4_0)");
 }
 
 int32_t vx_b200_fill_normal(void *out, int32_t as_bf16, int64_t n, uint64_t seed,

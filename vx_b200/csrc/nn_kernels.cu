@@ -24,7 +24,6 @@
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-#include <cuda_fp8.h>
 
 #include <algorithm>
 #include <cstdio>
@@ -129,19 +128,27 @@ template <typename W> struct Scaled { static constexpr bool yes = false; };
 template <> struct Scaled<Fp8W> { static constexpr bool yes = true; };
 template <> struct Scaled<Q4W> { static constexpr bool yes = true; };
 
-/* The 16 weights of an fp8 word, and the 32 of a Q4_0 word less 8 each, as
-   f32 (both exact). */
+/* The 16 weights of an fp8 word as f32 times 2^-120, exactly, two codes at a
+   time with integer instructions (the conversion instructions issue at a
+   quarter of the rate and made the kernel wait for them). The low 7 bits of a
+   code, e e e e m m m, moved to bits 10..4 of a 16-bit half are the bf16 bit
+   pattern of the code's value times 2^-120: e4m3's exponent has bias 7, bf16's
+   127, and a code with e = 0 becomes a bf16 subnormal of the right value. The
+   sign goes on top, and a half widens to f32 by sitting in the upper 16 bits.
+   The factor 2^120 is taken back with the block's scale (fma16): the sums
+   stay far inside f32's range, subnormal products are exact to 2^-149. */
+constexpr float kFp8Unscale = 1.329227995784916e36f; /* 2^120 */
 __device__ __forceinline__ void unpack_fp8(const uint4 &wv, float (&wf)[16]) {
   const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      const __half2_raw two = __nv_cvt_fp8x2_to_halfraw2(
-          (__nv_fp8x2_storage_t)(u[j] >> (16 * h)), __NV_E4M3);
-      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&two));
-      wf[4 * j + 2 * h] = f.x;
-      wf[4 * j + 2 * h + 1] = f.y;
+      /* codes 2h and 2h+1 into the high bytes of the two halves */
+      const uint32_t x = __byte_perm(u[j], 0, h == 0 ? 0x1404 : 0x3424);
+      const uint32_t y = ((x >> 4) & 0x07F007F0u) | (x & 0x80008000u);
+      wf[4 * j + 2 * h] = __uint_as_float(y << 16);
+      wf[4 * j + 2 * h + 1] = __uint_as_float(y & 0xFFFF0000u);
     }
   }
 }
@@ -201,13 +208,14 @@ fma16(const uint4 &wv, const float (&xv)[B][PerWord<W>::n], float (&acc)[B],
       acc[b] = fmaf(dot, scale, acc[b]);
     }
   } else if constexpr (Scaled<W>::yes) {
+    const float unscale = scale * kFp8Unscale; /* exact: a power of two */
 #pragma unroll
     for (int b = 0; b < B; ++b) {
       float dot = 0.0f;
 #pragma unroll
       for (int e = 0; e < E; ++e)
         dot = fmaf(wf[e], xv[b][e], dot);
-      acc[b] = fmaf(dot, scale, acc[b]);
+      acc[b] = fmaf(dot, unscale, acc[b]);
     }
   } else {
 #pragma unroll
@@ -792,9 +800,17 @@ const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
     return "a projection could not get its shared memory on this GPU";
   /* One block of 16 warps per SM with a 128 KiB ring (measured faster than
      two blocks of 8 warps with 64 KiB each: 31.7 vs 34.3 us on the 7B gate/up
-     projection). Fewer blocks when there are fewer items than warps. */
+     projection). With fewer items than warps (a rank's slice of a
+     tensor-parallel model) the items are spread over all SMs, some warps of
+     each block idle, rather than packed sixteen to a block on a few SMs: a
+     short projection is a matter of latency, and every SM's path to memory
+     helps. VXB_ROWDOT_PACK=1 packs (for measurements). */
+  static const bool pack = [] {
+    const char *e = getenv("VXB_ROWDOT_PACK");
+    return e && e[0] == '1';
+  }();
   int blocks = sm_count();
-  const int wanted = (p.items + WARPS - 1) / WARPS;
+  const int wanted = pack ? (p.items + WARPS - 1) / WARPS : p.items;
   if (blocks > wanted)
     blocks = wanted < 1 ? 1 : wanted;
   launch_chained(rowdot_kernel<W, B, EPI>, dim3(blocks), dim3(WARPS * 32), smem,

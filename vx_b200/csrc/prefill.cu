@@ -114,6 +114,10 @@ rows_gemm_kernel(const __grid_constant__ CUtensorMap map_x,
   ptx::tc_fence_before_sync();
   ptx::cluster_sync_all();
   ptx::tc_fence_after_sync();
+  /* Set up under the tail of the kernel before; its output (the terms) is read,
+     and the partial sums it may still read are overwritten, only from here. */
+  chain_release();
+  chain_wait();
   const uint32_t tmem = bars->tmem_base;
   volatile int *stop = &bars->stop;
   /* the K' blocks of run r: a balanced cut of 0 .. k_blocks */
@@ -284,6 +288,8 @@ __global__ void __launch_bounds__(256)
 norm_terms_kernel(__nv_bfloat16 *terms, const float *x, const void *w, int dim,
                   float eps) {
   __shared__ float red[8];
+  chain_release();
+  chain_wait();
   const int64_t t = blockIdx.x;
   const float *xr = x + t * dim;
   float ss = 0.0f;
@@ -310,6 +316,8 @@ qkv_finish_kernel(const float *partials, int splits, int t_count, int q_heads,
                   int kv_heads, int hd, const void *bias, const float *cos_t,
                   const float *sin_t, const int32_t *first_pos, float *q_out,
                   float *k_cache, float *v_cache) {
+  chain_release();
+  chain_wait();
   const int half = hd / 2, heads = q_heads + 2 * kv_heads;
   const int64_t n = (int64_t)heads * hd;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -346,6 +354,8 @@ qkv_finish_kernel(const float *partials, int splits, int t_count, int q_heads,
 __global__ void __launch_bounds__(256)
 residual_finish_kernel(float *x, const float *partials, int splits, int t_count,
                        int n) {
+  chain_release();
+  chain_wait();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)t_count * n)
     return;
@@ -358,6 +368,8 @@ residual_finish_kernel(float *x, const float *partials, int splits, int t_count,
 __global__ void __launch_bounds__(256)
 swiglu_finish_kernel(__nv_bfloat16 *terms, const float *partials, int splits,
                      int t_count, int hidden) {
+  chain_release();
+  chain_wait();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)t_count * hidden)
     return;
@@ -370,16 +382,18 @@ swiglu_finish_kernel(__nv_bfloat16 *terms, const float *partials, int splits,
 
 /* ---- attention over the prompt, f32 on the FMA pipe -------------------------
  * One block per (64 positions, query head): scores of the 64 queries against
- * 64 cache rows at a time, an online softmax (running maximum and sum per
+ * 32 cache rows at a time, an online softmax (running maximum and sum per
  * query), and the weighted sum of V; rows 0 .. first_pos + t of the cache for
  * the query at prompt position t (nn_attention, nn.vx:349-866, for every
  * position). head_dim 128. The output goes out as the three bf16 terms of the
  * output projection's input. */
-constexpr int AQ = 64, AK = 64, AD = 128;
+constexpr int AQ = 64, AK = 32, AD = 128;
 constexpr int ATT_THREADS = 256;
+/* 76 KiB: two blocks share an SM, so one block's loads and barriers run under
+   the other's arithmetic */
 constexpr int ATT_SMEM = (AQ * (AD + 4) + 2 * AK * (AD + 4) + AQ * (AK + 4)) * 4;
 
-__global__ void __launch_bounds__(ATT_THREADS)
+__global__ void __launch_bounds__(ATT_THREADS, 2)
 rows_attention_kernel(__nv_bfloat16 *terms, const float *q, const float *k_cache,
                       const float *v_cache, const int32_t *first_pos, int t_count,
                       int q_heads, int kv_heads) {
@@ -391,6 +405,8 @@ rows_attention_kernel(__nv_bfloat16 *terms, const float *q, const float *k_cache
   float (*sp)[AK + 4] =
       reinterpret_cast<float (*)[AK + 4]>(att_smem + (AQ + 2 * AK) * (AD + 4));
 
+  chain_release();
+  chain_wait();
   const int head = blockIdx.y, g = head / (q_heads / kv_heads);
   const int t0 = blockIdx.x * AQ;
   const int base = first_pos[0];
@@ -406,8 +422,9 @@ rows_attention_kernel(__nv_bfloat16 *terms, const float *q, const float *k_cache
           q + ((int64_t)(t0 + r) * q_heads + head) * AD + c4 * 4);
     *reinterpret_cast<float4 *>(&sq[r][c4 * 4]) = v;
   }
-  /* scores: thread (ty, tx) of 16 x 16 owns queries ty*4.. and keys tx*4..;
-     output: queries ty*4.., values tx*8.. */
+  /* scores: thread (ty, tx) of 16 x 16 owns queries ty*4.. and keys tx and
+     tx + 16; output: queries ty*4.., values tx*8.. */
+  constexpr int KB = AK / 16; /* keys per thread */
   const int ty = tid / 16, tx = tid % 16;
   float m[4], l[4], o[4][8];
 #pragma unroll
@@ -433,24 +450,24 @@ rows_attention_kernel(__nv_bfloat16 *terms, const float *q, const float *k_cache
       *reinterpret_cast<float4 *>(&sv[r][c4 * 4]) = vv;
     }
     __syncthreads();
-    float s[4][4];
+    float s[4][KB];
 #pragma unroll
     for (int a = 0; a < 4; ++a)
 #pragma unroll
-      for (int b = 0; b < 4; ++b)
+      for (int b = 0; b < KB; ++b)
         s[a][b] = 0.0f;
     for (int d = 0; d < AD; d += 4) {
-      float4 qa[4], kb[4];
+      float4 qa[4], kb[KB];
 #pragma unroll
       for (int a = 0; a < 4; ++a)
         qa[a] = *reinterpret_cast<const float4 *>(&sq[ty * 4 + a][d]);
 #pragma unroll
-      for (int b = 0; b < 4; ++b)
+      for (int b = 0; b < KB; ++b)
         kb[b] = *reinterpret_cast<const float4 *>(&sk[tx + 16 * b][d]);
 #pragma unroll
       for (int a = 0; a < 4; ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
+        for (int b = 0; b < KB; ++b) {
           s[a][b] = fmaf(qa[a].x, kb[b].x, s[a][b]);
           s[a][b] = fmaf(qa[a].y, kb[b].y, s[a][b]);
           s[a][b] = fmaf(qa[a].z, kb[b].z, s[a][b]);
@@ -464,7 +481,7 @@ rows_attention_kernel(__nv_bfloat16 *terms, const float *q, const float *k_cache
       const int qpos = base + t0 + ty * 4 + a;
       float big = -3.0e38f;
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
+      for (int b = 0; b < KB; ++b) {
         const int key = k0 + tx + 16 * b;
         s[a][b] = key <= qpos ? s[a][b] * scale : -3.0e38f;
         big = fmaxf(big, s[a][b]);
@@ -476,7 +493,7 @@ rows_attention_kernel(__nv_bfloat16 *terms, const float *q, const float *k_cache
       const float fix = expf(m[a] - mn);
       float sum = 0.0f;
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
+      for (int b = 0; b < KB; ++b) {
         const int key = k0 + tx + 16 * b;
         const float pw = key <= qpos ? expf(s[a][b] - mn) : 0.0f;
         sp[ty * 4 + a][tx + 16 * b] = pw;
@@ -604,25 +621,16 @@ const char *rows_gemm(const void *terms, const void *w, int t, int n, int cols,
   const int items = ((t + BM - 1) / BM) * ((n + BN - 1) / BN) * g.splits;
   if (pairs > items)
     pairs = items;
-  cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(THREADS);
-  cfg.gridDim = dim3(2 * pairs);
-  cfg.dynamicSmemBytes = SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, rows_gemm_kernel, mx, mw, g);
+  const cudaError_t e =
+      launch_chained_cluster_smem(rows_gemm_kernel, dim3(2 * pairs), dim3(THREADS), 2,
+                                  SMEM_BYTES, stream, mx, mw, g);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
 }
 
 const char *rows_norm_terms(void *terms, const float *x, const void *w, int t,
                             int dim, float eps, cudaStream_t stream) {
-  norm_terms_kernel<<<t, 256, 0, stream>>>((__nv_bfloat16 *)terms, x, w, dim, eps);
+  launch_chained(norm_terms_kernel, dim3(t), dim3(256), 0, stream,
+                 (__nv_bfloat16 *)terms, x, w, dim, eps);
   return last_launch("the multi-position RMSNorm");
 }
 
@@ -632,25 +640,26 @@ const char *rows_qkv_finish(const float *partials, int splits, int t, int q_head
                             const int32_t *first_pos, float *q_out, float *k_cache,
                             float *v_cache, cudaStream_t stream) {
   const int64_t n = (int64_t)t * (q_heads + 2 * kv_heads) * (hd / 2);
-  qkv_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
-      partials, splits, t, q_heads, kv_heads, hd, bias, cos_t, sin_t, first_pos,
-      q_out, k_cache, v_cache);
+  launch_chained(qkv_finish_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
+                 stream, partials, splits, t, q_heads, kv_heads, hd, bias, cos_t,
+                 sin_t, first_pos, q_out, k_cache, v_cache);
   return last_launch("the multi-position RoPE and cache store");
 }
 
 const char *rows_residual_finish(float *x, const float *partials, int splits, int t,
                                  int n, cudaStream_t stream) {
   const int64_t count = (int64_t)t * n;
-  residual_finish_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(
-      x, partials, splits, t, n);
+  launch_chained(residual_finish_kernel, dim3((unsigned)((count + 255) / 256)),
+                 dim3(256), 0, stream, x, partials, splits, t, n);
   return last_launch("the multi-position residual add");
 }
 
 const char *rows_swiglu_finish(void *terms, const float *partials, int splits, int t,
                                int hidden, cudaStream_t stream) {
   const int64_t count = (int64_t)t * hidden;
-  swiglu_finish_kernel<<<(unsigned)((count + 255) / 256), 256, 0, stream>>>(
-      (__nv_bfloat16 *)terms, partials, splits, t, hidden);
+  launch_chained(swiglu_finish_kernel, dim3((unsigned)((count + 255) / 256)),
+                 dim3(256), 0, stream, (__nv_bfloat16 *)terms, partials, splits, t,
+                 hidden);
   return last_launch("the multi-position SwiGLU");
 }
 
@@ -663,8 +672,9 @@ const char *rows_attention(void *terms, const float *q, const float *k_cache,
       cudaSuccess)
     return "the multi-position attention could not get its shared memory";
   const dim3 grid((t + AQ - 1) / AQ, q_heads);
-  rows_attention_kernel<<<grid, ATT_THREADS, ATT_SMEM, stream>>>(
-      (__nv_bfloat16 *)terms, q, k_cache, v_cache, first_pos, t, q_heads, kv_heads);
+  launch_chained(rows_attention_kernel, grid, dim3(ATT_THREADS), ATT_SMEM, stream,
+                 (__nv_bfloat16 *)terms, q, k_cache, v_cache, first_pos, t, q_heads,
+                 kv_heads);
   return last_launch("the multi-position attention");
 }
 

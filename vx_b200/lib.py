@@ -36,13 +36,15 @@ EXTRA_SYMBOLS = [
     "vx_nn_qkv_fp8", "vx_nn_swiglu_fp8",
     "vx_nn_matvec_q4", "vx_nn_matvec_q4_add", "vx_nn_matvec_q4_heads_add",
     "vx_nn_qkv_q4", "vx_nn_swiglu_q4",
+    "vx_nn_matvec_rows", "vx_nn_matvec_q4_rows", "vx_nn_rms_norm_rows",
+    "vx_nn_argmax_rows", "vx_nn_embed_rows",
     "vx_decoder_create", "vx_decoder_destroy", "vx_decoder_reset",
     "vx_decoder_step", "vx_decoder_prefill", "vx_decoder_logits",
     "vx_decoder_kernels_per_step",
     "vx_decoder_stream", "vx_b200_llama2c_config", "vx_decoder_from_llama2c",
     "vx_b200_last_error", "vx_b200_gemm", "vx_b200_kernel_status",
     "vx_b200_flash_attention", "vx_b200_gemm_column_split",
-    "vx_b200_fill_normal", "vx_b200_fill_uniform",
+    "vx_b200_fill_normal", "vx_b200_fill_uniform", "vx_b200_quantize",
     "vx_b200_attention_decode_static", "vx_b200_attention_kernel",
 ]
 
@@ -152,6 +154,8 @@ def lib():
     L.vx_b200_attention_decode_static.restype = i32
     L.vx_b200_attention_decode_static.argtypes = [vp, vp, vp, vp, i32, i32, i32,
                                                   i32]
+    L.vx_b200_quantize.restype = i32
+    L.vx_b200_quantize.argtypes = [i32, vp, i32, i32, vp, vp]
     L.vx_b200_llama2c_config.restype = i32
     L.vx_b200_llama2c_config.argtypes = [C.c_char_p, vp]
     L.vx_decoder_from_llama2c.restype = vp

@@ -313,6 +313,84 @@ def nn_bf16_model(dim, hidden, n_layers, q_heads, kv_heads, head_dim, vocab,
     return Decoder(cfg, weights, keep=tensors), tensors
 
 
+def nn_quant_model(quant, dim, hidden, n_layers, q_heads, kv_heads, head_dim,
+                   vocab, max_seq, seed=7, theta=10000.0, eps=1e-5):
+    """The std::nn model with the four projections of every layer quantised on
+    the GPU from the bf16 weights nn_bf16_model would make (quant "fp8" or
+    "q4"); norms, embedding and classifier stay bf16. One sequence, one rank.
+    Returns (Decoder, tensors)."""
+    import torch
+    dev = torch.device("cuda", torch.cuda.current_device())
+    L = lib()
+    code = 2 if quant == "fp8" else 3
+
+    def normal(shape, tensor_id):
+        t = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+        rc = L.vx_b200_fill_normal(t.data_ptr(), 1, t.numel(),
+                                   seed * 1000003 + tensor_id, 0.02)
+        assert rc == 0, L.vx_b200_last_error()
+        return t
+
+    def quantised(w):
+        rows, cols = w.shape
+        if quant == "fp8":
+            codes = torch.empty(rows * cols, dtype=torch.uint8, device=dev)
+            scales = torch.empty(((rows + 127) // 128) * (cols // 128),
+                                 dtype=torch.float32, device=dev)
+        else:
+            codes = torch.empty(rows * cols // 2, dtype=torch.uint8, device=dev)
+            scales = torch.empty(rows * (cols // 32), dtype=torch.float16,
+                                 device=dev)
+        rc = L.vx_b200_quantize(code, w.data_ptr(), rows, cols, codes.data_ptr(),
+                                scales.data_ptr())
+        assert rc == 0, L.vx_b200_last_error()
+        return codes.view(torch.int32), scales
+
+    keep = {k: [] for k in ("attn_norm", "wq", "s_qkv", "wo", "s_o", "ffn_norm",
+                            "w_gate", "s_gate_up", "w_down", "s_down")}
+    for l in range(n_layers):
+        base = 16 * (l + 1)
+        for name, sname, shape, tid in (
+                ("wq", "s_qkv", ((q_heads + 2 * kv_heads) * head_dim, dim), 0),
+                ("wo", "s_o", (dim, q_heads * head_dim), 1),
+                ("w_gate", "s_gate_up", (2 * hidden, dim), 2),
+                ("w_down", "s_down", (dim, hidden), 3)):
+            w = normal(shape, base + tid)
+            codes, scales = quantised(w)
+            torch.cuda.synchronize()
+            del w
+            keep[name].append(codes)
+            keep[sname].append(scales)
+        keep["attn_norm"].append(torch.ones(dim, dtype=torch.bfloat16, device=dev))
+        keep["ffn_norm"].append(torch.ones(dim, dtype=torch.bfloat16, device=dev))
+    embed = normal((vocab, dim), 1)
+    lm_head = normal((vocab, dim), 2)
+    final_norm = torch.ones(dim, dtype=torch.bfloat16, device=dev)
+    cos_h, sin_h = rope_tables(max_seq, head_dim, theta)
+    cos = torch.from_numpy(cos_h).to(dev)
+    sin = torch.from_numpy(sin_h).to(dev)
+    torch.cuda.synchronize()
+
+    def ptrs(name):
+        return [t.data_ptr() for t in keep[name]]
+
+    nothing = [None] * n_layers
+    weights = dict(embed=embed.data_ptr(), attn_norm=ptrs("attn_norm"),
+                   wq=ptrs("wq"), wk=nothing, wv=nothing, wo=ptrs("wo"),
+                   ffn_norm=ptrs("ffn_norm"), w_gate=ptrs("w_gate"), w_up=nothing,
+                   w_down=ptrs("w_down"), final_norm=final_norm.data_ptr(),
+                   lm_head=lm_head.data_ptr(), cos=cos.data_ptr(),
+                   sin=sin.data_ptr(), s_qkv=ptrs("s_qkv"), s_o=ptrs("s_o"),
+                   s_gate_up=ptrs("s_gate_up"), s_down=ptrs("s_down"))
+    cfg = DecoderConfig(dim=dim, hidden=hidden, n_layers=n_layers,
+                        q_heads=q_heads, kv_heads=kv_heads, head_dim=head_dim,
+                        vocab=vocab, max_seq=max_seq, eps=eps, rope_theta=theta,
+                        weights_bf16=code, batch=1, tp_ranks=1, tp_reduce=0)
+    tensors = dict(keep, embed=embed, lm_head=lm_head, final_norm=final_norm,
+                   cos=cos_h, sin=sin_h)
+    return Decoder(cfg, weights, keep=tensors), tensors
+
+
 LLAMA2_7B = dict(dim=4096, hidden=11008, n_layers=32, q_heads=32, kv_heads=32,
                  head_dim=128, vocab=32000)
 

@@ -195,3 +195,27 @@ def nn_qkv_quant(quant, q, k, v, w, scales, b, x, q_heads, kv_heads, head_dim,
 def nn_swiglu_quant(quant, out, w, scales, x, rows, cols):
     _call("vx_nn_swiglu_%s" % quant, out, w, scales, x, C.c_int32(rows),
           C.c_int32(cols))
+
+
+# ---- n positions at once ------------------------------------------------------------
+def nn_matvec_rows(y, w, x, n, rows, cols):
+    _call("vx_nn_matvec_rows", y, w, x, C.c_int32(n), C.c_int32(rows),
+          C.c_int32(cols))
+
+
+def nn_matvec_q4_rows(y, w, scales, x, n, rows, cols):
+    _call("vx_nn_matvec_q4_rows", y, w, scales, x, C.c_int32(n), C.c_int32(rows),
+          C.c_int32(cols))
+
+
+def nn_rms_norm_rows(y, x, w, n, dim, eps):
+    _call("vx_nn_rms_norm_rows", y, x, w, C.c_int32(n), C.c_int32(dim),
+          C.c_float(eps))
+
+
+def nn_argmax_rows(out, logits, n, count):
+    _call("vx_nn_argmax_rows", out, logits, C.c_int32(n), C.c_int32(count))
+
+
+def nn_embed_rows(x, table, tokens, n, dim):
+    _call("vx_nn_embed_rows", x, table, tokens, C.c_int32(n), C.c_int32(dim))
