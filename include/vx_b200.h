@@ -119,6 +119,26 @@ void vx_nn_qkv_q4(VX_TENSOR2(q), VX_TENSOR2(k), VX_TENSOR2(v), VX_TENSOR1(w),
 void vx_nn_swiglu_q4(VX_TENSOR1(out), VX_TENSOR1(w), VX_TENSOR1(scales),
                      VX_TENSOR1(x), int32_t rows, int32_t cols);
 
+/* A mixture-of-experts layer: the router and the two expert projections of one
+   token, in bf16 and in Q4_0. The experts' matrices sit one after another in
+   `w` (and `scales`); `ids` is device memory, normally nn_top_k's output.
+   nn_top_k nn.vx:904, nn_moe_swiglu :968, nn_moe_down_add :1019,
+   nn_moe_swiglu_q4 :2105, nn_moe_down_q4_add :2190. (The grouping kernels for
+   batched prefill, nn_moe_group* :1068-1294, are not provided.) */
+void vx_nn_top_k(VX_TENSOR1(ids), VX_TENSOR1(weights), VX_TENSOR1(logits), int32_t n,
+                 int32_t k);
+void vx_nn_moe_swiglu(VX_TENSOR2(out), VX_TENSOR1(w), VX_TENSOR1(ids), VX_TENSOR1(x),
+                      int32_t k, int32_t rows, int32_t cols, int32_t experts);
+void vx_nn_moe_down_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(ids),
+                        VX_TENSOR1(weights), VX_TENSOR2(h), int32_t k, int32_t rows,
+                        int32_t cols, int32_t experts);
+void vx_nn_moe_swiglu_q4(VX_TENSOR2(out), VX_TENSOR1(w), VX_TENSOR1(scales),
+                         VX_TENSOR1(ids), VX_TENSOR1(x), int32_t k, int32_t rows,
+                         int32_t cols, int32_t experts);
+void vx_nn_moe_down_q4_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                           VX_TENSOR1(ids), VX_TENSOR1(weights), VX_TENSOR2(h),
+                           int32_t k, int32_t rows, int32_t cols, int32_t experts);
+
 /* Kernels for n positions at once (nn.vx:2312-2950): each is the one-position
    kernel for every row t of its [n, ...] tensors, with bit-identical rows.
    nn_matvec_rows nn.vx:2802, nn_matvec_q4_rows :2317, nn_rms_norm_rows :2835,

@@ -823,6 +823,38 @@ void oracle_random_words(uint32_t *out, int64_t n, uint32_t seed, int fp8) {
   }
 }
 
+/* nn_top_k (nn.vx:904-938): keys = the value's bits in an order that keeps the
+   order of the values, then 255 - index; sorted descending; the softmax of
+   the k first, summed in that order. */
+void oracle_nn_top_k(int32_t *ids, float *weights, const float *logits, int n,
+                     int k) {
+  std::vector<int64_t> keys((size_t)n);
+  for (int l = 0; l < n; ++l) {
+    int32_t bits;
+    memcpy(&bits, &logits[l], 4);
+    const int32_t order = bits < 0 ? bits ^ 2147483647 : bits;
+    keys[(size_t)l] = (int64_t)order * 4294967296ll + (int64_t)(255 - l);
+  }
+  for (int a = 1; a < n; ++a) { /* insertion sort, descending */
+    const int64_t key = keys[(size_t)a];
+    int b = a - 1;
+    while (b >= 0 && keys[(size_t)b] < key) {
+      keys[(size_t)b + 1] = keys[(size_t)b];
+      --b;
+    }
+    keys[(size_t)b + 1] = key;
+  }
+  const float m = logits[255 - (int)(keys[0] & 255)];
+  float total = 0.0f;
+  for (int t = 0; t < k; ++t)
+    total = total + cr_expf(logits[255 - (int)(keys[(size_t)t] & 255)] - m);
+  for (int l = 0; l < k; ++l) {
+    const int id = 255 - (int)(keys[(size_t)l] & 255);
+    ids[l] = id;
+    weights[l] = cr_expf(logits[id] - m) / total;
+  }
+}
+
 /* ---- a decoder of std::nn operators (the 7B-shaped configuration) -----------
  * Per layer, in this order: attn_norm[dim], wqkv[(q+2kv)*hd, dim],
  * bqkv[(q+2kv)*hd], wo[dim, q*hd], ffn_norm[dim], w_gate_up[2*hidden, dim],

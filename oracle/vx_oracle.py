@@ -87,6 +87,7 @@ def _declare(L):
     L.oracle_nn_swiglu_q4.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int]
     L.oracle_q4_dot_f64.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int]
     L.oracle_random_words.argtypes = [vp, i64, C.c_uint32, C.c_int]
+    L.oracle_nn_top_k.argtypes = [vp, vp, vp, C.c_int, C.c_int]
     L.oracle_nn_decode_step_quant.argtypes = [C.POINTER(NnConfig), C.c_int, vp,
                                               vp, vp, vp, vp, vp, vp, vp, i32,
                                               i32, vp]
@@ -355,6 +356,15 @@ def quant_inputs(quant, rows, cols, seed):
         n = rows * (cols // 32)
         s = (np.float32(0.003) + random_f32(n, seed + 1, 0.001)).astype(np.float16)
     return w, s
+
+
+def nn_top_k(logits, k):
+    """nn_top_k: (ids, weights) of the k largest of `logits` (at most 256)."""
+    logits = np.ascontiguousarray(logits, np.float32)
+    ids = np.empty(k, np.int32)
+    weights = np.empty(k, np.float32)
+    lib().oracle_nn_top_k(_p(ids), _p(weights), _p(logits), logits.size, k)
+    return ids, weights
 
 
 def quant_model_from_tensors(tensors, cfgd, max_seq, quant):

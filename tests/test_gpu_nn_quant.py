@@ -100,3 +100,67 @@ def test_every_fp8_code(oracle):
     ops.nn_matvec_quant("fp8", ty, dev(w), dev(s), dev(x), rows, cols)
     want = oracle.quant_dot_f64("fp8", w, s, x, rows, cols)
     assert np.array_equal(ty.to_host().astype(np.float64), want)
+
+
+# ---- a mixture-of-experts layer (nn.vx:899-1066, 2104-2262) ---------------------------
+def test_top_k(oracle):
+    for n, k, seed in ((128, 8, 5), (256, 4, 6), (60, 60, 7), (1, 1, 8)):
+        logits = oracle.random_f32(n, seed, 3.0)
+        if n > 100:
+            logits[90] = logits[11] = 9.0         # equal largest: index 11 first
+        tid = abi.DeviceTensor.empty((k,), abi.I32)
+        tw = abi.DeviceTensor.empty((k,), abi.F32)
+        ops.nn_top_k(tid, tw, dev(logits), n, k)
+        ids, weights = oracle.nn_top_k(logits, k)
+        assert np.array_equal(tid.to_host(), ids), (n, k)
+        close(tw.to_host(), weights, 2e-6)
+
+
+@pytest.mark.parametrize("quant,experts,k,inter,hidden", [
+    ("q4", 32, 8, 96, 512), ("q4", 8, 4, 1056, 2080), ("bf16", 16, 4, 200, 896)])
+def test_moe_swiglu_and_down(oracle, quant, experts, k, inter, hidden):
+    """The two expert projections of one token on the reference's own cases
+    (std_nn_q4_kernels_match_loops_on_the_cpu.vx: 8 of 32 experts 96 x 512, 4
+    of 8 experts 1056 x 2080) and a bf16 one, against f64 loops; the down
+    projection takes the GPU's own activations, as the reference's test does."""
+    ids = np.array([((experts - 1 - e * 5) % experts + experts) % experts
+                    for e in range(k)], np.int32)
+    weights = (np.float32(0.5) + oracle.random_f32(k, 75, 0.4)).astype(np.float32)
+    x = oracle.random_f32(hidden, 76, 1.0)
+    y0 = oracle.random_f32(hidden, 77, 1.0)
+    if quant == "q4":
+        gu, gu_s = oracle.quant_inputs("q4", experts * 2 * inter, hidden, 71)
+        dn, dn_s = oracle.quant_inputs("q4", experts * hidden, inter, 73)
+        gu_rows = oracle.quant_dot_f64("q4", gu, gu_s, x, experts * 2 * inter, hidden)
+        t_gu, t_gus, t_dn, t_dns = dev(gu), dev(gu_s), dev(dn), dev(dn_s)
+    else:
+        gu = oracle.f32_to_bf16(oracle.random_f32(experts * 2 * inter * hidden, 71, 0.1))
+        dn = oracle.f32_to_bf16(oracle.random_f32(experts * hidden * inter, 73, 0.1))
+        gu_rows = oracle.bf16_to_f32(gu).astype(np.float64) \
+            .reshape(experts * 2 * inter, hidden) @ x.astype(np.float64)
+        t_gu, t_gus, t_dn, t_dns = dev(gu, True), None, dev(dn, True), None
+    act = abi.DeviceTensor.empty((k, inter), abi.F32)
+    ops.nn_moe_swiglu(act, t_gu, dev(ids), dev(x), k, inter, hidden, experts,
+                      scales=t_gus)
+    got_a = act.to_host()
+    want_a = np.empty((k, inter))
+    for e in range(k):
+        g = gu_rows[ids[e] * 2 * inter:ids[e] * 2 * inter + inter]
+        u = gu_rows[ids[e] * 2 * inter + inter:(ids[e] + 1) * 2 * inter]
+        want_a[e] = g / (1.0 + np.exp(-g)) * u
+    close(got_a.reshape(-1), want_a.reshape(-1))
+    ty = dev(y0)
+    ops.nn_moe_down_add(ty, t_dn, dev(ids), dev(weights), act, k, hidden, inter,
+                        experts, scales=t_dns)
+    want_y = y0.astype(np.float64)
+    for e in range(k):
+        if quant == "q4":
+            rows = oracle.quant_dot_f64("q4", dn, dn_s, got_a[e], experts * hidden,
+                                        inter)[ids[e] * hidden:(ids[e] + 1) * hidden]
+        else:
+            rows = oracle.bf16_to_f32(dn).astype(np.float64) \
+                .reshape(experts * hidden, inter)[ids[e] * hidden:(ids[e] + 1) * hidden] \
+                @ got_a[e].astype(np.float64)
+        want_y = want_y + float(weights[e]) * rows
+    close(ty.to_host(), want_y)
+    assert ops.kernel_status() == 0

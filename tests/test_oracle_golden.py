@@ -236,3 +236,18 @@ def test_fp8_code_values_follow_the_definition(oracle):
     assert np.array_equal(got.astype(np.float64), want)
     assert want[codes.index(0x38)] == 1.0 and want[codes.index(0x01)] == 2.0 ** -9
     assert want[codes.index(0x7e)] == 448.0 and want[codes.index(0xc0)] == -2.0
+
+
+def test_top_k_orders_by_value_then_index(oracle):
+    """nn_top_k (nn.vx:899-903): the k largest, the largest first, the lower
+    index first of two equal values; weights = the softmax over those k."""
+    logits = oracle.random_f32(200, 5, 3.0)
+    logits[150] = logits[20] = 7.5            # equal largest: index 20 first
+    logits[7] = -0.0
+    logits[8] = 0.0
+    ids, weights = oracle.nn_top_k(logits, 8)
+    order = sorted(range(200), key=lambda i: (-float(logits[i]), i))[:8]
+    assert list(ids) == order and list(ids[:2]) == [20, 150]
+    e = np.exp(logits[ids].astype(np.float64) - float(logits[ids[0]]))
+    assert np.abs(weights - e / e.sum()).max() <= 1e-6
+    assert abs(float(weights.sum()) - 1.0) <= 1e-6

@@ -65,6 +65,13 @@ struct MatvecArgs {
   bool norm_bf16;
   float eps;
   /* epilogue */
+  /* a mixture-of-experts layer (nn.vx:960-1066): w (and scales) hold `experts`
+     matrices of rows x cols one after another and this call takes matrix
+     expert_ids[expert_slot], an index in device memory; NULL: w is the matrix.
+     add_scale (mode 1): y += add_scale[0] * s, a device scalar. */
+  const int32_t *expert_ids;
+  int expert_slot, experts;
+  const float *add_scale;
   int mode;            /* 0 y = s, 1 y += s, 2 y = s + bias,
                           3 y += the sum of all ranks' s (see TpPush) */
   const void *bias;    /* mode 2, bf16 */
@@ -107,6 +114,9 @@ struct SwigluArgs {
   int wfmt;
   const void *scales, *scales_up; /* of w, and of w_up when that is given */
   int row_base;
+  /* as in MatvecArgs: w holds `experts` matrices of 2 rows x cols */
+  const int32_t *expert_ids;
+  int expert_slot, experts;
   int rows, cols;
   const void *w_up; /* NULL: up rows follow the gate rows in w */
   const float *x;
@@ -281,6 +291,11 @@ const char *rows_attention(void *terms, const float *q, const float *k_cache,
                            int q_heads, int kv_heads, int hd, cudaStream_t stream);
 int rows_status();
 
+/* nn_top_k (nn.vx:904-938): ids[j] = the index of the j-th largest of the
+   first n logits (n <= 256; of equal values the lower index first), weights[j]
+   = the softmax over those k values. */
+const char *top_k(int32_t *ids, float *weights, const float *logits, int n, int k,
+                  cudaStream_t stream);
 const char *argmax(int32_t *out, const float *logits, int n, int batch,
                    int64_t stride, cudaStream_t stream);
 const char *embed(float *x, const void *table, bool tbf16, const int32_t *token,

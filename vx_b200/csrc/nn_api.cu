@@ -550,6 +550,145 @@ QUANT_EXPORTS(q4, vxb::kFmtQ4, uint16_t, "q4")
 #undef QUANT_EXPORTS
 
 
+/* ------------------------------------------------ a mixture-of-experts layer
+ * nn_top_k nn.vx:904, nn_moe_swiglu :968, nn_moe_down_add :1019 (bf16), and
+ * nn_moe_swiglu_q4 :2105, nn_moe_down_q4_add :2190. The experts' matrices sit
+ * one after another in `w`; `ids` (device memory, from nn_top_k) names the k
+ * that a token uses. One projection launch per expert slot; the down
+ * projection adds the experts to y in slot order. */
+namespace {
+void moe_swiglu(const char *fn, int quant, float *out, int64_t out_rows,
+                int64_t out_pitch, const void *w, int64_t w_len,
+                const void *scales, const int32_t *ids, int64_t ids_len,
+                const float *x, int64_t x_len, int k, int rows, int cols,
+                int experts) {
+  const int per = quant ? 32 : 8;
+  if (k <= 0 || ids_len < k || out_rows < k || out_pitch < rows)
+    stop("%s: `ids` needs k values, and `out` a row of rows values for each", fn);
+  if (cols % per != 0 || x_len < cols || rows <= 0 || experts <= 0 ||
+      (quant ? w_len / (cols / 8) : w_len / cols) / 2 / rows < experts)
+    stop("%s: `w` needs 2 * rows rows of cols values for each expert", fn);
+  for (int e = 0; e < k; ++e) {
+    vxb::SwigluArgs a{};
+    a.w = w;
+    a.wbf16 = true;
+    a.wfmt = quant;
+    a.scales = scales;
+    a.rows = rows;
+    a.cols = cols;
+    a.x = x;
+    a.x_stride = cols;
+    a.out = out + (int64_t)e * out_pitch;
+    a.out_stride = out_pitch;
+    a.batch = 1;
+    a.expert_ids = ids;
+    a.expert_slot = e;
+    a.experts = experts;
+    must(vxb::swiglu(a, vxb::caller_stream()), fn);
+  }
+}
+void moe_down_add(const char *fn, int quant, float *y, int64_t y_len,
+                  const void *w, int64_t w_len, const void *scales,
+                  const int32_t *ids, int64_t ids_len, const float *weights,
+                  int64_t weights_len, const float *h, int64_t h_rows,
+                  int64_t h_pitch, int k, int rows, int cols, int experts) {
+  const int per = quant ? 32 : 8;
+  if (k <= 0 || ids_len < k || weights_len < k || h_rows < k || h_pitch < cols)
+    stop("%s: `ids` and `weights` need k values, and `h` a row of cols values for "
+         "each", fn);
+  if (cols % per != 0 || y_len < rows || rows <= 0 || experts <= 0 ||
+      (quant ? w_len / (cols / 8) : w_len / cols) / rows < experts)
+    stop("%s: `w` needs rows rows of cols values for each expert", fn);
+  for (int e = 0; e < k; ++e) {
+    vxb::MatvecArgs a{};
+    a.w = w;
+    a.wbf16 = true;
+    a.wfmt = quant;
+    a.scales = scales;
+    a.rows = rows;
+    a.cols = cols;
+    a.x = h + (int64_t)e * h_pitch;
+    a.x_stride = h_pitch;
+    a.y = y;
+    a.y_stride = rows;
+    a.batch = 1;
+    a.mode = 1;
+    a.expert_ids = ids;
+    a.expert_slot = e;
+    a.experts = experts;
+    a.add_scale = weights + e;
+    must(vxb::matvec(a, vxb::caller_stream()), fn);
+  }
+}
+} // namespace
+
+extern "C" {
+
+#define FN "nn_top_k"
+void vx_nn_top_k(VX_TENSOR1(ids), VX_TENSOR1(weights), VX_TENSOR1(logits), int32_t n,
+                 int32_t k) {
+  UNUSED_ALLOC(ids); UNUSED_ALLOC(weights); UNUSED_ALLOC(logits);
+  if (n <= 0 || n > 256 || k <= 0 || k > n)
+    stop("nn_top_k: n must be 1 to 256, and k must be 1 to n");
+  if (logits_n0 < n || ids_n0 < k || weights_n0 < k)
+    stop("nn_top_k: a tensor has too few values");
+  must(vxb::top_k(T1(int32_t, ids), T1(float, weights), T1(float, logits), n, k,
+                  vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+#define FN "nn_moe_swiglu"
+void vx_nn_moe_swiglu(VX_TENSOR2(out), VX_TENSOR1(w), VX_TENSOR1(ids), VX_TENSOR1(x),
+                      int32_t k, int32_t rows, int32_t cols, int32_t experts) {
+  UNUSED_ALLOC(out); UNUSED_ALLOC(w); UNUSED_ALLOC(ids); UNUSED_ALLOC(x);
+  moe_swiglu(FN, 0, T2(float, out), out_n0, out_n1, T1(uint16_t, w), w_n0, nullptr,
+             T1(int32_t, ids), ids_n0, T1(float, x), x_n0, k, rows, cols, experts);
+}
+#undef FN
+
+#define FN "nn_moe_down_add"
+void vx_nn_moe_down_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(ids),
+                        VX_TENSOR1(weights), VX_TENSOR2(h), int32_t k, int32_t rows,
+                        int32_t cols, int32_t experts) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(ids); UNUSED_ALLOC(weights);
+  UNUSED_ALLOC(h);
+  moe_down_add(FN, 0, T1(float, y), y_n0, T1(uint16_t, w), w_n0, nullptr,
+               T1(int32_t, ids), ids_n0, T1(float, weights), weights_n0,
+               T2(float, h), h_n0, h_n1, k, rows, cols, experts);
+}
+#undef FN
+
+#define FN "nn_moe_swiglu_q4"
+void vx_nn_moe_swiglu_q4(VX_TENSOR2(out), VX_TENSOR1(w), VX_TENSOR1(scales),
+                         VX_TENSOR1(ids), VX_TENSOR1(x), int32_t k, int32_t rows,
+                         int32_t cols, int32_t experts) {
+  UNUSED_ALLOC(out); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(ids);
+  UNUSED_ALLOC(x);
+  if (scales_n0 < (int64_t)experts * 2 * rows * (cols / 32))
+    stop("nn_moe_swiglu_q4: the scales are too few for the experts");
+  moe_swiglu(FN, vxb::kFmtQ4, T2(float, out), out_n0, out_n1, T1(uint32_t, w), w_n0,
+             T1(uint16_t, scales), T1(int32_t, ids), ids_n0, T1(float, x), x_n0, k,
+             rows, cols, experts);
+}
+#undef FN
+
+#define FN "nn_moe_down_q4_add"
+void vx_nn_moe_down_q4_add(VX_TENSOR1(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                           VX_TENSOR1(ids), VX_TENSOR1(weights), VX_TENSOR2(h),
+                           int32_t k, int32_t rows, int32_t cols, int32_t experts) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(ids);
+  UNUSED_ALLOC(weights); UNUSED_ALLOC(h);
+  if (scales_n0 < (int64_t)experts * rows * (cols / 32))
+    stop("nn_moe_down_q4_add: the scales are too few for the experts");
+  moe_down_add(FN, vxb::kFmtQ4, T1(float, y), y_n0, T1(uint32_t, w), w_n0,
+               T1(uint16_t, scales), T1(int32_t, ids), ids_n0, T1(float, weights),
+               weights_n0, T2(float, h), h_n0, h_n1, k, rows, cols, experts);
+}
+#undef FN
+
+} /* extern "C" */
+
 /* ---------------------------------------------- kernels for n positions
  * (nn.vx:2312-2950: "the kernel of the same name without _rows ... for each
  * position ... row t of the output is bit-identical to the one-position kernel

@@ -113,6 +113,14 @@ struct RowDotParams {
   int max_seq;
   /* EPI_PUSH */
   TpPush tp;
+  /* a mixture-of-experts layer: w0 (and s0) hold `experts` matrices one after
+     another, expert_bytes (scale_bytes) apart, and this launch takes matrix
+     expert_ids[expert_slot] (device memory: the router wrote it). add_scale
+     (EPI_ADD): y += add_scale[0] * s. */
+  const int32_t *expert_ids;
+  int expert_slot, experts;
+  int64_t expert_bytes, scale_bytes;
+  const float *add_scale;
 };
 
 /* Weight formats. A row is a run of 16-byte words; a word holds E weights:
@@ -281,20 +289,21 @@ __device__ __forceinline__ const char *scale_row(const void *scales, int row,
   return (const char *)scales + (int64_t)row * (cols / 32) * 2; /* Q4_0 */
 }
 template <typename W, int EPI>
-__device__ __forceinline__ ItemRows item_rows(const RowDotParams &p, int item) {
+__device__ __forceinline__ ItemRows item_rows(const RowDotParams &p, int item,
+                                              int64_t w_off = 0, int64_t s_off = 0) {
   ItemRows it;
   const int cols = p.cols;
   const int64_t row_bytes = (int64_t)cols * 16 / PerWord<W>::n;
   it.head = it.idx = it.kind = 0;
   it.sc0 = it.sc1 = nullptr;
   if (EPI == EPI_SWIGLU) {
-    it.r0 = (const char *)p.w0 + item * row_bytes;
+    it.r0 = (const char *)p.w0 + w_off + item * row_bytes;
     it.r1 = p.w1 ? (const char *)p.w1 + item * row_bytes
-                 : (const char *)p.w0 + (p.rows + item) * row_bytes;
+                 : (const char *)p.w0 + w_off + (p.rows + item) * row_bytes;
     if (Scaled<W>::yes) {
-      it.sc0 = scale_row<W>(p.s0, p.row_base + item, cols);
+      it.sc0 = scale_row<W>(p.s0, p.row_base + item, cols) + s_off;
       it.sc1 = p.w1 ? scale_row<W>(p.s1, item, cols)
-                    : scale_row<W>(p.s0, p.row_base + p.rows + item, cols);
+                    : scale_row<W>(p.s0, p.row_base + p.rows + item, cols) + s_off;
     }
   } else if (EPI == EPI_QKV) {
     const int half = p.head_dim / 2;
@@ -338,11 +347,11 @@ __device__ __forceinline__ ItemRows item_rows(const RowDotParams &p, int item) {
       it.sc1 = scale_row<W>(sbase, srow + local * p.head_dim + b, cols);
     }
   } else {
-    it.r0 = (const char *)p.w0 + (int64_t)(2 * item) * row_bytes;
+    it.r0 = (const char *)p.w0 + w_off + (int64_t)(2 * item) * row_bytes;
     it.r1 = 2 * item + 1 < p.rows ? it.r0 + row_bytes : nullptr;
     if (Scaled<W>::yes) {
-      it.sc0 = scale_row<W>(p.s0, p.row_base + 2 * item, cols);
-      it.sc1 = scale_row<W>(p.s0, p.row_base + 2 * item + 1, cols);
+      it.sc0 = scale_row<W>(p.s0, p.row_base + 2 * item, cols) + s_off;
+      it.sc1 = scale_row<W>(p.s0, p.row_base + 2 * item + 1, cols) + s_off;
     }
   }
   return it;
@@ -407,10 +416,24 @@ rowdot_kernel(const RowDotParams p) {
   /* The loading side walks the same units RING_STAGES ahead, with its own
      counters (no divisions on the way). Lane 0 issues the copies. */
   const int last_bytes = row_bytes - (nch - 1) * CHUNK_BYTES;
+  /* An expert's matrix is named by the router's output, which the kernel before
+     this one may have written: such a launch waits before it fetches weights. */
+  int64_t w_off = 0, s_off = 0;
+  bool expert_ok = true;
+  if (p.expert_ids) {
+    chain_release();
+    chain_wait();
+    const int id = p.expert_ids[p.expert_slot];
+    expert_ok = id >= 0 && id < p.experts;
+    w_off = expert_ok ? id * p.expert_bytes : 0;
+    s_off = expert_ok ? id * p.scale_bytes : 0;
+    if (!expert_ok && threadIdx.x == 0)
+      atomicCAS(&g_rowdot_status, 0, 0x5E); /* not the number of an expert */
+  }
   int ld_u = 0, ld_item = first, ld_ch = 0, ld_stage = 0;
   const char *ld_r0 = nullptr, *ld_r1 = nullptr;
   if (units > 0) {
-    const ItemRows it = item_rows<W, EPI>(p, first);
+    const ItemRows it = item_rows<W, EPI>(p, first, w_off, s_off);
     ld_r0 = it.r0;
     ld_r1 = it.r1 ? it.r1 : it.r0;
   }
@@ -431,7 +454,7 @@ rowdot_kernel(const RowDotParams p) {
       ld_ch = 0;
       ++ld_item;
       if (ld_u < units) {
-        const ItemRows it = item_rows<W, EPI>(p, ld_item);
+        const ItemRows it = item_rows<W, EPI>(p, ld_item, w_off, s_off);
         ld_r0 = it.r0;
         ld_r1 = it.r1 ? it.r1 : it.r0;
       }
@@ -596,7 +619,7 @@ rowdot_kernel(const RowDotParams p) {
     const float *xcol = xbase + ch * CHUNK_COLS + lane_x;
     const char *sc0 = nullptr, *sc1 = nullptr;
     if (Scaled<W>::yes) {
-      const ItemRows here = item_rows<W, EPI>(p, item);
+      const ItemRows here = item_rows<W, EPI>(p, item, w_off, s_off);
       sc0 = here.sc0;
       sc1 = here.r1 ? here.sc1 : here.sc0;
     }
@@ -616,7 +639,7 @@ rowdot_kernel(const RowDotParams p) {
       continue;
 
     /* ---- the item is complete: reduce, then the epilogue on lane 0 ---- */
-    const ItemRows it = item_rows<W, EPI>(p, item);
+    const ItemRows it = item_rows<W, EPI>(p, item, w_off, s_off);
     const char *r1 = it.r1;
     const int head = it.head, idx = it.idx, kind = it.kind;
     float t0[B], t1[B];
@@ -689,9 +712,10 @@ rowdot_kernel(const RowDotParams p) {
         const int ra = 2 * item, rb = 2 * item + 1;
         float v0 = t0[b], v1 = t1[b];
         if (EPI == EPI_ADD) {
-          v0 = y[ra] + v0;
+          const float scale = p.add_scale ? (expert_ok ? p.add_scale[0] : 0.0f) : 1.0f;
+          v0 = p.add_scale ? fmaf(scale, v0, y[ra]) : y[ra] + v0;
           if (r1)
-            v1 = y[rb] + v1;
+            v1 = p.add_scale ? fmaf(scale, v1, y[rb]) : y[rb] + v1;
         } else if (EPI == EPI_BIAS) {
           v0 += bf16_at(p.bias, ra);
           if (r1)
@@ -1234,6 +1258,45 @@ attention_decode_kernel(const AttnArgs a) {
                                  threadIdx.x >> 5, threadIdx.x & 31, sh, 0);
 }
 
+/* ----------------------------------------------------------------- top_k
+ * nn_top_k (nn.vx:904-938): the router of a mixture-of-experts layer. The
+ * reference sorts 64-bit keys -- the value's bits in an order that keeps the
+ * order of the values, then 255 - index, so that of equal values the lower
+ * index comes first -- and takes the first k; here each of the n <= 256
+ * values counts the keys above its own, which is its place. Then the softmax
+ * over the k values, summed in the order of their places. One block. */
+__global__ void __launch_bounds__(256)
+top_k_kernel(int32_t *ids, float *weights, const float *logits, int n, int k) {
+  __shared__ long long keys[256];
+  __shared__ int order[256];
+  chain_release();
+  chain_wait();
+  const int i = threadIdx.x;
+  if (i < n) {
+    const int bits = __float_as_int(logits[i]);
+    const int ordered = bits < 0 ? bits ^ 0x7fffffff : bits;
+    keys[i] = (long long)ordered * 4294967296ll + (255 - i);
+  }
+  __syncthreads();
+  if (i < n) {
+    const long long mine = keys[i];
+    int place = 0;
+    for (int j = 0; j < n; ++j)
+      place += keys[j] > mine;
+    order[place] = i; /* keys are distinct: every place is taken once */
+  }
+  __syncthreads();
+  if (i < k) {
+    const float top = logits[order[0]];
+    float total = 0.0f;
+    for (int t = 0; t < k; ++t)
+      total = total + expf(logits[order[t]] - top);
+    const int id = order[i];
+    ids[i] = id;
+    weights[i] = expf(logits[id] - top) / total;
+  }
+}
+
 /* ---------------------------------------------------------------- argmax
  * nn_argmax (nn.vx:870-897) and sample_argmax (llama2.vx:460-474): the lowest
  * index of the largest value. One block per sequence. */
@@ -1332,6 +1395,17 @@ const char *matvec(const MatvecArgs &a, cudaStream_t stream) {
   p.s0 = a.scales;
   p.row_base = a.row_base;
   const int fmt = a.wfmt ? a.wfmt : (a.wbf16 ? kFmtBf16 : kFmtF32);
+  const int per_word = fmt == kFmtF32 ? 4 : fmt == kFmtBf16 ? 8 : fmt == kFmtFp8 ? 16 : 32;
+  if (a.expert_ids) {
+    if (fmt == kFmtFp8)
+      return "the expert projections take bf16 or Q4_0 weights";
+    p.expert_ids = a.expert_ids;
+    p.expert_slot = a.expert_slot;
+    p.experts = a.experts;
+    p.expert_bytes = (int64_t)a.rows * (a.cols / per_word * 16);
+    p.scale_bytes = fmt == kFmtQ4 ? (int64_t)a.rows * (a.cols / 32) * 2 : 0;
+  }
+  p.add_scale = a.add_scale;
   switch (a.mode) {
   case 0: return launch_rowdot<EPI_STORE>(p, fmt, stream);
   case 1: return launch_rowdot<EPI_ADD>(p, fmt, stream);
@@ -1386,6 +1460,18 @@ const char *swiglu(const SwigluArgs &a, cudaStream_t stream) {
   p.s0 = a.scales;
   p.s1 = a.scales_up;
   p.row_base = a.row_base;
+  if (a.expert_ids) {
+    const int fmt = a.wfmt ? a.wfmt : (a.wbf16 ? kFmtBf16 : kFmtF32);
+    const int per_word = fmt == kFmtF32 ? 4 : fmt == kFmtBf16 ? 8 : fmt == kFmtFp8 ? 16 : 32;
+    if (fmt == kFmtFp8 || a.w_up)
+      return "the expert projections take bf16 or Q4_0 weights, gate and up rows "
+             "in one matrix";
+    p.expert_ids = a.expert_ids;
+    p.expert_slot = a.expert_slot;
+    p.experts = a.experts;
+    p.expert_bytes = (int64_t)2 * a.rows * (a.cols / per_word * 16);
+    p.scale_bytes = fmt == kFmtQ4 ? (int64_t)2 * a.rows * (a.cols / 32) * 2 : 0;
+  }
   return launch_rowdot<EPI_SWIGLU>(p, a.wfmt ? a.wfmt : (a.wbf16 ? kFmtBf16 : kFmtF32),
                                    stream);
 }
@@ -1499,11 +1585,15 @@ const char *attention_decode(const AttnArgs &a, cudaStream_t stream) {
   if (which == kAttnCluster) {
     const dim3 cgrid(ATT_CLUSTER, a.kv_heads * tiles, a.batch);
     /* Warps per block by how many blocks there are: with few heads (a rank of
-       a tensor-parallel job holds 4 of 32) sixteen warps per block put the
-       positions of a head on 128 warps, one round trip to memory each; with
-       every SM already holding several blocks, four. */
+       a tensor-parallel job holds 4 or 8 of 32) sixteen warps per block put
+       the positions of a head on 128 warps, one round trip to memory each;
+       with every SM already holding several blocks, four. Measured at
+       position 520 on one rank's share of the 7B shape, microseconds per
+       layer for 4 / 8 / 16 warps: 1/2 of the heads 53.4 / 51.8 / 54.3, 1/4
+       37.7 / 37.3 / 36.0, 1/8 28.6 / 27.3 / 26.5; all heads 387 / 389 / 361
+       tokens/s. */
     const int64_t blocks = (int64_t)cgrid.x * cgrid.y * cgrid.z;
-    int warps = blocks <= sm_count() ? 16 : (blocks <= 2 * sm_count() ? 8 : 4);
+    int warps = 2 * blocks <= sm_count() ? 16 : (blocks <= 2 * sm_count() ? 8 : 4);
     /* VXB_ATTN_WARPS=4, 8 or 16 pins it (for measurements) */
     if (const char *pin = getenv("VXB_ATTN_WARPS")) {
       const int v = atoi(pin);
@@ -1554,6 +1644,15 @@ const char *attention_decode_clustered(const AttnArgs &a, cudaStream_t stream) {
   b.counters = nullptr;
   b.kernel = kAttnCluster;
   return attention_decode(b, stream);
+}
+
+const char *top_k(int32_t *ids, float *weights, const float *logits, int n, int k,
+                  cudaStream_t stream) {
+  if (n < 1 || n > 256 || k < 1 || k > n)
+    return "n must be 1 to 256, and k must be 1 to n";
+  launch_chained(top_k_kernel, dim3(1), dim3(256), 0, stream, ids, weights, logits,
+                 n, k);
+  return check_launch("the router launch");
 }
 
 const char *argmax(int32_t *out, const float *logits, int n, int batch,

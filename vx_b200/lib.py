@@ -38,6 +38,8 @@ EXTRA_SYMBOLS = [
     "vx_nn_qkv_q4", "vx_nn_swiglu_q4",
     "vx_nn_matvec_rows", "vx_nn_matvec_q4_rows", "vx_nn_rms_norm_rows",
     "vx_nn_argmax_rows", "vx_nn_embed_rows",
+    "vx_nn_top_k", "vx_nn_moe_swiglu", "vx_nn_moe_down_add", "vx_nn_moe_swiglu_q4",
+    "vx_nn_moe_down_q4_add",
     "vx_decoder_create", "vx_decoder_destroy", "vx_decoder_reset",
     "vx_decoder_step", "vx_decoder_prefill", "vx_decoder_logits",
     "vx_decoder_kernels_per_step",

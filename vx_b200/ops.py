@@ -219,3 +219,26 @@ def nn_argmax_rows(out, logits, n, count):
 
 def nn_embed_rows(x, table, tokens, n, dim):
     _call("vx_nn_embed_rows", x, table, tokens, C.c_int32(n), C.c_int32(dim))
+
+
+# ---- a mixture-of-experts layer -----------------------------------------------------
+def nn_top_k(ids, weights, logits, n, k):
+    _call("vx_nn_top_k", ids, weights, logits, C.c_int32(n), C.c_int32(k))
+
+
+def nn_moe_swiglu(out, w, ids, x, k, rows, cols, experts, scales=None):
+    if scales is None:
+        _call("vx_nn_moe_swiglu", out, w, ids, x, C.c_int32(k), C.c_int32(rows),
+              C.c_int32(cols), C.c_int32(experts))
+    else:
+        _call("vx_nn_moe_swiglu_q4", out, w, scales, ids, x, C.c_int32(k),
+              C.c_int32(rows), C.c_int32(cols), C.c_int32(experts))
+
+
+def nn_moe_down_add(y, w, ids, weights, h, k, rows, cols, experts, scales=None):
+    if scales is None:
+        _call("vx_nn_moe_down_add", y, w, ids, weights, h, C.c_int32(k),
+              C.c_int32(rows), C.c_int32(cols), C.c_int32(experts))
+    else:
+        _call("vx_nn_moe_down_q4_add", y, w, scales, ids, weights, h, C.c_int32(k),
+              C.c_int32(rows), C.c_int32(cols), C.c_int32(experts))
