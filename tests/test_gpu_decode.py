@@ -88,6 +88,30 @@ def test_nn_decoder_tokens_match_oracle(oracle, batch):
         assert got[b] == want, "sequence %d: %s" % (b, report(got[b], want))
 
 
+def test_nn_decoder_keeps_every_device_table_it_reads(oracle):
+    """Whatever the model builder put on the GPU stays allocated while the
+    decoder lives: small and large blocks that torch hands out afterwards are
+    filled with NaN, and the tokens must not change."""
+    import torch
+    max_seq = 96
+    dec, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=1, **SMALL_NN)
+    hm = nn_host_model(oracle, tensors, SMALL_NN, max_seq)
+    junk = [torch.full((n,), float("nan"), device="cuda")
+            for n in (1, 128, 3072, 6144, 1 << 16, 1 << 18, 1 << 20) for _ in range(4)]
+    torch.cuda.synchronize()
+    prompt = list(np.random.default_rng(9).integers(0, SMALL_NN["vocab"], 20))
+    for t in prompt:
+        tok = dec.step([int(t)])[0]
+    got = []
+    for _ in range(16):
+        got.append(tok)
+        tok = dec.step(None)[0]
+    dec.close()
+    del junk
+    want = oracle_generate(oracle, hm, prompt, 16, max_seq)
+    assert got == want, report(got, want)
+
+
 def test_nn_decoder_with_the_split_attention_kernel(oracle):
     """The decoder recorded while the split kernel is chosen: the partial
     results go through the decoder's scratch and counters instead of a

@@ -310,7 +310,9 @@ def nn_bf16_model(dim, hidden, n_layers, q_heads, kv_heads, head_dim, vocab,
                         tp_reduce=tp_reduce if tp_ranks > 1 else 0)
     tensors = dict(keep, embed=embed, lm_head=lm_head, final_norm=final_norm,
                    cos=cos_h, sin=sin_h)
-    return Decoder(cfg, weights, keep=tensors), tensors
+    # The decoder reads the device tables for its whole life: hold them, or the
+    # caching allocator hands their block to the next small allocation.
+    return Decoder(cfg, weights, keep=(tensors, cos, sin)), tensors
 
 
 def nn_quant_model(quant, dim, hidden, n_layers, q_heads, kv_heads, head_dim,
@@ -388,7 +390,9 @@ def nn_quant_model(quant, dim, hidden, n_layers, q_heads, kv_heads, head_dim,
                         weights_bf16=code, batch=1, tp_ranks=1, tp_reduce=0)
     tensors = dict(keep, embed=embed, lm_head=lm_head, final_norm=final_norm,
                    cos=cos_h, sin=sin_h)
-    return Decoder(cfg, weights, keep=tensors), tensors
+    # The decoder reads the device tables for its whole life: hold them, or the
+    # caching allocator hands their block to the next small allocation.
+    return Decoder(cfg, weights, keep=(tensors, cos, sin)), tensors
 
 
 LLAMA2_7B = dict(dim=4096, hidden=11008, n_layers=32, q_heads=32, kv_heads=32,
