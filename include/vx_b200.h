@@ -244,6 +244,13 @@ const float *vx_decoder_logits(const vx_decoder *d);
 void *vx_decoder_stream(const vx_decoder *d);
 /* How many kernels one step launches (for accounting). */
 int32_t vx_decoder_kernels_per_step(const vx_decoder *d);
+/* A decoder created with VXB_STEP_TRACE=1 in the environment whose step is one
+   launch keeps six nanosecond clock readings per projection of the last step
+   (one block's view: loop top, after the barrier, after the input is staged,
+   after its rows, before and after the layer's attention); copies up to
+   `capacity` of them to `out` and returns how many, 0 when there are none. No
+   counterpart in the reference: a measuring aid. */
+int32_t vx_decoder_step_trace(vx_decoder *d, uint64_t *out, int32_t capacity);
 
 /* A llama2.c checkpoint: the file the reference's llama programs read through
    vx_load_config and vx_load_weights (stdlib/rust_core/src/ffi/llama.rs:11-47;

@@ -169,11 +169,33 @@ def shard(torch, args):
         dec.step([int(t)], fetch=False)
     ms = _timed(torch, torch.cuda.ExternalStream(dec.stream),
                 lambda: dec.step(None, fetch=False), max(args.iters, 20))
+    phases = None
+    trace = dec.step_trace()      # with VXB_STEP_TRACE=1 and the one-launch step
+    if trace is not None:
+        t = trace.astype(np.int64)
+        layers = t[:-1].reshape(32, 4, 6)[4:]          # skip the first layers
+        names = ["qkv", "wo", "gate_up", "down"]
+        phases = {}
+        for k, name in enumerate(names):
+            o = layers[:, k]
+            phases[name] = dict(barrier=float((o[:, 1] - o[:, 0]).mean()) / 1e3,
+                                stage_x=float((o[:, 2] - o[:, 1]).mean()) / 1e3,
+                                rows=float((o[:, 3] - o[:, 2]).mean()) / 1e3)
+        q = layers[:, 0]
+        phases["attention"] = dict(barrier=float((q[:, 4] - q[:, 3]).mean()) / 1e3,
+                                   units=float((q[:, 5] - q[:, 4]).mean()) / 1e3)
+        phases["layer"] = float((layers[1:, 0, 0] - layers[:-1, 0, 0]).mean()) / 1e3
+        phases["logits"] = dict(barrier=float(t[-1, 1] - t[-1, 0]) / 1e3,
+                                stage_x=float(t[-1, 2] - t[-1, 1]) / 1e3,
+                                rows=float(t[-1, 3] - t[-1, 2]) / 1e3)
+    per_step = dec.kernels_per_step
     dec.close()
     nbytes = llama.weight_bytes_per_token(**shape)
     return dict(kernel="decode step of 1/%d of the 7B shape, position %d" % (r, args.pos),
                 us=ms * 1e3, us_per_layer=ms * 1e3 / 32, tokens_per_s=1e3 / ms,
-                weight_gbs=nbytes / ms / 1e6, status=ops.kernel_status())
+                weight_gbs=nbytes / ms / 1e6, status=ops.kernel_status(),
+                kernels_per_step=per_step,
+                phases_us_seen_by_block_0=phases)
 
 
 def prefill(torch, args):

@@ -112,6 +112,52 @@ def test_nn_decoder_keeps_every_device_table_it_reads(oracle):
     assert got == want, report(got, want)
 
 
+@pytest.mark.parametrize("q_heads,kv_heads", [(4, 4), (4, 2), (8, 2)])
+def test_one_launch_step_matches_the_oracle_and_the_separate_kernels(
+        oracle, monkeypatch, q_heads, kv_heads):
+    """One sequence, bf16 weights and heads of 128 values, VXB_STEP_KERNEL=1:
+    every layer of a step runs as one cooperative launch (kept as a measured
+    alternative; the chain of kernels is faster). Its tokens must equal the oracle's,
+    and its logits the ones of the chain of separate kernels (the projections
+    sum in the same order; attention cuts the positions differently)."""
+    from vx_b200 import ops
+    shape = dict(dim=512, hidden=1408, n_layers=3, q_heads=q_heads,
+                 kv_heads=kv_heads, head_dim=128, vocab=4096)
+    max_seq = 160
+    prompt = list(np.random.default_rng(11).integers(0, shape["vocab"], 70))
+    steps = 40
+
+    def run(dec):
+        for t in prompt:
+            tok = dec.step([int(t)])[0]
+        said, logits = [], []
+        for _ in range(steps):
+            said.append(tok)
+            logits.append(dec.logits()[0].copy())
+            tok = dec.step(None)[0]
+        return said, logits
+
+    monkeypatch.setenv("VXB_STEP_KERNEL", "1")
+    dec, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=1, **shape)
+    assert dec.kernels_per_step == 0           # nothing recorded yet
+    got, got_logits = run(dec)
+    assert dec.kernels_per_step <= 5, "the step did not run as one launch"
+    assert ops.kernel_status() == 0
+    dec.close()
+    hm = nn_host_model(oracle, tensors, shape, max_seq)
+    want = oracle_generate(oracle, hm, prompt, steps, max_seq)
+    assert got == want, report(got, want)
+
+    monkeypatch.setenv("VXB_STEP_KERNEL", "0")
+    chain, _ = llama.nn_bf16_model(max_seq=max_seq, batch=1, **shape)
+    ref, ref_logits = run(chain)
+    assert chain.kernels_per_step > 5
+    chain.close()
+    assert ref == want
+    for a, b in zip(got_logits, ref_logits):
+        assert np.abs(a - b).max() <= 1e-5 * np.abs(b).max()
+
+
 def test_nn_decoder_with_the_split_attention_kernel(oracle):
     """The decoder recorded while the split kernel is chosen: the partial
     results go through the decoder's scratch and counters instead of a

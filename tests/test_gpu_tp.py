@@ -18,9 +18,12 @@ def gpu_count():
     return torch.cuda.device_count()
 
 
-def run(world, out, tmp_path, reduce=1):
+def run(world, out, tmp_path, reduce=1, shape=""):
     env = dict(os.environ)
     env["VX_TEST_TP_REDUCE"] = str(reduce)
+    env["VX_TEST_TP_SHAPE"] = shape
+    if shape == "one_launch":
+        env["VXB_STEP_KERNEL"] = "1"
     if world == 1:
         cmd = [sys.executable, WORKER, out]
     else:
@@ -43,6 +46,15 @@ def test_two_ranks_decode_the_tokens_of_one(tmp_path):
     nccl = run(2, str(tmp_path / "two_nccl.json"), tmp_path, reduce=0)
     assert one == pushed, "partials pushed through peer memory"
     assert one == nccl, "partials summed by NCCL"
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_two_ranks_with_the_step_as_one_launch(tmp_path):
+    """One sequence: every rank runs its slice of the step as one cooperative
+    launch, and the partial sums cross inside it."""
+    one = run(1, str(tmp_path / "one.json"), tmp_path, shape="one_launch")
+    two = run(2, str(tmp_path / "two.json"), tmp_path, shape="one_launch")
+    assert one == two
 
 
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")

@@ -15,6 +15,11 @@ from vx_b200 import collective, llama  # noqa: E402
 
 SHAPE = dict(dim=512, hidden=1408, n_layers=4, q_heads=8, kv_heads=4,
              head_dim=64, vocab=4096)
+BATCH = 2
+if os.environ.get("VX_TEST_TP_SHAPE") == "one_launch":
+    # one sequence and heads of 128 values: the step is one cooperative launch
+    SHAPE = dict(SHAPE, head_dim=128)
+    BATCH = 1
 
 
 def main():
@@ -24,18 +29,21 @@ def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     if world > 1:
         collective.join_job(rank, world)
-    dec, _ = llama.nn_bf16_model(max_seq=96, batch=2, tp_rank=rank,
+    dec, _ = llama.nn_bf16_model(max_seq=96, batch=BATCH, tp_rank=rank,
                                  tp_ranks=world,
                                  tp_reduce=int(os.environ.get("VX_TEST_TP_REDUCE", "1")),
                                  **SHAPE)
-    prompts = np.random.default_rng(8).integers(0, SHAPE["vocab"], (2, 24))
+    prompts = np.random.default_rng(8).integers(0, SHAPE["vocab"], (BATCH, 24))
     tokens = []
     for p in range(prompts.shape[1]):
         toks = dec.step(list(prompts[:, p]))
     for _ in range(24):
         tokens.append(list(toks))
         toks = dec.step(None)
+    per_step = dec.kernels_per_step
     dec.close()
+    if BATCH == 1:
+        assert per_step <= 6, "the step did not run as one launch"
     from vx_b200 import ops
     assert ops.kernel_status() == 0, "a bounded wait gave up"
     if world > 1:

@@ -220,6 +220,14 @@ struct vx_decoder {
   std::map<int, cudaGraphExec_t> graphs;
   int kernels_per_step;
   void *owned_weights; /* a checkpoint this decoder loaded itself, or NULL */
+  /* one sequence, bf16 weights, heads of 128 values: all layers and the logits
+     of a step are one cooperative launch (step_kernel.cu) */
+  bool one_kernel;
+  vxb::StepOp *step_ops;
+  int n_step_ops;
+  float *step_scratch;
+  int32_t *arrivals;
+  unsigned long long *step_trace; /* VXB_STEP_TRACE=1: clock readings of the last step */
 };
 
 namespace {
@@ -325,7 +333,153 @@ const float *normed(vx_decoder *d, const void *norm_w, int &launches) {
 }
 
 /* Queue one token on d->stream. */
+/* The projections of a step in the order they run (step_kernel.cu). */
+void build_step_ops(vx_decoder *d) {
+  const vx_decoder_config &c = d->c;
+  const int hd = c.head_dim;
+  const int64_t rb = (int64_t)c.dim * 2; /* bytes of a row of dim bf16 values */
+  std::vector<vxb::StepOp> ops;
+  for (int l = 0; l < c.n_layers; ++l) {
+    vxb::StepOp q{};
+    q.kind = vxb::kStepQkv;
+    q.w0 = d->wq[l];
+    q.w1 = d->wk[l] ? d->wk[l] : (const char *)d->wq[l] + (int64_t)d->q_local * hd * rb;
+    q.w2 = d->wv[l] ? d->wv[l]
+                    : (const char *)d->wq[l] +
+                          (int64_t)(d->q_local + d->kv_local) * hd * rb;
+    q.norm_w = d->attn_norm[l];
+    q.bias = d->bqkv[l];
+    q.x = d->x;
+    q.k_cache = d->k_cache + l * d->cache_layer_stride;
+    q.v_cache = d->v_cache + l * d->cache_layer_stride;
+    q.rows = (d->q_local + 2 * d->kv_local) * hd;
+    q.items = q.rows / 2;
+    q.cols = c.dim;
+    ops.push_back(q);
+    vxb::StepOp o{};
+    o.kind = vxb::kStepAdd;
+    o.w0 = d->wo[l];
+    o.x = d->att;
+    o.y = d->x;
+    o.rows = c.dim;
+    o.items = (c.dim + 1) / 2;
+    o.cols = d->q_local * hd;
+    ops.push_back(o);
+    vxb::StepOp g{};
+    g.kind = vxb::kStepSwiglu;
+    g.w0 = d->w_gate[l];
+    g.w1 = d->w_up[l] ? d->w_up[l]
+                      : (const char *)d->w_gate[l] + (int64_t)d->hidden_local * rb;
+    g.norm_w = d->ffn_norm[l];
+    g.x = d->x;
+    g.y = d->h;
+    g.rows = d->hidden_local;
+    g.items = d->hidden_local;
+    g.cols = c.dim;
+    ops.push_back(g);
+    vxb::StepOp w{};
+    w.kind = vxb::kStepAdd;
+    w.w0 = d->w_down[l];
+    w.x = d->h;
+    w.y = d->x;
+    w.rows = c.dim;
+    w.items = (c.dim + 1) / 2;
+    w.cols = d->hidden_local;
+    ops.push_back(w);
+  }
+  vxb::StepOp head{};
+  head.kind = vxb::kStepStore;
+  head.w0 = d->lm_head;
+  head.norm_w = d->final_norm;
+  head.x = d->x;
+  head.y = d->logits;
+  head.rows = d->vocab_local;
+  head.items = (d->vocab_local + 1) / 2;
+  head.cols = c.dim;
+  ops.push_back(head);
+  d->n_step_ops = (int)ops.size();
+  d->step_ops = dev_alloc<vxb::StepOp>(ops.size());
+  CUDA_OK(cudaMemcpy(d->step_ops, ops.data(), ops.size() * sizeof(vxb::StepOp),
+                     cudaMemcpyHostToDevice));
+  d->step_scratch = dev_alloc<float>(vxb::step_scratch_floats(d->q_local));
+  d->arrivals = dev_alloc<int32_t>(32);
+  const char *trace = getenv("VXB_STEP_TRACE");
+  if (trace && trace[0] == '1')
+    d->step_trace = dev_alloc<unsigned long long>(ops.size() * vxb::kStepTraceSlots);
+  d->one_kernel = true;
+}
+
+/* The end of a step: the token of every sequence (agreed between the ranks of
+   a vocabulary-split model), then the positions move on. */
+void record_tail(vx_decoder *d, int launches) {
+  const vx_decoder_config &c = d->c;
+  const int B = c.batch;
+  cudaStream_t s = d->stream;
+  if (d->ranks == 1) {
+    need(vxb::argmax(d->tokens, d->logits, d->vocab_local, B, d->vocab_local, s),
+         "argmax");
+    launches += 1;
+  } else {
+    need(vxb::argmax(d->local_best, d->logits, d->vocab_local, B,
+                     d->vocab_local, s),
+         "argmax");
+    if (d->push) {
+      tp_pick_kernel<<<1, d->ranks * 32, 0, s>>>(
+          d->tokens, d->local_best, d->logits, d->vocab_local, d->vocab_offset,
+          d->pick, d->ranks, d->tp.rank, B, d->pick_epoch, d->pick_gave_up);
+      launches += 2;
+    } else {
+    best_pair_kernel<<<1, B, 0, s>>>(d->pair, d->local_best, d->logits,
+                                     d->vocab_local, d->vocab_offset);
+    vx::NcclCollective *job = vxb::nccl_job();
+    const int r = job->api()->AllGather(d->pair, d->pairs_all, (size_t)B * 2,
+                                        vx::NcclFloat32, job->comm(), s);
+    if (r)
+      stop("vx_decoder: ncclAllGather failed: %s",
+           job->api()->GetErrorString(r));
+    pick_pair_kernel<<<1, 32, 0, s>>>(d->tokens, d->pairs_all, d->ranks, B);
+    launches += 4;
+    }
+  }
+  advance_kernel<<<1, 32, 0, s>>>(d->positions, B);
+  ++launches;
+  d->kernels_per_step = launches;
+}
+
+/* One sequence: embed, then every layer and the logits in one launch. */
+void record_one_kernel_step(vx_decoder *d) {
+  const vx_decoder_config &c = d->c;
+  cudaStream_t s = d->stream;
+  need(vxb::embed(d->x, d->embed, true, d->tokens, c.dim, c.vocab, 1, c.dim, s),
+       "embed");
+  CUDA_OK(cudaMemsetAsync(d->arrivals, 0, sizeof(int32_t), s));
+  vxb::StepArgs a{};
+  a.ops = d->step_ops;
+  a.n_ops = d->n_step_ops;
+  a.q_heads = d->q_local;
+  a.kv_heads = d->kv_local;
+  a.head_dim = c.head_dim;
+  a.eps = c.eps;
+  a.cos_t = d->cos_t;
+  a.sin_t = d->sin_t;
+  a.positions = d->positions;
+  a.q = d->q;
+  a.att = d->att;
+  a.scratch = d->step_scratch;
+  a.counters = d->counters;
+  a.arrivals = d->arrivals;
+  if (d->push)
+    a.tp = d->tp;
+  a.trace = d->step_trace;
+  need(vxb::decode_step(a, s), "the step kernel");
+  record_tail(d, 2);
+}
+
 void record_step(vx_decoder *d, int max_pos) {
+  if (d->one_kernel) {
+    record_one_kernel_step(d);
+    return;
+  }
   const vx_decoder_config &c = d->c;
   const bool bf = c.weights_bf16 != 0;
   const int B = c.batch, hd = c.head_dim;
@@ -530,35 +684,7 @@ void record_step(vx_decoder *d, int max_pos) {
   need(vxb::matvec(la, s), "the logits");
   ++launches;
   }
-  if (d->ranks == 1) {
-    need(vxb::argmax(d->tokens, d->logits, d->vocab_local, B, d->vocab_local, s),
-         "argmax");
-    launches += 1;
-  } else {
-    need(vxb::argmax(d->local_best, d->logits, d->vocab_local, B,
-                     d->vocab_local, s),
-         "argmax");
-    if (d->push) {
-      tp_pick_kernel<<<1, d->ranks * 32, 0, s>>>(
-          d->tokens, d->local_best, d->logits, d->vocab_local, d->vocab_offset,
-          d->pick, d->ranks, d->tp.rank, B, d->pick_epoch, d->pick_gave_up);
-      launches += 2;
-    } else {
-    best_pair_kernel<<<1, B, 0, s>>>(d->pair, d->local_best, d->logits,
-                                     d->vocab_local, d->vocab_offset);
-    vx::NcclCollective *job = vxb::nccl_job();
-    const int r = job->api()->AllGather(d->pair, d->pairs_all, (size_t)B * 2,
-                                        vx::NcclFloat32, job->comm(), s);
-    if (r)
-      stop("vx_decoder: ncclAllGather failed: %s",
-           job->api()->GetErrorString(r));
-    pick_pair_kernel<<<1, 32, 0, s>>>(d->tokens, d->pairs_all, d->ranks, B);
-    launches += 4;
-    }
-  }
-  advance_kernel<<<1, 32, 0, s>>>(d->positions, B);
-  ++launches;
-  d->kernels_per_step = launches;
+  record_tail(d, launches);
 }
 
 cudaGraphExec_t graph_for(vx_decoder *d, int bucket) {
@@ -718,6 +844,26 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
     d->mma_scratch = dev_alloc<float>(vxb::batched_proj_scratch_floats(rows_max, B));
     d->mma = true;
   }
+  d->one_kernel = false;
+  d->step_ops = nullptr;
+  d->n_step_ops = 0;
+  d->step_scratch = nullptr;
+  d->arrivals = nullptr;
+  d->step_trace = nullptr;
+  {
+    /* Measured slower than the chain of kernels, which already fills its rings
+       ahead of each wait (7B shape, position 520: 90 against 83 us per layer;
+       an eighth of it: 40 against 27): it runs only when asked for,
+       VXB_STEP_KERNEL=1. */
+    const char *on = getenv("VXB_STEP_KERNEL");
+    int widest = c.dim > d->hidden_local ? c.dim : d->hidden_local;
+    if (d->q_local * c.head_dim > widest)
+      widest = d->q_local * c.head_dim;
+    if (B == 1 && c.weights_bf16 == 1 && !d->mma && d->fused_norm &&
+        c.head_dim == 128 && (d->ranks == 1 || d->push) &&
+        widest <= vxb::kStepMaxCols && on && on[0] == '1')
+      build_step_ops(d);
+  }
   CUDA_OK(cudaDeviceSynchronize());
   return d;
 }
@@ -745,7 +891,9 @@ void vx_decoder_destroy(vx_decoder *d) {
                   (void *)d->local_best, (void *)d->pair,
                   (void *)d->pairs_all, d->mma_xs, (void *)d->mma_scratch,
                   (void *)d->rows_x, (void *)d->rows_q, (void *)d->rows_partials,
-                  d->rows_terms, (void *)d->rows_tokens})
+                  d->rows_terms, (void *)d->rows_tokens, (void *)d->step_ops,
+                  (void *)d->step_scratch, (void *)d->arrivals,
+                  (void *)d->step_trace})
     cudaFree(p);
   cudaFree(d->owned_weights);
   cudaStreamDestroy(d->stream);
@@ -776,7 +924,7 @@ int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
   const int pos = d->host_pos;
   if (pos >= d->c.max_seq)
     stop("vx_decoder_step: position %d is past max_seq %d", pos, d->c.max_seq);
-  cudaGraphExec_t exec = graph_for(d, pos / 256);
+  cudaGraphExec_t exec = graph_for(d, d->one_kernel ? 0 : pos / 256);
   if (tokens_in)
     CUDA_OK(cudaMemcpyAsync(d->tokens, tokens_in, d->c.batch * sizeof(int32_t),
                             cudaMemcpyHostToDevice, d->stream));
@@ -1104,6 +1252,18 @@ vx_decoder *vx_decoder_from_llama2c(const char *path, int32_t batch,
 
 const float *vx_decoder_logits(const vx_decoder *d) { return d->logits; }
 void *vx_decoder_stream(const vx_decoder *d) { return (void *)d->stream; }
+int32_t vx_decoder_step_trace(vx_decoder *d, uint64_t *out, int32_t capacity) {
+  if (!d->step_trace)
+    return 0;
+  int32_t n = d->n_step_ops * vxb::kStepTraceSlots;
+  if (n > capacity)
+    n = capacity;
+  CUDA_OK(cudaStreamSynchronize(d->stream));
+  CUDA_OK(cudaMemcpy(out, d->step_trace, (size_t)n * sizeof(uint64_t),
+                     cudaMemcpyDeviceToHost));
+  return n;
+}
+
 int32_t vx_decoder_kernels_per_step(const vx_decoder *d) {
   return d->kernels_per_step;
 }

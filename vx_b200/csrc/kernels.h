@@ -214,6 +214,50 @@ struct AttnArgs {
 size_t attn_scratch_floats(int batch, int q_heads, int head_dim, int max_seq,
                            int split);
 const char *attention_decode(const AttnArgs &a, cudaStream_t stream);
+/* One decode step of one sequence (bf16 weights, heads of 128 values, RoPE
+   from tables) as ONE cooperative launch: the list of its projections in the
+   order they run, with the layer's attention after each q/k/v projection. */
+enum { kStepQkv = 1, kStepAdd = 2, kStepSwiglu = 3, kStepStore = 4 };
+constexpr int kStepMaxCols = 11264; /* the widest input a projection may have */
+struct StepOp {
+  /* bf16 rows of `cols` values. kStepQkv: the rows of the q, k and v heads;
+     kStepSwiglu: gate rows, up rows; otherwise w0 */
+  const void *w0, *w1, *w2;
+  const void *norm_w; /* bf16 RMSNorm weights applied to x first, or NULL */
+  const void *bias;   /* kStepQkv: bf16, or NULL */
+  const float *x;     /* cols values */
+  /* kStepAdd: y[r] += row r . x (summed over the ranks); kStepStore: y[r] =;
+     kStepSwiglu: y[r] = silu(gate_r . x) * (up_r . x); kStepQkv: unused (q
+     goes to StepArgs::q) */
+  float *y;
+  float *k_cache, *v_cache; /* kStepQkv: this layer's, [position][kv_heads][128] */
+  int kind;
+  int items; /* pairs of rows: kStepSwiglu rows; kStepQkv heads * 64; else ceil(rows / 2) */
+  int rows, cols;
+};
+struct StepArgs {
+  const StepOp *ops; /* device memory */
+  int n_ops;
+  int q_heads, kv_heads, head_dim; /* of this rank */
+  float eps;
+  const float *cos_t, *sin_t; /* [position][64] */
+  const int32_t *positions;   /* device: the position of this step */
+  float *q, *att;             /* q_heads * 128 values each */
+  float *scratch;             /* attention parts: step_scratch_floats() */
+  int32_t *counters;          /* attention: one per KV head tile, zero */
+  int32_t *arrivals;          /* the barrier word: zero when the kernel starts */
+  TpPush tp;                  /* ranks <= 1: no exchange; done is unused */
+  /* NULL, or kStepTraceSlots nanosecond clock readings per projection that
+     thread 0 of block 0 leaves: at the top of the loop, after the barrier,
+     after the prologue, after its warp's items, and (q/k/v) after the barrier
+     in front of attention and after attention */
+  unsigned long long *trace;
+};
+constexpr int kStepTraceSlots = 6;
+size_t step_scratch_floats(int q_heads);
+const char *decode_step(const StepArgs &a, cudaStream_t stream);
+int step_status(cudaStream_t stream);
+
 /* The process-wide choice that kAttnAuto stands for; returns the one before. */
 int attention_kernel_choice(int which);
 /* Shorthand for kernel = kAttnCluster with no scratch. */

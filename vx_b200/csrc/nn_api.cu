@@ -838,7 +838,8 @@ int32_t vx_b200_kernel_status(void) {
   const int t = vxb::tp_status(vxb::caller_stream());
   const int m = vxb::batched_proj_status(vxb::caller_stream());
   const int r = vxb::rows_status();
-  return g ? g : (f ? f : (t ? t : (m ? m : r)));
+  const int s = vxb::step_status(vxb::caller_stream());
+  return g ? g : (f ? f : (t ? t : (m ? m : (r ? r : s))));
 }
 
 int32_t vx_b200_attention_kernel(int32_t which) {

@@ -19,6 +19,7 @@
  */
 #include "kernels.h"
 #include "launch.cuh"
+#include "nn_device.cuh"
 #include "ptx.cuh"
 
 #include <cooperative_groups.h>
@@ -35,28 +36,6 @@ namespace {
 
 constexpr int WARPS = 16;            /* per block, projection kernels */
 constexpr int MAX_SMEM_X = 96 * 1024; /* x (all batch rows) staged per block */
-
-__device__ __forceinline__ float bf_lo(uint32_t u) {
-  return __uint_as_float(u << 16);
-}
-__device__ __forceinline__ float bf_hi(uint32_t u) {
-  return __uint_as_float(u & 0xffff0000u);
-}
-__device__ __forceinline__ float bf16_at(const void *p, int64_t i) {
-  return __uint_as_float((uint32_t)((const uint16_t *)p)[i] << 16);
-}
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1)
-    v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1)
-    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
 
 /* Sum over the block; every thread gets the result. `red` holds 32 floats. */
 __device__ float block_sum(float v, float *red) {
@@ -136,29 +115,50 @@ template <typename W> struct Scaled { static constexpr bool yes = false; };
 template <> struct Scaled<Fp8W> { static constexpr bool yes = true; };
 template <> struct Scaled<Q4W> { static constexpr bool yes = true; };
 
-/* The 16 weights of an fp8 word as f32 times 2^-120, exactly, two codes at a
-   time with integer instructions (the conversion instructions issue at a
-   quarter of the rate and made the kernel wait for them). The low 7 bits of a
-   code, e e e e m m m, moved to bits 10..4 of a 16-bit half are the bf16 bit
-   pattern of the code's value times 2^-120: e4m3's exponent has bias 7, bf16's
-   127, and a code with e = 0 becomes a bf16 subnormal of the right value. The
-   sign goes on top, and a half widens to f32 by sitting in the upper 16 bits.
-   The factor 2^120 is taken back with the block's scale (fma16): the sums
-   stay far inside f32's range, subnormal products are exact to 2^-149. */
-constexpr float kFp8Unscale = 1.329227995784916e36f; /* 2^120 */
+/* The 16 weights of an fp8 word as f32: two codes to two f16 with the
+   conversion instruction, and an f16 to f32 by adding it to -0.0f in a
+   mixed-precision add, which issues with the other additions (a conversion to
+   f32 for every weight made the kernel wait for the conversion unit, and
+   building bf16 bit patterns with integer operations took more instructions:
+   3 560, 3 380 and 2 850 GB/s on the 7B gate/up projection). */
+__device__ __forceinline__ float widen_f16(unsigned short h) {
+  float d;
+  asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(h), "f"(-0.0f));
+  return d;
+}
 __device__ __forceinline__ void unpack_fp8(const uint4 &wv, float (&wf)[16]) {
   const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
+    unsigned short lo, hi;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(u[j]));
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      /* codes 2h and 2h+1 into the high bytes of the two halves */
-      const uint32_t x = __byte_perm(u[j], 0, h == 0 ? 0x1404 : 0x3424);
-      const uint32_t y = ((x >> 4) & 0x07F007F0u) | (x & 0x80008000u);
-      wf[4 * j + 2 * h] = __uint_as_float(y << 16);
-      wf[4 * j + 2 * h + 1] = __uint_as_float(y & 0xFFFF0000u);
+      uint32_t two;
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(two) : "h"(h == 0 ? lo : hi));
+      unsigned short a, b;
+      asm("mov.b32 {%0, %1}, %2;" : "=h"(a), "=h"(b) : "r"(two));
+      wf[4 * j + 2 * h] = widen_f16(a);
+      wf[4 * j + 2 * h + 1] = widen_f16(b);
     }
   }
+}
+/* d += a * b on two values at once (one instruction on sm_100) */
+__device__ __forceinline__ void fma_pair(float2 &d, const float2 a, const float2 b) {
+  unsigned long long dd = *reinterpret_cast<unsigned long long *>(&d);
+  asm("fma.rn.f32x2 %0, %1, %2, %0;"
+      : "+l"(dd)
+      : "l"(*reinterpret_cast<const unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<const unsigned long long *>(&b)));
+  d = *reinterpret_cast<float2 *>(&dd);
+}
+__device__ __forceinline__ float2 add_pair(const float2 a, const float2 b) {
+  unsigned long long dd;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(dd)
+      : "l"(*reinterpret_cast<const unsigned long long *>(&a)),
+        "l"(*reinterpret_cast<const unsigned long long *>(&b)));
+  return *reinterpret_cast<float2 *>(&dd);
 }
 __device__ __forceinline__ void unpack_q4(const uint4 &wv, float (&wf)[32]) {
   /* 0x4B000000 | c is the float 2^23 + c for c below 2^23, so a nibble left
@@ -166,17 +166,27 @@ __device__ __forceinline__ void unpack_q4(const uint4 &wv, float (&wf)[32]) {
      2^23 + 8 * 16^t leaves 16^t (c - 8), exactly: wf[8j + 4h + t] is the
      weight times 16^t, and fma16 takes the factor off the sums (the
      reference takes it off x, nn.vx:1659-1661). The upper four nibbles of a
-     32-bit word are shifted down first. */
+     32-bit word are shifted down first. Places t and t + 1 go through the
+     subtraction as a pair. */
   const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const uint32_t lo = u[j], hi = u[j] >> 16;
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const uint32_t mask = 15u << (4 * t);
-      const float off = 8388608.0f + 8.0f * (float)(1 << (4 * t));
-      wf[8 * j + t] = __uint_as_float((lo & mask) | 0x4B000000u) - off;
-      wf[8 * j + 4 + t] = __uint_as_float((hi & mask) | 0x4B000000u) - off;
+    for (int t = 0; t < 4; t += 2) {
+      const uint32_t m0 = 15u << (4 * t), m1 = 15u << (4 * t + 4);
+      const float2 off = make_float2(-(8388608.0f + 8.0f * (float)(1 << (4 * t))),
+                                     -(8388608.0f + 8.0f * (float)(1 << (4 * t + 4))));
+      const float2 a = add_pair(make_float2(__uint_as_float((lo & m0) | 0x4B000000u),
+                                            __uint_as_float((lo & m1) | 0x4B000000u)),
+                                off);
+      const float2 b = add_pair(make_float2(__uint_as_float((hi & m0) | 0x4B000000u),
+                                            __uint_as_float((hi & m1) | 0x4B000000u)),
+                                off);
+      wf[8 * j + t] = a.x;
+      wf[8 * j + t + 1] = a.y;
+      wf[8 * j + 4 + t] = b.x;
+      wf[8 * j + 4 + t + 1] = b.y;
     }
   }
 }
@@ -206,24 +216,29 @@ fma16(const uint4 &wv, const float (&xv)[B][PerWord<W>::n], float (&acc)[B],
   if constexpr (E == 32) {
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      float part[4] = {0.0f, 0.0f, 0.0f, 0.0f}; /* by nibble place */
+      float2 p01 = make_float2(0.0f, 0.0f), p23 = p01; /* by nibble place */
 #pragma unroll
-      for (int e = 0; e < E; ++e)
-        part[e & 3] = fmaf(wf[e], xv[b][e], part[e & 3]);
-      const float dot = fmaf(part[3], 1.0f / 4096.0f,
-                             fmaf(part[2], 1.0f / 256.0f,
-                                  fmaf(part[1], 1.0f / 16.0f, part[0])));
+      for (int e = 0; e < E; e += 4) {
+        fma_pair(p01, make_float2(wf[e], wf[e + 1]),
+                 make_float2(xv[b][e], xv[b][e + 1]));
+        fma_pair(p23, make_float2(wf[e + 2], wf[e + 3]),
+                 make_float2(xv[b][e + 2], xv[b][e + 3]));
+      }
+      const float dot = fmaf(p23.y, 1.0f / 4096.0f,
+                             fmaf(p23.x, 1.0f / 256.0f,
+                                  fmaf(p01.y, 1.0f / 16.0f, p01.x)));
       acc[b] = fmaf(dot, scale, acc[b]);
     }
   } else if constexpr (Scaled<W>::yes) {
-    const float unscale = scale * kFp8Unscale; /* exact: a power of two */
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      float dot = 0.0f;
+      float2 d2 = make_float2(0.0f, 0.0f); /* even and odd weights apart */
 #pragma unroll
-      for (int e = 0; e < E; ++e)
-        dot = fmaf(wf[e], xv[b][e], dot);
-      acc[b] = fmaf(dot, unscale, acc[b]);
+      for (int e = 0; e < E; e += 2)
+        fma_pair(d2, make_float2(wf[e], wf[e + 1]),
+                 make_float2(xv[b][e], xv[b][e + 1]));
+      const float dot = d2.x + d2.y;
+      acc[b] = fmaf(dot, scale, acc[b]);
     }
   } else {
 #pragma unroll
@@ -232,46 +247,6 @@ fma16(const uint4 &wv, const float (&xv)[B][PerWord<W>::n], float (&acc)[B],
       for (int e = 0; e < E; ++e)
         acc[b] = fmaf(wf[e], xv[b][e], acc[b]);
   }
-}
-
-/* The pushed exchange moves (value, call) pairs: an aligned 8-byte store
-   arrives whole, so a pair that carries the expected call number is complete
-   and is its own arrival flag. An item's two rows travel as two pairs in one
-   16-byte store; each half is still checked by its own call number. Stores
-   and loads bypass L1 (volatile): a pair is seen when it arrives. */
-__device__ __forceinline__ void pair_store(TpPair *at, float v, int call) {
-  asm volatile("st.volatile.global.v2.b32 [%0], {%1, %2};" ::"l"(at),
-               "r"(__float_as_uint(v)), "r"(call)
-               : "memory");
-}
-__device__ __forceinline__ void pair2_store(TpPair *at, float v0, float v1,
-                                            int call) {
-  asm volatile("st.volatile.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(at),
-               "r"(__float_as_uint(v0)), "r"(call), "r"(__float_as_uint(v1)),
-               "r"(call)
-               : "memory");
-}
-__device__ __forceinline__ bool pair_load(const TpPair *at, int call, float &v) {
-  uint32_t bits;
-  int seen;
-  asm volatile("ld.volatile.global.v2.b32 {%0, %1}, [%2];"
-               : "=r"(bits), "=r"(seen)
-               : "l"(at)
-               : "memory");
-  v = __uint_as_float(bits);
-  return seen == call;
-}
-__device__ __forceinline__ bool pair2_load(const TpPair *at, int call, float &v0,
-                                           float &v1) {
-  uint32_t b0, b1;
-  int c0, c1;
-  asm volatile("ld.volatile.global.v4.b32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(b0), "=r"(c0), "=r"(b1), "=r"(c1)
-               : "l"(at)
-               : "memory");
-  v0 = __uint_as_float(b0);
-  v1 = __uint_as_float(b1);
-  return c0 == call && c1 == call;
 }
 
 /* The two weight rows of an item (byte addresses), where their scales are,
@@ -934,303 +909,6 @@ __global__ void rope_store_kernel(float *q_out, float *k_cache, float *v_cache,
     k_cache[at] =
         __fadd_rn(__fmul_rn(kh[i], c), __fmul_rn(__fmul_rn(sign, kh[partner]), s));
     v_cache[at] = v[g * hd + i];
-  }
-}
-
-/* ------------------------------------------------------ decode attention
- * nn_attention with its parts and merge (nn.vx:349-866), and the attention
- * loops of llama2.vx:295-358.  A block owns one KV head, one run of `split`
- * positions and up to GH query heads that share the KV head; each warp takes
- * every fourth position, its lanes hold four values of head_dim each, keeps a
- * running (max, sum, weighted V) per query head, and the four warps are merged
- * in warp order.  The block that finishes last for a (sequence, head tile)
- * merges the parts of all splits in split order. */
-/* What the ATT_WARPS warps of one unit share. */
-template <int GH, int ATT_WARPS> struct AttnShared {
-  float m[ATT_WARPS][GH], l[ATT_WARPS][GH];
-  __align__(16) float acc[ATT_WARPS][GH][128];
-  int is_last;
-};
-template <int ATT_WARPS> __device__ __forceinline__ void sync_unit_warps(int bar_id) {
-  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(ATT_WARPS * 32) : "memory");
-}
-
-/* One unit of work: (split, KV head and head tile `y`, sequence b), done by the
-   ATT_WARPS warps (4, 8 or 16: as many as fill the GPU for the number of heads
-   there are) that meet at named barrier `bar_id`. CHAINED: the caller is a
-   kernel of its own in a chain of dependent launches. */
-template <int GH, bool CHAINED, int CL, int ATT_WARPS>
-__device__ __forceinline__ void
-attention_unit(const AttnArgs &a, int split_idx, int y, int b, int warp,
-               int lane, AttnShared<GH, ATT_WARPS> &sh, int bar_id) {
-  /* The position was written by the step before this one, and every cache row
-     below it by earlier steps: those may be read before the kernels of this
-     step have finished. Row `pos` and q come from the kernel just before. */
-  const int hd = a.head_dim, hd4 = hd / 4;
-  const int group = a.q_heads / a.kv_heads;
-  const int tiles = (group + GH - 1) / GH;
-  const int g = y / tiles, tile = y - g * tiles;
-  const int h0 = g * group + tile * GH;
-  const int nh = min(GH, group - tile * GH);
-  const int pos = a.positions[b];
-  /* CL > 0: the unit is one block of a cluster of CL that covers the whole
-     head; block r takes the r-th run of ceil((pos + 1) / CL) positions (maybe
-     none), and the runs are merged through distributed shared memory. */
-  const int run = CL > 0 ? (pos + CL) / CL : a.split;
-  const int t_begin = split_idx * run;
-  if (CL == 0 && t_begin > pos)
-    return;
-  const int t_end = max(t_begin, min(t_begin + run, pos + 1));
-  const int splits = pos / a.split + 1;
-  const float scale = 1.0f / sqrtf((float)hd);
-  const bool active = lane < hd4;
-
-  const float *kc = a.k_cache + b * a.cache_batch_stride;
-  const float *vc = a.v_cache + b * a.cache_batch_stride;
-  const float *qb = a.q + (int64_t)b * a.q_heads * hd;
-
-  /* Cache rows below `settled` were written by earlier steps and may be read
-     before the kernels of this step have finished; the rest only after. */
-  const int settled = !a.rows_settled ? 0
-                      : a.fresh_from  ? min(pos, a.fresh_from[0])
-                                      : pos;
-  /* A warp takes every ATT_WARPS-th position, NB of them at a time so that
-     their loads are in flight together: with 32 positions per block of four
-     warps that is one round trip to memory per warp. */
-  constexpr int NB = 8;
-  float4 kv[NB], vv[NB];
-  auto load_batch = [&](int t0, bool old_rows_only) {
-#pragma unroll
-    for (int j = 0; j < NB; ++j) {
-      const int t = t0 + j * ATT_WARPS;
-      const bool take = active && t < t_end &&
-                        (old_rows_only ? t < settled
-                                       : t >= settled || t0 != t_begin + warp || !CHAINED);
-      if (take) {
-        const int64_t row = ((int64_t)t * a.kv_heads + g) * hd + lane * 4;
-        kv[j] = *reinterpret_cast<const float4 *>(kc + row);
-        vv[j] = *reinterpret_cast<const float4 *>(vc + row);
-      } else if (!old_rows_only && !(active && t < t_end)) {
-        kv[j] = vv[j] = make_float4(0, 0, 0, 0);
-      }
-    }
-  };
-#pragma unroll
-  for (int j = 0; j < NB; ++j)
-    kv[j] = vv[j] = make_float4(0, 0, 0, 0);
-  if (CHAINED) {
-    load_batch(t_begin + warp, true);
-    chain_wait();
-  }
-  load_batch(t_begin + warp, false); /* CHAINED: only row `pos`, if it is here */
-
-  float4 qv[GH];
-  float m[GH], l[GH];
-  float4 acc[GH];
-#pragma unroll
-  for (int h = 0; h < GH; ++h) {
-    /* q is rewritten for every layer: read it past L1, which may still hold
-       the layer before when the layers share a kernel */
-    qv[h] = (active && h < nh)
-                ? __ldcg(reinterpret_cast<const float4 *>(qb + (h0 + h) * hd +
-                                                          lane * 4))
-                : make_float4(0, 0, 0, 0);
-    m[h] = -3.0e38f;
-    l[h] = 0.0f;
-    acc[h] = make_float4(0, 0, 0, 0);
-  }
-
-  for (int t0 = t_begin + warp; t0 < t_end; t0 += NB * ATT_WARPS) {
-    if (t0 != t_begin + warp)
-      load_batch(t0, false);
-#pragma unroll
-    for (int h = 0; h < GH; ++h) {
-      float d[NB];
-#pragma unroll
-      for (int j = 0; j < NB; ++j) {
-        d[j] = qv[h].x * kv[j].x;
-        d[j] = fmaf(qv[h].y, kv[j].y, d[j]);
-        d[j] = fmaf(qv[h].z, kv[j].z, d[j]);
-        d[j] = fmaf(qv[h].w, kv[j].w, d[j]);
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-        for (int j = 0; j < NB; ++j)
-          d[j] += __shfl_xor_sync(0xffffffffu, d[j], o);
-#pragma unroll
-      for (int j = 0; j < NB; ++j) {
-        if (t0 + j * ATT_WARPS >= t_end)
-          continue;
-        const float s = d[j] * scale;
-        const float mn = fmaxf(m[h], s);
-        const float fix = expf(m[h] - mn);
-        const float pw = expf(s - mn);
-        l[h] = l[h] * fix + pw;
-        acc[h].x = acc[h].x * fix + pw * vv[j].x;
-        acc[h].y = acc[h].y * fix + pw * vv[j].y;
-        acc[h].z = acc[h].z * fix + pw * vv[j].z;
-        acc[h].w = acc[h].w * fix + pw * vv[j].w;
-        m[h] = mn;
-      }
-    }
-  }
-
-  /* ---- merge the warps, in warp order ---- */
-  float (&sm_m)[ATT_WARPS][GH] = sh.m;
-  float (&sm_l)[ATT_WARPS][GH] = sh.l;
-  float (&sm_acc)[ATT_WARPS][GH][128] = sh.acc;
-  int &is_last = sh.is_last;
-#pragma unroll
-  for (int h = 0; h < GH; ++h) {
-    if (lane == 0) {
-      sm_m[warp][h] = m[h];
-      sm_l[warp][h] = l[h];
-    }
-    if (active)
-      *reinterpret_cast<float4 *>(&sm_acc[warp][h][lane * 4]) = acc[h];
-  }
-  sync_unit_warps<ATT_WARPS>(bar_id);
-  const int row_floats = hd + 2;
-  float *part = a.scratch;
-  auto part_at = [&](int head, int sp) {
-    return part + (((int64_t)b * a.q_heads + head) * (a.max_pos / a.split + 1) +
-                   sp) * row_floats;
-  };
-  if (CL > 0) {
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    if (warp == 0) {
-      /* the block's part, left in row 0 of its own shared arrays */
-      for (int h = 0; h < nh; ++h) {
-        float big = -3.0e38f;
-        for (int w = 0; w < ATT_WARPS; ++w)
-          big = fmaxf(big, sm_m[w][h]);
-        float total = 0.0f;
-        float4 o = make_float4(0, 0, 0, 0);
-        for (int w = 0; w < ATT_WARPS; ++w) {
-          const float f = expf(sm_m[w][h] - big);
-          total += f * sm_l[w][h];
-          if (active) {
-            const float4 v =
-                *reinterpret_cast<const float4 *>(&sm_acc[w][h][lane * 4]);
-            o.x += f * v.x; o.y += f * v.y; o.z += f * v.z; o.w += f * v.w;
-          }
-        }
-        __syncwarp();
-        if (active)
-          *reinterpret_cast<float4 *>(&sm_acc[0][h][lane * 4]) = o;
-        if (lane == 0) {
-          sm_m[0][h] = big;
-          sm_l[0][h] = total;
-        }
-      }
-    }
-    cluster.sync();
-    if (cluster.block_rank() == 0) {
-      /* block 0 merges the runs in order: warp h takes head h */
-      for (int h = warp; h < nh; h += ATT_WARPS) {
-        constexpr int NP = CL > 0 ? CL : 1; /* CL == 0 never gets here */
-        float pm[NP], pl[NP];
-        float4 pa[NP];
-#pragma unroll
-        for (int r = 0; r < CL; ++r) {
-          const AttnShared<GH, ATT_WARPS> *peer = cluster.map_shared_rank(&sh, r);
-          pm[r] = peer->m[0][h];
-          pl[r] = peer->l[0][h];
-          pa[r] = active
-                      ? *reinterpret_cast<const float4 *>(&peer->acc[0][h][lane * 4])
-                      : make_float4(0, 0, 0, 0);
-        }
-        float big = -3.0e38f;
-#pragma unroll
-        for (int r = 0; r < CL; ++r)
-          big = fmaxf(big, pm[r]);
-        float total = 0.0f;
-        float4 o = make_float4(0, 0, 0, 0);
-#pragma unroll
-        for (int r = 0; r < CL; ++r) {
-          const float f = expf(pm[r] - big);
-          total += f * pl[r];
-          o.x += f * pa[r].x; o.y += f * pa[r].y;
-          o.z += f * pa[r].z; o.w += f * pa[r].w;
-        }
-        if (active) {
-          float *dst = a.out + ((int64_t)b * a.q_heads + h0 + h) * hd + lane * 4;
-          *reinterpret_cast<float4 *>(dst) =
-              make_float4(o.x / total, o.y / total, o.z / total, o.w / total);
-        }
-      }
-    }
-    cluster.sync(); /* nobody leaves while block 0 may still read its part */
-    return;
-  }
-  if (warp == 0) {
-    for (int h = 0; h < nh; ++h) {
-      float big = -3.0e38f;
-      for (int w = 0; w < ATT_WARPS; ++w)
-        big = fmaxf(big, sm_m[w][h]);
-      float total = 0.0f;
-      float4 o = make_float4(0, 0, 0, 0);
-      for (int w = 0; w < ATT_WARPS; ++w) {
-        const float f = expf(sm_m[w][h] - big);
-        total += f * sm_l[w][h];
-        if (active) {
-          const float4 v = *reinterpret_cast<const float4 *>(&sm_acc[w][h][lane * 4]);
-          o.x += f * v.x; o.y += f * v.y; o.z += f * v.z; o.w += f * v.w;
-        }
-      }
-      /* A part row has head_dim + 2 floats, so rows are 8-byte aligned only. */
-      float *dst = part_at(h0 + h, split_idx);
-      if (active) {
-        *reinterpret_cast<float2 *>(dst + lane * 4) = make_float2(o.x, o.y);
-        *reinterpret_cast<float2 *>(dst + lane * 4 + 2) = make_float2(o.z, o.w);
-      }
-      if (lane == 0) {
-        dst[hd] = big;
-        dst[hd + 1] = total;
-      }
-    }
-    __threadfence();
-    __syncwarp();
-    if (lane == 0) {
-      int32_t *counter = a.counters + (int64_t)b * a.kv_heads * tiles + y;
-      const int seen = atomicAdd(counter, 1);
-      is_last = seen == splits - 1;
-      if (is_last)
-        *counter = 0; /* ready for the next launch */
-    }
-  }
-  sync_unit_warps<ATT_WARPS>(bar_id);
-  if (!is_last)
-    return;
-  __threadfence();
-
-  /* ---- the last block of this head tile merges the splits, in order ---- */
-  for (int h = warp; h < nh; h += ATT_WARPS) {
-    float big = -3.0e38f;
-    for (int sp = lane; sp < splits; sp += 32)
-      big = fmaxf(big, __ldcg(part_at(h0 + h, sp) + hd));
-    big = warp_max(big);
-    float total = 0.0f;
-    float4 o = make_float4(0, 0, 0, 0);
-#pragma unroll 8
-    for (int sp = 0; sp < splits; ++sp) {
-      const float *src = part_at(h0 + h, sp);
-      const float f = expf(__ldcg(src + hd) - big);
-      total += f * __ldcg(src + hd + 1);
-      if (active) {
-        const float2 va = __ldcg(reinterpret_cast<const float2 *>(src + lane * 4));
-        const float2 vb =
-            __ldcg(reinterpret_cast<const float2 *>(src + lane * 4 + 2));
-        o.x += f * va.x; o.y += f * va.y; o.z += f * vb.x; o.w += f * vb.y;
-      }
-    }
-    if (active) {
-      float *dst = a.out + ((int64_t)b * a.q_heads + h0 + h) * hd + lane * 4;
-      *reinterpret_cast<float4 *>(dst) =
-          make_float4(o.x / total, o.y / total, o.z / total, o.w / total);
-    }
   }
 }
 

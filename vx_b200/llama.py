@@ -111,8 +111,21 @@ class Decoder:
     def stream(self):
         return lib().vx_decoder_stream(self.handle)
 
+    def step_trace(self):
+        """[projections, 6] uint64 nanosecond readings of the last step (a
+        decoder made with VXB_STEP_TRACE=1 whose step is one launch), else
+        None."""
+        if not self.handle:
+            raise ValueError("the decoder is closed")
+        out = np.zeros(6 * (4 * self.cfg.n_layers + 1), np.uint64)
+        n = lib().vx_decoder_step_trace(self.handle,
+                                        out.ctypes.data_as(C.c_void_p), out.size)
+        return out[:n].reshape(-1, 6) if n else None
+
     @property
     def kernels_per_step(self):
+        if not self.handle:
+            raise ValueError("the decoder is closed")
         return lib().vx_decoder_kernels_per_step(self.handle)
 
     def close(self):
