@@ -572,11 +572,30 @@ rowdot_kernel(const RowDotParams p) {
     fma16<W, B>(wb, xv, s1, scale_b);
   };
 
+  /* One sequence: what lane 0's epilogue reads from global memory -- the
+     residual an item is added to, or the cosine and sine of its pair -- is
+     asked for when the item begins, so that the trip to L2 runs under the
+     item's weights instead of after them. */
+  float pre0 = 0.0f, pre1 = 0.0f;
+  const int pos_first = (B == 1 && EPI == EPI_QKV) ? p.positions[0] : 0;
   int next_item = first, next_ch = 0, next_stage = 0;
   uint32_t next_phase = 0;
   for (int u = 0; u < units; ++u) {
     const int item = next_item, ch = next_ch, s = next_stage;
     const uint32_t phase = next_phase;
+    if (B == 1 && ch == 0 && lane == 0) {
+      if (EPI == EPI_ADD || EPI == EPI_PUSH) {
+        pre0 = p.y[2 * item];
+        pre1 = 2 * item + 1 < p.rows ? p.y[2 * item + 1] : 0.0f;
+      } else if (EPI == EPI_QKV && p.rope_mode == 0) {
+        const int half = p.head_dim / 2;
+        const int h = item / half;
+        if (h < p.q_heads + p.kv_heads) {
+          pre0 = p.cos_t[(int64_t)pos_first * p.cs_cols + item - h * half];
+          pre1 = p.sin_t[(int64_t)pos_first * p.cs_cols + item - h * half];
+        }
+      }
+    }
     if (++next_ch == nch) {
       next_ch = 0;
       ++next_item;
@@ -662,8 +681,8 @@ rowdot_kernel(const RowDotParams p) {
           }
         }
         float *y = p.y + b * p.y_stride;
-        float s0v = lane == 0 ? y[ra] : 0.0f;
-        float s1v = (lane == 0 && r1) ? y[ra + 1] : 0.0f;
+        float s0v = lane == 0 ? (B == 1 ? pre0 : y[ra]) : 0.0f;
+        float s1v = (lane == 0 && r1) ? (B == 1 ? pre1 : y[ra + 1]) : 0.0f;
         for (int r = 0; r < p.tp.ranks; ++r) {
           s0v += __shfl_sync(0xffffffffu, v0, r);
           s1v += __shfl_sync(0xffffffffu, v1, r);
@@ -688,9 +707,12 @@ rowdot_kernel(const RowDotParams p) {
         float v0 = t0[b], v1 = t1[b];
         if (EPI == EPI_ADD) {
           const float scale = p.add_scale ? (expert_ok ? p.add_scale[0] : 0.0f) : 1.0f;
-          v0 = p.add_scale ? fmaf(scale, v0, y[ra]) : y[ra] + v0;
-          if (r1)
-            v1 = p.add_scale ? fmaf(scale, v1, y[rb]) : y[rb] + v1;
+          const float ya = B == 1 ? pre0 : y[ra];
+          v0 = p.add_scale ? fmaf(scale, v0, ya) : ya + v0;
+          if (r1) {
+            const float yb = B == 1 ? pre1 : y[rb];
+            v1 = p.add_scale ? fmaf(scale, v1, yb) : yb + v1;
+          }
         } else if (EPI == EPI_BIAS) {
           v0 += bf16_at(p.bias, ra);
           if (r1)
@@ -726,8 +748,8 @@ rowdot_kernel(const RowDotParams p) {
         float c, s;
         if (p.rope_mode == 0) {
           /* nn_rope_and_store (nn.vx:245-280) */
-          c = p.cos_t[(int64_t)pos * p.cs_cols + idx];
-          s = p.sin_t[(int64_t)pos * p.cs_cols + idx];
+          c = B == 1 ? pre0 : p.cos_t[(int64_t)pos * p.cs_cols + idx];
+          s = B == 1 ? pre1 : p.sin_t[(int64_t)pos * p.cs_cols + idx];
         } else {
           /* llama2.vx:264-293 with rope_freq (llama_rt.vx:82-85): the CPU
              functions are correctly rounded, so go through double. */
