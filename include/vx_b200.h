@@ -228,17 +228,33 @@ void vx_decoder_reset(vx_decoder *d);
    the call then waits for the GPU. Returns the position the step ran at. */
 int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
                         int32_t *tokens_out);
-/* A run of prompt tokens of a one-sequence decoder, sixteen positions per
-   pass through the layers (the reference's multi-row kernels, nn.vx:2317-3066:
-   its llama programs feed a prompt one decode step at a time). Fills the KV
-   cache and advances the position; computes no logits, so the caller gives
-   the last prompt token to vx_decoder_step. Returns how many tokens it took
-   (a multiple of 16, the rest is the caller's to step through), or -1 with
-   vx_b200_last_error() for a decoder that cannot (needs batch 1, one rank,
-   bf16 weights, head_dim 128, widths in multiples of 64). */
+/* A run of prompt tokens of a one-sequence decoder, all positions in one pass
+   through the layers as rows of tensor-core GEMMs (the reference's multi-row
+   kernels, nn.vx:2317-3066: its llama programs feed a prompt one decode step
+   at a time). Fills the KV cache and advances the position; computes no
+   logits, so the caller gives the last prompt token to vx_decoder_step.
+   Returns how many tokens it took (all of them, or 0 when there are fewer
+   than 32: the caller steps through those), or -1 with vx_b200_last_error()
+   for a decoder that cannot (needs batch 1, one rank, bf16 weights with the
+   q/k/v rows in one matrix and the gate/up rows in one, head_dim 128, widths
+   in multiples of 64). */
 int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count);
 /* The logits of the last step: device memory, [batch, vocab] f32. */
 const float *vx_decoder_logits(const vx_decoder *d);
+/* The K (which = 0) or V (which = 1) cache of this rank: device memory, f32
+   [layer][sequence][max_seq][kv_heads][head_dim], vx_decoder_kv_cache_bytes()
+   bytes each. What a prefill process hands to a decode process
+   (handoff_kv, tests/backend/pass/llama2.vx:431-458: the caches travel by
+   vx_plugin_transfer_peer). */
+float *vx_decoder_kv_cache(vx_decoder *d, int32_t which);
+int64_t vx_decoder_kv_cache_bytes(const vx_decoder *d);
+/* The receiving side of that hand-off: copies rows 0 .. positions-1 of every
+   layer and sequence from k and v (device memory laid out like this decoder's
+   own caches; on this GPU or on another one of the process) into the
+   decoder's caches and puts every sequence at `positions`. Returns positions,
+   or -1 with vx_b200_last_error(). k and v may be freed when it returns. */
+int32_t vx_decoder_adopt_kv(vx_decoder *d, const float *k, const float *v,
+                            int32_t positions);
 /* The CUDA stream (a CUstream) that the decoder's steps run on, for a host
    that wants to record events around them. */
 void *vx_decoder_stream(const vx_decoder *d);

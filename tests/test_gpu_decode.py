@@ -158,6 +158,51 @@ def test_one_launch_step_matches_the_oracle_and_the_separate_kernels(
         assert np.abs(a - b).max() <= 1e-5 * np.abs(b).max()
 
 
+def test_kv_cache_handed_from_a_prefill_decoder_to_a_decode_decoder(oracle):
+    """The disaggregated prefill/decode of the reference's llama program
+    (handoff_kv, tests/backend/pass/llama2.vx:431-458): one decoder reads the
+    prompt, its K and V caches travel through vx_plugin_transfer_peer, and a
+    second decoder that never saw the prompt goes on from them. The transfer
+    carries the result: with zeroed caches handed over the tokens differ."""
+    from vx_b200 import abi
+    from vx_b200.lib import lib
+    max_seq = 96
+    pre, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=1, **SMALL_NN)
+    dec, _ = llama.nn_bf16_model(max_seq=max_seq, batch=1, **SMALL_NN)
+    hm = nn_host_model(oracle, tensors, SMALL_NN, max_seq)
+    prompt = [int(t) for t in np.random.default_rng(12).integers(0, SMALL_NN["vocab"], 30)]
+    steps = 20
+    want = oracle_generate(oracle, hm, prompt, steps, max_seq)
+    for t in prompt[:-1]:
+        pre.step([t], fetch=False)
+    first = pre.step([prompt[-1]])[0]
+    nbytes = pre.kv_cache_bytes
+    assert nbytes == dec.kv_cache_bytes == 4 * SMALL_NN["n_layers"] * max_seq * \
+        SMALL_NN["kv_heads"] * SMALL_NN["head_dim"]
+
+    def go_on(k, v):
+        dec.adopt_kv(k, v, len(prompt))
+        got, tok = [], first
+        for _ in range(steps):
+            got.append(tok)
+            tok = dec.step([tok])[0]
+        return got
+
+    here = abi.home_gpu()
+    k = lib().vx_plugin_transfer_peer(pre.kv_cache(0), here, here, nbytes)
+    v = lib().vx_plugin_transfer_peer(pre.kv_cache(1), here, here, nbytes)
+    pre.close()                        # the prefill side is gone: only k, v remain
+    got = go_on(k, v)
+    lib().vx_plugin_free(k, here)
+    lib().vx_plugin_free(v, here)
+    assert got == want, report(got, want)
+
+    zeros = abi.DeviceTensor.from_host(np.zeros(nbytes // 4, np.float32))
+    assert go_on(zeros.ptr, zeros.ptr) != want
+    zeros.free()
+    dec.close()
+
+
 def test_nn_decoder_with_the_split_attention_kernel(oracle):
     """The decoder recorded while the split kernel is chosen: the partial
     results go through the decoder's scratch and counters instead of a

@@ -107,3 +107,48 @@ print("both GPUs ok")
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
                        timeout=600)
     assert r.returncode == 0 and "both GPUs ok" in r.stdout, r.stderr[-3000:]
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_kv_cache_handed_from_gpu_0_to_gpu_1():
+    """Prefill on GPU 0, decode on GPU 1 (handoff_kv, tests/backend/pass/
+    llama2.vx:431-458): the caches cross with vx_plugin_transfer_peer, and the
+    decoder on GPU 1 continues with the tokens of a single decoder."""
+    code = r"""
+import sys
+import numpy as np
+import torch
+sys.path.insert(0, %r)
+from vx_b200 import abi, llama, ops
+from vx_b200.lib import lib
+shape = dict(dim=512, hidden=1408, n_layers=4, q_heads=8, kv_heads=4, head_dim=64, vocab=4096)
+prompt = [int(t) for t in np.random.default_rng(12).integers(0, 4096, 30)]
+def tokens_after(dec, first, n=20):
+    out, tok = [], first
+    for _ in range(n):
+        out.append(tok)
+        tok = dec.step([tok])[0]
+    return out
+torch.cuda.set_device(0); abi.set_home_gpu(0)
+pre, _ = llama.nn_bf16_model(max_seq=96, batch=1, **shape)
+for t in prompt[:-1]:
+    pre.step([t], fetch=False)
+first = pre.step([prompt[-1]])[0]
+nbytes = pre.kv_cache_bytes
+k = lib().vx_plugin_transfer_peer(pre.kv_cache(0), abi.gpu(0), abi.gpu(1), nbytes)
+v = lib().vx_plugin_transfer_peer(pre.kv_cache(1), abi.gpu(0), abi.gpu(1), nbytes)
+want = tokens_after(pre, first)
+pre.close()
+torch.cuda.set_device(1); abi.set_home_gpu(1)
+dec, _ = llama.nn_bf16_model(max_seq=96, batch=1, **shape)
+dec.adopt_kv(k, v, len(prompt))
+got = tokens_after(dec, first)
+lib().vx_plugin_free(k, abi.gpu(1)); lib().vx_plugin_free(v, abi.gpu(1))
+dec.close()
+assert ops.kernel_status() == 0
+assert got == want, (got, want)
+print("handed over")
+""" % ROOT
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0 and "handed over" in r.stdout, r.stderr[-3000:]

@@ -72,6 +72,11 @@ __global__ void advance_by_kernel(int32_t *pos, int by) {
     pos[0] += by;
 }
 
+__global__ void set_positions_kernel(int32_t *positions, int batch, int to) {
+  if (threadIdx.x < batch)
+    positions[threadIdx.x] = to;
+}
+
 __global__ void advance_kernel(int32_t *positions, int batch) {
   if (threadIdx.x < batch)
     positions[threadIdx.x] += 1;
@@ -1251,6 +1256,38 @@ vx_decoder *vx_decoder_from_llama2c(const char *path, int32_t batch,
 }
 
 const float *vx_decoder_logits(const vx_decoder *d) { return d->logits; }
+
+float *vx_decoder_kv_cache(vx_decoder *d, int32_t which) {
+  return which == 0 ? d->k_cache : which == 1 ? d->v_cache : nullptr;
+}
+
+int64_t vx_decoder_kv_cache_bytes(const vx_decoder *d) {
+  return d->cache_layer_stride * d->c.n_layers * (int64_t)sizeof(float);
+}
+
+int32_t vx_decoder_adopt_kv(vx_decoder *d, const float *k, const float *v,
+                            int32_t positions) {
+  if (!k || !v || positions < 0 || positions > d->c.max_seq) {
+    vxb::set_last_error("vx_decoder_adopt_kv: needs both caches and 0 <= "
+                        "positions <= max_seq");
+    return -1;
+  }
+  /* rows 0 .. positions-1 of every layer and sequence; one copy each (the
+     source may be another GPU's memory: unified addressing finds the way) */
+  const size_t run = (size_t)positions * d->kv_local * d->c.head_dim * sizeof(float);
+  for (int l = 0; l < d->c.n_layers && run; ++l)
+    for (int b = 0; b < d->c.batch; ++b) {
+      const int64_t at = l * d->cache_layer_stride + b * d->cache_batch_stride;
+      CUDA_OK(cudaMemcpyAsync(d->k_cache + at, k + at, run, cudaMemcpyDefault,
+                              d->stream));
+      CUDA_OK(cudaMemcpyAsync(d->v_cache + at, v + at, run, cudaMemcpyDefault,
+                              d->stream));
+    }
+  set_positions_kernel<<<1, 32, 0, d->stream>>>(d->positions, d->c.batch, positions);
+  CUDA_OK(cudaStreamSynchronize(d->stream)); /* the caller may free k and v */
+  d->host_pos = positions;
+  return positions;
+}
 void *vx_decoder_stream(const vx_decoder *d) { return (void *)d->stream; }
 int32_t vx_decoder_step_trace(vx_decoder *d, uint64_t *out, int32_t capacity) {
   if (!d->step_trace)

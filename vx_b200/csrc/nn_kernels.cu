@@ -100,6 +100,7 @@ struct RowDotParams {
   int expert_slot, experts;
   int64_t expert_bytes, scale_bytes;
   const float *add_scale;
+  int scales_in_ring; /* Q4_0: set by the launcher */
 };
 
 /* Weight formats. A row is a run of 16-byte words; a word holds E weights:
@@ -338,7 +339,23 @@ __device__ __forceinline__ ItemRows item_rows(const RowDotParams &p, int item,
    boundaries, whatever its lanes are doing -- 128 KiB in flight per SM. */
 constexpr int RING_STAGES = 4;
 constexpr int CHUNK_BYTES = 1024; /* of one row */
-constexpr int RING_BYTES = WARPS * RING_STAGES * 2 * CHUNK_BYTES;
+/* Q4_0: the f16 scales of a chunk (one per 16 bytes of codes) travel with it,
+   behind the two rows' codes in the same stage, when a row's scales are a
+   multiple of 16 bytes: read from global memory at their first use they were
+   a miss in L1 for every word, and the kernel waited for them. */
+template <typename W> struct ChunkScales { static constexpr int bytes = 0; };
+template <> struct ChunkScales<Q4W> { static constexpr int bytes = CHUNK_BYTES / 16 * 2; };
+template <typename W> __host__ __device__ constexpr int stage_bytes() {
+  return 2 * CHUNK_BYTES + 2 * ChunkScales<W>::bytes;
+}
+template <typename W> __host__ __device__ constexpr int ring_bytes() {
+  return WARPS * RING_STAGES * stage_bytes<W>();
+}
+/* x (all sequences) staged per block: what the ring leaves of 227 KiB */
+template <typename W> __host__ __device__ constexpr int max_smem_x() {
+  return MAX_SMEM_X < 226 * 1024 - ring_bytes<W>() ? MAX_SMEM_X
+                                                   : 226 * 1024 - ring_bytes<W>();
+}
 
 __device__ int g_rowdot_status; /* non-zero: a ring wait gave up */
 __device__ int g_tp_status;     /* non-zero: a peer's flag never arrived */
@@ -351,7 +368,10 @@ __global__ void __maxnreg__(B == 1 && !Scaled<W>::yes ? 96 : 128)
 rowdot_kernel(const RowDotParams p) {
   extern __shared__ __align__(128) unsigned char smem_dyn[];
   unsigned char *ring = smem_dyn;                    /* [warp][stage][2][chunk] */
-  float *xs = (float *)(smem_dyn + RING_BYTES);      /* [B][cols] when x_in_smem */
+  float *xs = (float *)(smem_dyn + ring_bytes<W>()); /* [B][cols] when x_in_smem */
+  constexpr int STAGE = stage_bytes<W>();
+  constexpr int SC = ChunkScales<W>::bytes;
+  const bool ring_scales = SC > 0 && p.scales_in_ring;
   __shared__ float ssq[B][WARPS]; /* per-warp sums of squares of x */
   __shared__ __align__(8) uint64_t bars[WARPS][RING_STAGES];
   constexpr int E = PerWord<W>::n;                   /* weights per 16 bytes */
@@ -379,7 +399,7 @@ rowdot_kernel(const RowDotParams p) {
   const int row_bytes = cols / E * 16;
   const int nch = (row_bytes + CHUNK_BYTES - 1) / CHUNK_BYTES;
   const int units = (last - first) * nch;
-  unsigned char *my_ring = ring + warp * (RING_STAGES * 2 * CHUNK_BYTES);
+  unsigned char *my_ring = ring + warp * (RING_STAGES * STAGE);
 
   if (lane == 0) {
     for (int s = 0; s < RING_STAGES; ++s)
@@ -406,22 +426,29 @@ rowdot_kernel(const RowDotParams p) {
       atomicCAS(&g_rowdot_status, 0, 0x5E); /* not the number of an expert */
   }
   int ld_u = 0, ld_item = first, ld_ch = 0, ld_stage = 0;
-  const char *ld_r0 = nullptr, *ld_r1 = nullptr;
+  const char *ld_r0 = nullptr, *ld_r1 = nullptr, *ld_s0 = nullptr, *ld_s1 = nullptr;
   if (units > 0) {
     const ItemRows it = item_rows<W, EPI>(p, first, w_off, s_off);
     ld_r0 = it.r0;
     ld_r1 = it.r1 ? it.r1 : it.r0;
+    ld_s0 = it.sc0;
+    ld_s1 = it.r1 ? it.sc1 : it.sc0;
   }
   auto issue_next = [&]() {
     if (ld_u >= units)
       return;
     if (lane == 0) {
       const int bytes = ld_ch == nch - 1 ? last_bytes : CHUNK_BYTES;
-      unsigned char *dst = my_ring + ld_stage * (2 * CHUNK_BYTES);
+      unsigned char *dst = my_ring + ld_stage * STAGE;
       uint64_t *bar = &bars[warp][ld_stage];
-      ptx::mbar_expect_tx(bar, 2 * bytes);
+      const int sbytes = ring_scales ? bytes / 8 : 0;
+      ptx::mbar_expect_tx(bar, 2 * bytes + 2 * sbytes);
       ptx::bulk_load(dst, ld_r0 + ld_ch * CHUNK_BYTES, bytes, bar);
       ptx::bulk_load(dst + CHUNK_BYTES, ld_r1 + ld_ch * CHUNK_BYTES, bytes, bar);
+      if (ring_scales) {
+        ptx::bulk_load(dst + 2 * CHUNK_BYTES, ld_s0 + ld_ch * SC, sbytes, bar);
+        ptx::bulk_load(dst + 2 * CHUNK_BYTES + SC, ld_s1 + ld_ch * SC, sbytes, bar);
+      }
     }
     ++ld_u;
     ld_stage = ld_stage + 1 == RING_STAGES ? 0 : ld_stage + 1;
@@ -432,6 +459,8 @@ rowdot_kernel(const RowDotParams p) {
         const ItemRows it = item_rows<W, EPI>(p, ld_item, w_off, s_off);
         ld_r0 = it.r0;
         ld_r1 = it.r1 ? it.r1 : it.r0;
+        ld_s0 = it.sc0;
+        ld_s1 = it.r1 ? it.sc1 : it.sc0;
       }
     }
   };
@@ -553,8 +582,16 @@ rowdot_kernel(const RowDotParams p) {
       scale_a = __ldg(reinterpret_cast<const float *>(sc0) + col / 128);
       scale_b = __ldg(reinterpret_cast<const float *>(sc1) + col / 128);
     } else if (E == 32) {
-      scale_a = __half2float(__ldg(reinterpret_cast<const __half *>(sc0) + col / 32));
-      scale_b = __half2float(__ldg(reinterpret_cast<const __half *>(sc1) + col / 32));
+      if (ring_scales) {
+        /* the stage's scales sit behind its codes: one per word of each row */
+        const __half *sa = reinterpret_cast<const __half *>(
+            src - lane * 16 + 2 * CHUNK_BYTES) + off / 16 + lane;
+        scale_a = __half2float(sa[0]);
+        scale_b = __half2float(sa[SC / 2]);
+      } else {
+        scale_a = __half2float(__ldg(reinterpret_cast<const __half *>(sc0) + col / 32));
+        scale_b = __half2float(__ldg(reinterpret_cast<const __half *>(sc1) + col / 32));
+      }
     }
     const float *xw = xcol + off / 16 * E;
     float xv[B][E];
@@ -609,7 +646,7 @@ rowdot_kernel(const RowDotParams p) {
       atomicCAS(&g_rowdot_status, 0, 1);
       break;
     }
-    const unsigned char *src = my_ring + s * (2 * CHUNK_BYTES) + lane * 16;
+    const unsigned char *src = my_ring + s * STAGE + lane * 16;
     const float *xcol = xbase + ch * CHUNK_COLS + lane_x;
     const char *sc0 = nullptr, *sc1 = nullptr;
     if (Scaled<W>::yes) {
@@ -811,13 +848,17 @@ const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
   constexpr int GROUP = 32 * PerWord<W>::n;
   const size_t xbytes =
       (size_t)B * ((p.cols + GROUP - 1) / GROUP * GROUP) * sizeof(float);
-  p.x_in_smem = xbytes <= (size_t)MAX_SMEM_X;
+  p.x_in_smem = xbytes <= (size_t)max_smem_x<W>();
   if (p.norm_w && !p.x_in_smem)
     return "a fused RMSNorm needs the activations of all sequences to fit in "
-           "96 KiB of shared memory";
-  const size_t smem = RING_BYTES + (p.x_in_smem ? xbytes : 0);
+           "shared memory beside the ring (96 KiB; 80 KiB with Q4_0 weights)";
+  /* Q4_0 scales ride the ring when every row's scales start and end on a
+     16-byte boundary */
+  p.scales_in_ring = ChunkScales<W>::bytes > 0 && p.cols % 256 == 0 &&
+                     !(((uintptr_t)p.s0 | (uintptr_t)p.s1 | (uintptr_t)p.s2) & 15);
+  const size_t smem = ring_bytes<W>() + (p.x_in_smem ? xbytes : 0);
   if (allow_dynamic_smem((const void *)rowdot_kernel<W, B, EPI>,
-                         RING_BYTES + MAX_SMEM_X) != cudaSuccess)
+                         ring_bytes<W>() + max_smem_x<W>()) != cudaSuccess)
     return "a projection could not get its shared memory on this GPU";
   /* One block of 16 warps per SM with a 128 KiB ring (measured faster than
      two blocks of 8 warps with 64 KiB each: 31.7 vs 34.3 us on the 7B gate/up

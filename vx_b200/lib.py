@@ -44,6 +44,7 @@ EXTRA_SYMBOLS = [
     "vx_decoder_step", "vx_decoder_prefill", "vx_decoder_logits",
     "vx_decoder_kernels_per_step",
     "vx_decoder_step_trace",
+    "vx_decoder_kv_cache", "vx_decoder_kv_cache_bytes", "vx_decoder_adopt_kv",
     "vx_decoder_stream", "vx_b200_llama2c_config", "vx_decoder_from_llama2c",
     "vx_b200_last_error", "vx_b200_gemm", "vx_b200_kernel_status",
     "vx_b200_flash_attention", "vx_b200_gemm_column_split",
@@ -135,6 +136,12 @@ def lib():
     L.vx_decoder_prefill.argtypes = [vp, vp, i32]
     L.vx_decoder_logits.restype = vp
     L.vx_decoder_logits.argtypes = [vp]
+    L.vx_decoder_kv_cache.restype = vp
+    L.vx_decoder_kv_cache.argtypes = [vp, i32]
+    L.vx_decoder_kv_cache_bytes.restype = i64
+    L.vx_decoder_kv_cache_bytes.argtypes = [vp]
+    L.vx_decoder_adopt_kv.restype = i32
+    L.vx_decoder_adopt_kv.argtypes = [vp, vp, vp, i32]
     L.vx_decoder_step_trace.restype = i32
     L.vx_decoder_step_trace.argtypes = [vp, vp, i32]
     L.vx_decoder_kernels_per_step.restype = i32

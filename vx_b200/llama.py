@@ -111,6 +111,22 @@ class Decoder:
     def stream(self):
         return lib().vx_decoder_stream(self.handle)
 
+    def kv_cache(self, which):
+        """Device address of the K (0) or V (1) cache; kv_cache_bytes each."""
+        return lib().vx_decoder_kv_cache(self.handle, which)
+
+    @property
+    def kv_cache_bytes(self):
+        return lib().vx_decoder_kv_cache_bytes(self.handle)
+
+    def adopt_kv(self, k, v, positions):
+        """Take over rows 0..positions-1 of caches laid out like this decoder's
+        (device addresses, any GPU of the process) and continue from there."""
+        got = lib().vx_decoder_adopt_kv(self.handle, k, v, positions)
+        if got < 0:
+            raise ValueError(lib().vx_b200_last_error().decode())
+        return got
+
     def step_trace(self):
         """[projections, 6] uint64 nanosecond readings of the last step (a
         decoder made with VXB_STEP_TRACE=1 whose step is one launch), else
