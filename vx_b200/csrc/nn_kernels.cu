@@ -52,70 +52,6 @@ __device__ float block_sum(float v, float *red) {
   return t;
 }
 
-/* ---------------------------------------------------------------- row dots
- * One kernel for every projection of the decoder.  An ITEM is a pair of weight
- * rows whose results the epilogue needs together; a warp owns a contiguous,
- * balanced range of items and streams both rows of an item at once. */
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_BIAS = 2, EPI_SWIGLU = 3, EPI_QKV = 4,
-       EPI_PUSH = 5 };
-
-struct RowDotParams {
-  /* weights */
-  const void *w0, *w1, *w2; /* matvec: w0; swiglu: gate w0, up w1; qkv: q,k,v */
-  /* the scales of w0, w1, w2 (fp8: f32 [ceil(rows/128), cols/128]; Q4_0: f16
-     [rows, cols/32]); row_base: the row of the whole matrix that row 0 of w0
-     is, when w0 is a run of rows inside a matrix with one table of scales */
-  const void *s0, *s1, *s2;
-  int row_base;
-  int rows, cols;
-  int items;
-  /* activations */
-  const float *x;
-  int64_t x_stride;
-  int batch;
-  int x_in_smem;
-  const void *norm_w;
-  int norm_bf16;
-  float eps;
-  /* outputs */
-  float *y;
-  int64_t y_stride;
-  const void *bias;
-  /* qkv */
-  int q_heads, kv_heads, head_dim, rope_mode;
-  const float *cos_t, *sin_t;
-  int cs_cols;
-  float theta;
-  const int32_t *positions;
-  float *k_cache, *v_cache;
-  int64_t cache_batch_stride;
-  int max_seq;
-  /* EPI_PUSH */
-  TpPush tp;
-  /* a mixture-of-experts layer: w0 (and s0) hold `experts` matrices one after
-     another, expert_bytes (scale_bytes) apart, and this launch takes matrix
-     expert_ids[expert_slot] (device memory: the router wrote it). add_scale
-     (EPI_ADD): y += add_scale[0] * s. */
-  const int32_t *expert_ids;
-  int expert_slot, experts;
-  int64_t expert_bytes, scale_bytes;
-  const float *add_scale;
-  int scales_in_ring; /* Q4_0: set by the launcher */
-};
-
-/* Weight formats. A row is a run of 16-byte words; a word holds E weights:
-   4 f32, 8 bf16, 16 fp8 (f8e4m3 codes with an f32 scale per block of 128 x 128
-   weights, nn.vx:1296-1303) or 32 Q4_0 codes (4 bits, weight = (code - 8) *
-   an f16 scale per 32 weights of a row, nn.vx:1645-1663). */
-struct Fp8W {};
-struct Q4W {};
-template <typename W> struct PerWord { static constexpr int n = 16 / (int)sizeof(W); };
-template <> struct PerWord<Fp8W> { static constexpr int n = 16; };
-template <> struct PerWord<Q4W> { static constexpr int n = 32; };
-template <typename W> struct Scaled { static constexpr bool yes = false; };
-template <> struct Scaled<Fp8W> { static constexpr bool yes = true; };
-template <> struct Scaled<Q4W> { static constexpr bool yes = true; };
-
 /* The 16 weights of an fp8 word as f32: two codes to two f16 with the
    conversion instruction, and an f16 to f32 by adding it to -0.0f in a
    mixed-precision add, which issues with the other additions (a conversion to
@@ -248,89 +184,6 @@ fma16(const uint4 &wv, const float (&xv)[B][PerWord<W>::n], float (&acc)[B],
       for (int e = 0; e < E; ++e)
         acc[b] = fmaf(wf[e], xv[b][e], acc[b]);
   }
-}
-
-/* The two weight rows of an item (byte addresses), where their scales are,
-   and for q/k/v which head and pair it is. */
-struct ItemRows {
-  const char *r0, *r1; /* r1 == nullptr: an odd last row */
-  const char *sc0, *sc1; /* scaled formats: the scales of the rows' first column */
-  int head, idx, kind; /* qkv: kind 0 q, 1 k, 2 v */
-};
-template <typename W>
-__device__ __forceinline__ const char *scale_row(const void *scales, int row,
-                                                 int cols) {
-  if (PerWord<W>::n == 16) /* fp8: one row of scales per 128 rows */
-    return (const char *)scales + (int64_t)(row / 128) * (cols / 128) * 4;
-  return (const char *)scales + (int64_t)row * (cols / 32) * 2; /* Q4_0 */
-}
-template <typename W, int EPI>
-__device__ __forceinline__ ItemRows item_rows(const RowDotParams &p, int item,
-                                              int64_t w_off = 0, int64_t s_off = 0) {
-  ItemRows it;
-  const int cols = p.cols;
-  const int64_t row_bytes = (int64_t)cols * 16 / PerWord<W>::n;
-  it.head = it.idx = it.kind = 0;
-  it.sc0 = it.sc1 = nullptr;
-  if (EPI == EPI_SWIGLU) {
-    it.r0 = (const char *)p.w0 + w_off + item * row_bytes;
-    it.r1 = p.w1 ? (const char *)p.w1 + item * row_bytes
-                 : (const char *)p.w0 + w_off + (p.rows + item) * row_bytes;
-    if (Scaled<W>::yes) {
-      it.sc0 = scale_row<W>(p.s0, p.row_base + item, cols) + s_off;
-      it.sc1 = p.w1 ? scale_row<W>(p.s1, item, cols)
-                    : scale_row<W>(p.s0, p.row_base + p.rows + item, cols) + s_off;
-    }
-  } else if (EPI == EPI_QKV) {
-    const int half = p.head_dim / 2;
-    it.head = item / half;
-    it.idx = item - it.head * half;
-    const int a = p.rope_mode == 0 ? it.idx : 2 * it.idx;
-    const int b = p.rope_mode == 0 ? it.idx + half : 2 * it.idx + 1;
-    const char *base;
-    const void *sbase = p.s0;
-    int local = it.head, srow = p.row_base;
-    if (it.head < p.q_heads) {
-      base = (const char *)p.w0;
-    } else if (it.head < p.q_heads + p.kv_heads) {
-      it.kind = 1;
-      local = it.head - p.q_heads;
-      if (p.w1) {
-        base = (const char *)p.w1;
-        sbase = p.s1;
-        srow = 0;
-      } else {
-        base = (const char *)p.w0 + p.q_heads * p.head_dim * row_bytes;
-        srow += p.q_heads * p.head_dim;
-      }
-    } else {
-      it.kind = 2;
-      local = it.head - p.q_heads - p.kv_heads;
-      if (p.w2) {
-        base = (const char *)p.w2;
-        sbase = p.s2;
-        srow = 0;
-      } else {
-        base = (const char *)p.w0 +
-               (p.q_heads + p.kv_heads) * p.head_dim * row_bytes;
-        srow += (p.q_heads + p.kv_heads) * p.head_dim;
-      }
-    }
-    it.r0 = base + ((int64_t)local * p.head_dim + a) * row_bytes;
-    it.r1 = base + ((int64_t)local * p.head_dim + b) * row_bytes;
-    if (Scaled<W>::yes) {
-      it.sc0 = scale_row<W>(sbase, srow + local * p.head_dim + a, cols);
-      it.sc1 = scale_row<W>(sbase, srow + local * p.head_dim + b, cols);
-    }
-  } else {
-    it.r0 = (const char *)p.w0 + w_off + (int64_t)(2 * item) * row_bytes;
-    it.r1 = 2 * item + 1 < p.rows ? it.r0 + row_bytes : nullptr;
-    if (Scaled<W>::yes) {
-      it.sc0 = scale_row<W>(p.s0, p.row_base + 2 * item, cols) + s_off;
-      it.sc1 = scale_row<W>(p.s0, p.row_base + 2 * item + 1, cols) + s_off;
-    }
-  }
-  return it;
 }
 
 /* Weights reach the SM through a per-warp ring in shared memory that bulk
@@ -892,6 +745,8 @@ const char *launch_rowdot_w(RowDotParams &p, cudaStream_t stream) {
   }
 }
 
+#include "rowdot_quant_mma.cuh"
+
 /* fmt: a kFmt* code of kernels.h. */
 template <int EPI>
 const char *launch_rowdot(RowDotParams &p, int fmt, cudaStream_t stream) {
@@ -913,9 +768,16 @@ const char *launch_rowdot(RowDotParams &p, int fmt, cudaStream_t stream) {
     if (EPI == EPI_PUSH)
       return "the quantised projections are not sharded";
     /* the switch is on a constant: only the instantiations below exist */
-    if (EPI != EPI_PUSH)
-      return fmt == kFmtFp8 ? launch_rowdot_b<Fp8W, 1, EPI == EPI_PUSH ? EPI_STORE : EPI>(p, stream)
-                            : launch_rowdot_b<Q4W, 1, EPI == EPI_PUSH ? EPI_STORE : EPI>(p, stream);
+    if (EPI != EPI_PUSH) {
+      constexpr int E = EPI == EPI_PUSH ? EPI_STORE : EPI;
+      /* on the tensor cores where the shape allows, else on the FMA pipe */
+      const char *r = fmt == kFmtFp8 ? launch_quant_mma<Fp8W, E>(p, stream)
+                                     : launch_quant_mma<Q4W, E>(p, stream);
+      if (!r || r[0])
+        return r;
+      return fmt == kFmtFp8 ? launch_rowdot_b<Fp8W, 1, E>(p, stream)
+                            : launch_rowdot_b<Q4W, 1, E>(p, stream);
+    }
   }
   return fmt == kFmtBf16 ? launch_rowdot_w<__nv_bfloat16, EPI>(p, stream)
                          : launch_rowdot_w<float, EPI>(p, stream);
