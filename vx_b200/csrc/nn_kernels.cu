@@ -216,7 +216,7 @@ __device__ int g_tp_status;     /* non-zero: a peer's flag never arrived */
 /* 96 registers for one sequence: 512 threads then leave a quarter of the
    register file, so that the blocks of the attention kernel that follows
    q/k/v can start (and fetch their old cache rows) beside these. */
-template <typename W, int B, int EPI>
+template <typename W, int B, int EPI, bool EARLY>
 __global__ void __maxnreg__(B == 1 && !Scaled<W>::yes ? 96 : 128)
 rowdot_kernel(const RowDotParams p) {
   extern __shared__ __align__(128) unsigned char smem_dyn[];
@@ -462,18 +462,24 @@ rowdot_kernel(const RowDotParams p) {
     fma16<W, B>(wb, xv, s1, scale_b);
   };
 
-  /* One sequence: what lane 0's epilogue reads from global memory -- the
-     residual an item is added to, or the cosine and sine of its pair -- is
-     asked for when the item begins, so that the trip to L2 runs under the
-     item's weights instead of after them. */
+  /* One sequence and no more items than warps (a rank's slice of a sharded
+     model: the launch is a matter of latency): what lane 0's epilogue reads
+     from global memory -- the residual an item is added to, or the cosine and
+     sine of its pair -- is asked for when the item begins, so that the trip
+     to L2 runs under the item's weights instead of after them (27.4 -> 24.2
+     us per layer on an eighth of the 7B shape). With several items per warp
+     the same loads cost the stream 2 % (82.4 -> 83.9 us per layer on the whole
+     shape), so there the epilogue fetches them itself. */
+  constexpr bool early = EARLY; /* a kernel of its own: as a run-time choice
+                                   it slowed the long launches by 3 % */
   float pre0 = 0.0f, pre1 = 0.0f;
-  const int pos_first = (B == 1 && EPI == EPI_QKV) ? p.positions[0] : 0;
+  const int pos_first = (early && EPI == EPI_QKV) ? p.positions[0] : 0;
   int next_item = first, next_ch = 0, next_stage = 0;
   uint32_t next_phase = 0;
   for (int u = 0; u < units; ++u) {
     const int item = next_item, ch = next_ch, s = next_stage;
     const uint32_t phase = next_phase;
-    if (B == 1 && ch == 0 && lane == 0) {
+    if (early && ch == 0 && lane == 0) {
       if (EPI == EPI_ADD || EPI == EPI_PUSH) {
         pre0 = p.y[2 * item];
         pre1 = 2 * item + 1 < p.rows ? p.y[2 * item + 1] : 0.0f;
@@ -571,8 +577,8 @@ rowdot_kernel(const RowDotParams p) {
           }
         }
         float *y = p.y + b * p.y_stride;
-        float s0v = lane == 0 ? (B == 1 ? pre0 : y[ra]) : 0.0f;
-        float s1v = (lane == 0 && r1) ? (B == 1 ? pre1 : y[ra + 1]) : 0.0f;
+        float s0v = lane == 0 ? (early ? pre0 : y[ra]) : 0.0f;
+        float s1v = (lane == 0 && r1) ? (early ? pre1 : y[ra + 1]) : 0.0f;
         for (int r = 0; r < p.tp.ranks; ++r) {
           s0v += __shfl_sync(0xffffffffu, v0, r);
           s1v += __shfl_sync(0xffffffffu, v1, r);
@@ -597,10 +603,10 @@ rowdot_kernel(const RowDotParams p) {
         float v0 = t0[b], v1 = t1[b];
         if (EPI == EPI_ADD) {
           const float scale = p.add_scale ? (expert_ok ? p.add_scale[0] : 0.0f) : 1.0f;
-          const float ya = B == 1 ? pre0 : y[ra];
+          const float ya = early ? pre0 : y[ra];
           v0 = p.add_scale ? fmaf(scale, v0, ya) : ya + v0;
           if (r1) {
-            const float yb = B == 1 ? pre1 : y[rb];
+            const float yb = early ? pre1 : y[rb];
             v1 = p.add_scale ? fmaf(scale, v1, yb) : yb + v1;
           }
         } else if (EPI == EPI_BIAS) {
@@ -638,8 +644,8 @@ rowdot_kernel(const RowDotParams p) {
         float c, s;
         if (p.rope_mode == 0) {
           /* nn_rope_and_store (nn.vx:245-280) */
-          c = B == 1 ? pre0 : p.cos_t[(int64_t)pos * p.cs_cols + idx];
-          s = B == 1 ? pre1 : p.sin_t[(int64_t)pos * p.cs_cols + idx];
+          c = early ? pre0 : p.cos_t[(int64_t)pos * p.cs_cols + idx];
+          s = early ? pre1 : p.sin_t[(int64_t)pos * p.cs_cols + idx];
         } else {
           /* llama2.vx:264-293 with rope_freq (llama_rt.vx:82-85): the CPU
              functions are correctly rounded, so go through double. */
@@ -710,7 +716,7 @@ const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
   p.scales_in_ring = ChunkScales<W>::bytes > 0 && p.cols % 256 == 0 &&
                      !(((uintptr_t)p.s0 | (uintptr_t)p.s1 | (uintptr_t)p.s2) & 15);
   const size_t smem = ring_bytes<W>() + (p.x_in_smem ? xbytes : 0);
-  if (allow_dynamic_smem((const void *)rowdot_kernel<W, B, EPI>,
+  if (allow_dynamic_smem((const void *)rowdot_kernel<W, B, EPI, false>,
                          ring_bytes<W>() + max_smem_x<W>()) != cudaSuccess)
     return "a projection could not get its shared memory on this GPU";
   /* One block of 16 warps per SM with a 128 KiB ring (measured faster than
@@ -728,8 +734,16 @@ const char *launch_rowdot_b(RowDotParams &p, cudaStream_t stream) {
   const int wanted = pack ? (p.items + WARPS - 1) / WARPS : p.items;
   if (blocks > wanted)
     blocks = wanted < 1 ? 1 : wanted;
-  launch_chained(rowdot_kernel<W, B, EPI>, dim3(blocks), dim3(WARPS * 32), smem,
-                 stream, p);
+  if (B == 1 && (int64_t)p.items <= (int64_t)blocks * WARPS) {
+    if (allow_dynamic_smem((const void *)rowdot_kernel<W, B, EPI, B == 1>,
+                           ring_bytes<W>() + max_smem_x<W>()) != cudaSuccess)
+      return "a projection could not get its shared memory on this GPU";
+    launch_chained(rowdot_kernel<W, B, EPI, B == 1>, dim3(blocks), dim3(WARPS * 32),
+                   smem, stream, p);
+  } else {
+    launch_chained(rowdot_kernel<W, B, EPI, false>, dim3(blocks), dim3(WARPS * 32),
+                   smem, stream, p);
+  }
   return check_launch("a projection launch");
 }
 
