@@ -33,13 +33,7 @@
 #ifndef VXB_ROWDOT_QUANT_MMA_CUH
 #define VXB_ROWDOT_QUANT_MMA_CUH
 
-/* Up to 20 warps per block: the arithmetic of a k-step is a chain of loads,
-   conversions and tensor-core instructions that one warp cannot overlap with
-   itself, so the warps of an SM hide it for one another. */
-constexpr int QWARPS = 20;
-constexpr int QTHREADS = QWARPS * 32;
-constexpr int MAX_KSTEPS = 96; /* of a unit, for the staged fp8 scales */
-constexpr int QUANT_DYN_SMEM = 208 * 1024; /* beside 18 KiB of static arrays */
+constexpr int QTHREADS = WARPS * 32;
 constexpr int STEP_ROW_BYTES = 128; /* of one row per k-step */
 
 __device__ int g_quant_status; /* non-zero: a ring wait gave up */
@@ -193,9 +187,6 @@ struct QuantPlan {
      the shared memory the others would have had goes into deeper rings: what
      is in flight per SM, not the number of warps, feeds HBM. */
   int warps, stages;
-  /* k-steps that travel together (1, 2 or 4): their copies are issued back
-     to back, so that HBM sees runs of 256 or 512 bytes of a row, not 128 */
-  int together;
 };
 
 template <typename W, int EPI>
@@ -215,22 +206,19 @@ quant_mma_kernel(const RowDotParams p, const QuantPlan plan,
   const int nthreads = nwarps * 32;
   /* a warp's ring: its stages of codes, then its stages of scales, rounded up
      to the 1 KiB the swizzled boxes of the next warp want */
-  const int kps = plan.together;
-  const int slots = stages * kps; /* of one k-step each; a stage is kps of them */
-  const int warp_ring = (slots * (STAGE_CODES_BYTES + F::scale_bytes) + 1023) & ~1023;
+  const int warp_ring = (stages * (STAGE_CODES_BYTES + F::scale_bytes) + 1023) & ~1023;
   unsigned char *ring = smem_dyn;
   unsigned char *xterms = smem_dyn + nwarps * warp_ring;
-  __shared__ float ssq[QWARPS];
-  __shared__ float2 parts[QWARPS][8];
-  __shared__ __align__(8) uint64_t bars[QWARPS][MAX_STAGES];
-  __shared__ float step_scales[FP8 ? QWARPS : 1][2][FP8 ? MAX_KSTEPS : 1];
+  __shared__ float ssq[WARPS];
+  __shared__ float2 parts[WARPS][8];
+  __shared__ __align__(8) uint64_t bars[WARPS][MAX_STAGES];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int cols = p.cols;
   const int xstride = x_term_stride(cols, F::x_pad);
   unsigned char *my_ring = ring + warp * warp_ring;
-  unsigned char *my_scales = my_ring + slots * STAGE_CODES_BYTES;
+  unsigned char *my_scales = my_ring + stages * STAGE_CODES_BYTES;
 
   if (lane == 0) {
     for (int s = 0; s < stages; ++s)
@@ -265,25 +253,20 @@ quant_mma_kernel(const RowDotParams p, const QuantPlan plan,
   auto issue_next = [&]() {
     if (ld_ks >= ld_end)
       return;
-    const int n = ld_end - ld_ks < kps ? ld_end - ld_ks : kps;
     if (lane == 0) {
+      unsigned char *dst = my_ring + ld_stage * STAGE_CODES_BYTES;
       uint64_t *bar = &bars[warp][ld_stage];
-      ptx::mbar_expect_tx(bar, n * (STAGE_CODES_BYTES + F::scale_bytes));
-      for (int j = 0; j < n; ++j) {
-        const int slot = ld_stage * kps + j;
-        unsigned char *dst = my_ring + slot * STAGE_CODES_BYTES;
-        ptx::tma_load_2d(dst, &map_a, (ld_ks + j) * STEP_ROW_BYTES, ld_ya, bar);
-        ptx::tma_load_2d(dst + 1024, &map_b, (ld_ks + j) * STEP_ROW_BYTES, ld_yb, bar);
+      ptx::mbar_expect_tx(bar, STAGE_CODES_BYTES + F::scale_bytes);
+      ptx::tma_load_2d(dst, &map_a, ld_ks * STEP_ROW_BYTES, ld_ya, bar);
+      ptx::tma_load_2d(dst + 1024, &map_b, ld_ks * STEP_ROW_BYTES, ld_yb, bar);
+      if (!FP8) {
+        unsigned char *sd = my_scales + ld_stage * F::scale_bytes;
+        ptx::tma_load_2d(sd, &map_sa, ld_ks * 16, ld_ya, bar);
+        ptx::tma_load_2d(sd + 128, &map_sb, ld_ks * 16, ld_yb, bar);
       }
-      if (!FP8)
-        for (int j = 0; j < n; ++j) {
-          unsigned char *sd = my_scales + (ld_stage * kps + j) * F::scale_bytes;
-          ptx::tma_load_2d(sd, &map_sa, (ld_ks + j) * 16, ld_ya, bar);
-          ptx::tma_load_2d(sd + 128, &map_sb, (ld_ks + j) * 16, ld_yb, bar);
-        }
     }
-    issued += 1;
-    ld_ks += n;
+    ++issued;
+    ++ld_ks;
     ld_stage = ld_stage + 1 == stages ? 0 : ld_stage + 1;
   };
   /* The weights do not depend on the kernel before this one: start them. */
@@ -385,22 +368,9 @@ quant_mma_kernel(const RowDotParams p, const QuantPlan plan,
       if (item >= p.items)
         item = p.items - 1;
       const ItemRows mine = item_rows<W, EPI>(p, item);
-      if (FP8) {
-        /* the eight r0 rows of a tile lie in one block of 128 rows, and so do
-           its r1 rows: one scale per k-step for each half, fetched for the
-           whole unit now instead of one trip to L2 per k-step */
-        const float *sc_lo = reinterpret_cast<const float *>(__shfl_sync(
-            0xffffffffu, (unsigned long long)mine.sc0, 0));
-        const float *sc_hi = reinterpret_cast<const float *>(__shfl_sync(
-            0xffffffffu, (unsigned long long)(mine.r1 ? mine.sc1 : mine.sc0), 0));
-        __syncwarp();
-        for (int i = lane; i < ks1 - ks0; i += 32) {
-          step_scales[warp][0][i] = __ldg(sc_lo + ks0 + i);
-          step_scales[warp][1][i] = __ldg(sc_hi + ks0 + i);
-        }
-        __syncwarp();
-      }
-      for (int ks_first = ks0; ks_first < ks1; ks_first += kps) {
+      const float *sc_lo = reinterpret_cast<const float *>(mine.sc0);
+      const float *sc_hi = reinterpret_cast<const float *>(mine.r1 ? mine.sc1 : mine.sc0);
+      for (int ks = ks0; ks < ks1; ++ks) {
         /* a wait that runs out is reported, and the warp goes on without
            waiting again: its results are wrong, but it meets the block at
            every barrier */
@@ -409,61 +379,47 @@ quant_mma_kernel(const RowDotParams p, const QuantPlan plan,
           atomicCAS(&g_quant_status, 0, 0x51);
           gave_up = true;
         }
-        const int first_slot = c_stage * kps;
+        const unsigned char *st = my_ring + c_stage * STAGE_CODES_BYTES;
+        const unsigned char *ssc = my_scales + c_stage * F::scale_bytes;
+        (void)ssc;
         ++consumed;
         if (++c_stage == stages) {
           c_stage = 0;
           c_phase ^= 1;
         }
-        const int n = ks1 - ks_first < kps ? ks1 - ks_first : kps;
-        for (int sub = 0; sub < n; ++sub) {
-        const int ks = ks_first + sub;
-        const unsigned char *st = my_ring + (first_slot + sub) * STAGE_CODES_BYTES;
-        const unsigned char *ssc = my_scales + (first_slot + sub) * F::scale_bytes;
-        (void)ssc;
         if (FP8) {
-          /* all loads, all conversions, and the eight
-             products into four independent accumulators: a chain of two, not
-             of eight, dependent tensor-core instructions */
-          const float s_lo = step_scales[FP8 ? warp : 0][0][FP8 ? ks - ks0 : 0];
-          const float s_hi = step_scales[FP8 ? warp : 0][1][FP8 ? ks - ks0 : 0];
-          uint4 al[2], ah[2], bq[2][2];
+          float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
           for (int grp = 0; grp < 2; ++grp) {
             /* 16-byte chunk c of box row g sits at chunk c ^ g (128-byte swizzle) */
             const int at = g * 128 + (((grp * 4 + t) ^ g) << 4);
-            al[grp] = *reinterpret_cast<const uint4 *>(st + at);
-            ah[grp] = *reinterpret_cast<const uint4 *>(st + 1024 + at);
-            const uint4 *bp = reinterpret_cast<const uint4 *>(
-                xb + ((int64_t)ks * 128 + grp * 64 + t * 16) * 2);
-            const uint4 zero = make_uint4(0, 0, 0, 0);
-            bq[grp][0] = g < 3 ? bp[0] : zero;
-            bq[grp][1] = g < 3 ? bp[1] : zero;
-          }
-          float c[4][4];
-#pragma unroll
-          for (int m = 0; m < 4; ++m)
-            c[m][0] = c[m][1] = c[m][2] = c[m][3] = 0.0f;
-#pragma unroll
-          for (int grp = 0; grp < 2; ++grp) {
-            const uint32_t wl[4] = {al[grp].x, al[grp].y, al[grp].z, al[grp].w};
-            const uint32_t wh[4] = {ah[grp].x, ah[grp].y, ah[grp].z, ah[grp].w};
-            const uint32_t bw[8] = {bq[grp][0].x, bq[grp][0].y, bq[grp][0].z,
-                                    bq[grp][0].w, bq[grp][1].x, bq[grp][1].y,
-                                    bq[grp][1].z, bq[grp][1].w};
+            const uint4 al = *reinterpret_cast<const uint4 *>(st + at);
+            const uint4 ah = *reinterpret_cast<const uint4 *>(st + 1024 + at);
+            uint4 b01 = make_uint4(0, 0, 0, 0), b23 = b01;
+            if (g < 3) {
+              const uint4 *bp = reinterpret_cast<const uint4 *>(
+                  xb + ((int64_t)ks * 128 + grp * 64 + t * 16) * 2);
+              b01 = bp[0];
+              b23 = bp[1];
+            }
+            const uint32_t wl[4] = {al.x, al.y, al.z, al.w};
+            const uint32_t wh[4] = {ah.x, ah.y, ah.z, ah.w};
+            const uint32_t bw[8] = {b01.x, b01.y, b01.z, b01.w,
+                                    b23.x, b23.y, b23.z, b23.w};
 #pragma unroll
             for (int m = 0; m < 4; ++m) {
               const uint32_t a[4] = {fp8x2_to_f16x2<false>(wl[m]),
                                      fp8x2_to_f16x2<false>(wh[m]),
                                      fp8x2_to_f16x2<true>(wl[m]),
                                      fp8x2_to_f16x2<true>(wh[m])};
-              mma_f16(c[m], a, bw[2 * m], bw[2 * m + 1]);
+              mma_f16(c, a, bw[2 * m], bw[2 * m + 1]);
             }
           }
-          lo0 = fmaf(s_lo, (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]), lo0);
-          lo1 = fmaf(s_lo, (c[0][1] + c[1][1]) + (c[2][1] + c[3][1]), lo1);
-          hi0 = fmaf(s_hi, (c[0][2] + c[1][2]) + (c[2][2] + c[3][2]), hi0);
-          hi1 = fmaf(s_hi, (c[0][3] + c[1][3]) + (c[2][3] + c[3][3]), hi1);
+          const float s_lo = __ldg(sc_lo + ks), s_hi = __ldg(sc_hi + ks);
+          lo0 = fmaf(s_lo, c[0], lo0);
+          lo1 = fmaf(s_lo, c[1], lo1);
+          hi0 = fmaf(s_hi, c[2], hi0);
+          hi1 = fmaf(s_hi, c[3], hi1);
         } else {
           const uint4 sl = *reinterpret_cast<const uint4 *>(ssc + g * 16);
           const uint4 sh = *reinterpret_cast<const uint4 *>(ssc + 128 + g * 16);
@@ -474,10 +430,10 @@ quant_mma_kernel(const RowDotParams p, const QuantPlan plan,
             const int at = g * 128 + ((b ^ g) << 4) + 4 * t;
             const uint32_t wl = *reinterpret_cast<const uint32_t *>(st + at);
             const uint32_t wh = *reinterpret_cast<const uint32_t *>(st + 1024 + at);
-            uint4 bx = *reinterpret_cast<const uint4 *>(
-                xb + ((int64_t)ks * 256 + 32 * b + 8 * t) * 2);
-            if (g >= 3)
-              bx = make_uint4(0, 0, 0, 0);
+            uint4 bx = make_uint4(0, 0, 0, 0);
+            if (g < 3)
+              bx = *reinterpret_cast<const uint4 *>(
+                  xb + ((int64_t)ks * 256 + 32 * b + 8 * t) * 2);
             /* a nibble OR-ed into 0x4300 is the bf16 128 + code; less 136 it
                is code - 8, exactly */
             constexpr uint32_t MAGIC = 0x43004300u, OFF = 0x43084308u, M = 0x000F000Fu;
@@ -504,7 +460,6 @@ quant_mma_kernel(const RowDotParams p, const QuantPlan plan,
             hi0 = fmaf(s_hi, c[2], hi0);
             hi1 = fmaf(s_hi, c[3], hi1);
           }
-        }
         }
         __syncwarp(); /* every lane has read the stage: it may be filled again */
         issue_next();
@@ -564,51 +519,30 @@ const char *launch_quant_mma(RowDotParams &p, cudaStream_t stream) {
   plan.tiles = (p.items + 7) / 8;
   plan.ksteps = p.cols / F::codes;
   const int blocks = sm_count();
-  /* measured on the 7B shape: fp8 454 tokens/s with at most 16 warps per block,
-     434 with 20; Q4_0 428 and 435 */
-  const int cap = FP8 ? 16 : QWARPS;
   plan.split = 1;
   while (plan.split < 16 && 2 * plan.split <= plan.ksteps &&
-         (int64_t)plan.tiles * plan.split * 2 <= (int64_t)blocks * cap)
+         (int64_t)plan.tiles * plan.split * 2 <= (int64_t)blocks * WARPS)
     plan.split *= 2;
-  if (FP8 && (plan.ksteps + plan.split - 1) / plan.split + 1 > MAX_KSTEPS)
-    return "";
   const int64_t units = (int64_t)plan.tiles * plan.split;
   int warps = (int)((units + blocks - 1) / blocks);
   warps = (warps + plan.split - 1) / plan.split * plan.split;
-  if (warps > cap)
-    warps = cap / plan.split * plan.split;
+  if (warps > WARPS)
+    warps = WARPS;
   if (warps < 4)
     warps = 4 > plan.split ? 4 : plan.split; /* enough threads to stage x */
   const size_t xbytes = 3 * (size_t)x_term_stride(p.cols, F::x_pad);
-  const size_t budget = QUANT_DYN_SMEM - 1024;
-  auto ring_of = [](int slots) { /* as the kernel lays it out */
-    return (size_t)((slots * (STAGE_CODES_BYTES + F::scale_bytes) + 1023) & ~1023);
+  const size_t budget = 223 * 1024;
+  auto ring_of = [](int stages) { /* as the kernel lays it out */
+    return (size_t)((stages * (STAGE_CODES_BYTES + F::scale_bytes) + 1023) & ~1023);
   };
-  int slots = 2 * MAX_STAGES;
-  while (slots > 2 && xbytes + warps * ring_of(slots) > budget)
-    --slots;
-  if (xbytes + warps * ring_of(slots) > budget)
+  int stages = MAX_STAGES;
+  while (stages > 2 && xbytes + warps * ring_of(stages) > budget)
+    --stages;
+  if (xbytes + warps * ring_of(stages) > budget)
     return "";
-  /* at least three stages; k-steps travel in fours or pairs where the ring
-     is deep enough for that */
-  static const int together_wanted = [] {
-    const char *e = getenv("VXB_QUANT_TOGETHER");
-    return e ? atoi(e) : 4;
-  }();
-  int together = 1;
-  for (int k = 4; k > 1; k /= 2)
-    if (k <= together_wanted && slots / k >= 3) {
-      together = k;
-      break;
-    }
-  int stages = slots / together;
-  if (stages > MAX_STAGES)
-    stages = MAX_STAGES;
-  plan.together = together;
   plan.warps = warps;
   plan.stages = stages;
-  const size_t smem = 1024 + warps * ring_of(stages * together) + xbytes;
+  const size_t smem = 1024 + warps * ring_of(stages) + xbytes;
   /* the rows of the tiles' r0 and r1 halves as two maps (see item_rows) */
   const uint64_t rb = (uint64_t)p.cols / PerWord<W>::n * 16; /* bytes of a row */
   const uint64_t sb = (uint64_t)p.cols / 16;                 /* Q4_0: of its scales */
@@ -645,7 +579,7 @@ const char *launch_quant_mma(RowDotParams &p, cudaStream_t stream) {
   if (FP8)
     msa = msb = ma;
   auto kernel = quant_mma_kernel<W, EPI>;
-  if (allow_dynamic_smem((const void *)kernel, QUANT_DYN_SMEM) != cudaSuccess)
+  if (allow_dynamic_smem((const void *)kernel, 224 * 1024) != cudaSuccess)
     return "a quantised projection could not get its shared memory on this GPU";
   launch_chained(kernel, dim3(blocks), dim3(plan.warps * 32), smem, stream, p, plan, ma, mb,
                  msa, msb);
