@@ -516,14 +516,17 @@ def bench_decode_quant(torch, llama, shape, peaks, quant):
                 frac_of_measured_hbm=gbs / peaks["hbm_gbs"])
 
 
-def bench_skinny_layers(torch, llama, rank, world):
+def bench_skinny_layers(torch, llama, rank, world, alone=False):
     """The per-layer cost that is not weight streaming: a model with the 7B
     width but almost no weights (one head per rank, 64 MLP rows per rank),
-    32 layers. At N > 1 the difference from N = 1 is two exchanges per layer."""
-    skinny = dict(dim=4096, hidden=64 * world, n_layers=32, q_heads=world,
-                  kv_heads=world, head_dim=128, vocab=64 * world)
-    dec, tensors = llama.nn_bf16_model(max_seq=64, batch=1, tp_rank=rank,
-                                       tp_ranks=world, **skinny)
+    32 layers. alone: the rank's share as a model of its own, no exchange; the
+    difference is two exchanges per layer."""
+    ranks = 1 if alone else world
+    skinny = dict(dim=4096, hidden=64 * ranks, n_layers=32, q_heads=ranks,
+                  kv_heads=ranks, head_dim=128, vocab=64 * ranks)
+    dec, tensors = llama.nn_bf16_model(max_seq=64, batch=1,
+                                       tp_rank=0 if alone else rank,
+                                       tp_ranks=ranks, **skinny)
     stream = torch.cuda.ExternalStream(dec.stream)
     dec.step([1], fetch=False)
     for _ in range(8):
@@ -789,6 +792,12 @@ def run_ours(args):
         line_extra = {}
         line_extra["skinny_us_per_layer"] = bench_skinny_layers(torch, llama, rank,
                                                                 world)
+        if multi:
+            # the same share of the skinny model run alone on this GPU: what is
+            # left is the exchange, twice per layer
+            alone = bench_skinny_layers(torch, llama, rank, world, alone=True)
+            line_extra["skinny_alone_us_per_layer"] = alone
+            line_extra["exchange_us"] = (line_extra["skinny_us_per_layer"] - alone) / 2.0
         if multi and not args.no_extras:
             line_extra["gemm_column_split"] = bench_column_split(torch, dist, rank,
                                                                  world)
