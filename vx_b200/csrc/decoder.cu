@@ -1002,12 +1002,14 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
                   c.dim, s),
        "embed");
   int splits = 1;
+  const bool fuse_norm = c.dim <= 8192;
+  need(vxb::rows_norm_terms(d->rows_terms, d->rows_x, d->attn_norm[0], T, c.dim, c.eps,
+                            s),
+       "RMSNorm");
   for (int l = 0; l < c.n_layers; ++l) {
+    /* rows_terms hold the terms of RMSNorm(x) * attn_norm[l] here */
     float *kc = d->k_cache + l * d->cache_layer_stride;
     float *vc = d->v_cache + l * d->cache_layer_stride;
-    need(vxb::rows_norm_terms(d->rows_terms, d->rows_x, d->attn_norm[l], T, c.dim,
-                              c.eps, s),
-         "RMSNorm");
     need(vxb::rows_gemm(d->rows_terms, d->wq[l], T, qkv_rows, c.dim,
                         d->rows_partials, &splits, s),
          "q/k/v");
@@ -1015,17 +1017,27 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
                               hd, d->bqkv[l], d->cos_t, d->sin_t, d->positions,
                               d->rows_q, kc, vc, s),
          "RoPE and the cache store");
+    /* No logits are computed: once the last layer's K and V are in the cache,
+       nothing of what follows them is read by anyone. */
+    if (l == c.n_layers - 1)
+      break;
     need(vxb::rows_attention(d->rows_terms, d->rows_q, kc, vc, d->positions, T,
                              d->q_local, d->kv_local, hd, s),
          "attention");
     need(vxb::rows_gemm(d->rows_terms, d->wo[l], T, c.dim, att_cols,
                         d->rows_partials, &splits, s),
          "the output projection");
-    need(vxb::rows_residual_finish(d->rows_x, d->rows_partials, splits, T, c.dim, s),
-         "the residual add");
-    need(vxb::rows_norm_terms(d->rows_terms, d->rows_x, d->ffn_norm[l], T, c.dim,
-                              c.eps, s),
-         "RMSNorm");
+    if (fuse_norm) {
+      need(vxb::rows_residual_norm(d->rows_terms, d->rows_x, d->rows_partials, splits,
+                                   T, d->ffn_norm[l], c.dim, c.eps, s),
+           "the residual add and RMSNorm");
+    } else {
+      need(vxb::rows_residual_finish(d->rows_x, d->rows_partials, splits, T, c.dim, s),
+           "the residual add");
+      need(vxb::rows_norm_terms(d->rows_terms, d->rows_x, d->ffn_norm[l], T, c.dim,
+                                c.eps, s),
+           "RMSNorm");
+    }
     need(vxb::rows_gemm(d->rows_terms, d->w_gate[l], T, 2 * d->hidden_local, c.dim,
                         d->rows_partials, &splits, s),
          "gate/up");
@@ -1035,8 +1047,17 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
     need(vxb::rows_gemm(d->rows_terms, d->w_down[l], T, c.dim, d->hidden_local,
                         d->rows_partials, &splits, s),
          "the down projection");
-    need(vxb::rows_residual_finish(d->rows_x, d->rows_partials, splits, T, c.dim, s),
-         "the residual add");
+    if (fuse_norm) {
+      need(vxb::rows_residual_norm(d->rows_terms, d->rows_x, d->rows_partials, splits,
+                                   T, d->attn_norm[l + 1], c.dim, c.eps, s),
+           "the residual add and RMSNorm");
+    } else {
+      need(vxb::rows_residual_finish(d->rows_x, d->rows_partials, splits, T, c.dim, s),
+           "the residual add");
+      need(vxb::rows_norm_terms(d->rows_terms, d->rows_x, d->attn_norm[l + 1], T, c.dim,
+                                c.eps, s),
+           "RMSNorm");
+    }
   }
   advance_by_kernel<<<1, 32, 0, s>>>(d->positions, T);
   d->host_pos += T;

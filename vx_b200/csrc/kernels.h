@@ -326,6 +326,11 @@ const char *rows_qkv_finish(const float *partials, int splits, int t, int q_head
 const char *rows_residual_finish(float *x, const float *partials, int splits, int t,
                                  int n, cudaStream_t stream);
 /* terms of silu(gate) * up; partials have 2 hidden rows: gate, then up. */
+/* x[t] += the product, then the terms of RMSNorm(x[t]) * w: the residual add
+   and the normalisation that follows it, in one pass (dim <= 8192). */
+const char *rows_residual_norm(void *terms, float *x, const float *partials,
+                               int splits, int t, const void *w, int dim, float eps,
+                               cudaStream_t stream);
 const char *rows_swiglu_finish(void *terms, const float *partials, int splits, int t,
                                int hidden, cudaStream_t stream);
 /* Causal attention of the T prompt positions over cache rows 0 ..

@@ -282,6 +282,48 @@ __device__ __forceinline__ float sum_runs(const float *partials, int splits,
   return s;
 }
 
+/* The same for four consecutive values (r a multiple of 4). */
+__device__ __forceinline__ float4 sum_runs4(const float *partials, int splits,
+                                            int64_t t_count, int64_t n, int64_t t,
+                                            int64_t r) {
+  float4 s = *reinterpret_cast<const float4 *>(partials + t * n + r);
+  for (int k = 1; k < splits; ++k) {
+    const float4 v = *reinterpret_cast<const float4 *>(
+        partials + ((int64_t)k * t_count + t) * n + r);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  return s;
+}
+/* Eight consecutive values (i a multiple of 8) as their three terms: one
+   16-byte store per term. */
+__device__ __forceinline__ void store_terms8(__nv_bfloat16 *terms, int cols,
+                                             int64_t t, int i, const float (&v)[8]) {
+  uint32_t w1[4], w2[4], w3[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t parts[3] = {0, 0, 0};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float x = v[2 * j + h];
+      const __nv_bfloat16 t1 = __float2bfloat16(x);
+      const float r1 = x - __bfloat162float(t1);
+      const __nv_bfloat16 t2 = __float2bfloat16(r1);
+      const float r2 = r1 - __bfloat162float(t2);
+      const __nv_bfloat16 t3 = __float2bfloat16(r2);
+      parts[0] |= (uint32_t)__bfloat16_as_ushort(t1) << (16 * h);
+      parts[1] |= (uint32_t)__bfloat16_as_ushort(t2) << (16 * h);
+      parts[2] |= (uint32_t)__bfloat16_as_ushort(t3) << (16 * h);
+    }
+    w1[j] = parts[0];
+    w2[j] = parts[1];
+    w3[j] = parts[2];
+  }
+  __nv_bfloat16 *row = terms + t * 3 * cols;
+  *reinterpret_cast<uint4 *>(row + i) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+  *reinterpret_cast<uint4 *>(row + cols + i) = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+  *reinterpret_cast<uint4 *>(row + 2 * cols + i) = make_uint4(w3[0], w3[1], w3[2], w3[3]);
+}
+
 /* nn_rms_norm_rows (nn.vx:2835): terms of x[t] / sqrt(mean(x[t]^2) + eps) * w;
    one block per position. */
 __global__ void __launch_bounds__(256)
@@ -308,6 +350,48 @@ norm_terms_kernel(__nv_bfloat16 *terms, const float *x, const void *w, int dim,
     store_terms(terms, dim, t, i, xr[i] * bf16_val(w, i) * inv);
 }
 
+/* After the output or the down projection, when an RMSNorm follows: x[t] += the
+   product, and the terms of the normalised x[t] for the next GEMM, in one pass
+   over the row (the sums in the order of residual_finish_kernel and
+   norm_terms_kernel). One block per position; dim <= 256 * 32. */
+__global__ void __launch_bounds__(256)
+residual_norm_kernel(__nv_bfloat16 *terms, float *x, const float *partials,
+                     int splits, int t_count, const void *w, int dim, float eps) {
+  __shared__ float red[8];
+  chain_release();
+  chain_wait();
+  const int64_t t = blockIdx.x;
+  float *xr = x + t * dim;
+  constexpr int PER = 32;
+  float v[PER];
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int i = threadIdx.x + k * 256;
+    v[k] = 0.0f;
+    if (i < dim) {
+      v[k] = xr[i] + sum_runs(partials, splits, t_count, dim, t, i);
+      xr[i] = v[k];
+      ss = fmaf(v[k], v[k], ss);
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1)
+    ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0)
+    red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.0f;
+  for (int k = 0; k < 8; ++k) /* fixed order */
+    total += red[k];
+  const float inv = 1.0f / sqrtf(total / (float)dim + eps);
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < dim)
+      store_terms(terms, dim, t, i, v[k] * bf16_val(w, i) * inv);
+  }
+}
+
 /* After the q/k/v GEMM: bias, half-split RoPE (nn_rope_and_store,
    nn.vx:245-280), q to q_out[t], k and v to row first_pos + t of the cache.
    One thread per (position, head, pair i / i + hd/2). */
@@ -318,36 +402,47 @@ qkv_finish_kernel(const float *partials, int splits, int t_count, int q_heads,
                   float *k_cache, float *v_cache) {
   chain_release();
   chain_wait();
-  const int half = hd / 2, heads = q_heads + 2 * kv_heads;
+  /* one thread per (position, head, four pairs i..i+3 / i + hd/2 ..) */
+  const int half = hd / 2, quads = half / 4, heads = q_heads + 2 * kv_heads;
   const int64_t n = (int64_t)heads * hd;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)t_count * heads * half)
+  if (idx >= (int64_t)t_count * heads * quads)
     return;
-  const int i = (int)(idx % half);
-  const int head = (int)((idx / half) % heads);
-  const int64_t t = idx / ((int64_t)half * heads);
+  const int i = (int)(idx % quads) * 4;
+  const int head = (int)((idx / quads) % heads);
+  const int64_t t = idx / ((int64_t)quads * heads);
   const int64_t ra = (int64_t)head * hd + i, rb = ra + half;
-  float va = sum_runs(partials, splits, t_count, n, t, ra);
-  float vb = sum_runs(partials, splits, t_count, n, t, rb);
+  float4 va = sum_runs4(partials, splits, t_count, n, t, ra);
+  float4 vb = sum_runs4(partials, splits, t_count, n, t, rb);
   if (bias) {
-    va += bf16_val(bias, ra);
-    vb += bf16_val(bias, rb);
+    va.x += bf16_val(bias, ra); va.y += bf16_val(bias, ra + 1);
+    va.z += bf16_val(bias, ra + 2); va.w += bf16_val(bias, ra + 3);
+    vb.x += bf16_val(bias, rb); vb.y += bf16_val(bias, rb + 1);
+    vb.z += bf16_val(bias, rb + 2); vb.w += bf16_val(bias, rb + 3);
   }
   const int pos = first_pos[0] + (int)t;
   if (head >= q_heads + kv_heads) {
     float *row = v_cache + ((int64_t)pos * kv_heads + (head - q_heads - kv_heads)) * hd;
-    row[i] = va;
-    row[i + half] = vb;
+    *reinterpret_cast<float4 *>(row + i) = va;
+    *reinterpret_cast<float4 *>(row + i + half) = vb;
     return;
   }
-  const float c = cos_t[(int64_t)pos * half + i], s = sin_t[(int64_t)pos * half + i];
-  const float oa = __fsub_rn(__fmul_rn(va, c), __fmul_rn(vb, s));
-  const float ob = __fadd_rn(__fmul_rn(vb, c), __fmul_rn(va, s));
+  const float4 c = *reinterpret_cast<const float4 *>(cos_t + (int64_t)pos * half + i);
+  const float4 s = *reinterpret_cast<const float4 *>(sin_t + (int64_t)pos * half + i);
+  float4 oa, ob;
+  oa.x = __fsub_rn(__fmul_rn(va.x, c.x), __fmul_rn(vb.x, s.x));
+  oa.y = __fsub_rn(__fmul_rn(va.y, c.y), __fmul_rn(vb.y, s.y));
+  oa.z = __fsub_rn(__fmul_rn(va.z, c.z), __fmul_rn(vb.z, s.z));
+  oa.w = __fsub_rn(__fmul_rn(va.w, c.w), __fmul_rn(vb.w, s.w));
+  ob.x = __fadd_rn(__fmul_rn(vb.x, c.x), __fmul_rn(va.x, s.x));
+  ob.y = __fadd_rn(__fmul_rn(vb.y, c.y), __fmul_rn(va.y, s.y));
+  ob.z = __fadd_rn(__fmul_rn(vb.z, c.z), __fmul_rn(va.z, s.z));
+  ob.w = __fadd_rn(__fmul_rn(vb.w, c.w), __fmul_rn(va.w, s.w));
   float *dst = head < q_heads
                    ? q_out + (t * q_heads + head) * hd
                    : k_cache + ((int64_t)pos * kv_heads + (head - q_heads)) * hd;
-  dst[i] = oa;
-  dst[i + half] = ob;
+  *reinterpret_cast<float4 *>(dst + i) = oa;
+  *reinterpret_cast<float4 *>(dst + i + half) = ob;
 }
 
 /* After the output or the down projection: x[t, r] += the product. */
@@ -370,14 +465,25 @@ swiglu_finish_kernel(__nv_bfloat16 *terms, const float *partials, int splits,
                      int t_count, int hidden) {
   chain_release();
   chain_wait();
+  /* one thread per (position, eight consecutive rows): hidden % 8 == 0 */
+  const int per_row = hidden / 8;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)t_count * hidden)
+  if (idx >= (int64_t)t_count * per_row)
     return;
-  const int64_t t = idx / hidden, r = idx - t * hidden;
-  const float gate = sum_runs(partials, splits, t_count, 2 * (int64_t)hidden, t, r);
-  const float up =
-      sum_runs(partials, splits, t_count, 2 * (int64_t)hidden, t, hidden + r);
-  store_terms(terms, hidden, t, (int)r, gate / (1.0f + expf(0.0f - gate)) * up);
+  const int64_t t = idx / per_row;
+  const int r = (int)(idx - t * per_row) * 8;
+  const int64_t n = 2 * (int64_t)hidden;
+  const float4 g0 = sum_runs4(partials, splits, t_count, n, t, r);
+  const float4 g1 = sum_runs4(partials, splits, t_count, n, t, r + 4);
+  const float4 u0 = sum_runs4(partials, splits, t_count, n, t, hidden + r);
+  const float4 u1 = sum_runs4(partials, splits, t_count, n, t, hidden + r + 4);
+  const float gate[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+  const float up[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+  float out[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    out[e] = gate[e] / (1.0f + expf(0.0f - gate[e])) * up[e];
+  store_terms8(terms, hidden, t, r, out);
 }
 
 /* ---- attention over the prompt, f32 on the FMA pipe -------------------------
@@ -639,7 +745,9 @@ const char *rows_qkv_finish(const float *partials, int splits, int t, int q_head
                             const float *cos_t, const float *sin_t,
                             const int32_t *first_pos, float *q_out, float *k_cache,
                             float *v_cache, cudaStream_t stream) {
-  const int64_t n = (int64_t)t * (q_heads + 2 * kv_heads) * (hd / 2);
+  if (hd % 8 != 0)
+    return "the multi-position RoPE takes head_dim in multiples of 8";
+  const int64_t n = (int64_t)t * (q_heads + 2 * kv_heads) * (hd / 8);
   launch_chained(qkv_finish_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
                  stream, partials, splits, t, q_heads, kv_heads, hd, bias, cos_t,
                  sin_t, first_pos, q_out, k_cache, v_cache);
@@ -654,9 +762,21 @@ const char *rows_residual_finish(float *x, const float *partials, int splits, in
   return last_launch("the multi-position residual add");
 }
 
+const char *rows_residual_norm(void *terms, float *x, const float *partials,
+                               int splits, int t, const void *w, int dim, float eps,
+                               cudaStream_t stream) {
+  if (dim > 256 * 32)
+    return "the fused residual and RMSNorm take rows of at most 8192 values";
+  launch_chained(residual_norm_kernel, dim3(t), dim3(256), 0, stream,
+                 (__nv_bfloat16 *)terms, x, partials, splits, t, w, dim, eps);
+  return last_launch("the multi-position residual add and RMSNorm");
+}
+
 const char *rows_swiglu_finish(void *terms, const float *partials, int splits, int t,
                                int hidden, cudaStream_t stream) {
-  const int64_t count = (int64_t)t * hidden;
+  if (hidden % 8 != 0)
+    return "the multi-position SwiGLU takes a hidden size in multiples of 8";
+  const int64_t count = (int64_t)t * (hidden / 8);
   launch_chained(swiglu_finish_kernel, dim3((unsigned)((count + 255) / 256)),
                  dim3(256), 0, stream, (__nv_bfloat16 *)terms, partials, splits, t,
                  hidden);
