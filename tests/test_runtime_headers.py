@@ -4,8 +4,8 @@ repository's headers (vx_b200/runtime/*.h, include/vx_hardware_runtime.h).
 The test sources stay where they are under the reference tree; a scratch
 directory mirrors the reference's layout with links, so their relative includes
 (`../../runtime/x.h`) land on our headers. Needs the reference tree (its path
-comes from VX_REFERENCE_ROOT, default /root/reference), so this runs where
-that is mounted and skips elsewhere.
+comes from VX_REFERENCE_ROOT), so this runs where that is mounted and skips
+elsewhere.
 """
 import os
 import subprocess
