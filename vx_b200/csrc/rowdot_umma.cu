@@ -179,37 +179,66 @@ rowdot_mma_kernel(const __grid_constant__ CUtensorMap map_w0,
       ptx::tma_prefetch_desc(&map_x);
       int it = 0;
       bool ok = true;
-      /* The weights do not depend on the kernel before; the x terms do. */
-      bool waited = false;
-      for (int item = blockIdx.x; ok && item < items; item += gridDim.x) {
-        int tile, split, kb0, kb1;
-        item_range(item, tile, split, kb0, kb1);
-        int which[2], row0[2];
-        half_source(p, tile, 0, which[0], row0[0]);
-        half_source(p, tile, 1, which[1], row0[1]);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          if (!ptx::mbar_wait(&bars->empty[s], ((it / STAGES) & 1) ^ 1, stop)) {
-            atomicCAS(&g_rowmma_status, 0, RM_LOADER);
-            *stop = 1;
-            ok = false;
-            break;
+      /* This block's (item, K block) pairs in order. */
+      int cur_item = blockIdx.x, cur_kb = 0, cur_kb1 = 0;
+      bool opened = false;
+      int which[2] = {0, 0}, row0[2] = {0, 0};
+      auto next_block = [&](int &kb_out) -> bool {
+        for (;;) {
+          if (!opened) {
+            if (cur_item >= items)
+              return false;
+            int tile, split, kb0;
+            item_range(cur_item, tile, split, kb0, cur_kb1);
+            half_source(p, tile, 0, which[0], row0[0]);
+            half_source(p, tile, 1, which[1], row0[1]);
+            cur_kb = kb0;
+            opened = true;
           }
-          uint8_t *sa = smem + s * stage_bytes, *sb = sa + A_BYTES;
-          ptx::mbar_expect_tx(&bars->full[s], A_BYTES + b_bytes);
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const CUtensorMap *m = which[h] == 0 ? &map_w0
-                                   : which[h] == 1 ? &map_w1 : &map_w2;
-            ptx::tma_load_2d(sa + h * (A_BYTES / 2), m, kb * BK, row0[h],
-                             &bars->full[s]);
+          if (cur_kb < cur_kb1) {
+            kb_out = cur_kb++;
+            return true;
           }
-          if (!waited) {
-            chain_wait();
-            waited = true;
-          }
-          ptx::tma_load_2d(sb, &map_x, kb * BK, 0, &bars->full[s]);
+          opened = false;
+          cur_item += gridDim.x;
         }
+      };
+      auto load_weights = [&](int s, int kb) {
+        uint8_t *sa = smem + s * stage_bytes;
+        ptx::mbar_expect_tx(&bars->full[s], A_BYTES + b_bytes);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const CUtensorMap *m = which[h] == 0 ? &map_w0
+                                 : which[h] == 1 ? &map_w1 : &map_w2;
+          ptx::tma_load_2d(sa + h * (A_BYTES / 2), m, kb * BK, row0[h],
+                           &bars->full[s]);
+        }
+      };
+      /* The weights do not depend on the kernel before; the x terms do: the
+         whole ring of weights is asked for first, then the wait, then the
+         terms of those stages. */
+      int kbs[STAGES];
+      int kb = 0;
+      while (it < STAGES && next_block(kb)) {
+        load_weights(it, kb);
+        kbs[it++] = kb;
+      }
+      chain_wait();
+      for (int s = 0; s < it; ++s)
+        ptx::tma_load_2d(smem + s * stage_bytes + A_BYTES, &map_x, kbs[s] * BK, 0,
+                         &bars->full[s]);
+      while (ok && next_block(kb)) {
+        const int s = it % STAGES;
+        if (!ptx::mbar_wait(&bars->empty[s], ((it / STAGES) & 1) ^ 1, stop)) {
+          atomicCAS(&g_rowmma_status, 0, RM_LOADER);
+          *stop = 1;
+          ok = false;
+          break;
+        }
+        load_weights(s, kb);
+        ptx::tma_load_2d(smem + s * stage_bytes + A_BYTES, &map_x, kb * BK, 0,
+                         &bars->full[s]);
+        ++it;
       }
       for (int back = 0; back < STAGES && back < it; ++back) {
         const int j = it - 1 - back;
