@@ -158,7 +158,8 @@ def test_one_launch_step_matches_the_oracle_and_the_separate_kernels(
         assert np.abs(a - b).max() <= 1e-5 * np.abs(b).max()
 
 
-def test_kv_cache_handed_from_a_prefill_decoder_to_a_decode_decoder(oracle):
+@pytest.mark.parametrize("batch", [1, 2])
+def test_kv_cache_handed_from_a_prefill_decoder_to_a_decode_decoder(oracle, batch):
     """The disaggregated prefill/decode of the reference's llama program
     (handoff_kv, tests/backend/pass/llama2.vx:431-458): one decoder reads the
     prompt, its K and V caches travel through vx_plugin_transfer_peer, and a
@@ -167,25 +168,26 @@ def test_kv_cache_handed_from_a_prefill_decoder_to_a_decode_decoder(oracle):
     from vx_b200 import abi
     from vx_b200.lib import lib
     max_seq = 96
-    pre, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=1, **SMALL_NN)
-    dec, _ = llama.nn_bf16_model(max_seq=max_seq, batch=1, **SMALL_NN)
+    pre, tensors = llama.nn_bf16_model(max_seq=max_seq, batch=batch, **SMALL_NN)
+    dec, _ = llama.nn_bf16_model(max_seq=max_seq, batch=batch, **SMALL_NN)
     hm = nn_host_model(oracle, tensors, SMALL_NN, max_seq)
-    prompt = [int(t) for t in np.random.default_rng(12).integers(0, SMALL_NN["vocab"], 30)]
+    prompts = np.random.default_rng(12).integers(0, SMALL_NN["vocab"], (batch, 30))
     steps = 20
-    want = oracle_generate(oracle, hm, prompt, steps, max_seq)
-    for t in prompt[:-1]:
-        pre.step([t], fetch=False)
-    first = pre.step([prompt[-1]])[0]
+    want = [oracle_generate(oracle, hm, [int(t) for t in prompts[b]], steps, max_seq)
+            for b in range(batch)]
+    for p in range(prompts.shape[1]):
+        first = pre.step([int(t) for t in prompts[:, p]])
     nbytes = pre.kv_cache_bytes
-    assert nbytes == dec.kv_cache_bytes == 4 * SMALL_NN["n_layers"] * max_seq * \
+    assert nbytes == dec.kv_cache_bytes == 4 * SMALL_NN["n_layers"] * batch * max_seq * \
         SMALL_NN["kv_heads"] * SMALL_NN["head_dim"]
 
     def go_on(k, v):
-        dec.adopt_kv(k, v, len(prompt))
-        got, tok = [], first
+        dec.adopt_kv(k, v, prompts.shape[1])
+        got, toks = [[] for _ in range(batch)], list(first)
         for _ in range(steps):
-            got.append(tok)
-            tok = dec.step([tok])[0]
+            for b in range(batch):
+                got[b].append(toks[b])
+            toks = dec.step(toks)
         return got
 
     here = abi.home_gpu()
@@ -195,7 +197,8 @@ def test_kv_cache_handed_from_a_prefill_decoder_to_a_decode_decoder(oracle):
     got = go_on(k, v)
     lib().vx_plugin_free(k, here)
     lib().vx_plugin_free(v, here)
-    assert got == want, report(got, want)
+    for b in range(batch):
+        assert got[b] == want[b], "sequence %d: %s" % (b, report(got[b], want[b]))
 
     zeros = abi.DeviceTensor.from_host(np.zeros(nbytes // 4, np.float32))
     assert go_on(zeros.ptr, zeros.ptr) != want

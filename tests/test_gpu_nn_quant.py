@@ -23,7 +23,10 @@ def dev(a, bf16=False):
 
 @pytest.mark.parametrize("quant", ["fp8", "q4"])
 @pytest.mark.parametrize("rows,cols", [(296, 896), (64, 4864), (8, 128),
-                                       (4096, 4096)])
+                                       (4096, 4096),
+                                       # a last tile of six row pairs; more
+                                       # 16-row tiles than the GPU has warps
+                                       (300, 512), (40960, 256)])
 def test_matvec_and_add(oracle, quant, rows, cols):
     w, s = oracle.quant_inputs(quant, rows, cols, 1)
     x = oracle.random_f32(cols, 3, 1.0)
