@@ -296,6 +296,17 @@ def bench_gemm_f32(torch, oracle, n=1024, iters=50):
         ms = event_ms(torch, stream, lambda: [ops.matmul_into(tc, ta, tb)
                                               for _ in range(iters)]) / iters
     got = tc.to_host()
+    # the same product on the FP32 pipe (the tensor-core route switched off)
+    os.environ["VXB_F32_TENSOR"] = "0"
+    try:
+        with on_stream(stream):
+            ops.matmul_into(tc, ta, tb)
+            stream.synchronize()
+            pipe_ms = event_ms(torch, stream, lambda: [ops.matmul_into(tc, ta, tb)
+                                                       for _ in range(iters)]) / iters
+        got_pipe = tc.to_host()
+    finally:
+        del os.environ["VXB_F32_TENSOR"]
     t0 = time.perf_counter()
     host = ops.matmul_host(a, b, slot=False)
     host_ms = (time.perf_counter() - t0) * 1e3
@@ -311,10 +322,15 @@ def bench_gemm_f32(torch, oracle, n=1024, iters=50):
     for t in (ta, tb, tc):
         t.free()
     flop = 2.0 * n ** 3
-    return dict(workload="f32 %d^3, uniform[-1,1) seeds 0/1, true FP32" % n,
+    return dict(workload="f32 %d^3, uniform[-1,1) seeds 0/1; f32 in and out, "
+                         "on the tensor cores as three exact bf16 terms per value"
+                         % n,
                 tflops=flop / ms / 1e9, ms=ms, iters=iters,
                 rel_frobenius_err=float(np.linalg.norm(got - want) /
                                         np.linalg.norm(want)),
+                fp32_pipe_tflops=flop / pipe_ms / 1e9, fp32_pipe_ms=pipe_ms,
+                fp32_pipe_rel_frobenius_err=float(np.linalg.norm(got_pipe - want) /
+                                                  np.linalg.norm(want)),
                 host_operands_ms=host_ms,
                 host_operands_rel_err=float(np.linalg.norm(host - want) /
                                             np.linalg.norm(want)),

@@ -96,6 +96,37 @@ def test_f32_ragged_shapes(oracle, m, n, k):
     assert rel_frobenius(device_matmul(a, b), oracle.gemm(a, b)) <= 1e-5
 
 
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 1024), (300, 260, 128),
+                                   (257, 512, 192), (128, 4096, 64)])
+def test_f32_on_the_tensor_cores_is_as_good_as_the_fp32_kernel(m, n, k, monkeypatch):
+    """An f32 product large enough runs as exact bf16 terms on the tensor
+    cores (k a multiple of 64, n of 4). Against an f64 product its error must
+    be of the size of the FP32 kernel's own, and both far inside the 1e-4 of
+    the reference's check."""
+    rng = np.random.default_rng(m + n + k)
+    a = (rng.uniform(-1, 1, (m, k)) * np.exp(rng.uniform(-6, 6, (m, k)))).astype(np.float32)
+    b = (rng.uniform(-1, 1, (k, n)) * np.exp(rng.uniform(-6, 6, (k, n)))).astype(np.float32)
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    split = device_matmul(a, b)
+    monkeypatch.setenv("VXB_F32_TENSOR", "0")
+    plain = device_matmul(a, b)
+    assert ops.kernel_status() == 0
+    e_split, e_plain = rel_frobenius(split, want), rel_frobenius(plain, want)
+    assert e_plain <= 2e-6 and e_split <= 2e-6, (e_split, e_plain)
+    assert e_split <= 4 * e_plain + 1e-7, (e_split, e_plain)
+    assert not np.array_equal(split, plain) or m * n * k < 2 ** 24
+
+
+def test_f32_on_the_tensor_cores_is_exact_on_integers():
+    """Integers below 2^24 are sums of three bf16 terms exactly, their products
+    and sums below 2^24 are exact in f32: no tolerance."""
+    rng = np.random.default_rng(77)
+    a = rng.integers(-2000, 2000, (256, 256)).astype(np.float32)
+    b = rng.integers(-3, 4, (256, 512)).astype(np.float32)
+    want = (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    assert np.array_equal(device_matmul(a, b), want)
+
+
 def test_strided_view_with_offset(oracle):
     # A view into a larger buffer: non-zero offset, row stride > width.
     rng = np.random.default_rng(9)

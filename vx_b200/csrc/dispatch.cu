@@ -257,10 +257,41 @@ void started_kernel(const char *name) {
 std::mutex g_on_stream_mu;
 std::unordered_map<void *, cudaStream_t> g_on_stream; /* cudaMallocAsync'd */
 
+/* Stream-ordered temporaries come from a pool of this library's own, one per
+   device, that keeps what is freed (the default pool gives its memory back to
+   the driver at the next synchronisation, and a product that needs 100 MB of
+   scratch on every call then pays for the allocation every time). */
+cudaMemPool_t stream_pool() {
+  static std::mutex mu;
+  static cudaMemPool_t pools[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!pools[dev]) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    cudaMemPool_t pool = nullptr;
+    if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    uint64_t keep = UINT64_MAX;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    pools[dev] = pool;
+  }
+  return pools[dev];
+}
+
 cudaError_t device_alloc(void **ptr, size_t bytes) {
   if (!t_stream)
     return cudaMalloc(ptr, bytes);
-  const cudaError_t e = cudaMallocAsync(ptr, bytes, t_stream);
+  cudaMemPool_t pool = stream_pool();
+  const cudaError_t e = pool ? cudaMallocFromPoolAsync(ptr, bytes, pool, t_stream)
+                             : cudaMallocAsync(ptr, bytes, t_stream);
   if (e == cudaSuccess) {
     std::lock_guard<std::mutex> lock(g_on_stream_mu);
     g_on_stream[*ptr] = t_stream;
@@ -623,11 +654,27 @@ void gemm_on_device(const vx_gemm_plan &p, const Staged &a, const Staged &b,
                     void *c, int64_t ldc) {
   const char *why = nullptr;
   switch (p.dtype) {
-  case VX_DTYPE_F32:
+  case VX_DTYPE_F32: {
+    /* on the tensor cores as exact bf16 terms where the shape is for it
+       (VXB_F32_TENSOR=0: always the FP32 pipe), else the FP32 kernel */
+    const char *off = getenv("VXB_F32_TENSOR");
+    const size_t need = (off && off[0] == '0')
+                            ? 0
+                            : vxb::gemm_f32_split_scratch_bytes(p.m, p.n, p.k, ldc);
+    if (need) {
+      Staged scratch = Staged::temporary(need, 0, true);
+      if (scratch.ptr) {
+        why = vxb::gemm_f32_split((const float *)a.ptr, a.row_stride,
+                                  (const float *)b.ptr, b.row_stride, (float *)c,
+                                  ldc, p.m, p.n, p.k, scratch.ptr, t_stream);
+        break;
+      }
+    }
     why = vxb::gemm_f32((const float *)a.ptr, a.row_stride,
                         (const float *)b.ptr, b.row_stride, (float *)c, ldc,
                         p.m, p.n, p.k, t_stream);
     break;
+  }
   case VX_DTYPE_F64:
     why = vxb::gemm_f64((const double *)a.ptr, a.row_stride,
                         (const double *)b.ptr, b.row_stride, (double *)c, ldc,

@@ -15,6 +15,15 @@ namespace vxb {
 const char *gemm_f32(const float *a, int64_t lda, const float *b, int64_t ldb,
                      float *c, int64_t ldc, int64_t m, int64_t n, int64_t k,
                      cudaStream_t stream);
+/* The f32 product on the tensor cores (gemm_f32_split.cu): A and B as three
+   bf16 terms each, the six largest of the nine term products summed in f32
+   (what is left out is below 2^-24 of |a||b|). scratch_bytes: 0 when the shape
+   is not for it (k must be a multiple of 64; small products stay on the FMA
+   pipe), else the size of the scratch the call needs. */
+size_t gemm_f32_split_scratch_bytes(int64_t m, int64_t n, int64_t k, int64_t ldc);
+const char *gemm_f32_split(const float *a, int64_t lda, const float *b, int64_t ldb,
+                           float *c, int64_t ldc, int64_t m, int64_t n, int64_t k,
+                           void *scratch, cudaStream_t stream);
 const char *gemm_f64(const double *a, int64_t lda, const double *b, int64_t ldb,
                      double *c, int64_t ldc, int64_t m, int64_t n, int64_t k,
                      cudaStream_t stream);
@@ -312,6 +321,12 @@ size_t rows_gemm_partial_floats(int t, int n, int cols);
    w bf16 [n, cols], cols a multiple of 64. */
 const char *rows_gemm(const void *terms, const void *w, int t, int n, int cols,
                       float *partials, int *splits_out, cudaStream_t stream);
+/* The same GEMM for any two bf16 matrices: terms [t, term_cols], w [n, w_cols];
+   K block kb of the terms meets K block kb mod (w_cols / 64) of w. */
+int rows_gemm_splits_of(int t, int n, int64_t term_cols);
+const char *rows_gemm_of(const void *terms, int64_t term_cols, const void *w,
+                         int64_t w_cols, int t, int n, float *partials,
+                         int *splits_out, cudaStream_t stream);
 /* terms of RMSNorm(x[t]) * w for every position (nn_rms_norm_rows). */
 const char *rows_norm_terms(void *terms, const float *x, const void *w, int t,
                             int dim, float eps, cudaStream_t stream);

@@ -681,8 +681,12 @@ int resident_pairs() {
 } // namespace
 
 int rows_gemm_splits(int t, int n, int cols) {
+  return rows_gemm_splits_of(t, n, 3 * (int64_t)cols);
+}
+
+int rows_gemm_splits_of(int t, int n, int64_t term_cols) {
   const int tiles = ((t + BM - 1) / BM) * ((n + BN - 1) / BN);
-  const int k_blocks = 3 * cols / BK;
+  const int k_blocks = (int)(term_cols / BK);
   const int pairs = 74;
   /* the number of runs, up to 12, that leaves the last wave fullest */
   int best = 1;
@@ -704,21 +708,28 @@ size_t rows_gemm_partial_floats(int t, int n, int cols) {
 
 const char *rows_gemm(const void *terms, const void *w, int t, int n, int cols,
                       float *partials, int *splits_out, cudaStream_t stream) {
-  if (cols % BK != 0)
+  return rows_gemm_of(terms, 3 * (int64_t)cols, w, cols, t, n, partials, splits_out,
+                      stream);
+}
+
+const char *rows_gemm_of(const void *terms, int64_t term_cols, const void *w,
+                         int64_t w_cols, int t, int n, float *partials,
+                         int *splits_out, cudaStream_t stream) {
+  if (term_cols % BK != 0 || w_cols % BK != 0 || term_cols % w_cols != 0)
     return "the multi-position projections need columns in multiples of 64";
   if (allow_dynamic_smem((const void *)rows_gemm_kernel, SMEM_BYTES) != cudaSuccess)
     return "the multi-position GEMM could not get its shared memory";
   CUtensorMap mx, mw;
-  if (!make_map_16(&mx, terms, 3 * (int64_t)cols, t, 3 * (int64_t)cols, BK, HM, true))
+  if (!make_map_16(&mx, terms, term_cols, t, term_cols, BK, HM, true))
     return "cuTensorMapEncodeTiled refused the activations";
-  if (!make_map_16(&mw, w, cols, n, cols, BK, HN, true))
+  if (!make_map_16(&mw, w, w_cols, n, w_cols, BK, HN, true))
     return "cuTensorMapEncodeTiled refused the weights";
   RowsGemm g;
   g.t = t;
   g.n = n;
-  g.k_blocks = 3 * cols / BK;
-  g.w_blocks = cols / BK;
-  g.splits = rows_gemm_splits(t, n, cols);
+  g.k_blocks = (int)(term_cols / BK);
+  g.w_blocks = (int)(w_cols / BK);
+  g.splits = rows_gemm_splits_of(t, n, term_cols);
   g.partials = partials;
   *splits_out = g.splits;
   int pairs = resident_pairs();
