@@ -145,6 +145,32 @@ def test_strided_view_with_offset(oracle):
     assert rel_frobenius(tc.to_host(), want) <= 1e-6
 
 
+def test_strided_views_on_the_tensor_core_f32_route():
+    """Views large enough for the tensor-core route: A and B inside wider
+    buffers at an offset, C into the middle of a wider buffer (row stride >
+    width, so the partial sums go through the adding kernel)."""
+    rng = np.random.default_rng(19)
+    abig = rng.uniform(-1, 1, (300, 200)).astype(np.float32)
+    bbig = rng.uniform(-1, 1, (140, 520)).astype(np.float32)
+    cbig = np.full((260, 600), 7.0, np.float32)
+    ta, tb, tc = (abi.DeviceTensor.from_host(x) for x in (abig, bbig, cbig))
+    m, n, k = 256, 512, 128
+    da = abi.descriptor(ta.ptr, (m, k), strides=(200, 1), offset=5 * 200 + 8)
+    db = abi.descriptor(tb.ptr, (k, n), strides=(520, 1), offset=2 * 520 + 4)
+    dc = abi.descriptor(tc.ptr, (m, n), strides=(600, 1), offset=600 + 12)
+    blob = abi.payload("k", abi=1, kind="matmul", roles="a:0,b:1,out:2",
+                       outkind="buffer", topo=abi.gpu(0))
+    abi.dispatch(blob, [da, db, dc], [abi.memref_tag(abi.F32, 2)] * 3)
+    got = tc.to_host()
+    want = abig[5:5 + m, 8:8 + k].astype(np.float64) @ \
+        bbig[2:2 + k, 4:4 + n].astype(np.float64)
+    assert rel_frobenius(got[1:1 + m, 12:12 + n], want) <= 2e-6
+    untouched = got.copy()
+    untouched[1:1 + m, 12:12 + n] = 7.0
+    assert np.all(untouched == 7.0)
+    assert ops.kernel_status() == 0
+
+
 def test_flat_matvec(oracle):
     rng = np.random.default_rng(3)
     w = rng.uniform(-1, 1, (300, 288)).astype(np.float32)
