@@ -87,6 +87,15 @@ def rowdot(torch, args):
 
 def gemm(torch, args):
     n = args.n
+    if args.fmt == "f32":
+        ta, tb, tc = (abi.DeviceTensor.empty((n, n), abi.F32) for _ in range(3))
+        ops.fill_uniform(ta, 3, -1.0, 1.0)
+        ops.fill_uniform(tb, 1003, -1.0, 1.0)
+        ms = _timed(torch, torch.cuda.Stream(),
+                    lambda: ops.matmul_into(tc, ta, tb), args.iters)
+        return dict(kernel="f32 gemm %d^3 (three bf16 terms per value on tcgen05 "
+                           "unless VXB_F32_TENSOR=0)" % n, us=ms * 1e3,
+                    tflops=2.0 * n ** 3 / ms / 1e9, status=ops.kernel_status())
     ta, tb, tc = (abi.DeviceTensor.empty((n, n), abi.BF16) for _ in range(3))
     ops.fill_uniform(ta, 3, -1.0, 1.0)
     ops.fill_uniform(tb, 1003, -1.0, 1.0)
@@ -228,7 +237,7 @@ def main():
     ap.add_argument("case", choices=["rowdot", "gemm", "flash", "attn", "decode16",
                                      "shard", "prefill"])
     ap.add_argument("--ranks", type=int, default=8)
-    ap.add_argument("--fmt", default="bf16", choices=["bf16", "fp8", "q4"])
+    ap.add_argument("--fmt", default="bf16", choices=["bf16", "fp8", "q4", "f32"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--n", type=int, default=4096)

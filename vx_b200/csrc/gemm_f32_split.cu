@@ -29,25 +29,39 @@ __device__ __forceinline__ void three_terms(float v, __nv_bfloat16 &t1,
   t3 = __float2bfloat16(r1 - __bfloat162float(t2));
 }
 
-/* A' from A: one thread per element. */
+/* A' from A: one thread per eight consecutive values of a row (k is a
+   multiple of 64), six 16-byte stores. */
 __global__ void __launch_bounds__(256)
 split_a_kernel(__nv_bfloat16 *out, const float *a, int64_t lda, int m, int k) {
   chain_release();
   chain_wait();
+  const int per_row = k / 8;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)m * k)
+  if (idx >= (int64_t)m * per_row)
     return;
-  const int64_t r = idx / k;
-  const int c = (int)(idx - r * k);
-  __nv_bfloat16 t1, t2, t3;
-  three_terms(a[r * lda + c], t1, t2, t3);
-  __nv_bfloat16 *row = out + r * 6 * k;
-  row[c] = t1;
-  row[k + c] = t1;
-  row[2 * (int64_t)k + c] = t1;
-  row[3 * (int64_t)k + c] = t2;
-  row[4 * (int64_t)k + c] = t2;
-  row[5 * (int64_t)k + c] = t3;
+  const int64_t r = idx / per_row;
+  const int c = (int)(idx - r * per_row) * 8;
+  const float *src = a + r * lda + c;
+  uint32_t w1[4], w2[4], w3[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat16 x1, x2, x3, y1, y2, y3;
+    three_terms(src[2 * j], x1, x2, x3);
+    three_terms(src[2 * j + 1], y1, y2, y3);
+    w1[j] = (uint32_t)__bfloat16_as_ushort(x1) | (uint32_t)__bfloat16_as_ushort(y1) << 16;
+    w2[j] = (uint32_t)__bfloat16_as_ushort(x2) | (uint32_t)__bfloat16_as_ushort(y2) << 16;
+    w3[j] = (uint32_t)__bfloat16_as_ushort(x3) | (uint32_t)__bfloat16_as_ushort(y3) << 16;
+  }
+  const uint4 t1 = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+  const uint4 t2 = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+  const uint4 t3 = make_uint4(w3[0], w3[1], w3[2], w3[3]);
+  __nv_bfloat16 *row = out + r * 6 * k + c;
+  *reinterpret_cast<uint4 *>(row) = t1;
+  *reinterpret_cast<uint4 *>(row + k) = t1;
+  *reinterpret_cast<uint4 *>(row + 2 * (int64_t)k) = t1;
+  *reinterpret_cast<uint4 *>(row + 3 * (int64_t)k) = t2;
+  *reinterpret_cast<uint4 *>(row + 4 * (int64_t)k) = t2;
+  *reinterpret_cast<uint4 *>(row + 5 * (int64_t)k) = t3;
 }
 
 /* B' from B [k, n]: a block transposes a 32 x 32 tile through shared memory,
@@ -83,20 +97,32 @@ split_bt_kernel(__nv_bfloat16 *out, const float *b, int64_t ldb, int k, int n) {
   }
 }
 
-/* C = the runs' partial sums, in run order. */
+/* C = the runs' partial sums, in run order; four values per thread (n is a
+   multiple of 4). vec: C's rows are 16-byte aligned. */
 __global__ void __launch_bounds__(256)
 sum_runs_kernel(float *c, int64_t ldc, const float *partials, int splits, int m,
-                int n) {
+                int n, int vec) {
   chain_release();
   chain_wait();
+  const int per_row = n / 4;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)m * n)
+  if (idx >= (int64_t)m * per_row)
     return;
-  const int64_t r = idx / n, j = idx - r * n;
-  float s = partials[idx];
-  for (int q = 1; q < splits; ++q)
-    s += partials[(int64_t)q * m * n + idx];
-  c[r * ldc + j] = s;
+  const int64_t r = idx / per_row;
+  const int j = (int)(idx - r * per_row) * 4;
+  const int64_t at = r * n + j;
+  float4 s = *reinterpret_cast<const float4 *>(partials + at);
+  for (int q = 1; q < splits; ++q) {
+    const float4 v =
+        *reinterpret_cast<const float4 *>(partials + (int64_t)q * m * n + at);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+  }
+  float *dst = c + r * ldc + j;
+  if (vec) {
+    *reinterpret_cast<float4 *>(dst) = s;
+  } else {
+    dst[0] = s.x; dst[1] = s.y; dst[2] = s.z; dst[3] = s.w;
+  }
 }
 
 bool direct(int splits, int64_t n, int64_t ldc) { return splits == 1 && ldc == n; }
@@ -125,8 +151,8 @@ const char *gemm_f32_split(const float *a, int64_t lda, const float *b, int64_t 
   __nv_bfloat16 *b6 = a6 + m * 6 * k;
   const size_t terms_bytes = ((size_t)(m + n) * 6 * k * 2 + 255) & ~(size_t)255;
   float *partials = (float *)((char *)scratch + terms_bytes);
-  launch_chained(split_a_kernel, dim3((unsigned)((m * k + 255) / 256)), dim3(256), 0,
-                 stream, a6, a, lda, (int)m, (int)k);
+  launch_chained(split_a_kernel, dim3((unsigned)((m * (k / 8) + 255) / 256)), dim3(256),
+                 0, stream, a6, a, lda, (int)m, (int)k);
   launch_chained(split_bt_kernel, dim3((unsigned)((n + 31) / 32), (unsigned)((k + 31) / 32)),
                  dim3(256), 0, stream, b6, b, ldb, (int)k, (int)n);
   if (cudaGetLastError() != cudaSuccess)
@@ -137,8 +163,9 @@ const char *gemm_f32_split(const float *a, int64_t lda, const float *b, int64_t 
                                      stream))
     return why;
   if (out != c) {
-    launch_chained(sum_runs_kernel, dim3((unsigned)((m * n + 255) / 256)), dim3(256), 0,
-                   stream, c, ldc, partials, splits, (int)m, (int)n);
+    const int vec = ldc % 4 == 0 && ((uintptr_t)c & 15) == 0;
+    launch_chained(sum_runs_kernel, dim3((unsigned)((m * (n / 4) + 255) / 256)),
+                   dim3(256), 0, stream, c, ldc, partials, splits, (int)m, (int)n, vec);
     if (cudaGetLastError() != cudaSuccess)
       return "the launch that adds the runs failed";
   }
