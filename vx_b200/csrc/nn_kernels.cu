@@ -563,14 +563,16 @@ rowdot_kernel(const RowDotParams p) {
           const TpPair *from = p.tp.slots[p.tp.rank] +
                                (push_set * p.tp.ranks + lane) * p.tp.count + in_set;
           const long long began = clock64();
-          for (;;) {
+          for (int polls = 1;; ++polls) {
             const bool here = r1 ? pair2_load(from, push_call, v0, v1)
                                  : pair_load(from, push_call, v0);
             if (here)
               break;
-            /* a wait that ran out anywhere ends every later wait at once */
-            if (*(volatile int *)&g_tp_status != 0 ||
-                clock64() - began > ptx::kWaitCycles) {
+            /* a wait that ran out anywhere ends every later wait at once; the
+               status word is a trip to L2 of its own, so it is looked at on
+               every eighth poll only */
+            if ((polls & 7) == 0 && (*(volatile int *)&g_tp_status != 0 ||
+                                     clock64() - began > ptx::kWaitCycles)) {
               atomicCAS(&g_tp_status, 0, 0x53);
               break;
             }
