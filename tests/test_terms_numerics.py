@@ -1,0 +1,75 @@
+"""The arithmetic facts the tensor-core routes for f32 data rest on, checked on
+the CPU with numpy: an f32 value is the exact sum of three bf16 terms (the f32
+GEMM, the prefill GEMMs, the batched and the Q4_0 projections), or of three f16
+terms with the second and third scaled by 2^11 and 2^22 (the fp8 projections),
+and the six largest of the nine term products are the product to f32 accuracy."""
+import numpy as np
+
+
+def to_bf16(x):
+    """Round f32 to bf16 (nearest even), returned as f32."""
+    bits = np.asarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    rounded = (bits + 0x7FFF + ((bits >> 16) & 1)) >> 16
+    return (rounded << 16).astype(np.uint32).view(np.float32)
+
+
+def three_bf16(x):
+    x = np.asarray(x, np.float32)
+    t1 = to_bf16(x)
+    r1 = (x - t1).astype(np.float32)
+    t2 = to_bf16(r1)
+    t3 = to_bf16((r1 - t2).astype(np.float32))
+    return t1, t2, t3
+
+
+def samples(seed, n=200000):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(n) * np.exp(rng.uniform(-20, 20, n))
+    return np.concatenate([x, [0.0, 1.0, -1.0, 3.0e38, 1.0e-30, 2.0 ** -126]]) \
+        .astype(np.float32)
+
+
+def test_three_bf16_terms_sum_to_the_value_exactly():
+    x = samples(1)
+    t1, t2, t3 = three_bf16(x)
+    total = (t1.astype(np.float64) + t2.astype(np.float64)) + t3.astype(np.float64)
+    assert np.array_equal(total.astype(np.float32), x)
+    assert np.array_equal(total, x.astype(np.float64))        # nothing left over
+
+
+def test_six_term_products_are_the_product_to_f32_accuracy():
+    a, b = samples(2, 50000)[:50000], samples(3, 50000)[:50000]
+    a, b = np.clip(a, -1e15, 1e15), np.clip(b, -1e15, 1e15)
+    a1, a2, a3 = (t.astype(np.float64) for t in three_bf16(a))
+    b1, b2, b3 = (t.astype(np.float64) for t in three_bf16(b))
+    six = a1 * b1 + a1 * b2 + a2 * b1 + a1 * b3 + a2 * b2 + a3 * b1
+    exact = a.astype(np.float64) * b.astype(np.float64)
+    bound = 3.0 * 2.0 ** -24 * np.abs(exact) + 1e-300
+    assert np.all(np.abs(six - exact) <= bound)
+
+
+def test_three_scaled_f16_terms_sum_to_the_value_exactly():
+    """h1 = f16(x), h2 = f16((x - h1) 2^11), h3 = f16(((x - h1) 2^11 - h2) 2^11):
+    x = h1 + h2 2^-11 + h3 2^-22 for every f32 inside f16's range that is not
+    tiny (activations after an RMSNorm are neither)."""
+    rng = np.random.default_rng(4)
+    x = (rng.standard_normal(200000) * np.exp(rng.uniform(-6, 9, 200000))) \
+        .astype(np.float32)
+    x = x[(np.abs(x) < 60000) & (np.abs(x) > 2.0 ** -10)]
+    h1 = x.astype(np.float16)
+    r1 = ((x - h1.astype(np.float32)) * np.float32(2048)).astype(np.float32)
+    h2 = r1.astype(np.float16)
+    r2 = ((r1 - h2.astype(np.float32)) * np.float32(2048)).astype(np.float32)
+    h3 = r2.astype(np.float16)
+    total = h1.astype(np.float64) + h2.astype(np.float64) / 2048 + \
+        h3.astype(np.float64) / 4194304
+    assert np.array_equal(total, x.astype(np.float64))
+
+
+def test_a_q4_code_is_an_exact_bf16_after_the_magic_or():
+    """0x4300 | code is the bf16 128 + code; less 136 it is code - 8."""
+    codes = np.arange(16, dtype=np.uint32)
+    as_f32 = ((0x4300 | codes) << 16).astype(np.uint32).view(np.float32)
+    assert np.array_equal(as_f32, (128 + codes).astype(np.float32))
+    assert np.array_equal(to_bf16(as_f32 - np.float32(136)),
+                          (codes.astype(np.float32) - 8))
