@@ -123,8 +123,7 @@ void vx_nn_swiglu_q4(VX_TENSOR1(out), VX_TENSOR1(w), VX_TENSOR1(scales),
    token, in bf16 and in Q4_0. The experts' matrices sit one after another in
    `w` (and `scales`); `ids` is device memory, normally nn_top_k's output.
    nn_top_k nn.vx:904, nn_moe_swiglu :968, nn_moe_down_add :1019,
-   nn_moe_swiglu_q4 :2105, nn_moe_down_q4_add :2190. (The grouping kernels for
-   batched prefill, nn_moe_group* :1068-1294, are not provided.) */
+   nn_moe_swiglu_q4 :2105, nn_moe_down_q4_add :2190. */
 void vx_nn_top_k(VX_TENSOR1(ids), VX_TENSOR1(weights), VX_TENSOR1(logits), int32_t n,
                  int32_t k);
 void vx_nn_moe_swiglu(VX_TENSOR2(out), VX_TENSOR1(w), VX_TENSOR1(ids), VX_TENSOR1(x),
@@ -153,6 +152,50 @@ void vx_nn_argmax_rows(VX_TENSOR1(out), VX_TENSOR2(logits), int32_t n,
                        int32_t count);
 void vx_nn_embed_rows(VX_TENSOR2(x), VX_TENSOR1(table), VX_TENSOR1(tokens),
                       int32_t n, int32_t dim);
+/* nn_top_k_rows nn.vx:2897, nn_matvec_q4_heads_add_rows :2459, nn_qkv_q4_rows
+   :2614, nn_moe_swiglu_q4_rows :2958, nn_moe_down_q4_add_rows :3066. ids and
+   weights are [n, k]; out and h hold a row for each of the n * k (position,
+   slot) pairs, pair t * k + e being slot e of position t. */
+void vx_nn_top_k_rows(VX_TENSOR2(ids), VX_TENSOR2(weights), VX_TENSOR2(logits),
+                      int32_t n, int32_t count, int32_t k);
+void vx_nn_matvec_q4_heads_add_rows(VX_TENSOR2(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                                    VX_TENSOR3(x), int32_t n, int32_t rows,
+                                    int32_t heads, int32_t head_dim);
+void vx_nn_qkv_q4_rows(VX_TENSOR3(q), VX_TENSOR3(k), VX_TENSOR3(v), VX_TENSOR1(w),
+                       VX_TENSOR1(scales), VX_TENSOR1(b), VX_TENSOR2(x), int32_t n,
+                       int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                       int32_t cols);
+void vx_nn_moe_swiglu_q4_rows(VX_TENSOR2(out), VX_TENSOR1(w), VX_TENSOR1(scales),
+                              VX_TENSOR2(ids), VX_TENSOR2(x), int32_t n, int32_t k,
+                              int32_t rows, int32_t cols, int32_t experts);
+void vx_nn_moe_down_q4_add_rows(VX_TENSOR2(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                                VX_TENSOR2(ids), VX_TENSOR2(weights), VX_TENSOR2(h),
+                                int32_t n, int32_t k, int32_t rows, int32_t cols,
+                                int32_t experts);
+
+/* The (position, slot) pairs of a mixture-of-experts layer grouped by expert: a
+   stable counting sort in three kernels, and all three in nn_moe_group
+   (nn_moe_group_count nn.vx:1070, nn_moe_group_offsets :1110,
+   nn_moe_group_place :1252, nn_moe_group :1287). ids[p] is the expert of pair
+   p. order gets the pairs expert by expert, each group starting at a multiple
+   of `align` and padded to one, with n + i at a position i that holds no pair
+   (order needs n + experts * (align - 1) positions); starts[e] is where group e
+   begins and starts[experts] where the last ends; tile_expert[t] is the expert
+   of positions align * t .. align * t + align - 1, or -1 past the last group.
+   counts and base are [ceil(n / 256), experts]: the pairs of each expert among
+   each 256 pairs, and where the first of them goes. An id that names no expert
+   is skipped and reported once by vx_b200_kernel_status() (0x6E). */
+void vx_nn_moe_group_count(VX_TENSOR2(counts), VX_TENSOR1(ids), int32_t n,
+                           int32_t experts);
+void vx_nn_moe_group_offsets(VX_TENSOR2(base), VX_TENSOR1(starts),
+                             VX_TENSOR1(tile_expert), VX_TENSOR1(order),
+                             VX_TENSOR2(counts), int32_t n, int32_t experts,
+                             int32_t align);
+void vx_nn_moe_group_place(VX_TENSOR1(order), VX_TENSOR1(ids), VX_TENSOR2(base),
+                           int32_t n);
+void vx_nn_moe_group(VX_TENSOR1(order), VX_TENSOR2(counts), VX_TENSOR2(base),
+                     VX_TENSOR1(starts), VX_TENSOR1(tile_expert), VX_TENSOR1(ids),
+                     int32_t experts, int32_t align);
 
 /* ---- a whole decoder token -------------------------------------------------- */
 typedef struct {

@@ -521,3 +521,134 @@ def all_reduce_sum_f32(inputs):
     out = np.empty_like(inputs[0])
     lib().oracle_all_reduce_sum_f32(ptrs, len(inputs), _p(out), out.size)
     return out
+
+
+# ---- the pairs of a mixture-of-experts layer grouped by expert ----------------------
+def moe_group(ids, experts, align, room=None):
+    """nn_moe_group (stdlib/std/nn.vx:1056-1294) as the plain loops its own test
+    compares the kernels with (tests/optimizations/pass/
+    std_nn_moe_group_sorts_pairs_by_expert.vx:83-110): a stable sort of the pairs
+    by expert, each group padded to a multiple of `align`, n + i at a position i
+    with no pair, -1 for a tile past the last group. counts and base follow the
+    kernels' doc comments (nn.vx:1068-1069, 1105-1107): the pairs of each expert
+    in each block of 256, and where the first of them goes."""
+    ids = np.ascontiguousarray(ids, np.int32)
+    n = ids.size
+    if room is None:
+        room = n + experts * (align - 1)
+    tiles = (room + align - 1) // align
+    order = (n + np.arange(room)).astype(np.int32)
+    tile_expert = np.full(tiles, -1, np.int32)
+    starts = np.zeros(experts + 1, np.int32)
+    blocks = (n + 255) // 256
+    counts = np.zeros((blocks, experts), np.int32)
+    base = np.zeros((blocks, experts), np.int32)
+    for b in range(blocks):
+        counts[b] = np.bincount(ids[b * 256:(b + 1) * 256], minlength=experts)
+    nxt = 0
+    for e in range(experts):
+        starts[e] = nxt
+        members = np.flatnonzero(ids == e)
+        order[nxt:nxt + members.size] = members
+        padded = (members.size + align - 1) // align * align
+        tile_expert[nxt // align:(nxt + padded) // align] = e
+        base[:, e] = nxt + np.concatenate(([0], np.cumsum(counts[:-1, e]))) \
+            if blocks else base[:, e]
+        nxt += padded
+    starts[experts] = nxt
+    return dict(order=order, starts=starts, tile_expert=tile_expert, counts=counts,
+                base=base)
+
+
+def moe_group_as_the_kernels(ids, experts, align, room=None):
+    """The same result by the route of the reference's three kernels: the
+    per-block counts (nn.vx:1070-1102), the starts as a scan in groups of 32
+    experts with a binary search for the expert of a tile (:1110-1246), and each
+    pair placed after the equal ids before it in its block (:1252-1281). A second
+    statement of the contract, for checking the first."""
+    ids = np.ascontiguousarray(ids, np.int32)
+    n = ids.size
+    if room is None:
+        room = n + experts * (align - 1)
+    tiles = (room + align - 1) // align
+    blocks = (n + 255) // 256
+    counts = np.zeros((blocks, experts), np.int32)
+    for b in range(blocks):
+        keys = ids[b * 256:(b + 1) * 256]
+        for e in range(experts):
+            counts[b, e] = int(np.count_nonzero(keys == e))
+    size = counts.sum(axis=0).astype(np.int64) if blocks else np.zeros(experts, np.int64)
+    first = (size + align - 1) // align * align
+    group = np.zeros(32, np.int64)
+    for g in range(32):
+        total = 0
+        for x in range(32 * g, min(32 * g + 32, experts)):
+            padded = first[x]
+            first[x] = total
+            total += padded
+        group[g] = total
+    before = 0
+    for g in range(32):
+        added = group[g]
+        group[g] = before
+        before += added
+    end = before
+    starts = np.zeros(experts + 1, np.int32)
+    base = np.zeros((blocks, experts), np.int32)
+    for e in range(experts):
+        first[e] += group[e // 32]
+        starts[e] = first[e]
+        at = first[e]
+        for b in range(blocks):
+            base[b, e] = at
+            at += counts[b, e]
+    starts[experts] = end
+    order = np.full(room, -7, np.int32)
+    tile_expert = np.zeros(tiles, np.int32)
+    for t in range(tiles):
+        at = t * align
+        if at < end:
+            e, above = 0, experts
+            while above - e > 1:
+                mid = (e + above) // 2
+                if first[mid] <= at:
+                    e = mid
+                else:
+                    above = mid
+            tile_expert[t] = e
+            for i in range(max(first[e] + size[e], at), at + align):
+                order[i] = n + i
+        else:
+            tile_expert[t] = -1
+            for i in range(at, min(at + align, room)):
+                order[i] = n + i
+    for b in range(blocks):
+        keys = ids[b * 256:(b + 1) * 256]
+        for l in range(keys.size):
+            rank = int(np.count_nonzero(keys[:l] == keys[l]))
+            order[base[b, keys[l]] + rank] = b * 256 + l
+    return dict(order=order, starts=starts, tile_expert=tile_expert, counts=counts,
+                base=base)
+
+
+def moe_group_reference_cases():
+    """The six cases of the reference's test of nn_moe_group
+    (std_nn_moe_group_sorts_pairs_by_expert.vx:160-203): (name, ids, experts,
+    align)."""
+    a = (np.arange(600) * 7 % 5).astype(np.int32)
+    b = np.empty(1000, np.int32)
+    state = 12345
+    for p in range(1000):
+        state = (state * 1103515245 + 12345) % 2147483648
+        b[p] = (state // 65536) % 128
+        if b[p] == 64:
+            b[p] = 65
+    c = np.zeros(300, np.int32)
+    p = np.arange(2600)
+    d = np.where(p % 2 == 1, (p // 2) % 40, 3).astype(np.int32)
+    return [("600 pairs, 5 experts", a, 5, 1),
+            ("1000 pairs, 160 experts", b, 160, 1),
+            ("1000 pairs, 160 experts, align 16", b, 160, 16),
+            ("300 pairs, 1 expert", c, 1, 1),
+            ("2600 pairs, 40 experts, skewed", d, 40, 1),
+            ("2600 pairs, 40 experts, skewed, align 2", d, 40, 2)]

@@ -251,3 +251,45 @@ def test_top_k_orders_by_value_then_index(oracle):
     e = np.exp(logits[ids].astype(np.float64) - float(logits[ids[0]]))
     assert np.abs(weights - e / e.sum()).max() <= 1e-6
     assert abs(float(weights.sum()) - 1.0) <= 1e-6
+
+
+def test_moe_group_on_the_reference_cases(oracle):
+    """The six cases of std_nn_moe_group_sorts_pairs_by_expert.vx. The plain
+    stable sort (what that test calls `want`) and the restatement of the three
+    kernels must agree, and the order must pass the test's `positions` check:
+    every position names a distinct element."""
+    for name, ids, experts, align in oracle.moe_group_reference_cases():
+        want = oracle.moe_group(ids, experts, align)
+        twin = oracle.moe_group_as_the_kernels(ids, experts, align)
+        for key in want:
+            assert np.array_equal(want[key], twin[key]), (name, key)
+        n, order = ids.size, want["order"]
+        room = n + experts * (align - 1)
+        assert order.size == room, name
+        at = np.full(n + room, -1)
+        at[order] = np.arange(room)
+        assert np.array_equal(at[order], np.arange(room)), name
+        # each group: its pairs in rising order, all of its expert, then padding
+        for e in range(experts):
+            lo, hi = want["starts"][e], want["starts"][e + 1]
+            assert lo % align == 0 and hi % align == 0, name
+            members = order[lo:hi][order[lo:hi] < n]
+            assert np.all(ids[members] == e) and np.all(np.diff(members) > 0), name
+            assert members.size == np.count_nonzero(ids == e), name
+            assert np.all(want["tile_expert"][lo // align:hi // align] == e), name
+        assert np.all(want["tile_expert"][want["starts"][experts] // align:] == -1)
+    # the sizes the cases are named for
+    sizes = [(c[1].size, c[2], c[3]) for c in oracle.moe_group_reference_cases()]
+    assert sizes == [(600, 5, 1), (1000, 160, 1), (1000, 160, 16), (300, 1, 1),
+                     (2600, 40, 1), (2600, 40, 2)]
+
+
+def test_moe_group_edges(oracle):
+    for ids, experts, align in ((np.zeros(0, np.int32), 3, 4),
+                                (np.array([2, 2, 2], np.int32), 3, 4),
+                                (np.arange(256, dtype=np.int32) % 7, 7, 8),
+                                (np.arange(257, dtype=np.int32) % 1024, 1024, 1)):
+        want = oracle.moe_group(ids, experts, align)
+        twin = oracle.moe_group_as_the_kernels(ids, experts, align)
+        for key in want:
+            assert np.array_equal(want[key], twin[key]), (ids.size, experts, key)

@@ -360,6 +360,28 @@ int rows_status();
    = the softmax over those k values. */
 const char *top_k(int32_t *ids, float *weights, const float *logits, int n, int k,
                   cudaStream_t stream);
+/* nn_top_k_rows (nn.vx:2897-2929): the same for `positions` rows of logits,
+   one block each; row t of a tensor starts t * its pitch values in. */
+const char *top_k_rows(int32_t *ids, float *weights, const float *logits,
+                       int positions, int n, int k, int64_t ids_pitch,
+                       int64_t weights_pitch, int64_t logits_pitch,
+                       cudaStream_t stream);
+
+/* ---- the pairs of a mixture-of-experts layer grouped by expert (moe_group.cu;
+   nn.vx:1056-1294). counts and base: a row of `pitch` values for each 256
+   pairs. order: `room` positions; tile_expert: `tiles` values. */
+const char *moe_group_count(int32_t *counts, int64_t pitch, const int32_t *ids, int n,
+                            int experts, cudaStream_t stream);
+const char *moe_group_offsets(int32_t *base, int64_t base_pitch, int32_t *starts,
+                              int32_t *tile_expert, int tiles, int32_t *order,
+                              int room, const int32_t *counts, int64_t counts_pitch,
+                              int n, int experts, int align, cudaStream_t stream);
+const char *moe_group_place(int32_t *order, int room, const int32_t *ids,
+                            const int32_t *base, int64_t pitch, int n, int experts,
+                            cudaStream_t stream);
+/* 0, or once 0x6E after an id that named no expert (0x6F: a `base` that sent a
+   pair outside `order`); waits for the stream. */
+int moe_group_status(cudaStream_t stream);
 const char *argmax(int32_t *out, const float *logits, int n, int batch,
                    int64_t stride, cudaStream_t stream);
 const char *embed(float *x, const void *table, bool tbf16, const int32_t *token,

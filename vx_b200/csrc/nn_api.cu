@@ -10,6 +10,7 @@
 #include "vx_hardware_runtime.h"
 
 #include <cstdarg>
+#include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -801,6 +802,194 @@ void vx_nn_embed_rows(VX_TENSOR2(x), VX_TENSOR1(table), VX_TENSOR1(tokens),
 }
 #undef FN
 
+#define FN "nn_top_k_rows"
+void vx_nn_top_k_rows(VX_TENSOR2(ids), VX_TENSOR2(weights), VX_TENSOR2(logits),
+                      int32_t n, int32_t count, int32_t k) {
+  UNUSED_ALLOC(ids); UNUSED_ALLOC(weights); UNUSED_ALLOC(logits);
+  if (count <= 0 || count > 256 || k <= 0 || k > count)
+    stop("nn_top_k_rows: count must be 1 to 256, and k must be 1 to count");
+  if (logits_n1 < count || ids_n1 < k || weights_n1 < k)
+    stop("nn_top_k_rows: a row has too few values");
+  if (n <= 0 || logits_n0 < n || ids_n0 < n || weights_n0 < n)
+    stop("nn rows: each tensor needs n rows");
+  must(vxb::top_k_rows(T2(int32_t, ids), T2(float, weights), T2(float, logits), n,
+                       count, k, ids_n1, weights_n1, logits_n1,
+                       vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+#define FN "nn_matvec_q4_heads_add_rows"
+void vx_nn_matvec_q4_heads_add_rows(VX_TENSOR2(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                                    VX_TENSOR3(x), int32_t n, int32_t rows,
+                                    int32_t heads, int32_t head_dim) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(x);
+  check_heads(FN, x_n1, x_n2, heads, head_dim);
+  check_rows(FN, n, x_n0, y_n0);
+  float *yp = T2(float, y);
+  const float *xp = T3(float, x);
+  for (int t = 0; t < n; ++t)
+    quant_matvec(FN, vxb::kFmtQ4, yp + (int64_t)t * y_n1, y_n1, T1(uint32_t, w),
+                 w_n0, T1(uint16_t, scales), scales_n0,
+                 xp + (int64_t)t * x_n1 * x_n2, (int64_t)heads * head_dim, rows,
+                 heads * head_dim, 1);
+}
+#undef FN
+
+#define FN "nn_qkv_q4_rows"
+void vx_nn_qkv_q4_rows(VX_TENSOR3(q), VX_TENSOR3(k), VX_TENSOR3(v), VX_TENSOR1(w),
+                       VX_TENSOR1(scales), VX_TENSOR1(b), VX_TENSOR2(x), int32_t n,
+                       int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                       int32_t cols) {
+  UNUSED_ALLOC(q); UNUSED_ALLOC(k); UNUSED_ALLOC(v); UNUSED_ALLOC(w);
+  UNUSED_ALLOC(scales); UNUSED_ALLOC(b); UNUSED_ALLOC(x);
+  check_heads(FN, q_n1, q_n2, q_heads, head_dim);
+  check_heads(FN, k_n1, k_n2, kv_heads, head_dim);
+  check_heads(FN, v_n1, v_n2, kv_heads, head_dim);
+  if (n <= 0 || x_n0 < n || q_n0 < n || k_n0 < n || v_n0 < n)
+    stop("nn rows: `x`, `q`, `k` and `v` need n rows");
+  float *qp = T3(float, q), *kp = T3(float, k), *vp = T3(float, v);
+  const float *xp = T2(float, x);
+  for (int t = 0; t < n; ++t)
+    quant_qkv(FN, vxb::kFmtQ4, qp + (int64_t)t * q_n1 * q_n2,
+              kp + (int64_t)t * k_n1 * k_n2, vp + (int64_t)t * v_n1 * v_n2,
+              T1(uint32_t, w), w_n0, T1(uint16_t, scales), scales_n0,
+              T1(uint16_t, b), b_n0, xp + (int64_t)t * x_n1, x_n1, q_heads,
+              kv_heads, head_dim, cols);
+}
+#undef FN
+
+/* The experts of n positions (nn.vx:2952-3155). Position t runs the
+   one-position projections on ids[t], x[t] and h[t * k ..]: row t is the
+   one-position kernel's own result, bit for bit. */
+#define FN "nn_moe_swiglu_q4_rows"
+void vx_nn_moe_swiglu_q4_rows(VX_TENSOR2(out), VX_TENSOR1(w), VX_TENSOR1(scales),
+                              VX_TENSOR2(ids), VX_TENSOR2(x), int32_t n, int32_t k,
+                              int32_t rows, int32_t cols, int32_t experts) {
+  UNUSED_ALLOC(out); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(ids);
+  UNUSED_ALLOC(x);
+  if (k <= 0 || n <= 0 || ids_n0 < n || ids_n1 < k || x_n0 < n ||
+      out_n0 < (int64_t)n * k || out_n1 < rows)
+    stop("nn_moe_swiglu_q4_rows: `ids` needs n rows of k values, `x` n rows, and "
+         "`out` a row of rows values for each of the n * k");
+  if (cols <= 0 || cols % 32 != 0 ||
+      scales_n0 < (int64_t)experts * 2 * rows * (cols / 32))
+    stop("nn_moe_swiglu_q4_rows: the scales are too few for the experts");
+  float *op = T2(float, out);
+  const int32_t *ip = T2(int32_t, ids);
+  const float *xp = T2(float, x);
+  for (int t = 0; t < n; ++t)
+    moe_swiglu(FN, vxb::kFmtQ4, op + (int64_t)t * k * out_n1, k, out_n1,
+               T1(uint32_t, w), w_n0, T1(uint16_t, scales), ip + (int64_t)t * ids_n1,
+               ids_n1, xp + (int64_t)t * x_n1, x_n1, k, rows, cols, experts);
+}
+#undef FN
+
+#define FN "nn_moe_down_q4_add_rows"
+void vx_nn_moe_down_q4_add_rows(VX_TENSOR2(y), VX_TENSOR1(w), VX_TENSOR1(scales),
+                                VX_TENSOR2(ids), VX_TENSOR2(weights), VX_TENSOR2(h),
+                                int32_t n, int32_t k, int32_t rows, int32_t cols,
+                                int32_t experts) {
+  UNUSED_ALLOC(y); UNUSED_ALLOC(w); UNUSED_ALLOC(scales); UNUSED_ALLOC(ids);
+  UNUSED_ALLOC(weights); UNUSED_ALLOC(h);
+  if (k <= 0 || n <= 0 || ids_n0 < n || ids_n1 < k || weights_n0 < n ||
+      weights_n1 < k || h_n0 < (int64_t)n * k || h_n1 < cols || y_n0 < n)
+    stop("nn_moe_down_q4_add_rows: `ids` and `weights` need n rows of k values, `h` "
+         "a row of cols values for each of the n * k, and `y` n rows");
+  if (cols <= 0 || cols % 32 != 0 ||
+      scales_n0 < (int64_t)experts * rows * (cols / 32))
+    stop("nn_moe_down_q4_add_rows: the scales are too few for the experts");
+  float *yp = T2(float, y);
+  const int32_t *ip = T2(int32_t, ids);
+  const float *wp = T2(float, weights), *hp = T2(float, h);
+  for (int t = 0; t < n; ++t)
+    moe_down_add(FN, vxb::kFmtQ4, yp + (int64_t)t * y_n1, y_n1, T1(uint32_t, w),
+                 w_n0, T1(uint16_t, scales), ip + (int64_t)t * ids_n1, ids_n1,
+                 wp + (int64_t)t * weights_n1, weights_n1,
+                 hp + (int64_t)t * k * h_n1, k, h_n1, k, rows, cols, experts);
+}
+#undef FN
+
+/* ------------------------------------------- pairs grouped by expert
+ * nn_moe_group_count nn.vx:1070, nn_moe_group_offsets :1110,
+ * nn_moe_group_place :1252, nn_moe_group :1287. The asserts of those functions
+ * are the checks here. */
+#define FN "nn_moe_group_count"
+void vx_nn_moe_group_count(VX_TENSOR2(counts), VX_TENSOR1(ids), int32_t n,
+                           int32_t experts) {
+  UNUSED_ALLOC(counts); UNUSED_ALLOC(ids);
+  if (experts <= 0 || experts > 1024 || n < 0 || n > ids_n0)
+    stop("nn_moe_group_count: `experts` must be 1 to 1024, and `ids` needs n values");
+  if (counts_n0 * 256 < n || counts_n1 < experts)
+    stop("nn_moe_group_count: `counts` needs a row for each 256 pairs, and a column "
+         "for each expert");
+  must(vxb::moe_group_count(T2(int32_t, counts), counts_n1, T1(int32_t, ids), n,
+                            experts, vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+#define FN "nn_moe_group_offsets"
+void vx_nn_moe_group_offsets(VX_TENSOR2(base), VX_TENSOR1(starts),
+                             VX_TENSOR1(tile_expert), VX_TENSOR1(order),
+                             VX_TENSOR2(counts), int32_t n, int32_t experts,
+                             int32_t align) {
+  UNUSED_ALLOC(base); UNUSED_ALLOC(starts); UNUSED_ALLOC(tile_expert);
+  UNUSED_ALLOC(order); UNUSED_ALLOC(counts);
+  if (experts <= 0 || experts > 1024 || align <= 0 || n < 0)
+    stop("nn_moe_group_offsets: `experts` must be 1 to 1024, and `align` above 0");
+  if (starts_n0 <= experts || counts_n0 * 256 < n || counts_n1 < experts ||
+      base_n0 * 256 < n || base_n1 < experts)
+    stop("nn_moe_group_offsets: `starts` needs experts + 1 values, and `counts` and "
+         "`base` a row for each 256 pairs");
+  if (order_n0 < (int64_t)n + (int64_t)experts * (align - 1) ||
+      tile_expert_n0 * align < order_n0 || order_n0 > INT32_MAX ||
+      tile_expert_n0 > INT32_MAX)
+    stop("nn_moe_group_offsets: `order` needs n + experts * (align - 1) positions, "
+         "and `tile_expert` one for each align of them");
+  must(vxb::moe_group_offsets(T2(int32_t, base), base_n1, T1(int32_t, starts),
+                              T1(int32_t, tile_expert), (int)tile_expert_n0,
+                              T1(int32_t, order), (int)order_n0,
+                              T2(int32_t, counts), counts_n1, n, experts, align,
+                              vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+#define FN "nn_moe_group_place"
+void vx_nn_moe_group_place(VX_TENSOR1(order), VX_TENSOR1(ids), VX_TENSOR2(base),
+                           int32_t n) {
+  UNUSED_ALLOC(order); UNUSED_ALLOC(ids); UNUSED_ALLOC(base);
+  if (n < 0 || n > ids_n0 || base_n0 * 256 < n || order_n0 < n ||
+      order_n0 > INT32_MAX)
+    stop("nn_moe_group_place: `ids` needs n values, and `base` a row for each 256 "
+         "pairs");
+  /* the columns of `base` bound the ids; nn_moe_group_count has refused an id
+     that names no expert */
+  const int experts = base_n1 > 1024 ? 1024 : (int)base_n1;
+  must(vxb::moe_group_place(T1(int32_t, order), (int)order_n0, T1(int32_t, ids),
+                            T2(int32_t, base), base_n1, n, experts,
+                            vxb::caller_stream()),
+       FN);
+}
+#undef FN
+
+#define PASS1(t) t##_allocated, t##_aligned, t##_offset, t##_n0, t##_s0
+#define PASS2(t) t##_allocated, t##_aligned, t##_offset, t##_n0, t##_n1, t##_s0, t##_s1
+void vx_nn_moe_group(VX_TENSOR1(order), VX_TENSOR2(counts), VX_TENSOR2(base),
+                     VX_TENSOR1(starts), VX_TENSOR1(tile_expert), VX_TENSOR1(ids),
+                     int32_t experts, int32_t align) {
+  if (ids_n0 > INT32_MAX)
+    stop("nn_moe_group: too many pairs");
+  const int32_t n = (int32_t)ids_n0;
+  vx_nn_moe_group_count(PASS2(counts), PASS1(ids), n, experts);
+  vx_nn_moe_group_offsets(PASS2(base), PASS1(starts), PASS1(tile_expert),
+                          PASS1(order), PASS2(counts), n, experts, align);
+  vx_nn_moe_group_place(PASS1(order), PASS1(ids), PASS2(base), n);
+}
+#undef PASS1
+#undef PASS2
+
 } /* extern "C" */
 
 extern "C" {
@@ -839,7 +1028,8 @@ int32_t vx_b200_kernel_status(void) {
   const int m = vxb::batched_proj_status(vxb::caller_stream());
   const int r = vxb::rows_status();
   const int s = vxb::step_status(vxb::caller_stream());
-  return g ? g : (f ? f : (t ? t : (m ? m : (r ? r : s))));
+  const int e = vxb::moe_group_status(vxb::caller_stream());
+  return g ? g : (f ? f : (t ? t : (m ? m : (r ? r : (s ? s : e)))));
 }
 
 int32_t vx_b200_attention_kernel(int32_t which) {

@@ -885,11 +885,16 @@ attention_decode_kernel(const AttnArgs a) {
  * values counts the keys above its own, which is its place. Then the softmax
  * over the k values, summed in the order of their places. One block. */
 __global__ void __launch_bounds__(256)
-top_k_kernel(int32_t *ids, float *weights, const float *logits, int n, int k) {
+top_k_kernel(int32_t *ids, float *weights, const float *logits, int n, int k,
+             int64_t ids_pitch, int64_t weights_pitch, int64_t logits_pitch) {
   __shared__ long long keys[256];
   __shared__ int order[256];
   chain_release();
   chain_wait();
+  /* nn_top_k_rows (nn.vx:2897-2929): a block per position, the same arithmetic */
+  ids += blockIdx.x * ids_pitch;
+  weights += blockIdx.x * weights_pitch;
+  logits += blockIdx.x * logits_pitch;
   const int i = threadIdx.x;
   if (i < n) {
     const int bits = __float_as_int(logits[i]);
@@ -1267,10 +1272,19 @@ const char *attention_decode_clustered(const AttnArgs &a, cudaStream_t stream) {
 
 const char *top_k(int32_t *ids, float *weights, const float *logits, int n, int k,
                   cudaStream_t stream) {
+  return top_k_rows(ids, weights, logits, 1, n, k, 0, 0, 0, stream);
+}
+
+const char *top_k_rows(int32_t *ids, float *weights, const float *logits,
+                       int positions, int n, int k, int64_t ids_pitch,
+                       int64_t weights_pitch, int64_t logits_pitch,
+                       cudaStream_t stream) {
   if (n < 1 || n > 256 || k < 1 || k > n)
     return "n must be 1 to 256, and k must be 1 to n";
-  launch_chained(top_k_kernel, dim3(1), dim3(256), 0, stream, ids, weights, logits,
-                 n, k);
+  if (positions < 1)
+    return nullptr;
+  launch_chained(top_k_kernel, dim3(positions), dim3(256), 0, stream, ids, weights,
+                 logits, n, k, ids_pitch, weights_pitch, logits_pitch);
   return check_launch("the router launch");
 }
 

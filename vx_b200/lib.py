@@ -38,6 +38,10 @@ EXTRA_SYMBOLS = [
     "vx_nn_qkv_q4", "vx_nn_swiglu_q4",
     "vx_nn_matvec_rows", "vx_nn_matvec_q4_rows", "vx_nn_rms_norm_rows",
     "vx_nn_argmax_rows", "vx_nn_embed_rows",
+    "vx_nn_top_k_rows", "vx_nn_matvec_q4_heads_add_rows", "vx_nn_qkv_q4_rows",
+    "vx_nn_moe_swiglu_q4_rows", "vx_nn_moe_down_q4_add_rows",
+    "vx_nn_moe_group_count", "vx_nn_moe_group_offsets", "vx_nn_moe_group_place",
+    "vx_nn_moe_group",
     "vx_nn_top_k", "vx_nn_moe_swiglu", "vx_nn_moe_down_add", "vx_nn_moe_swiglu_q4",
     "vx_nn_moe_down_q4_add",
     "vx_decoder_create", "vx_decoder_destroy", "vx_decoder_reset",

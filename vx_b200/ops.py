@@ -242,3 +242,51 @@ def nn_moe_down_add(y, w, ids, weights, h, k, rows, cols, experts, scales=None):
     else:
         _call("vx_nn_moe_down_q4_add", y, w, scales, ids, weights, h, C.c_int32(k),
               C.c_int32(rows), C.c_int32(cols), C.c_int32(experts))
+
+
+# ---- the experts and the quantised projections of n positions -----------------------
+def _i32(*values):
+    return [C.c_int32(v) for v in values]
+
+
+def nn_top_k_rows(ids, weights, logits, n, count, k):
+    _call("vx_nn_top_k_rows", ids, weights, logits, *_i32(n, count, k))
+
+
+def nn_matvec_q4_heads_add_rows(y, w, scales, x, n, rows, heads, head_dim):
+    _call("vx_nn_matvec_q4_heads_add_rows", y, w, scales, x,
+          *_i32(n, rows, heads, head_dim))
+
+
+def nn_qkv_q4_rows(q, k, v, w, scales, b, x, n, q_heads, kv_heads, head_dim, cols):
+    _call("vx_nn_qkv_q4_rows", q, k, v, w, scales, b, x,
+          *_i32(n, q_heads, kv_heads, head_dim, cols))
+
+
+def nn_moe_swiglu_q4_rows(out, w, scales, ids, x, n, k, rows, cols, experts):
+    _call("vx_nn_moe_swiglu_q4_rows", out, w, scales, ids, x,
+          *_i32(n, k, rows, cols, experts))
+
+
+def nn_moe_down_q4_add_rows(y, w, scales, ids, weights, h, n, k, rows, cols, experts):
+    _call("vx_nn_moe_down_q4_add_rows", y, w, scales, ids, weights, h,
+          *_i32(n, k, rows, cols, experts))
+
+
+# ---- pairs grouped by expert --------------------------------------------------------
+def nn_moe_group_count(counts, ids, n, experts):
+    _call("vx_nn_moe_group_count", counts, ids, *_i32(n, experts))
+
+
+def nn_moe_group_offsets(base, starts, tile_expert, order, counts, n, experts, align):
+    _call("vx_nn_moe_group_offsets", base, starts, tile_expert, order, counts,
+          *_i32(n, experts, align))
+
+
+def nn_moe_group_place(order, ids, base, n):
+    _call("vx_nn_moe_group_place", order, ids, base, *_i32(n))
+
+
+def nn_moe_group(order, counts, base, starts, tile_expert, ids, experts, align):
+    _call("vx_nn_moe_group", order, counts, base, starts, tile_expert, ids,
+          *_i32(experts, align))
