@@ -349,6 +349,32 @@ int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,
                                 void *out, int32_t B, int32_t H, int32_t S,
                                 int32_t D, float scale, int32_t causal);
 
+/* The Q4_0 experts of n positions on the tensor cores, fed by the grouping:
+   order and tile_expert are vx_nn_moe_group's outputs for the n * k ids (row t
+   of a packed [n, k] tensor is pairs t * k .. t * k + k - 1) with `align` 8 or
+   16, and tiles the length of tile_expert (tiles * align >= n * k + experts *
+   (align - 1)). An expert's sixteen rows are unpacked once for all pairs of a
+   tile. Plain device pointers, packed rows: x [n, cols], out [n * k, rows]; for
+   the down projection h [n * k, cols], weights [n * k], y [n, rows] (added to,
+   a position's k experts in slot order) and a scratch of n * k * rows floats.
+   The arithmetic of nn_moe_swiglu_q4_rows / nn_moe_down_q4_add_rows
+   (nn.vx:2958, 3066) in another order of sums: results agree with the
+   vx_nn_*_rows exports within rounding, not bit for bit. rows a multiple of 8,
+   cols of 32 (fastest with cols a multiple of 128). */
+int32_t vx_b200_moe_swiglu_q4_grouped(float *out, const uint32_t *w,
+                                      const uint16_t *scales, const int32_t *order,
+                                      const int32_t *tile_expert, int32_t tiles,
+                                      int32_t align, const float *x, int32_t n,
+                                      int32_t k, int32_t rows, int32_t cols,
+                                      int32_t experts);
+int32_t vx_b200_moe_down_q4_add_grouped(float *y, const uint32_t *w,
+                                        const uint16_t *scales, const int32_t *order,
+                                        const int32_t *tile_expert, int32_t tiles,
+                                        int32_t align, const float *weights,
+                                        const float *h, float *scratch, int32_t n,
+                                        int32_t k, int32_t rows, int32_t cols,
+                                        int32_t experts);
+
 /* Which kernel vx_nn_attention and the decoder's attention run from now on:
    1 = the parts of a head merged inside a thread-block cluster (no scratch
    used; the default), 2 = the reference's scheme (nn.vx:343-368, 823-866):

@@ -8,6 +8,7 @@ larger than the 126 MB L2 where DRAM figures matter).
   python microbench.py attn    [--pos 600]
   python microbench.py shard   [--ranks 8] [--pos 520]
   python microbench.py prefill [--layers 4]
+  python microbench.py moe     [--n 512]
 Each prints one JSON line with the CUDA-event time per launch.
 """
 import argparse
@@ -231,11 +232,91 @@ def prefill(torch, args):
                 ms=best, ms_per_layer=best / args.layers, status=ops.kernel_status())
 
 
+def moe(torch, args):
+    """The experts of a mixture-of-experts layer for --n positions: 8 experts of
+    14336 x 4096 in Q4_0, 2 a position. The router, the grouping by expert, and
+    the two expert projections: grouped on the tensor cores, and position by
+    position through the one-position kernels."""
+    experts, k, dim, inter, n = 8, 2, 4096, 14336, args.n
+    logits = abi.DeviceTensor.empty((n, experts), abi.F32)
+    ops.fill_normal(logits, 7, 1.0)
+    ids = abi.DeviceTensor.empty((n, k), abi.I32)
+    wts = abi.DeviceTensor.empty((n, k), abi.F32)
+    x = abi.DeviceTensor.empty((n, dim), abi.F32)
+    ops.fill_normal(x, 8, 1.0)
+    y = abi.DeviceTensor.empty((n, dim), abi.F32)
+    ops.fill_normal(y, 9, 1.0)
+
+    def q4_experts(rows, cols, seed):
+        codes = abi.DeviceTensor.empty((experts * rows * cols // 8,), abi.I32)
+        scales = abi.DeviceTensor.empty((experts * rows * (cols // 32),), abi.F16)
+        src = abi.DeviceTensor.empty((rows * cols,), abi.BF16)
+        for e in range(experts):
+            ops.fill_normal(src, seed + e, 0.02)
+            rc = lib().vx_b200_quantize(
+                3, src.ptr, rows, cols, codes.ptr + e * rows * cols // 2,
+                scales.ptr + e * rows * (cols // 32) * 2)
+            assert rc == 0
+        src.free()
+        return codes, scales
+    gu, gu_s = q4_experts(2 * inter, dim, 100)
+    dn, dn_s = q4_experts(dim, inter, 200)
+    pairs = n * k
+    blocks = (pairs + 255) // 256
+    counts = abi.DeviceTensor.empty((blocks, experts), abi.I32)
+    base = abi.DeviceTensor.empty((blocks, experts), abi.I32)
+    starts = abi.DeviceTensor.empty((experts + 1,), abi.I32)
+    mid = abi.DeviceTensor.empty((pairs, inter), abi.F32)
+    mid_rows = abi.DeviceTensor.empty((pairs, inter), abi.F32)
+    scratch = abi.DeviceTensor.empty((pairs, dim), abi.F32)
+    flat = ids.view(0, (pairs,))
+    stream = torch.cuda.Stream()
+    t_router = _timed(torch, stream,
+                      lambda: ops.nn_top_k_rows(ids, wts, logits, n, experts, k), args.iters)
+    grouped = {}
+    for align in (8, 16):
+        room = pairs + experts * (align - 1)
+        order = abi.DeviceTensor.empty((room,), abi.I32)
+        tile_expert = abi.DeviceTensor.empty(((room + align - 1) // align,), abi.I32)
+        t_group = _timed(torch, stream,
+                         lambda: ops.nn_moe_group(order, counts, base, starts, tile_expert,
+                                                  flat, experts, align), args.iters)
+        t_up = _timed(torch, stream,
+                      lambda: ops.moe_swiglu_q4_grouped(mid, gu, gu_s, order, tile_expert,
+                                                        align, x, n, k, inter, dim,
+                                                        experts), args.iters)
+        t_down = _timed(torch, stream,
+                        lambda: ops.moe_down_q4_add_grouped(
+                            y, dn, dn_s, order, tile_expert, align, wts.view(0, (pairs,)),
+                            mid, scratch, n, k, dim, inter, experts), args.iters)
+        grouped[align] = (t_group, t_up, t_down)
+    t_group, t_up, t_down = grouped[16]
+    t_up_rows = _timed(torch, stream,
+                       lambda: ops.nn_moe_swiglu_q4_rows(mid_rows, gu, gu_s, ids, x, n, k,
+                                                         inter, dim, experts), 1)
+    t_down_rows = _timed(torch, stream,
+                         lambda: ops.nn_moe_down_q4_add_rows(y, dn, dn_s, ids, wts,
+                                                             mid_rows, n, k, dim, inter,
+                                                             experts), 1)
+    a, b = mid.to_host(), mid_rows.to_host()
+    flop = 2.0 * pairs * 3 * inter * dim
+    weight_bytes = experts * 3 * inter * dim * (0.5 + 2.0 / 32)
+    return dict(kernel="experts of %d positions: 8 x (14336 x 4096) Q4_0, 2 a position" % n,
+                router_us=t_router * 1e3, group_us=t_group * 1e3,
+                swiglu_grouped_ms=t_up, down_grouped_ms=t_down,
+                swiglu_grouped_align8_ms=grouped[8][1], down_grouped_align8_ms=grouped[8][2],
+                swiglu_rows_ms=t_up_rows, down_rows_ms=t_down_rows,
+                grouped_tflops=flop / ((t_up + t_down) * 1e-3) / 1e12,
+                weights_gb=weight_bytes / 1e9,
+                grouped_vs_rows_max_rel=float(np.abs(a - b).max() / np.abs(b).max()),
+                status=ops.kernel_status())
+
+
 def main():
     import torch
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["rowdot", "gemm", "flash", "attn", "decode16",
-                                     "shard", "prefill"])
+                                     "shard", "prefill", "moe"])
     ap.add_argument("--ranks", type=int, default=8)
     ap.add_argument("--fmt", default="bf16", choices=["bf16", "fp8", "q4", "f32"])
     ap.add_argument("--layers", type=int, default=4)
@@ -249,7 +330,7 @@ def main():
     torch.cuda.set_device(0)
     print(json.dumps(dict(rowdot=rowdot, gemm=gemm, flash=flash, attn=attn,
                           decode16=decode16, shard=shard,
-                          prefill=prefill)[args.case](torch, args)))
+                          prefill=prefill, moe=moe)[args.case](torch, args)))
 
 
 if __name__ == "__main__":

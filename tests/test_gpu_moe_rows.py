@@ -217,3 +217,95 @@ def test_experts_of_n_positions(oracle):
     used = np.count_nonzero(np.diff(got["starts"]))
     assert used == np.unique(flat).size and 4 < used < 16
     assert ops.kernel_status() == 0
+
+
+def grouped_layer(oracle, n, experts, k, inter, hidden, seed, align):
+    """Router -> grouping in tiles of `align` -> the two expert projections on the
+    tensor cores; returns what the f64 check needs."""
+    logits = oracle.random_f32(n * experts, seed, 2.0).reshape(n, experts)
+    tid, tw = empty((n, k)), empty((n, k), abi.F32)
+    ops.nn_top_k_rows(tid, tw, dev(logits), n, experts, k)
+    ids, weights = tid.to_host(), tw.to_host()
+    gu, gu_s = oracle.quant_inputs("q4", experts * 2 * inter, hidden, seed + 1)
+    dn, dn_s = oracle.quant_inputs("q4", experts * hidden, inter, seed + 3)
+    x = oracle.random_f32(n * hidden, seed + 5, 1.0).reshape(n, hidden)
+    y0 = oracle.random_f32(n * hidden, seed + 6, 1.0).reshape(n, hidden)
+    pairs = n * k
+    room = pairs + experts * (align - 1)
+    tiles = (room + align - 1) // align
+    blocks = (pairs + 255) // 256
+    order, tile_expert = empty((room,)), empty((tiles,))
+    ops.nn_moe_group(order, empty((blocks, experts)), empty((blocks, experts)),
+                     empty((experts + 1,)), tile_expert, tid.view(0, (pairs,)), experts,
+                     align)
+    t_gu, t_gus, t_dn, t_dns = dev(gu), dev(gu_s), dev(dn), dev(dn_s)
+    mid = dev(np.full((pairs, inter), np.nan, np.float32))
+    ops.moe_swiglu_q4_grouped(mid, t_gu, t_gus, order, tile_expert, align, dev(x), n, k,
+                              inter, hidden, experts)
+    ty = dev(y0)
+    scratch = dev(np.full((pairs, hidden), np.nan, np.float32))
+    ops.moe_down_q4_add_grouped(ty, t_dn, t_dns, order, tile_expert, align,
+                                tw.view(0, (pairs,)), mid, scratch, n, k, hidden, inter,
+                                experts)
+    return dict(ids=ids, weights=weights, gu=gu, gu_s=gu_s, dn=dn, dn_s=dn_s, x=x, y0=y0,
+                mid=mid.to_host(), y=ty.to_host(), dev=(t_gu, t_gus, t_dn, t_dns, tid, tw))
+
+
+@pytest.mark.parametrize("align", [8, 16])
+@pytest.mark.parametrize("n,experts,k,inter,hidden", [
+    (5, 16, 4, 64, 256),        # the reference test's sizes
+    (40, 8, 2, 352, 1056),      # two column chunks, the second of 32 columns
+    (24, 8, 2, 128, 1408),      # columns in steps of 128; 1408 = 1024 + 384
+    (3, 4, 1, 32, 32)])         # one group of columns, tiles mostly padding
+def test_grouped_experts_against_f64_loops(oracle, n, experts, k, inter, hidden, align):
+    r = grouped_layer(oracle, n, experts, k, inter, hidden, 61, align)
+    ids, weights = r["ids"], r["weights"]
+    for t in range(n):
+        gate_up = oracle.quant_dot_f64("q4", r["gu"], r["gu_s"], r["x"][t],
+                                       experts * 2 * inter, hidden)
+        want_y = r["y0"][t].astype(np.float64)
+        for e in range(k):
+            at = ids[t, e] * 2 * inter
+            g, u = gate_up[at:at + inter], gate_up[at + inter:at + 2 * inter]
+            close(r["mid"][t * k + e], g / (1.0 + np.exp(-g)) * u)
+            down = oracle.quant_dot_f64("q4", r["dn"], r["dn_s"], r["mid"][t * k + e],
+                                        experts * hidden, inter)
+            want_y += float(weights[t, e]) * down[ids[t, e] * hidden:
+                                                  (ids[t, e] + 1) * hidden]
+        close(r["y"][t], want_y)
+    # and next to the position-by-position exports, which sum in another order
+    t_gu, t_gus, t_dn, t_dns, tid, tw = r["dev"]
+    mid_rows = empty((n * k, inter), abi.F32)
+    ops.nn_moe_swiglu_q4_rows(mid_rows, t_gu, t_gus, tid, dev(r["x"]), n, k, inter, hidden,
+                              experts)
+    close(r["mid"].ravel(), mid_rows.to_host().ravel(), 2e-5)
+    assert ops.kernel_status() == 0
+
+
+@pytest.mark.parametrize("align", [8, 16])
+def test_grouped_down_projection_with_a_last_tile_of_eight_rows(oracle, align):
+    """40 output rows: two 16-row tiles and a half one."""
+    n, experts, k, rows, cols = 9, 3, 2, 40, 96
+    ids = np.array([[(t + e) % experts for e in range(k)] for t in range(n)], np.int32)
+    weights = (np.float32(0.3) + oracle.random_f32(n * k, 71, 0.2)).reshape(n, k)
+    dn, dn_s = oracle.quant_inputs("q4", experts * rows, cols, 72)
+    h = oracle.random_f32(n * k * cols, 73, 1.0).reshape(n * k, cols)
+    y0 = oracle.random_f32(n * rows, 74, 1.0).reshape(n, rows)
+    pairs, room = n * k, n * k + experts * (align - 1)
+    tiles = (room + align - 1) // align
+    order, tile_expert = empty((room,)), empty((tiles,))
+    ops.nn_moe_group(order, empty((1, experts)), empty((1, experts)),
+                     empty((experts + 1,)), tile_expert, dev(ids).view(0, (pairs,)),
+                     experts, align)
+    ty = dev(y0)
+    ops.moe_down_q4_add_grouped(ty, dev(dn), dev(dn_s), order, tile_expert, align,
+                                dev(weights).view(0, (pairs,)), dev(h),
+                                empty((pairs, rows), abi.F32), n, k, rows, cols, experts)
+    got = ty.to_host()
+    for t in range(n):
+        want = y0[t].astype(np.float64)
+        for e in range(k):
+            down = oracle.quant_dot_f64("q4", dn, dn_s, h[t * k + e], experts * rows, cols)
+            want += float(weights[t, e]) * down[ids[t, e] * rows:(ids[t, e] + 1) * rows]
+        close(got[t], want)
+    assert ops.kernel_status() == 0

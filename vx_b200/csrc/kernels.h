@@ -379,6 +379,25 @@ const char *moe_group_offsets(int32_t *base, int64_t base_pitch, int32_t *starts
 const char *moe_group_place(int32_t *order, int room, const int32_t *ids,
                             const int32_t *base, int64_t pitch, int n, int experts,
                             cudaStream_t stream);
+/* The Q4_0 experts of n positions on the tensor cores (moe_grouped.cu), an
+   expert's rows unpacked once for each tile of `align` (8 or 16) pairs. order
+   and tile_expert: nn_moe_group's, with that align, of the n * k ids. */
+struct MoeGroupedArgs {
+  const void *w, *scales;       /* all experts, one matrix after another */
+  const int32_t *order, *tile_expert;
+  int tiles, align;
+  const float *x;               /* swiglu: [n, cols]; down: [n * k, cols] */
+  int64_t x_pitch;
+  float *out;                   /* swiglu: [n * k, rows] */
+  int64_t out_pitch;
+  float *y;                     /* down: [n, rows], added to */
+  int64_t y_pitch;
+  const float *pair_weights;    /* down: [n * k], the router's weights */
+  float *scratch;               /* down: n * k * rows values */
+  int n, k, rows, cols, experts;
+};
+const char *moe_swiglu_q4_grouped(const MoeGroupedArgs &m, cudaStream_t stream);
+const char *moe_down_q4_add_grouped(const MoeGroupedArgs &m, cudaStream_t stream);
 /* 0, or once 0x6E after an id that named no expert (0x6F: a `base` that sent a
    pair outside `order`); waits for the stream. */
 int moe_group_status(cudaStream_t stream);

@@ -1021,6 +1021,61 @@ int32_t vx_b200_gemm(int32_t dtype, int32_t route, int64_t m, int64_t n,
   }
 }
 
+int32_t vx_b200_moe_swiglu_q4_grouped(float *out, const uint32_t *w,
+                                      const uint16_t *scales, const int32_t *order,
+                                      const int32_t *tile_expert, int32_t tiles,
+                                      int32_t align, const float *x, int32_t n,
+                                      int32_t k,
+                                      int32_t rows, int32_t cols, int32_t experts) {
+  vxb::MoeGroupedArgs m{};
+  m.w = w;
+  m.scales = scales;
+  m.order = order;
+  m.tile_expert = tile_expert;
+  m.tiles = tiles;
+  m.align = align;
+  m.x = x;
+  m.x_pitch = cols;
+  m.out = out;
+  m.out_pitch = rows;
+  m.n = n;
+  m.k = k;
+  m.rows = rows;
+  m.cols = cols;
+  m.experts = experts;
+  return done(vxb::moe_swiglu_q4_grouped(m, vxb::caller_stream()),
+              "moe_swiglu_q4_grouped");
+}
+
+int32_t vx_b200_moe_down_q4_add_grouped(float *y, const uint32_t *w,
+                                        const uint16_t *scales, const int32_t *order,
+                                        const int32_t *tile_expert, int32_t tiles,
+                                        int32_t align, const float *weights,
+                                        const float *h,
+                                        float *scratch, int32_t n, int32_t k,
+                                        int32_t rows, int32_t cols, int32_t experts) {
+  vxb::MoeGroupedArgs m{};
+  m.w = w;
+  m.scales = scales;
+  m.order = order;
+  m.tile_expert = tile_expert;
+  m.tiles = tiles;
+  m.align = align;
+  m.x = h;
+  m.x_pitch = cols;
+  m.y = y;
+  m.y_pitch = rows;
+  m.pair_weights = weights;
+  m.scratch = scratch;
+  m.n = n;
+  m.k = k;
+  m.rows = rows;
+  m.cols = cols;
+  m.experts = experts;
+  return done(vxb::moe_down_q4_add_grouped(m, vxb::caller_stream()),
+              "moe_down_q4_add_grouped");
+}
+
 int32_t vx_b200_kernel_status(void) {
   const int g = vxb::gemm_status(vxb::caller_stream());
   const int f = vxb::flash_status(vxb::caller_stream());

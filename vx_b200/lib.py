@@ -54,6 +54,7 @@ EXTRA_SYMBOLS = [
     "vx_b200_flash_attention", "vx_b200_gemm_column_split",
     "vx_b200_fill_normal", "vx_b200_fill_uniform", "vx_b200_quantize",
     "vx_b200_attention_decode_static", "vx_b200_attention_kernel",
+    "vx_b200_moe_swiglu_q4_grouped", "vx_b200_moe_down_q4_add_grouped",
 ]
 
 _lib = None
@@ -178,6 +179,10 @@ def lib():
     L.vx_decoder_from_llama2c.argtypes = [C.c_char_p, i32, i32]
     L.vx_b200_attention_kernel.restype = i32
     L.vx_b200_attention_kernel.argtypes = [i32]
+    L.vx_b200_moe_swiglu_q4_grouped.restype = i32
+    L.vx_b200_moe_swiglu_q4_grouped.argtypes = [vp] * 5 + [i32, i32, vp] + [i32] * 5
+    L.vx_b200_moe_down_q4_add_grouped.restype = i32
+    L.vx_b200_moe_down_q4_add_grouped.argtypes = [vp] * 5 + [i32, i32, vp, vp, vp] + [i32] * 5
     _lib = L
     return L
 

@@ -290,3 +290,19 @@ def nn_moe_group_place(order, ids, base, n):
 def nn_moe_group(order, counts, base, starts, tile_expert, ids, experts, align):
     _call("vx_nn_moe_group", order, counts, base, starts, tile_expert, ids,
           *_i32(experts, align))
+
+
+def moe_swiglu_q4_grouped(out, w, scales, order, tile_expert, align, x, n, k, rows,
+                          cols, experts):
+    """The SwiGLU inputs of the experts of n positions, pairs grouped by
+    nn_moe_group with `align` 8 or 16 (tile_expert gives the number of tiles)."""
+    check(lib().vx_b200_moe_swiglu_q4_grouped(
+        out.ptr, w.ptr, scales.ptr, order.ptr, tile_expert.ptr, tile_expert.count,
+        align, x.ptr, n, k, rows, cols, experts))
+
+
+def moe_down_q4_add_grouped(y, w, scales, order, tile_expert, align, weights, h,
+                            scratch, n, k, rows, cols, experts):
+    check(lib().vx_b200_moe_down_q4_add_grouped(
+        y.ptr, w.ptr, scales.ptr, order.ptr, tile_expert.ptr, tile_expert.count,
+        align, weights.ptr, h.ptr, scratch.ptr, n, k, rows, cols, experts))
