@@ -22,6 +22,13 @@
  *   C (16 x 8, f32)    the 32 columns of a group; times the group's two scales
  *                      it is added to the lane's running sums.
  *
+ * A warp carries two 16-row tiles, so a B fragment read from shared memory
+ * feeds both. Its codes come 128 columns at a time through a small buffer of
+ * its own (cp.async, 16 bytes a lane, the next step in flight under the
+ * current one) and are read back a word a lane: asked for straight from global
+ * memory, a word a lane is sixteen rows of 16 bytes per load, and the load
+ * pipe, not the tensor pipe, set the pace (81 % against 38 % busy).
+ *
  * SwiGLU takes rows 0-7 of A from the gate matrix and rows 8-15 from the up
  * matrix, so a lane ends with the gate and the up value of the same (row,
  * pair) and finishes in registers. The down projection writes weight * dot for
@@ -44,12 +51,22 @@
 namespace vxb {
 namespace {
 
-constexpr int kWarps = 8;          /* a warp carries one tile of 16 rows */
-constexpr int kChunk = 1024;       /* columns staged at a time */
+constexpr int kWarps = 8;
+constexpr int kRowTiles = 2;       /* 16-row tiles a warp carries: they share B */
+constexpr int kChunk = 512;        /* columns staged at a time: 16 groups */
 /* a pair's terms of a chunk, padded so that the two pairs a quarter-warp reads
    together fall in different banks */
 constexpr int kTermStride = kChunk * 2 + 64;
-constexpr int smem_bytes(int pairs) { return 3 * pairs * kTermStride; }
+/* A warp's weights of one step (128 columns of its 32 rows) pass through shared
+   memory: 64 bytes a row, rows 80 bytes apart so that the eight rows a load
+   touches fall in different banks; two steps in flight. */
+constexpr int kRowStride = 80;
+constexpr int kStepBytes = 2 * kRowTiles * 8 * kRowStride;
+static_assert(kChunk == 4 * 128, "lane t of a row keeps the scales of step t: four steps a chunk");
+constexpr int kWarpBytes = 2 * kStepBytes;
+constexpr int smem_bytes(int pairs) {
+  return 3 * pairs * kTermStride + kWarps * kWarpBytes;
+}
 
 struct GroupedArgs {
   const uint32_t *w;          /* all experts, [experts * expert_rows, cols / 8] */
@@ -64,7 +81,8 @@ struct GroupedArgs {
   const float *pair_scale;    /* down: the router's weight of pair p */
   int pairs, rows, cols, experts;
   int64_t expert_rows;        /* 2 * rows (gate then up) or rows */
-  int four_groups;            /* cols % 128 == 0 and the scales 8-byte aligned */
+  int four_groups;            /* cols % 128 == 0, codes 16-byte and scales 8-byte
+                                 aligned: 128 columns a step through shared memory */
 };
 
 __device__ __forceinline__ void mma_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1,
@@ -90,8 +108,8 @@ __device__ __forceinline__ unsigned short bf16_bits(float v) {
 __device__ __forceinline__ float bf16_value(unsigned short b) {
   return __uint_as_float((uint32_t)b << 16);
 }
-__device__ __forceinline__ float half_value(unsigned short b) {
-  return __half2float(__ushort_as_half(b));
+__device__ __forceinline__ float half_value(uint32_t b) {
+  return __half2float(__ushort_as_half((unsigned short)b));
 }
 
 /* v = t[0] + t[1] + t[2] exactly (24 bits of mantissa in three times 8) */
@@ -103,12 +121,26 @@ __device__ __forceinline__ void three_bf16(float v, unsigned short (&t)[3]) {
   t[2] = bf16_bits(r2);
 }
 
+__device__ __forceinline__ void copy16_async(void *smem_dst, const void *src) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void copies_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int LEFT> __device__ __forceinline__ void copies_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(LEFT) : "memory");
+}
+
 /* NT: the tile's pairs in MMA columns of eight (1: align 8, 2: align 16). */
 template <bool SWIGLU, int NT>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 moe_grouped_kernel(const GroupedArgs a) {
   constexpr int PAIRS = 8 * NT;
-  extern __shared__ __align__(16) unsigned char terms[];
+  constexpr int M = kRowTiles;
+  extern __shared__ __align__(16) unsigned char smem[];
+  unsigned char *terms = smem;
   __shared__ int pair_of[PAIRS];
   chain_release();
   chain_wait();
@@ -118,68 +150,110 @@ moe_grouped_kernel(const GroupedArgs a) {
     return; /* past the last group: the whole block leaves together */
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
+  unsigned char *mine = smem + 3 * PAIRS * kTermStride + warp * kWarpBytes;
   if (threadIdx.x < PAIRS) {
     const int p = a.order[tile * PAIRS + threadIdx.x];
     pair_of[threadIdx.x] = p >= 0 && p < a.pairs ? p : -1;
   }
 
   const int words = a.cols / 8, groups = a.cols / 32;
-  /* the rows behind A rows g and g + 8 of this warp's 16-row tile */
+  /* The rows behind A rows g (h = 0) and g + 8 (h = 1) of each 16-row tile of
+     this warp. A tile past the end reads row 0 and is not written. */
   const int row_tiles = SWIGLU ? a.rows / 8 : (a.rows + 15) / 16;
-  const int rt = blockIdx.y * kWarps + warp;
-  const bool live = rt < row_tiles;
-  int64_t r0, r1;
-  if (SWIGLU) {
-    r0 = live ? rt * 8 + g : 0;
-    r1 = r0 + a.rows;
-  } else {
-    r0 = live ? rt * 16 + g : 0;
-    r1 = r0 + 8 < a.rows ? r0 + 8 : r0; /* a last tile of 8 rows */
-  }
-  const uint32_t *wa_row =
-      a.w + ((int64_t)expert * a.expert_rows + r0) * words + t;
-  const uint32_t *wb_row =
-      a.w + ((int64_t)expert * a.expert_rows + r1) * words + t;
-  const unsigned short *sa_row = reinterpret_cast<const unsigned short *>(a.scales) +
-                                 ((int64_t)expert * a.expert_rows + r0) * groups;
-  const unsigned short *sb_row = reinterpret_cast<const unsigned short *>(a.scales) +
-                                 ((int64_t)expert * a.expert_rows + r1) * groups;
-  float acc[NT][4];
+  bool live[M];
+  int64_t row[M][2];
+  const uint32_t *wrow[M][2];
+  const unsigned short *srow[M][2];
 #pragma unroll
-  for (int n = 0; n < NT; ++n)
-    acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+  for (int m = 0; m < M; ++m) {
+    const int rt = (blockIdx.y * kWarps + warp) * M + m;
+    live[m] = rt < row_tiles;
+    if (SWIGLU) {
+      row[m][0] = live[m] ? rt * 8 + g : 0;
+      row[m][1] = row[m][0] + a.rows;
+    } else {
+      row[m][0] = live[m] ? rt * 16 + g : 0;
+      row[m][1] = row[m][0] + 8 < a.rows ? row[m][0] + 8 : row[m][0]; /* a last tile of 8 rows */
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t r = (int64_t)expert * a.expert_rows + row[m][h];
+      wrow[m][h] = a.w + r * words;
+      srow[m][h] = reinterpret_cast<const unsigned short *>(a.scales) + r * groups;
+    }
+  }
+  const bool any = live[0]; /* tiles are handed out in order: the first is the test */
+  float acc[M][NT][4];
+#pragma unroll
+  for (int m = 0; m < M; ++m)
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+      acc[m][n][0] = acc[m][n][1] = acc[m][n][2] = acc[m][n][3] = 0.0f;
 
-  /* One group of 32 columns: the two words of this lane, the group's two
-     scales, group `q` of the staged chunk. */
-  auto group = [&](int q, uint32_t wa, uint32_t wb, float sa, float sb) {
-    constexpr uint32_t M = 0x000f000fu;
-    const uint32_t a00 = codes_to_bf16x2(wa & M), a80 = codes_to_bf16x2(wb & M);
-    const uint32_t a01 = codes_to_bf16x2((wa >> 4) & M),
-                   a81 = codes_to_bf16x2((wb >> 4) & M);
-    const uint32_t a02 = codes_to_bf16x2((wa >> 8) & M),
-                   a82 = codes_to_bf16x2((wb >> 8) & M);
-    const uint32_t a03 = codes_to_bf16x2((wa >> 12) & M),
-                   a83 = codes_to_bf16x2((wb >> 12) & M);
+  /* One group of 32 columns, group `q` of the staged chunk: this lane's word of
+     each of its four rows and the rows' scales. B is read once for both tiles. */
+  auto group = [&](int q, const uint32_t (&wd)[M][2], const float (&sc)[M][2]) {
+    constexpr uint32_t MASK = 0x000f000fu;
+    uint32_t ac[M][2][4];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          ac[m][h][i] = codes_to_bf16x2((wd[m][h] >> (4 * i)) & MASK);
+    float c[M][NT][4];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+        c[m][n][0] = c[m][n][1] = c[m][n][2] = c[m][n][3] = 0.0f;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
-      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int k = 0; k < 3; ++k) {
         const uint4 b = *reinterpret_cast<const uint4 *>(
             terms + (k * PAIRS + n * 8 + g) * kTermStride + q * 64 + t * 16);
-        mma_16x8x16(c, a00, a80, a01, a81, b.x, b.y);
-        mma_16x8x16(c, a02, a82, a03, a83, b.z, b.w);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          mma_16x8x16(c[m][n], ac[m][0][0], ac[m][1][0], ac[m][0][1], ac[m][1][1], b.x,
+                      b.y);
+          mma_16x8x16(c[m][n], ac[m][0][2], ac[m][1][2], ac[m][0][3], ac[m][1][3], b.z,
+                      b.w);
+        }
       }
-      acc[n][0] = fmaf(sa, c[0], acc[n][0]);
-      acc[n][1] = fmaf(sa, c[1], acc[n][1]);
-      acc[n][2] = fmaf(sb, c[2], acc[n][2]);
-      acc[n][3] = fmaf(sb, c[3], acc[n][3]);
     }
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        acc[m][n][0] = fmaf(sc[m][0], c[m][n][0], acc[m][n][0]);
+        acc[m][n][1] = fmaf(sc[m][0], c[m][n][1], acc[m][n][1]);
+        acc[m][n][2] = fmaf(sc[m][1], c[m][n][2], acc[m][n][2]);
+        acc[m][n][3] = fmaf(sc[m][1], c[m][n][3], acc[m][n][3]);
+      }
+  };
+
+  /* The codes of step `s` of the chunk at group g0 (128 columns of the four
+     rows of this lane's g) on their way to stage s & 1 of the warp's buffer. */
+  auto fetch_step = [&](int g0, int s) {
+    unsigned char *dst = mine + (s & 1) * kStepBytes + g * kRowStride + t * 16;
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        copy16_async(dst + (m * 2 + h) * 8 * kRowStride,
+                     wrow[m][h] + (g0 + 4 * s) * 4 + 4 * t);
+    copies_commit();
   };
 
   for (int c0 = 0; c0 < a.cols; c0 += kChunk) {
     const int ncols = a.cols - c0 < kChunk ? a.cols - c0 : kChunk;
+    const int g0 = c0 / 32, nq = ncols / 32;
+    const int steps = a.four_groups && any ? nq / 4 : 0;
     __syncthreads(); /* pair_of is written; the last chunk has been read */
+    if (steps > 0)
+      fetch_step(g0, 0); /* under the staging below */
     /* eight columns of one pair per step: three words of permuted terms */
     for (int item = threadIdx.x; item < PAIRS * (ncols / 8); item += kWarps * 32) {
       const int j = item / (ncols / 8), word = item - j * (ncols / 8);
@@ -206,61 +280,99 @@ moe_grouped_kernel(const GroupedArgs a) {
         *reinterpret_cast<uint4 *>(terms + (k * PAIRS + j) * kTermStride + word * 16) = q;
       }
     }
+    /* Lane t keeps the four scales of step t of each of its rows: one 8-byte
+       load a row and chunk, handed round by shuffles. */
+    uint2 my_scales[M][2];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        my_scales[m][h] = t < steps
+                              ? __ldg(reinterpret_cast<const uint2 *>(srow[m][h] + g0 + 4 * t))
+                              : make_uint2(0, 0);
     __syncthreads();
-    if (!live)
+    if (!any)
       continue;
 
-    const int g0 = c0 / 32, nq = ncols / 32;
-    int q = 0;
-    if (a.four_groups) {
-      /* Four groups a step: the sixteen loads leave together, so a trip to L2
-         is paid once for 128 columns of both rows, and the four scales of a
-         row come as one 8-byte word. */
-      for (; q + 4 <= nq; q += 4) {
-        uint32_t wa[4], wb[4];
+    for (int s = 0; s < steps; ++s) {
+      if (s + 1 < steps) {
+        fetch_step(g0, s + 1);
+        copies_wait<1>();
+      } else {
+        copies_wait<0>();
+      }
+      __syncwarp(); /* every lane's part of step s has landed */
+      uint2 four[M][2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          wa[u] = __ldg(wa_row + (g0 + q + u) * 4);
-          wb[u] = __ldg(wb_row + (g0 + q + u) * 4);
+      for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          four[m][h].x = __shfl_sync(0xffffffffu, my_scales[m][h].x, (lane & ~3) | s);
+          four[m][h].y = __shfl_sync(0xffffffffu, my_scales[m][h].y, (lane & ~3) | s);
         }
-        const uint2 sa = __ldg(reinterpret_cast<const uint2 *>(sa_row + g0 + q));
-        const uint2 sb = __ldg(reinterpret_cast<const uint2 *>(sb_row + g0 + q));
-        group(q, wa[0], wb[0], half_value(sa.x & 0xffffu), half_value(sb.x & 0xffffu));
-        group(q + 1, wa[1], wb[1], half_value(sa.x >> 16), half_value(sb.x >> 16));
-        group(q + 2, wa[2], wb[2], half_value(sa.y & 0xffffu), half_value(sb.y & 0xffffu));
-        group(q + 3, wa[3], wb[3], half_value(sa.y >> 16), half_value(sb.y >> 16));
-      }
-    }
-    for (; q < nq; ++q)
-      group(q, __ldg(wa_row + (g0 + q) * 4), __ldg(wb_row + (g0 + q) * 4),
-            half_value(__ldg(sa_row + g0 + q)), half_value(__ldg(sb_row + g0 + q)));
-  }
-  if (!live)
-    return;
-
-  /* acc[n][0..1]: A row g, pairs 8 n + 2t and 8 n + 2t + 1; acc[n][2..3]: row g + 8 */
+      const unsigned char *src = mine + (s & 1) * kStepBytes + g * kRowStride + t * 4;
 #pragma unroll
-  for (int n = 0; n < NT; ++n) {
-    const int p0 = pair_of[n * 8 + 2 * t], p1 = pair_of[n * 8 + 2 * t + 1];
-    if (SWIGLU) {
-      const float g0v = acc[n][0], g1v = acc[n][1];
-      if (p0 >= 0)
-        a.out[p0 * a.out_pitch + r0] = g0v / (1.0f + expf(0.0f - g0v)) * acc[n][2];
-      if (p1 >= 0)
-        a.out[p1 * a.out_pitch + r0] = g1v / (1.0f + expf(0.0f - g1v)) * acc[n][3];
-    } else {
-      const bool second = r1 != r0;
-      if (p0 >= 0) {
-        const float s = a.pair_scale[p0];
-        a.out[p0 * a.out_pitch + r0] = s * acc[n][0];
-        if (second)
-          a.out[p0 * a.out_pitch + r1] = s * acc[n][2];
+      for (int u = 0; u < 4; ++u) {
+        uint32_t wd[M][2];
+        float sc[M][2];
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            wd[m][h] = *reinterpret_cast<const uint32_t *>(
+                src + (m * 2 + h) * 8 * kRowStride + u * 16);
+            const uint32_t two = u < 2 ? four[m][h].x : four[m][h].y;
+            sc[m][h] = half_value((u & 1) ? two >> 16 : two & 0xffffu);
+          }
+        group(4 * s + u, wd, sc);
       }
-      if (p1 >= 0) {
-        const float s = a.pair_scale[p1];
-        a.out[p1 * a.out_pitch + r0] = s * acc[n][1];
-        if (second)
-          a.out[p1 * a.out_pitch + r1] = s * acc[n][3];
+      __syncwarp(); /* stage s & 1 may be filled again */
+    }
+    /* what the steps did not take: a chunk that is not a multiple of 128
+       columns, or operands not aligned for them */
+    for (int q = 4 * steps; q < nq; ++q) {
+      uint32_t wd[M][2];
+      float sc[M][2];
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          wd[m][h] = __ldg(wrow[m][h] + (g0 + q) * 4 + t);
+          sc[m][h] = half_value(__ldg(srow[m][h] + g0 + q));
+        }
+      group(q, wd, sc);
+    }
+  }
+
+  /* acc[m][n][0..1]: A row g, pairs 8 n + 2t and 8 n + 2t + 1; [2..3]: row g + 8 */
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    if (!live[m])
+      continue;
+    const int64_t r0 = row[m][0], r1 = row[m][1];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const int p0 = pair_of[n * 8 + 2 * t], p1 = pair_of[n * 8 + 2 * t + 1];
+      if (SWIGLU) {
+        const float g0v = acc[m][n][0], g1v = acc[m][n][1];
+        if (p0 >= 0)
+          a.out[p0 * a.out_pitch + r0] = g0v / (1.0f + expf(0.0f - g0v)) * acc[m][n][2];
+        if (p1 >= 0)
+          a.out[p1 * a.out_pitch + r0] = g1v / (1.0f + expf(0.0f - g1v)) * acc[m][n][3];
+      } else {
+        const bool second = r1 != r0;
+        if (p0 >= 0) {
+          const float s = a.pair_scale[p0];
+          a.out[p0 * a.out_pitch + r0] = s * acc[m][n][0];
+          if (second)
+            a.out[p0 * a.out_pitch + r1] = s * acc[m][n][2];
+        }
+        if (p1 >= 0) {
+          const float s = a.pair_scale[p1];
+          a.out[p1 * a.out_pitch + r0] = s * acc[m][n][1];
+          if (second)
+            a.out[p1 * a.out_pitch + r1] = s * acc[m][n][3];
+        }
       }
     }
   }
@@ -322,9 +434,11 @@ const char *launch_grouped_nt(GroupedArgs &g, int tiles, cudaStream_t stream) {
   if (allow_dynamic_smem((const void *)moe_grouped_kernel<SWIGLU, NT>, bytes) !=
       cudaSuccess)
     return "the grouped expert projection could not get its shared memory on this GPU";
-  g.four_groups = g.cols % 128 == 0 && ((uintptr_t)g.scales & 7) == 0;
+  g.four_groups = g.cols % 128 == 0 && ((uintptr_t)g.scales & 7) == 0 &&
+                  ((uintptr_t)g.w & 15) == 0;
   const int row_tiles = SWIGLU ? g.rows / 8 : (g.rows + 15) / 16;
-  const dim3 grid(tiles, (row_tiles + kWarps - 1) / kWarps);
+  const int per_block = kWarps * kRowTiles;
+  const dim3 grid(tiles, (row_tiles + per_block - 1) / per_block);
   if (grid.y > 65535)
     return "too many rows";
   launch_chained(moe_grouped_kernel<SWIGLU, NT>, grid, dim3(kWarps * 32), bytes, stream,
