@@ -94,6 +94,16 @@ __device__ __forceinline__ void mma_16x8x16(float (&c)[4], uint32_t a0, uint32_t
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+/* the same with C = 0: the first product of a group needs no cleared registers */
+__device__ __forceinline__ void mma_16x8x16_first(float (&c)[4], uint32_t a0,
+                                                  uint32_t a1, uint32_t a2, uint32_t a3,
+                                                  uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+               "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+               : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 /* two codes (bits 0-3 and 16-19 of `two`) as two bf16 values code - 8 */
 __device__ __forceinline__ uint32_t codes_to_bf16x2(uint32_t two) {
   uint32_t d;
@@ -102,23 +112,40 @@ __device__ __forceinline__ uint32_t codes_to_bf16x2(uint32_t two) {
   return d;
 }
 
-__device__ __forceinline__ unsigned short bf16_bits(float v) {
-  return __bfloat16_as_ushort(__float2bfloat16_rn(v));
-}
-__device__ __forceinline__ float bf16_value(unsigned short b) {
-  return __uint_as_float((uint32_t)b << 16);
-}
+/* an f16 as f32 by a mixed-precision add, which runs on the FMA pipe (a cvt
+   goes to the quarter-rate pipe) */
 __device__ __forceinline__ float half_value(uint32_t b) {
-  return __half2float(__ushort_as_half((unsigned short)b));
+  float d;
+  asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"((unsigned short)b), "f"(-0.0f));
+  return d;
+}
+/* d[0..1] += s * c[0..1] in one instruction */
+__device__ __forceinline__ void scale_add2(float &d0, float &d1, float s, float c0,
+                                           float c1) {
+  unsigned long long d, cc, ss;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(d0), "f"(d1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(cc) : "f"(c0), "f"(c1));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(ss) : "f"(s));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(ss), "l"(cc));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
 }
 
-/* v = t[0] + t[1] + t[2] exactly (24 bits of mantissa in three times 8) */
-__device__ __forceinline__ void three_bf16(float v, unsigned short (&t)[3]) {
-  t[0] = bf16_bits(v);
-  const float r1 = v - bf16_value(t[0]);
-  t[1] = bf16_bits(r1);
-  const float r2 = r1 - bf16_value(t[1]);
-  t[2] = bf16_bits(r2);
+/* Two values as three words of two bf16 each (lo in the low half), term by
+   term: v = t[0] + t[1] + t[2] exactly, 24 bits of mantissa in three times 8.
+   One conversion rounds both values. */
+__device__ __forceinline__ uint32_t bf16x2_of(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ void three_bf16x2(float lo, float hi, uint32_t (&t)[3]) {
+  t[0] = bf16x2_of(lo, hi);
+  lo -= __uint_as_float(t[0] << 16);
+  hi -= __uint_as_float(t[0] & 0xffff0000u);
+  t[1] = bf16x2_of(lo, hi);
+  lo -= __uint_as_float(t[1] << 16);
+  hi -= __uint_as_float(t[1] & 0xffff0000u);
+  t[2] = bf16x2_of(lo, hi);
 }
 
 __device__ __forceinline__ void copy16_async(void *smem_dst, const void *src) {
@@ -204,11 +231,6 @@ moe_grouped_kernel(const GroupedArgs a) {
           ac[m][h][i] = codes_to_bf16x2((wd[m][h] >> (4 * i)) & MASK);
     float c[M][NT][4];
 #pragma unroll
-    for (int m = 0; m < M; ++m)
-#pragma unroll
-      for (int n = 0; n < NT; ++n)
-        c[m][n][0] = c[m][n][1] = c[m][n][2] = c[m][n][3] = 0.0f;
-#pragma unroll
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
       for (int k = 0; k < 3; ++k) {
@@ -216,8 +238,12 @@ moe_grouped_kernel(const GroupedArgs a) {
             terms + (k * PAIRS + n * 8 + g) * kTermStride + q * 64 + t * 16);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          mma_16x8x16(c[m][n], ac[m][0][0], ac[m][1][0], ac[m][0][1], ac[m][1][1], b.x,
-                      b.y);
+          if (k == 0)
+            mma_16x8x16_first(c[m][n], ac[m][0][0], ac[m][1][0], ac[m][0][1],
+                              ac[m][1][1], b.x, b.y);
+          else
+            mma_16x8x16(c[m][n], ac[m][0][0], ac[m][1][0], ac[m][0][1], ac[m][1][1],
+                        b.x, b.y);
           mma_16x8x16(c[m][n], ac[m][0][2], ac[m][1][2], ac[m][0][3], ac[m][1][3], b.z,
                       b.w);
         }
@@ -227,10 +253,8 @@ moe_grouped_kernel(const GroupedArgs a) {
     for (int m = 0; m < M; ++m)
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
-        acc[m][n][0] = fmaf(sc[m][0], c[m][n][0], acc[m][n][0]);
-        acc[m][n][1] = fmaf(sc[m][0], c[m][n][1], acc[m][n][1]);
-        acc[m][n][2] = fmaf(sc[m][1], c[m][n][2], acc[m][n][2]);
-        acc[m][n][3] = fmaf(sc[m][1], c[m][n][3], acc[m][n][3]);
+        scale_add2(acc[m][n][0], acc[m][n][1], sc[m][0], c[m][n][0], c[m][n][1]);
+        scale_add2(acc[m][n][2], acc[m][n][3], sc[m][1], c[m][n][2], c[m][n][3]);
       }
   };
 
@@ -266,19 +290,14 @@ moe_grouped_kernel(const GroupedArgs a) {
         v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
         v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
       }
-      unsigned short tm[8][3];
+      uint32_t tm[4][3]; /* columns (i, i + 4) of the word, as the codes pair up */
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        three_bf16(v[i], tm[i]);
+      for (int i = 0; i < 4; ++i)
+        three_bf16x2(v[i], v[i + 4], tm[i]);
 #pragma unroll
-      for (int k = 0; k < 3; ++k) {
-        uint4 q;
-        q.x = tm[0][k] | ((uint32_t)tm[4][k] << 16);
-        q.y = tm[1][k] | ((uint32_t)tm[5][k] << 16);
-        q.z = tm[2][k] | ((uint32_t)tm[6][k] << 16);
-        q.w = tm[3][k] | ((uint32_t)tm[7][k] << 16);
-        *reinterpret_cast<uint4 *>(terms + (k * PAIRS + j) * kTermStride + word * 16) = q;
-      }
+      for (int k = 0; k < 3; ++k)
+        *reinterpret_cast<uint4 *>(terms + (k * PAIRS + j) * kTermStride + word * 16) =
+            make_uint4(tm[0][k], tm[1][k], tm[2][k], tm[3][k]);
     }
     /* Lane t keeps the four scales of step t of each of its rows: one 8-byte
        load a row and chunk, handed round by shuffles. */
