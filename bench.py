@@ -532,6 +532,27 @@ def bench_decode_quant(torch, llama, shape, peaks, quant):
                 frac_of_measured_hbm=gbs / peaks["hbm_gbs"])
 
 
+def bench_moe_experts(torch, positions=512):
+    """A mixture-of-experts layer's experts for a prompt of `positions`: 8 Q4_0
+    experts of 14336 x 4096, 2 a position; router, grouping by expert, and both
+    projections grouped on the tensor cores, beside the position-by-position
+    exports (the same case as `python microbench.py moe`)."""
+    import argparse
+    import microbench
+    r = microbench.moe(torch, argparse.Namespace(n=positions, iters=3))
+    torch.cuda.empty_cache()
+    grouped = r["router_us"] / 1e3 + r["group_us"] / 1e3 + r["swiglu_grouped_ms"] + \
+        r["down_grouped_ms"]
+    return dict(workload=r["kernel"], layer_ms_grouped=grouped,
+                layer_ms_position_by_position=r["swiglu_rows_ms"] + r["down_rows_ms"],
+                router_us=r["router_us"], group_us=r["group_us"],
+                swiglu_grouped_ms=r["swiglu_grouped_ms"],
+                down_grouped_ms=r["down_grouped_ms"],
+                useful_tflops=r["grouped_tflops"],
+                grouped_vs_rows_max_rel=r["grouped_vs_rows_max_rel"],
+                kernel_status=r["status"])
+
+
 def bench_skinny_layers(torch, llama, rank, world, alone=False):
     """The per-layer cost that is not weight streaming: a model with the 7B
     width but almost no weights (one head per rank, 64 MLP rows per rank),
@@ -829,6 +850,7 @@ def run_ours(args):
             line["decode_batch16"] = bench_decode_batch(torch, llama, shape, peaks, 16)
             line["decode_fp8"] = bench_decode_quant(torch, llama, shape, peaks, "fp8")
             line["decode_q4"] = bench_decode_quant(torch, llama, shape, peaks, "q4")
+            line["moe_experts_q4"] = bench_moe_experts(torch)
             line["gemm_f32_1024"] = bench_gemm_f32(torch, oracle)
             line["small_llama_f32"] = bench_small_llama(torch, oracle, llama)
             # attention before the big GEMMs: seconds of dense GEMM leave the GPU

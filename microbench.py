@@ -290,6 +290,8 @@ def moe(torch, args):
                             y, dn, dn_s, order, tile_expert, align, wts.view(0, (pairs,)),
                             mid, scratch, n, k, dim, inter, experts), args.iters)
         grouped[align] = (t_group, t_up, t_down)
+        order.free()
+        tile_expert.free()
     t_group, t_up, t_down = grouped[16]
     t_up_rows = _timed(torch, stream,
                        lambda: ops.nn_moe_swiglu_q4_rows(mid_rows, gu, gu_s, ids, x, n, k,
@@ -299,6 +301,10 @@ def moe(torch, args):
                                                              mid_rows, n, k, dim, inter,
                                                              experts), 1)
     a, b = mid.to_host(), mid_rows.to_host()
+    status = ops.kernel_status()
+    for held in (logits, ids, wts, x, y, gu, gu_s, dn, dn_s, counts, base, starts, mid,
+                 mid_rows, scratch):
+        held.free()
     flop = 2.0 * pairs * 3 * inter * dim
     weight_bytes = experts * 3 * inter * dim * (0.5 + 2.0 / 32)
     return dict(kernel="experts of %d positions: 8 x (14336 x 4096) Q4_0, 2 a position" % n,
@@ -309,7 +315,7 @@ def moe(torch, args):
                 grouped_tflops=flop / ((t_up + t_down) * 1e-3) / 1e12,
                 weights_gb=weight_bytes / 1e9,
                 grouped_vs_rows_max_rel=float(np.abs(a - b).max() / np.abs(b).max()),
-                status=ops.kernel_status())
+                status=status)
 
 
 def main():
