@@ -503,9 +503,31 @@ def bench_decode_quant(torch, llama, shape, peaks, quant):
     stream = torch.cuda.ExternalStream(dec.stream)
     prompt = np.random.default_rng(8).integers(0, shape["vocab"], PROMPT)
     steps = 64
+    prompt_ms = {}
     try:
-        for t in prompt:
-            dec.step([int(t)], fetch=False)
+        if quant == "q4":
+            # the prompt in one pass (Q4_0 weights on the grouped tensor-core
+            # kernel) beside one decode step per token; same first token?
+            def timed_prompt(fn):
+                dec.reset()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                tok = fn()
+                torch.cuda.synchronize()
+                return (time.perf_counter() - t0) * 1e3, tok
+
+            def stepped():
+                for t in prompt[:-1]:
+                    dec.step([int(t)], fetch=False)
+                return dec.step([int(prompt[-1])])[0]
+            timed_prompt(lambda: dec.prefill(prompt))        # warm
+            rows_ms, tok_rows = timed_prompt(lambda: dec.prefill(prompt))
+            step_ms, tok_steps = timed_prompt(stepped)
+            prompt_ms = dict(prefill_ms=rows_ms, one_step_per_token_ms=step_ms,
+                             first_token_equal=bool(tok_rows == tok_steps))
+        else:
+            for t in prompt:
+                dec.step([int(t)], fetch=False)
         for _ in range(4):
             dec.step(None, fetch=False)
         torch.cuda.synchronize()
@@ -529,7 +551,7 @@ def bench_decode_quant(torch, llama, shape, peaks, quant):
     return dict(workload="same model, layer projections in %s, batch 1" % quant,
                 tokens_per_s=steps / (ms / 1e3), ms_per_step=ms / steps,
                 steps=steps, bytes_per_step=total, hbm_gbs=gbs,
-                frac_of_measured_hbm=gbs / peaks["hbm_gbs"])
+                frac_of_measured_hbm=gbs / peaks["hbm_gbs"], **prompt_ms)
 
 
 def bench_moe_experts(torch, positions=512):

@@ -278,9 +278,10 @@ int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
    logits, so the caller gives the last prompt token to vx_decoder_step.
    Returns how many tokens it took (all of them, or 0 when there are fewer
    than 32: the caller steps through those), or -1 with vx_b200_last_error()
-   for a decoder that cannot (needs batch 1, one rank, bf16 weights with the
-   q/k/v rows in one matrix and the gate/up rows in one, head_dim 128, widths
-   in multiples of 64). */
+   for a decoder that cannot (needs batch 1, one rank, bf16 or Q4_0 weights
+   with the q/k/v rows in one matrix and the gate/up rows in one, head_dim 128,
+   widths in multiples of 64). With Q4_0 weights the GEMMs run on the kernel of
+   the grouped experts, the codes unpacked once for sixteen positions. */
 int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count);
 /* The logits of the last step: device memory, [batch, vocab] f32. */
 const float *vx_decoder_logits(const vx_decoder *d);

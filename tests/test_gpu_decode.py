@@ -388,6 +388,45 @@ def test_quantised_decoder_tokens_match_oracle(oracle, quant):
     assert got == want, report(got, want)
 
 
+def test_prefill_with_q4_weights(oracle):
+    """A 100-token prompt through vx_decoder_prefill of a decoder with Q4_0
+    weights (the prompt's GEMMs on the grouped tensor-core kernel, the codes
+    unpacked once for sixteen positions), then greedy steps: the oracle's
+    tokens, which come from one step per prompt token. Then 37 single steps and
+    the other 62 positions in one pass."""
+    from vx_b200 import ops
+    from vx_b200.lib import lib
+    max_seq, steps = 128, 12
+    dec, tensors = llama.nn_quant_model("q4", max_seq=max_seq, **WIDE_NN)
+    hm = oracle.quant_model_from_tensors(tensors, WIDE_NN, max_seq, "q4")
+    prompt = [int(t) for t in
+              np.random.default_rng(34).integers(0, WIDE_NN["vocab"], 100)]
+    want = oracle.quant_generate(hm, prompt, steps, max_seq)
+
+    def greedy(tok):
+        got = []
+        for _ in range(steps):
+            got.append(tok)
+            tok = dec.step(None)[0]
+        return got
+
+    arr = (C.c_int32 * 99)(*prompt[:-1])
+    assert lib().vx_decoder_prefill(dec.handle, arr, 99) == 99
+    got = greedy(dec.step([prompt[-1]])[0])
+    assert ops.kernel_status() == 0
+    assert got == want, report(got, want)
+
+    dec.reset()
+    for t in prompt[:37]:
+        dec.step([t], fetch=False)
+    rest = (C.c_int32 * 62)(*prompt[37:99])
+    assert lib().vx_decoder_prefill(dec.handle, rest, 62) == 62
+    got = greedy(dec.step([prompt[-1]])[0])
+    dec.close()
+    assert ops.kernel_status() == 0
+    assert got == want, report(got, want)
+
+
 def test_quantisers_follow_their_definitions(oracle):
     """vx_b200_quantize against numpy: fp8 scale = block amax / 448 and codes
     that decode (by the definition of f8e4m3) to within half a step of w /

@@ -960,14 +960,26 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
   bool fused = true;
   for (int l = 0; l < c.n_layers; ++l)
     fused = fused && !d->wk[l] && !d->wv[l] && !d->w_up[l];
-  if (c.batch != 1 || c.weights_bf16 != 1 || d->ranks != 1 || hd != 128 ||
+  const bool q4 = d->wfmt == vxb::kFmtQ4;
+  if (c.batch != 1 || (c.weights_bf16 != 1 && !q4) || d->ranks != 1 || hd != 128 ||
       c.dim % 64 != 0 || d->hidden_local % 64 != 0 || !fused) {
-    vxb::set_last_error("vx_decoder_prefill: needs one sequence, one rank, bf16 "
-                        "weights with q/k/v rows in one matrix and gate/up rows "
-                        "in one matrix, head_dim 128 and widths in multiples "
+    vxb::set_last_error("vx_decoder_prefill: needs one sequence, one rank, bf16 or "
+                        "Q4_0 weights with q/k/v rows in one matrix and gate/up "
+                        "rows in one matrix, head_dim 128 and widths in multiples "
                         "of 64");
     return -1;
   }
+  /* One GEMM of the prompt: on CTA pairs for bf16 weights, on the grouped
+     kernel of the experts (one matrix, tiles of sixteen positions) for Q4_0;
+     either way sums[run][t][r] for the finishing kernels. */
+  auto gemm = [&](const void *w, const void *scales, int n, int cols, int *runs) {
+    if (!q4)
+      return vxb::rows_gemm(d->rows_terms, w, count, n, cols, d->rows_partials, runs,
+                            d->stream);
+    *runs = 1;
+    return vxb::rows_gemm_q4(d->rows_terms, w, scales, count, n, cols,
+                             d->rows_partials, d->stream);
+  };
   if (count < 0 || d->host_pos + count > c.max_seq) {
     vxb::set_last_error("vx_decoder_prefill: the prompt does not fit max_seq");
     return -1;
@@ -1010,9 +1022,7 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
     /* rows_terms hold the terms of RMSNorm(x) * attn_norm[l] here */
     float *kc = d->k_cache + l * d->cache_layer_stride;
     float *vc = d->v_cache + l * d->cache_layer_stride;
-    need(vxb::rows_gemm(d->rows_terms, d->wq[l], T, qkv_rows, c.dim,
-                        d->rows_partials, &splits, s),
-         "q/k/v");
+    need(gemm(d->wq[l], d->s_qkv[l], qkv_rows, c.dim, &splits), "q/k/v");
     need(vxb::rows_qkv_finish(d->rows_partials, splits, T, d->q_local, d->kv_local,
                               hd, d->bqkv[l], d->cos_t, d->sin_t, d->positions,
                               d->rows_q, kc, vc, s),
@@ -1024,9 +1034,7 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
     need(vxb::rows_attention(d->rows_terms, d->rows_q, kc, vc, d->positions, T,
                              d->q_local, d->kv_local, hd, s),
          "attention");
-    need(vxb::rows_gemm(d->rows_terms, d->wo[l], T, c.dim, att_cols,
-                        d->rows_partials, &splits, s),
-         "the output projection");
+    need(gemm(d->wo[l], d->s_o[l], c.dim, att_cols, &splits), "the output projection");
     if (fuse_norm) {
       need(vxb::rows_residual_norm(d->rows_terms, d->rows_x, d->rows_partials, splits,
                                    T, d->ffn_norm[l], c.dim, c.eps, s),
@@ -1038,14 +1046,12 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
                                 c.eps, s),
            "RMSNorm");
     }
-    need(vxb::rows_gemm(d->rows_terms, d->w_gate[l], T, 2 * d->hidden_local, c.dim,
-                        d->rows_partials, &splits, s),
+    need(gemm(d->w_gate[l], d->s_gate_up[l], 2 * d->hidden_local, c.dim, &splits),
          "gate/up");
     need(vxb::rows_swiglu_finish(d->rows_terms, d->rows_partials, splits, T,
                                  d->hidden_local, s),
          "SwiGLU");
-    need(vxb::rows_gemm(d->rows_terms, d->w_down[l], T, c.dim, d->hidden_local,
-                        d->rows_partials, &splits, s),
+    need(gemm(d->w_down[l], d->s_down[l], c.dim, d->hidden_local, &splits),
          "the down projection");
     if (fuse_norm) {
       need(vxb::rows_residual_norm(d->rows_terms, d->rows_x, d->rows_partials, splits,

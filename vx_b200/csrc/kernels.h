@@ -397,6 +397,10 @@ struct MoeGroupedArgs {
   int n, k, rows, cols, experts;
 };
 const char *moe_swiglu_q4_grouped(const MoeGroupedArgs &m, cudaStream_t stream);
+/* The prompt's GEMM for Q4_0 weights on the same kernel: partials[t][r] = (row r
+   of w) . x[t], x as the terms of prefill.cu ([t, 3 cols] bf16), one run. */
+const char *rows_gemm_q4(const void *terms, const void *w, const void *scales, int t,
+                         int n, int cols, float *partials, cudaStream_t stream);
 const char *moe_down_q4_add_grouped(const MoeGroupedArgs &m, cudaStream_t stream);
 /* 0, or once 0x6E after an id that named no expert (0x6F: a `base` that sent a
    pair outside `order`); waits for the stream. */

@@ -71,11 +71,14 @@ constexpr int smem_bytes(int pairs) {
 struct GroupedArgs {
   const uint32_t *w;          /* all experts, [experts * expert_rows, cols / 8] */
   const __half *scales;       /* [experts * expert_rows, cols / 32] */
-  const int32_t *order;       /* from nn_moe_group, align 8 or 16 */
-  const int32_t *tile_expert;
+  const int32_t *order;       /* from nn_moe_group, align 8 or 16; null: position
+                                 i of tile t is pair t * align + i */
+  const int32_t *tile_expert; /* null: one matrix, every tile its own */
   const float *x;             /* input of pair p: row p / x_div, x_pitch apart */
   int64_t x_pitch;
   int x_div;
+  const uint16_t *x_terms;    /* or the input as three bf16 terms, [rows, 3 cols]
+                                 (x1 | x2 | x3 of a row, as prefill.cu leaves them) */
   float *out;                 /* output of pair p: row p, out_pitch apart */
   int64_t out_pitch;
   const float *pair_scale;    /* down: the router's weight of pair p */
@@ -172,14 +175,15 @@ moe_grouped_kernel(const GroupedArgs a) {
   chain_release();
   chain_wait();
   const int tile = blockIdx.x;
-  const int expert = a.tile_expert[tile];
+  const int expert = a.tile_expert ? a.tile_expert[tile] : 0;
   if (expert < 0 || expert >= a.experts)
     return; /* past the last group: the whole block leaves together */
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   unsigned char *mine = smem + 3 * PAIRS * kTermStride + warp * kWarpBytes;
   if (threadIdx.x < PAIRS) {
-    const int p = a.order[tile * PAIRS + threadIdx.x];
+    const int at = tile * PAIRS + threadIdx.x;
+    const int p = a.order ? a.order[at] : at;
     pair_of[threadIdx.x] = p >= 0 && p < a.pairs ? p : -1;
   }
 
@@ -282,6 +286,23 @@ moe_grouped_kernel(const GroupedArgs a) {
     for (int item = threadIdx.x; item < PAIRS * (ncols / 8); item += kWarps * 32) {
       const int j = item / (ncols / 8), word = item - j * (ncols / 8);
       const int p = pair_of[j];
+      unsigned char *dst = terms + j * kTermStride + word * 16;
+      if (a.x_terms) {
+        /* made by an earlier kernel: only the order inside the word changes */
+        const uint16_t *src =
+            a.x_terms + (int64_t)(p < 0 ? 0 : p / a.x_div) * 3 * a.cols + c0 + word * 8;
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+          uint4 q = make_uint4(0, 0, 0, 0);
+          if (p >= 0) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(src + (int64_t)k * a.cols);
+            q = make_uint4(__byte_perm(v.x, v.z, 0x5410), __byte_perm(v.x, v.z, 0x7632),
+                           __byte_perm(v.y, v.w, 0x5410), __byte_perm(v.y, v.w, 0x7632));
+          }
+          *reinterpret_cast<uint4 *>(dst + k * PAIRS * kTermStride) = q;
+        }
+        continue;
+      }
       float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       if (p >= 0) {
         const float4 *src = reinterpret_cast<const float4 *>(
@@ -296,7 +317,7 @@ moe_grouped_kernel(const GroupedArgs a) {
         three_bf16x2(v[i], v[i + 4], tm[i]);
 #pragma unroll
       for (int k = 0; k < 3; ++k)
-        *reinterpret_cast<uint4 *>(terms + (k * PAIRS + j) * kTermStride + word * 16) =
+        *reinterpret_cast<uint4 *>(dst + k * PAIRS * kTermStride) =
             make_uint4(tm[0][k], tm[1][k], tm[2][k], tm[3][k]);
     }
     /* Lane t keeps the four scales of step t of each of its rows: one 8-byte
@@ -381,13 +402,13 @@ moe_grouped_kernel(const GroupedArgs a) {
       } else {
         const bool second = r1 != r0;
         if (p0 >= 0) {
-          const float s = a.pair_scale[p0];
+          const float s = a.pair_scale ? a.pair_scale[p0] : 1.0f;
           a.out[p0 * a.out_pitch + r0] = s * acc[m][n][0];
           if (second)
             a.out[p0 * a.out_pitch + r1] = s * acc[m][n][2];
         }
         if (p1 >= 0) {
-          const float s = a.pair_scale[p1];
+          const float s = a.pair_scale ? a.pair_scale[p1] : 1.0f;
           a.out[p1 * a.out_pitch + r0] = s * acc[m][n][1];
           if (second)
             a.out[p1 * a.out_pitch + r1] = s * acc[m][n][3];
@@ -472,6 +493,31 @@ const char *launch_grouped(GroupedArgs &g, int tiles, int align, cudaStream_t st
 }
 
 } // namespace
+
+/* partials[t][r] = (row r of the Q4_0 matrix) . x[t], x given as terms: the
+   prompt's GEMM for a decoder with Q4_0 weights. One "expert", the positions
+   in tiles of sixteen as they come. */
+const char *rows_gemm_q4(const void *terms, const void *w, const void *scales, int t,
+                         int n, int cols, float *partials, cudaStream_t stream) {
+  if (t <= 0 || n <= 0 || n % 8 != 0 || cols <= 0 || cols % 32 != 0)
+    return "a Q4_0 product over a prompt needs rows in multiples of 8 and columns "
+           "in multiples of 32";
+  if (((uintptr_t)terms | (uintptr_t)partials) & 15)
+    return "the terms and the sums must be 16-byte aligned";
+  GroupedArgs g{};
+  g.w = (const uint32_t *)w;
+  g.scales = (const __half *)scales;
+  g.x_terms = (const uint16_t *)terms;
+  g.x_div = 1;
+  g.out = partials;
+  g.out_pitch = n;
+  g.pairs = t;
+  g.rows = n;
+  g.cols = cols;
+  g.experts = 1;
+  g.expert_rows = n;
+  return launch_grouped<false>(g, (t + 15) / 16, 16, stream);
+}
 
 const char *moe_swiglu_q4_grouped(const MoeGroupedArgs &m, cudaStream_t stream) {
   if (const char *why = check_common(m))
