@@ -362,6 +362,14 @@ int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,
    (nn.vx:2958, 3066) in another order of sums: results agree with the
    vx_nn_*_rows exports within rounding, not bit for bit. rows a multiple of 8,
    cols of 32 (fastest with cols a multiple of 128). */
+/* y[n, rows] = x[n, cols] . W^T for a Q4_0 matrix W [rows, cols] (codes 8 to a
+   u32 word, an f16 scale per 32 weights of a row: the layout of nn_matvec_q4,
+   nn.vx:1645-1666) and n rows of f32 activations, on the tensor cores: the
+   same kernel, one matrix, the rows in tiles of sixteen. What
+   vx_nn_matvec_q4_rows computes, in another order of sums. Plain device
+   pointers, packed rows; rows a multiple of 8, cols of 32. */
+int32_t vx_b200_gemm_q4(float *y, const uint32_t *w, const uint16_t *scales,
+                        const float *x, int32_t n, int32_t rows, int32_t cols);
 int32_t vx_b200_moe_swiglu_q4_grouped(float *out, const uint32_t *w,
                                       const uint16_t *scales, const int32_t *order,
                                       const int32_t *tile_expert, int32_t tiles,

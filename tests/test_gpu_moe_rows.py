@@ -309,3 +309,21 @@ def test_grouped_down_projection_with_a_last_tile_of_eight_rows(oracle, align):
             want += float(weights[t, e]) * down[ids[t, e] * rows:(ids[t, e] + 1) * rows]
         close(got[t], want)
     assert ops.kernel_status() == 0
+
+
+@pytest.mark.parametrize("n,rows,cols", [(5, 64, 256), (37, 296, 896), (512, 128, 4096),
+                                         (1, 8, 32)])
+def test_q4_product_of_many_rows_on_the_tensor_cores(oracle, n, rows, cols):
+    """vx_b200_gemm_q4 against f64 loops, and beside vx_nn_matvec_q4_rows."""
+    w, s = oracle.quant_inputs("q4", rows, cols, 81)
+    x = oracle.random_f32(n * cols, 82, 1.0).reshape(n, cols)
+    tw, ts, tx = dev(w), dev(s), dev(x)
+    ty = dev(np.full((n, rows), np.nan, np.float32))
+    ops.gemm_q4(ty, tw, ts, tx, n, rows, cols)
+    got = ty.to_host()
+    for t in range(0, n, max(1, n // 7)):
+        close(got[t], oracle.quant_dot_f64("q4", w, s, x[t], rows, cols))
+    other = empty((n, rows), abi.F32)
+    ops.nn_matvec_q4_rows(other, tw, ts, tx, n, rows, cols)
+    close(got.ravel(), other.to_host().ravel(), 2e-5)
+    assert ops.kernel_status() == 0

@@ -397,6 +397,10 @@ struct MoeGroupedArgs {
   int n, k, rows, cols, experts;
 };
 const char *moe_swiglu_q4_grouped(const MoeGroupedArgs &m, cudaStream_t stream);
+/* y[n, rows] = x[n, cols] times the transpose of a Q4_0 matrix [rows, cols], on
+   the same kernel. */
+const char *gemm_q4(float *y, const void *w, const void *scales, const float *x, int n,
+                    int rows, int cols, cudaStream_t stream);
 /* The prompt's GEMM for Q4_0 weights on the same kernel: partials[t][r] = (row r
    of w) . x[t], x as the terms of prefill.cu ([t, 3 cols] bf16), one run. */
 const char *rows_gemm_q4(const void *terms, const void *w, const void *scales, int t,

@@ -519,6 +519,31 @@ const char *rows_gemm_q4(const void *terms, const void *w, const void *scales, i
   return launch_grouped<false>(g, (t + 15) / 16, 16, stream);
 }
 
+/* y[t][r] = (row r of the Q4_0 matrix) . x[t] for n rows of f32 activations:
+   the same kernel as one matrix, fed f32 values instead of terms. */
+const char *gemm_q4(float *y, const void *w, const void *scales, const float *x, int n,
+                    int rows, int cols, cudaStream_t stream) {
+  if (n <= 0 || rows <= 0 || rows % 8 != 0 || cols <= 0 || cols % 32 != 0)
+    return "a Q4_0 product needs rows in multiples of 8 and columns in multiples of 32";
+  if (((uintptr_t)x | (uintptr_t)y) & 15)
+    return "the activations and the output must be 16-byte aligned";
+  GroupedArgs g{};
+  g.w = (const uint32_t *)w;
+  g.scales = (const __half *)scales;
+  g.x = x;
+  g.x_pitch = cols;
+  g.x_div = 1;
+  g.out = y;
+  g.out_pitch = rows;
+  g.pairs = n;
+  g.rows = rows;
+  g.cols = cols;
+  g.experts = 1;
+  g.expert_rows = rows;
+  return n > 8 ? launch_grouped<false>(g, (n + 15) / 16, 16, stream)
+               : launch_grouped<false>(g, 1, 8, stream);
+}
+
 const char *moe_swiglu_q4_grouped(const MoeGroupedArgs &m, cudaStream_t stream) {
   if (const char *why = check_common(m))
     return why;

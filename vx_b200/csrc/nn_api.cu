@@ -1021,6 +1021,12 @@ int32_t vx_b200_gemm(int32_t dtype, int32_t route, int64_t m, int64_t n,
   }
 }
 
+int32_t vx_b200_gemm_q4(float *y, const uint32_t *w, const uint16_t *scales,
+                        const float *x, int32_t n, int32_t rows, int32_t cols) {
+  return done(vxb::gemm_q4(y, w, scales, x, n, rows, cols, vxb::caller_stream()),
+              "gemm_q4");
+}
+
 int32_t vx_b200_moe_swiglu_q4_grouped(float *out, const uint32_t *w,
                                       const uint16_t *scales, const int32_t *order,
                                       const int32_t *tile_expert, int32_t tiles,

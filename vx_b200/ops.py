@@ -306,3 +306,8 @@ def moe_down_q4_add_grouped(y, w, scales, order, tile_expert, align, weights, h,
     check(lib().vx_b200_moe_down_q4_add_grouped(
         y.ptr, w.ptr, scales.ptr, order.ptr, tile_expert.ptr, tile_expert.count,
         align, weights.ptr, h.ptr, scratch.ptr, n, k, rows, cols, experts))
+
+
+def gemm_q4(y, w, scales, x, n, rows, cols):
+    """y[n, rows] = x[n, cols] times the transpose of a Q4_0 matrix."""
+    check(lib().vx_b200_gemm_q4(y.ptr, w.ptr, scales.ptr, x.ptr, n, rows, cols))
