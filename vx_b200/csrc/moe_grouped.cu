@@ -39,6 +39,10 @@
  * (vx_b200_moe_*_grouped), checked against f64 loops by the criterion of the
  * reference's Q4_0 tests, and the vx_nn_*_rows exports keep the bit-for-bit
  * property.
+ *
+ * One matrix and the positions as they come (no order, no tile_expert) is a
+ * Q4_0 GEMM: vx_b200_gemm_q4 on f32 activations, and rows_gemm_q4 on the terms
+ * that the prompt pass of a decoder keeps between its GEMMs (prefill.cu).
  */
 #include "kernels.h"
 #include "launch.cuh"
