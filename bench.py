@@ -505,9 +505,10 @@ def bench_decode_quant(torch, llama, shape, peaks, quant):
     steps = 64
     prompt_ms = {}
     try:
-        if quant == "q4":
-            # the prompt in one pass (Q4_0 weights on the grouped tensor-core
-            # kernel) beside one decode step per token; same first token?
+        if quant in ("q4", "fp8"):
+            # the prompt in one pass (the codes unpacked once for sixteen
+            # positions, on the tensor cores) beside one decode step per token;
+            # same first token?
             def timed_prompt(fn):
                 dec.reset()
                 torch.cuda.synchronize()

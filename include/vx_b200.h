@@ -278,10 +278,11 @@ int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
    logits, so the caller gives the last prompt token to vx_decoder_step.
    Returns how many tokens it took (all of them, or 0 when there are fewer
    than 32: the caller steps through those), or -1 with vx_b200_last_error()
-   for a decoder that cannot (needs batch 1, one rank, bf16 or Q4_0 weights
-   with the q/k/v rows in one matrix and the gate/up rows in one, head_dim 128,
-   widths in multiples of 64). With Q4_0 weights the GEMMs run on the kernel of
-   the grouped experts, the codes unpacked once for sixteen positions. */
+   for a decoder that cannot (needs batch 1, one rank, bf16, fp8 or Q4_0
+   weights with the q/k/v rows in one matrix and the gate/up rows in one,
+   head_dim 128, widths in multiples of 64, of 128 for fp8). With Q4_0 or fp8
+   weights the GEMMs unpack the codes once for sixteen positions (the kernel
+   of the grouped experts, and its fp8 twin). */
 int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count);
 /* The logits of the last step: device memory, [batch, vocab] f32. */
 const float *vx_decoder_logits(const vx_decoder *d);
@@ -370,6 +371,12 @@ int32_t vx_b200_flash_attention(const void *q, const void *k, const void *v,
    pointers, packed rows; rows a multiple of 8, cols of 32. */
 int32_t vx_b200_gemm_q4(float *y, const uint32_t *w, const uint16_t *scales,
                         const float *x, int32_t n, int32_t rows, int32_t cols);
+/* The same for an fp8 matrix: f8e4m3 codes 4 to a u32 word and an f32 scale per
+   block of 128 x 128, the layout of nn_matvec_fp8 (nn.vx:1296-1306). cols a
+   multiple of 128. The reference has no fp8 kernel for n positions; this is
+   the product a decoder with fp8 weights reads a prompt with. */
+int32_t vx_b200_gemm_fp8(float *y, const uint32_t *w, const float *scales,
+                         const float *x, int32_t n, int32_t rows, int32_t cols);
 int32_t vx_b200_moe_swiglu_q4_grouped(float *out, const uint32_t *w,
                                       const uint16_t *scales, const int32_t *order,
                                       const int32_t *tile_expert, int32_t tiles,

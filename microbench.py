@@ -3,7 +3,7 @@ that ends quickly (a few launches, at most a few GB on the device, inputs
 larger than the 126 MB L2 where DRAM figures matter).
 
   python microbench.py rowdot  [--layers 4] [--iters 3]
-  python microbench.py gemm    [--n 4096] [--iters 3] [--fmt bf16|f32|q4]
+  python microbench.py gemm    [--n 4096] [--iters 3] [--fmt bf16|f32|q4|fp8]
   python microbench.py flash   [--batch 1] [--heads 8] [--seq 4096]
   python microbench.py attn    [--pos 600]
   python microbench.py shard   [--ranks 8] [--pos 520]
@@ -97,21 +97,28 @@ def gemm(torch, args):
         return dict(kernel="f32 gemm %d^3 (three bf16 terms per value on tcgen05 "
                            "unless VXB_F32_TENSOR=0)" % n, us=ms * 1e3,
                     tflops=2.0 * n ** 3 / ms / 1e9, status=ops.kernel_status())
-    if args.fmt == "q4":
-        # n positions against the 7B gate/up matrix in Q4_0
+    if args.fmt in ("q4", "fp8"):
+        # n positions against the 7B gate/up matrix in Q4_0 or fp8
         rows, cols = 22016, 4096
         src = abi.DeviceTensor.empty((rows * cols,), abi.BF16)
         ops.fill_normal(src, 100, 0.02)
-        codes = abi.DeviceTensor.empty((rows * cols // 8,), abi.I32)
-        scales = abi.DeviceTensor.empty((rows * (cols // 32),), abi.F16)
-        assert lib().vx_b200_quantize(3, src.ptr, rows, cols, codes.ptr, scales.ptr) == 0
+        if args.fmt == "q4":
+            codes = abi.DeviceTensor.empty((rows * cols // 8,), abi.I32)
+            scales = abi.DeviceTensor.empty((rows * (cols // 32),), abi.F16)
+            product = ops.gemm_q4
+        else:
+            codes = abi.DeviceTensor.empty((rows * cols // 4,), abi.I32)
+            scales = abi.DeviceTensor.empty((rows // 128 * (cols // 128),), abi.F32)
+            product = ops.gemm_fp8
+        assert lib().vx_b200_quantize(3 if args.fmt == "q4" else 2, src.ptr, rows, cols,
+                                      codes.ptr, scales.ptr) == 0
         x = abi.DeviceTensor.empty((n, cols), abi.F32)
         ops.fill_normal(x, 8, 1.0)
         y = abi.DeviceTensor.empty((n, rows), abi.F32)
         ms = _timed(torch, torch.cuda.Stream(),
-                    lambda: ops.gemm_q4(y, codes, scales, x, n, rows, cols), args.iters)
-        return dict(kernel="Q4_0 gemm: %d positions x (22016 x 4096), mma.sync with the "
-                           "codes unpacked in registers" % n, us=ms * 1e3,
+                    lambda: product(y, codes, scales, x, n, rows, cols), args.iters)
+        return dict(kernel="%s gemm: %d positions x (22016 x 4096), mma.sync with the "
+                           "codes unpacked in registers" % (args.fmt, n), us=ms * 1e3,
                     tflops=2.0 * n * rows * cols / ms / 1e9, status=ops.kernel_status())
     ta, tb, tc = (abi.DeviceTensor.empty((n, n), abi.BF16) for _ in range(3))
     ops.fill_uniform(ta, 3, -1.0, 1.0)

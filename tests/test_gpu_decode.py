@@ -388,17 +388,18 @@ def test_quantised_decoder_tokens_match_oracle(oracle, quant):
     assert got == want, report(got, want)
 
 
-def test_prefill_with_q4_weights(oracle):
-    """A 100-token prompt through vx_decoder_prefill of a decoder with Q4_0
-    weights (the prompt's GEMMs on the grouped tensor-core kernel, the codes
-    unpacked once for sixteen positions), then greedy steps: the oracle's
-    tokens, which come from one step per prompt token. Then 37 single steps and
-    the other 62 positions in one pass."""
+@pytest.mark.parametrize("quant", ["q4", "fp8"])
+def test_prefill_with_quantised_weights(oracle, quant):
+    """A 100-token prompt through vx_decoder_prefill of a decoder with Q4_0 or
+    fp8 weights (the prompt's GEMMs on tensor-core kernels that unpack the
+    codes once for sixteen positions), then greedy steps: the oracle's tokens,
+    which come from one step per prompt token. Then 37 single steps and the
+    other 62 positions in one pass."""
     from vx_b200 import ops
     from vx_b200.lib import lib
     max_seq, steps = 128, 12
-    dec, tensors = llama.nn_quant_model("q4", max_seq=max_seq, **WIDE_NN)
-    hm = oracle.quant_model_from_tensors(tensors, WIDE_NN, max_seq, "q4")
+    dec, tensors = llama.nn_quant_model(quant, max_seq=max_seq, **WIDE_NN)
+    hm = oracle.quant_model_from_tensors(tensors, WIDE_NN, max_seq, quant)
     prompt = [int(t) for t in
               np.random.default_rng(34).integers(0, WIDE_NN["vocab"], 100)]
     want = oracle.quant_generate(hm, prompt, steps, max_seq)

@@ -327,3 +327,40 @@ def test_q4_product_of_many_rows_on_the_tensor_cores(oracle, n, rows, cols):
     ops.nn_matvec_q4_rows(other, tw, ts, tx, n, rows, cols)
     close(got.ravel(), other.to_host().ravel(), 2e-5)
     assert ops.kernel_status() == 0
+
+
+@pytest.mark.parametrize("n,rows,cols", [(5, 64, 256), (37, 296, 896), (300, 128, 4096),
+                                         (1, 4, 128), (16, 20, 640)])
+def test_fp8_product_of_many_rows_on_the_tensor_cores(oracle, n, rows, cols):
+    """vx_b200_gemm_fp8 against f64 loops over the definition of the format,
+    and beside the one-position kernel run row by row."""
+    w, s = oracle.quant_inputs("fp8", rows, cols, 91)
+    x = oracle.random_f32(n * cols, 92, 1.0).reshape(n, cols)
+    tw, ts = dev(w), dev(s)
+    ty = dev(np.full((n, rows), np.nan, np.float32))
+    ops.gemm_fp8(ty, tw, ts, dev(x), n, rows, cols)
+    got = ty.to_host()
+    for t in range(0, n, max(1, n // 7)):
+        close(got[t], oracle.quant_dot_f64("fp8", w, s, x[t], rows, cols))
+        one = empty((rows,), abi.F32)
+        ops.nn_matvec_quant("fp8", one, tw, ts, dev(x[t]), rows, cols)
+        close(got[t], one.to_host(), 2e-5)
+    assert ops.kernel_status() == 0
+
+
+def test_fp8_product_unpacks_every_code(oracle):
+    """A matrix whose first row block holds every e4m3 code but the two NaNs,
+    subnormal codes among them, against a unit vector per column: exact."""
+    rows, cols = 4, 256
+    codes = np.array([c for c in range(256) if (c & 0x7f) != 0x7f] + [0, 0], np.uint8)
+    w = np.tile(codes, rows).reshape(rows, cols)
+    w[1] = w[1][::-1]
+    words = np.ascontiguousarray(w).view(np.uint32).reshape(-1)
+    s = np.array([0.5, 2.0], np.float32)                 # the two column blocks
+    x = np.eye(cols, dtype=np.float32)
+    ty = dev(np.full((cols, rows), np.nan, np.float32))
+    ops.gemm_fp8(ty, dev(words), dev(s), dev(x), cols, rows, cols)
+    got = ty.to_host().astype(np.float64)
+    for j in range(0, cols, 5):
+        want = oracle.quant_dot_f64("fp8", words, s, x[j], rows, cols)
+        assert np.array_equal(got[j], want), j

@@ -17,7 +17,7 @@ LIB = os.path.join(HERE, "libvx_cuda_dispatch.so")
 
 SOURCES = ["dispatch.cu", "gemm_simt.cu", "gemm_umma.cu", "gemm_umma_pair.cu", "nn_kernels.cu",
            "nn_api.cu", "decoder.cu", "flash_attn.cu", "flash_attn_v2.cu", "static_scratch.cu", "rowdot_umma.cu", "prefill.cu", "quantize.cu", "step_kernel.cu", "gemm_f32_split.cu",
-           "moe_group.cu", "moe_grouped.cu"]
+           "moe_group.cu", "moe_grouped.cu", "gemm_fp8_rows.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3",
               "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall",
               "-I" + os.path.join(ROOT, "include"),

@@ -960,25 +960,29 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
   bool fused = true;
   for (int l = 0; l < c.n_layers; ++l)
     fused = fused && !d->wk[l] && !d->wv[l] && !d->w_up[l];
-  const bool q4 = d->wfmt == vxb::kFmtQ4;
-  if (c.batch != 1 || (c.weights_bf16 != 1 && !q4) || d->ranks != 1 || hd != 128 ||
-      c.dim % 64 != 0 || d->hidden_local % 64 != 0 || !fused) {
-    vxb::set_last_error("vx_decoder_prefill: needs one sequence, one rank, bf16 or "
-                        "Q4_0 weights with q/k/v rows in one matrix and gate/up "
+  const bool q4 = d->wfmt == vxb::kFmtQ4, fp8 = d->wfmt == vxb::kFmtFp8;
+  if (c.batch != 1 || (c.weights_bf16 != 1 && !q4 && !fp8) || d->ranks != 1 ||
+      hd != 128 || c.dim % 64 != 0 || d->hidden_local % 64 != 0 || !fused ||
+      (fp8 && (c.dim % 128 != 0 || d->hidden_local % 128 != 0))) {
+    vxb::set_last_error("vx_decoder_prefill: needs one sequence, one rank, bf16, fp8 "
+                        "or Q4_0 weights with q/k/v rows in one matrix and gate/up "
                         "rows in one matrix, head_dim 128 and widths in multiples "
-                        "of 64");
+                        "of 64 (of 128 for fp8)");
     return -1;
   }
-  /* One GEMM of the prompt: on CTA pairs for bf16 weights, on the grouped
-     kernel of the experts (one matrix, tiles of sixteen positions) for Q4_0;
-     either way sums[run][t][r] for the finishing kernels. */
+  /* One GEMM of the prompt: on CTA pairs for bf16 weights; for Q4_0 on the
+     grouped kernel of the experts (one matrix, tiles of sixteen positions) and
+     for fp8 on its twin (gemm_fp8_rows.cu); every way sums[run][t][r] for the
+     finishing kernels. */
   auto gemm = [&](const void *w, const void *scales, int n, int cols, int *runs) {
-    if (!q4)
+    if (!q4 && !fp8)
       return vxb::rows_gemm(d->rows_terms, w, count, n, cols, d->rows_partials, runs,
                             d->stream);
     *runs = 1;
-    return vxb::rows_gemm_q4(d->rows_terms, w, scales, count, n, cols,
-                             d->rows_partials, d->stream);
+    return q4 ? vxb::rows_gemm_q4(d->rows_terms, w, scales, count, n, cols,
+                                  d->rows_partials, d->stream)
+              : vxb::rows_gemm_fp8(d->rows_terms, w, scales, count, n, cols,
+                                   d->rows_partials, d->stream);
   };
   if (count < 0 || d->host_pos + count > c.max_seq) {
     vxb::set_last_error("vx_decoder_prefill: the prompt does not fit max_seq");

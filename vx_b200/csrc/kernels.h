@@ -397,6 +397,12 @@ struct MoeGroupedArgs {
   int n, k, rows, cols, experts;
 };
 const char *moe_swiglu_q4_grouped(const MoeGroupedArgs &m, cudaStream_t stream);
+/* The same two for an fp8 matrix (gemm_fp8_rows.cu): e4m3 codes 4 to a word, an
+   f32 scale per block of 128 x 128; cols a multiple of 128. */
+const char *gemm_fp8(float *y, const void *w, const void *scales, const float *x, int n,
+                     int rows, int cols, cudaStream_t stream);
+const char *rows_gemm_fp8(const void *terms, const void *w, const void *scales, int t,
+                          int n, int cols, float *partials, cudaStream_t stream);
 /* y[n, rows] = x[n, cols] times the transpose of a Q4_0 matrix [rows, cols], on
    the same kernel. */
 const char *gemm_q4(float *y, const void *w, const void *scales, const float *x, int n,

@@ -1027,6 +1027,12 @@ int32_t vx_b200_gemm_q4(float *y, const uint32_t *w, const uint16_t *scales,
               "gemm_q4");
 }
 
+int32_t vx_b200_gemm_fp8(float *y, const uint32_t *w, const float *scales,
+                         const float *x, int32_t n, int32_t rows, int32_t cols) {
+  return done(vxb::gemm_fp8(y, w, scales, x, n, rows, cols, vxb::caller_stream()),
+              "gemm_fp8");
+}
+
 int32_t vx_b200_moe_swiglu_q4_grouped(float *out, const uint32_t *w,
                                       const uint16_t *scales, const int32_t *order,
                                       const int32_t *tile_expert, int32_t tiles,

@@ -55,7 +55,7 @@ EXTRA_SYMBOLS = [
     "vx_b200_fill_normal", "vx_b200_fill_uniform", "vx_b200_quantize",
     "vx_b200_attention_decode_static", "vx_b200_attention_kernel",
     "vx_b200_moe_swiglu_q4_grouped", "vx_b200_moe_down_q4_add_grouped",
-    "vx_b200_gemm_q4",
+    "vx_b200_gemm_q4", "vx_b200_gemm_fp8",
 ]
 
 _lib = None
@@ -180,6 +180,8 @@ def lib():
     L.vx_decoder_from_llama2c.argtypes = [C.c_char_p, i32, i32]
     L.vx_b200_attention_kernel.restype = i32
     L.vx_b200_attention_kernel.argtypes = [i32]
+    L.vx_b200_gemm_fp8.restype = i32
+    L.vx_b200_gemm_fp8.argtypes = [vp, vp, vp, vp, i32, i32, i32]
     L.vx_b200_gemm_q4.restype = i32
     L.vx_b200_gemm_q4.argtypes = [vp, vp, vp, vp, i32, i32, i32]
     L.vx_b200_moe_swiglu_q4_grouped.restype = i32

@@ -311,3 +311,8 @@ def moe_down_q4_add_grouped(y, w, scales, order, tile_expert, align, weights, h,
 def gemm_q4(y, w, scales, x, n, rows, cols):
     """y[n, rows] = x[n, cols] times the transpose of a Q4_0 matrix."""
     check(lib().vx_b200_gemm_q4(y.ptr, w.ptr, scales.ptr, x.ptr, n, rows, cols))
+
+
+def gemm_fp8(y, w, scales, x, n, rows, cols):
+    """y[n, rows] = x[n, cols] times the transpose of an fp8 matrix."""
+    check(lib().vx_b200_gemm_fp8(y.ptr, w.ptr, scales.ptr, x.ptr, n, rows, cols))
