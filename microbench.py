@@ -7,7 +7,7 @@ larger than the 126 MB L2 where DRAM figures matter).
   python microbench.py flash   [--batch 1] [--heads 8] [--seq 4096]
   python microbench.py attn    [--pos 600]
   python microbench.py shard   [--ranks 8] [--pos 520]
-  python microbench.py prefill [--layers 4]
+  python microbench.py prefill [--layers 4] [--fmt bf16|q4|fp8]
   python microbench.py moe     [--n 512]
 Each prints one JSON line with the CUDA-event time per launch.
 """
@@ -239,7 +239,10 @@ def prefill(torch, args):
     from vx_b200 import llama
     shape = dict(llama.LLAMA2_7B)
     shape["n_layers"] = args.layers
-    dec, tensors = llama.nn_bf16_model(max_seq=1024, batch=1, **shape)
+    if args.fmt in ("q4", "fp8"):
+        dec, tensors = llama.nn_quant_model(args.fmt, max_seq=1024, **shape)
+    else:
+        dec, tensors = llama.nn_bf16_model(max_seq=1024, batch=1, **shape)
     prompt = np.random.default_rng(8).integers(0, shape["vocab"], 512)
     best = None
     for _ in range(max(2, args.iters)):
@@ -251,8 +254,8 @@ def prefill(torch, args):
         ms = (time.perf_counter() - t0) * 1e3
         best = ms if best is None else min(best, ms)
     dec.close()
-    return dict(kernel="prefill of 512 tokens, %d layers of the 7B shape" % args.layers,
-                ms=best, ms_per_layer=best / args.layers, status=ops.kernel_status())
+    return dict(kernel="prefill of 512 tokens, %d layers of the 7B shape, %s weights"
+                       % (args.layers, args.fmt), ms=best, ms_per_layer=best / args.layers, status=ops.kernel_status())
 
 
 def moe(torch, args):
