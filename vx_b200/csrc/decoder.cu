@@ -216,6 +216,9 @@ struct vx_decoder {
      sums */
   float *rows_x, *rows_q, *rows_partials;
   void *rows_terms;
+  /* Q4_0 weights: the matrix in hand as two bf16 terms, and the doubled terms */
+  void *rows_w_terms, *rows_terms6;
+  size_t rows_partial_floats;
   int32_t *rows_tokens;
   int rows_cap;
   int64_t cache_layer_stride, cache_batch_stride;
@@ -829,6 +832,8 @@ vx_decoder *vx_decoder_create(const vx_decoder_config *config,
   }
   d->rows_x = d->rows_q = d->rows_partials = nullptr;
   d->rows_terms = nullptr;
+  d->rows_w_terms = d->rows_terms6 = nullptr;
+  d->rows_partial_floats = 0;
   d->rows_tokens = nullptr;
   d->rows_cap = 0;
   d->mma = false;
@@ -896,7 +901,8 @@ void vx_decoder_destroy(vx_decoder *d) {
                   (void *)d->local_best, (void *)d->pair,
                   (void *)d->pairs_all, d->mma_xs, (void *)d->mma_scratch,
                   (void *)d->rows_x, (void *)d->rows_q, (void *)d->rows_partials,
-                  d->rows_terms, (void *)d->rows_tokens, (void *)d->step_ops,
+                  d->rows_terms, d->rows_w_terms, d->rows_terms6,
+                  (void *)d->rows_tokens, (void *)d->step_ops,
                   (void *)d->step_scratch, (void *)d->arrivals,
                   (void *)d->step_trace})
     cudaFree(p);
@@ -970,6 +976,11 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
                         "of 64 (of 128 for fp8)");
     return -1;
   }
+  /* VXB_Q4_PREFILL=mma keeps the Q4_0 GEMMs on the mma.sync kernel (for
+     measurements); the default unpacks a matrix to two bf16 terms and runs the
+     CTA-pair GEMM. */
+  const char *route = getenv("VXB_Q4_PREFILL");
+  const bool q4_on_pairs = q4 && !(route && strcmp(route, "mma") == 0);
   /* One GEMM of the prompt: on CTA pairs for bf16 weights; for Q4_0 on the
      grouped kernel of the experts (one matrix, tiles of sixteen positions) and
      for fp8 on its twin (gemm_fp8_rows.cu); every way sums[run][t][r] for the
@@ -978,6 +989,19 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
     if (!q4 && !fp8)
       return vxb::rows_gemm(d->rows_terms, w, count, n, cols, d->rows_partials, runs,
                             d->stream);
+    if (q4 && q4_on_pairs) {
+      /* exact all the same: two bf16 terms a weight, three an activation, six
+         products on tcgen05 instead of three on mma.sync */
+      if (const char *why = vxb::rows_q4_two_terms(d->rows_w_terms, w, scales, n, cols,
+                                                   d->stream))
+        return why;
+      if (const char *why = vxb::rows_dup_terms(d->rows_terms6, d->rows_terms, count,
+                                                cols, d->stream))
+        return why;
+      return vxb::rows_gemm_of(d->rows_terms6, 6 * (int64_t)cols, d->rows_w_terms,
+                               2 * (int64_t)cols, count, n, d->rows_partials, runs,
+                               d->stream);
+    }
     *runs = 1;
     return q4 ? vxb::rows_gemm_q4(d->rows_terms, w, scales, count, n, cols,
                                   d->rows_partials, d->stream)
@@ -991,25 +1015,45 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
   if (count < 32)
     return 0;
   const int T = count;
-  if (T > d->rows_cap) {
+  int widest = c.dim > d->hidden_local ? c.dim : d->hidden_local;
+  if (att_cols > widest)
+    widest = att_cols;
+  const int shapes[4][2] = {{qkv_rows, c.dim}, {c.dim, att_cols},
+                            {2 * d->hidden_local, c.dim}, {c.dim, d->hidden_local}};
+  if (T > d->rows_cap || (q4_on_pairs && !d->rows_w_terms)) {
+    const int cap = T > d->rows_cap ? T : d->rows_cap;
     for (void *p : {(void *)d->rows_x, (void *)d->rows_q, d->rows_terms,
-                    (void *)d->rows_partials, (void *)d->rows_tokens})
+                    (void *)d->rows_tokens})
       cudaFree(p);
-    int widest = c.dim > d->hidden_local ? c.dim : d->hidden_local;
-    if (att_cols > widest)
-      widest = att_cols;
-    size_t partial = vxb::rows_gemm_partial_floats(T, qkv_rows, c.dim);
-    for (size_t other : {vxb::rows_gemm_partial_floats(T, c.dim, att_cols),
-                         vxb::rows_gemm_partial_floats(T, 2 * d->hidden_local, c.dim),
-                         vxb::rows_gemm_partial_floats(T, c.dim, d->hidden_local)})
-      if (other > partial)
-        partial = other;
-    d->rows_x = dev_alloc<float>((size_t)T * c.dim);
-    d->rows_q = dev_alloc<float>((size_t)T * att_cols);
-    d->rows_terms = dev_alloc<uint16_t>((size_t)T * 3 * widest);
-    d->rows_partials = dev_alloc<float>(partial);
-    d->rows_tokens = dev_alloc<int32_t>(T);
-    d->rows_cap = T;
+    if (q4_on_pairs) {
+      cudaFree(d->rows_w_terms);
+      cudaFree(d->rows_terms6);
+      size_t widest_matrix = 0;
+      for (const auto &sh : shapes)
+        if ((size_t)sh[0] * sh[1] > widest_matrix)
+          widest_matrix = (size_t)sh[0] * sh[1];
+      d->rows_w_terms = dev_alloc<uint16_t>(2 * widest_matrix);
+      d->rows_terms6 = dev_alloc<uint16_t>((size_t)cap * 6 * widest);
+    }
+    d->rows_x = dev_alloc<float>((size_t)cap * c.dim);
+    d->rows_q = dev_alloc<float>((size_t)cap * att_cols);
+    d->rows_terms = dev_alloc<uint16_t>((size_t)cap * 3 * widest);
+    d->rows_tokens = dev_alloc<int32_t>(cap);
+    d->rows_cap = cap;
+  }
+  /* The sums of this call's GEMMs: the number of runs depends on T, and a
+     shorter prompt can ask for more of them than a longer one did. */
+  size_t sums = 0;
+  for (const auto &sh : shapes) {
+    const int64_t k_cols = (q4_on_pairs ? 6 : 3) * (int64_t)sh[1];
+    const size_t one = (size_t)vxb::rows_gemm_splits_of(T, sh[0], k_cols) * T * sh[0];
+    if (one > sums)
+      sums = one;
+  }
+  if (sums > d->rows_partial_floats) {
+    cudaFree(d->rows_partials);
+    d->rows_partials = dev_alloc<float>(sums);
+    d->rows_partial_floats = sums;
   }
   cudaStream_t s = d->stream;
   CUDA_OK(cudaMemcpyAsync(d->rows_tokens, tokens, (size_t)T * sizeof(int32_t),

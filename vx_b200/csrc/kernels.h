@@ -327,6 +327,14 @@ int rows_gemm_splits_of(int t, int n, int64_t term_cols);
 const char *rows_gemm_of(const void *terms, int64_t term_cols, const void *w,
                          int64_t w_cols, int t, int n, float *partials,
                          int *splits_out, cudaStream_t stream);
+/* For Q4_0 weights on that GEMM: a matrix [n, cols] as [n, 2 cols] bf16 = w1 | w2
+   with w1 + w2 = (code - 8) * scale exactly, and terms [t, 3 cols] doubled to
+   [t, 6 cols] = x1 | x1 | x2 | x2 | x3 | x3; rows_gemm_of(doubled, 6 cols, two,
+   2 cols, ...) then sums all six products. */
+const char *rows_q4_two_terms(void *out, const void *codes, const void *scales, int n,
+                              int cols, cudaStream_t stream);
+const char *rows_dup_terms(void *out, const void *terms, int t, int cols,
+                           cudaStream_t stream);
 /* terms of RMSNorm(x[t]) * w for every position (nn_rms_norm_rows). */
 const char *rows_norm_terms(void *terms, const float *x, const void *w, int t,
                             int dim, float eps, cudaStream_t stream);

@@ -640,6 +640,64 @@ rows_attention_kernel(__nv_bfloat16 *terms, const float *q, const float *k_cache
   }
 }
 
+/* ---- Q4_0 weights for the CTA-pair GEMM --------------------------------------
+ * A Q4_0 weight is (code - 8) * scale with an f16 scale: 4 + 11 significant
+ * bits, so two bf16 terms hold it exactly. A matrix goes to a scratch as
+ * [n, 2 cols] = w1 | w2; the activations' terms are laid out as
+ * x1 | x1 | x2 | x2 | x3 | x3, and the GEMM, which lets K block kb of the first
+ * operand meet K block kb mod (2 cols / 64) of the second, multiplies every x
+ * term with every w term. */
+__global__ void __launch_bounds__(256)
+q4_two_terms_kernel(__nv_bfloat16 *out, const uint32_t *codes, const __half *scales,
+                    int64_t words_total, int cols) {
+  chain_release();
+  chain_wait();
+  const int words = cols / 8;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < words_total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / words;
+    const int wd = (int)(i - r * words);
+    const uint32_t code = codes[i];
+    const float scale = __half2float(scales[r * (cols / 32) + wd / 4]);
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t h2 = 0, l2 = 0;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float v = (float)((int)((code >> (8 * j + 4 * h)) & 15u) - 8) * scale;
+        const __nv_bfloat16 t1 = __float2bfloat16(v);
+        const __nv_bfloat16 t2 = __float2bfloat16(v - __bfloat162float(t1));
+        h2 |= (uint32_t)__bfloat16_as_ushort(t1) << (16 * h);
+        l2 |= (uint32_t)__bfloat16_as_ushort(t2) << (16 * h);
+      }
+      hi[j] = h2;
+      lo[j] = l2;
+    }
+    __nv_bfloat16 *row = out + r * 2 * cols + wd * 8;
+    *reinterpret_cast<uint4 *>(row) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4 *>(row + cols) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  }
+}
+
+/* [t, 3 cols] = x1 | x2 | x3  ->  [t, 6 cols] = x1 | x1 | x2 | x2 | x3 | x3 */
+__global__ void __launch_bounds__(256)
+dup_terms_kernel(uint4 *out, const uint4 *in, int64_t quads_total, int cols) {
+  chain_release();
+  chain_wait();
+  const int per_term = cols / 8;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < quads_total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / (3 * per_term);
+    const int rest = (int)(i - row * 3 * per_term);
+    const int k = rest / per_term, c = rest - k * per_term;
+    const uint4 v = in[i];
+    uint4 *dst = out + row * 6 * per_term + 2 * k * per_term + c;
+    dst[0] = v;
+    dst[per_term] = v;
+  }
+}
+
 const char *last_launch(const char *what) {
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess)
@@ -742,6 +800,33 @@ const char *rows_gemm_of(const void *terms, int64_t term_cols, const void *w,
       launch_chained_cluster_smem(rows_gemm_kernel, dim3(2 * pairs), dim3(THREADS), 2,
                                   SMEM_BYTES, stream, mx, mw, g);
   return e == cudaSuccess ? nullptr : cudaGetErrorString(e);
+}
+
+const char *rows_q4_two_terms(void *out, const void *codes, const void *scales, int n,
+                              int cols, cudaStream_t stream) {
+  if (cols % 32 != 0 || ((uintptr_t)out & 15))
+    return "a Q4_0 matrix has columns in multiples of 32";
+  const int64_t words = (int64_t)n * (cols / 8);
+  int blocks = (int)((words + 255) / 256);
+  if (blocks > 148 * 16)
+    blocks = 148 * 16;
+  launch_chained(q4_two_terms_kernel, dim3(blocks), dim3(256), 0, stream,
+                 (__nv_bfloat16 *)out, (const uint32_t *)codes, (const __half *)scales,
+                 words, cols);
+  return last_launch("the Q4_0 weights as two bf16 terms");
+}
+
+const char *rows_dup_terms(void *out, const void *terms, int t, int cols,
+                           cudaStream_t stream) {
+  if (cols % 8 != 0 || (((uintptr_t)out | (uintptr_t)terms) & 15))
+    return "terms come in multiples of 8 columns";
+  const int64_t quads = (int64_t)t * 3 * (cols / 8);
+  int blocks = (int)((quads + 255) / 256);
+  if (blocks > 148 * 16)
+    blocks = 148 * 16;
+  launch_chained(dup_terms_kernel, dim3(blocks), dim3(256), 0, stream, (uint4 *)out,
+                 (const uint4 *)terms, quads, cols);
+  return last_launch("the doubled terms");
 }
 
 const char *rows_norm_terms(void *terms, const float *x, const void *w, int t,
