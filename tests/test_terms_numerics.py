@@ -2,7 +2,9 @@
 the CPU with numpy: an f32 value is the exact sum of three bf16 terms (the f32
 GEMM, the prefill GEMMs, the batched and the Q4_0 projections), or of three f16
 terms with the second and third scaled by 2^11 and 2^22 (the fp8 projections),
-and the six largest of the nine term products are the product to f32 accuracy."""
+and the six largest of the nine term products are the product to f32 accuracy;
+a Q4_0 code, a Q4_0 weight and an e4m3 code as exact bf16 values (the products
+of many rows with quantised weights)."""
 import numpy as np
 
 
@@ -73,3 +75,55 @@ def test_a_q4_code_is_an_exact_bf16_after_the_magic_or():
     assert np.array_equal(as_f32, (128 + codes).astype(np.float32))
     assert np.array_equal(to_bf16(as_f32 - np.float32(136)),
                           (codes.astype(np.float32) - 8))
+
+
+def bf16_bits_to_f64(bits):
+    """The value of bf16 bit patterns (subnormals included), as f64."""
+    bits = np.asarray(bits, np.uint32)
+    return (bits << 16).astype(np.uint32).view(np.float32).astype(np.float64)
+
+
+def test_a_q4_code_is_exact_in_bf16_through_the_bias_trick():
+    """0x4300 | code is the bf16 128 + code (one unit in the last place at 128
+    is 1), so subtracting 136 leaves code - 8: what the Q4_0 tensor-core kernels
+    build their A operand from."""
+    for code in range(16):
+        biased = bf16_bits_to_f64(0x4300 | code)
+        assert biased == 128.0 + code
+        assert to_bf16(np.float32(biased - 136.0)) == np.float32(code - 8)
+    assert bf16_bits_to_f64(0x4308) == 136.0
+
+
+def test_a_q4_weight_is_the_exact_sum_of_two_bf16_terms():
+    """(code - 8) * scale with an f16 scale has 4 + 11 significant bits: the
+    first bf16 term and the rounded remainder hold all of them, for every code
+    and every finite f16 scale. The prompt pass of a Q4_0 decoder rests on it."""
+    scales = np.arange(0x0001, 0x7C00, dtype=np.uint16).view(np.float16) \
+        .astype(np.float32)                                # every positive finite f16
+    for code in range(16):
+        v = (np.float32(code - 8) * scales).astype(np.float32)
+        assert np.array_equal(v.astype(np.float64),
+                              np.float64(code - 8) * scales.astype(np.float64))
+        t1 = to_bf16(v)
+        t2 = to_bf16((v - t1).astype(np.float32))
+        assert np.array_equal(t1.astype(np.float64) + t2.astype(np.float64),
+                              v.astype(np.float64)), code
+
+
+def test_an_e4m3_code_becomes_bf16_by_a_shift_and_a_multiply_by_2_to_the_120():
+    """The seven low bits of a code, shifted left by four, are a bf16 with the
+    code's mantissa and an exponent field 120 too small (a bf16 subnormal for
+    the eight subnormal codes); times 2^120 that is the code's value, which bf16
+    holds exactly. The fp8 product of many rows unpacks its weights this way."""
+    def e4m3(c):
+        sign = -1.0 if c & 0x80 else 1.0
+        e, m = (c >> 3) & 15, c & 7
+        return sign * (m * 2.0 ** -9 if e == 0 else 2.0 ** (e - 7) * (1 + m / 8))
+    assert bf16_bits_to_f64(0x7B80) == 2.0 ** 120
+    for c in range(256):
+        if (c & 0x7F) == 0x7F:
+            continue                                        # the two NaN codes
+        small = ((c & 0x7F) << 4) | ((c & 0x80) << 8)
+        value = bf16_bits_to_f64(small) * 2.0 ** 120
+        assert value == e4m3(c), c
+        assert to_bf16(np.float32(value)) == np.float32(value)   # 4 bits: exact
