@@ -1,10 +1,15 @@
-"""The mixture-of-experts kernels for many positions: the pairs grouped by
-expert (nn_moe_group*, stdlib/std/nn.vx:1056-1294) bit-exact against the plain
-stable sort on the reference's own cases (tests/optimizations/pass/
-std_nn_moe_group_sorts_pairs_by_expert.vx), and the `_rows` router and Q4_0
+"""The mixture-of-experts kernels for many positions, and the quantised products
+of many rows that share their tensor-core kernel.
+
+The pairs grouped by expert (nn_moe_group*, stdlib/std/nn.vx:1056-1294) bit-exact
+against the plain stable sort on the reference's own cases (tests/optimizations/
+pass/std_nn_moe_group_sorts_pairs_by_expert.vx). The `_rows` router and Q4_0
 projections on the sizes of apple_gpu_kernels_for_n_positions_match_one_position.vx
 (5 positions; 16 experts, 4 a position): every row bit for bit the one-position
-kernel's, and within the reference's criterion of f64 loops."""
+kernel's, and within the reference's criterion of f64 loops. The grouped expert
+projections (vx_b200_moe_*_grouped) and the Q4_0 / fp8 products of many rows
+(vx_b200_gemm_q4, vx_b200_gemm_fp8) against f64 loops by the same criterion, max
+|got - want| <= 1e-5 * max |want|."""
 import numpy as np
 import pytest
 
