@@ -127,3 +127,53 @@ def test_an_e4m3_code_becomes_bf16_by_a_shift_and_a_multiply_by_2_to_the_120():
         value = bf16_bits_to_f64(small) * 2.0 ** 120
         assert value == e4m3(c), c
         assert to_bf16(np.float32(value)) == np.float32(value)   # 4 bits: exact
+
+
+def mma_16x8x16(a_regs, b_regs):
+    """mma.sync.m16n8k16 from per-lane registers, by the fragment layout of the
+    PTX manual: lane = 4 g + t holds A[g or g + 8][2t, 2t + 1 (+ 8)] and
+    B[2t, 2t + 1 (+ 8)][g], and gets C[g or g + 8][2t, 2t + 1]. a_regs[lane] =
+    (a0, a1, a2, a3), b_regs[lane] = (b0, b1), each a pair of values."""
+    A, B = np.zeros((16, 16)), np.zeros((16, 8))
+    for lane in range(32):
+        g, t = lane >> 2, lane & 3
+        a0, a1, a2, a3 = a_regs[lane]
+        A[g, 2 * t:2 * t + 2], A[g + 8, 2 * t:2 * t + 2] = a0, a1
+        A[g, 2 * t + 8:2 * t + 10], A[g + 8, 2 * t + 8:2 * t + 10] = a2, a3
+        b0, b1 = b_regs[lane]
+        B[2 * t:2 * t + 2, g], B[2 * t + 8:2 * t + 10, g] = b0, b1
+    return A @ B
+
+
+def test_the_column_orders_of_the_quantised_tensor_core_kernels():
+    """Which column of a 32-column Q4_0 group (of a 16-column fp8 step) a lane
+    feeds into which k slot of the MMA is free, as long as A and B agree. The
+    Q4_0 kernels pair the codes of a word as (0,4) (1,5) (2,6) (3,7), one mask
+    per pair, and stage the activations in that order; the fp8 kernel pairs
+    (0,2) (1,3). With the layouts restated here the sixteen rows times eight
+    positions come out as the plain product."""
+    rng = np.random.default_rng(9)
+    # Q4_0: lane t of a row holds word t (columns 8t .. 8t + 7); two MMAs a group
+    codes = rng.integers(-8, 8, (16, 32)).astype(np.float64)
+    x = rng.standard_normal((8, 32))
+    total = np.zeros((16, 8))
+    for first in (0, 2):                          # pairs P0, P1 then P2, P3
+        a_regs, b_regs = [], []
+        for lane in range(32):
+            g, t = lane >> 2, lane & 3
+            cols = [(8 * t + first + i, 8 * t + first + i + 4) for i in (0, 1)]
+            a_regs.append((codes[g, list(cols[0])], codes[g + 8, list(cols[0])],
+                           codes[g, list(cols[1])], codes[g + 8, list(cols[1])]))
+            b_regs.append((x[g, list(cols[0])], x[g, list(cols[1])]))
+        total += mma_16x8x16(a_regs, b_regs)
+    assert np.allclose(total, codes @ x.T, rtol=0, atol=1e-12)
+    # fp8: lane t holds one word (columns 4t .. 4t + 3) of a 16-column step
+    w = rng.standard_normal((16, 16))
+    x = rng.standard_normal((8, 16))
+    a_regs, b_regs = [], []
+    for lane in range(32):
+        g, t = lane >> 2, lane & 3
+        even, odd = [4 * t, 4 * t + 2], [4 * t + 1, 4 * t + 3]
+        a_regs.append((w[g, even], w[g + 8, even], w[g, odd], w[g + 8, odd]))
+        b_regs.append((x[g, even], x[g, odd]))
+    assert np.allclose(mma_16x8x16(a_regs, b_regs), w @ x.T, rtol=0, atol=1e-12)
