@@ -189,3 +189,32 @@ def test_llama2c_header_is_read_and_checked(tmp_path):
     junk.write_bytes(np.zeros(64, np.int32).tobytes())
     assert L.vx_b200_llama2c_config(str(junk).encode(), None) == -1
     assert b"does not begin with a llama2.c header" in L.vx_b200_last_error()
+
+
+@pytest.mark.parametrize("call,message", [
+    ("ops.nn_moe_group_count(t((1, 4)), t((10,)), 10, 0)",
+     "nn_moe_group_count: `experts` must be 1 to 1024"),
+    ("ops.nn_moe_group_count(t((1, 4)), t((600,)), 600, 4)",
+     "`counts` needs a row for each 256 pairs"),
+    ("ops.nn_moe_group_offsets(t((1, 4)), t((5,)), t((3,)), t((20,)), t((1, 4)), 10, 4, 8)",
+     "`order` needs n + experts * (align - 1) positions"),
+    ("ops.nn_moe_group_place(t((10,)), t((5,)), t((1, 4)), 10)",
+     "nn_moe_group_place: `ids` needs n values"),
+    ("ops.nn_top_k_rows(t((5, 4)), t((5, 4), abi.F32), t((5, 16), abi.F32), 5, 16, 17)",
+     "nn_top_k_rows: count must be 1 to 256, and k must be 1 to count"),
+    ("ops.nn_moe_swiglu_q4_rows(t((19, 64), abi.F32), t((100,)), t((100,), abi.F16), "
+     "t((5, 4)), t((5, 256), abi.F32), 5, 4, 64, 256, 16)",
+     "`out` a row of rows values for each of the n * k"),
+])
+def test_refused_shapes_of_the_expert_functions_stop_with_the_function_name(call, message):
+    """The asserts of nn_moe_group_count / _offsets / _place, nn_top_k_rows and
+    nn_moe_swiglu_q4_rows (stdlib/std/nn.vx:1071-1072, 1111-1113, 1253, 2898-2900,
+    2959) are checked before anything touches the GPU: a refused shape stops
+    the program with the function's name, with or without a GPU."""
+    code = ("from vx_b200 import abi, ops\n"
+            "def t(shape, elem=abi.I32):\n"
+            "    return abi.DeviceTensor(0x10000, shape, elem, 0)\n" + call + "\n"
+            "print('went on')\n")
+    r = run_child(code)
+    assert r.returncode < 0 and "went on" not in r.stdout, r.stderr[-500:]
+    assert "FATAL" in r.stderr and message in r.stderr, r.stderr[-500:]
