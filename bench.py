@@ -526,17 +526,17 @@ def bench_decode_quant(torch, llama, shape, peaks, quant):
             step_ms, tok_steps = timed_prompt(stepped)
             prompt_ms = dict(prefill_ms=rows_ms, one_step_per_token_ms=step_ms,
                              first_token_equal=bool(tok_rows == tok_steps))
-            if quant == "q4":
-                # the other route: codes unpacked in registers, mma.sync
-                os.environ["VXB_Q4_PREFILL"] = "mma"
-                try:
-                    timed_prompt(lambda: dec.prefill(prompt))
-                    mma_ms, tok_mma = timed_prompt(lambda: dec.prefill(prompt))
-                finally:
-                    del os.environ["VXB_Q4_PREFILL"]
-                prompt_ms.update(prefill_mma_sync_ms=mma_ms,
-                                 first_token_equal_mma_sync=bool(tok_mma == tok_steps))
-                timed_prompt(lambda: dec.prefill(prompt))   # the cache as the default leaves it
+            # the other route: codes unpacked in registers, mma.sync
+            knob = "VXB_Q4_PREFILL" if quant == "q4" else "VXB_FP8_PREFILL"
+            os.environ[knob] = "mma"
+            try:
+                timed_prompt(lambda: dec.prefill(prompt))
+                mma_ms, tok_mma = timed_prompt(lambda: dec.prefill(prompt))
+            finally:
+                del os.environ[knob]
+            prompt_ms.update(prefill_mma_sync_ms=mma_ms,
+                             first_token_equal_mma_sync=bool(tok_mma == tok_steps))
+            timed_prompt(lambda: dec.prefill(prompt))   # the cache as the default leaves it
         else:
             for t in prompt:
                 dec.step([int(t)], fetch=False)

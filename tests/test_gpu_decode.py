@@ -388,18 +388,20 @@ def test_quantised_decoder_tokens_match_oracle(oracle, quant):
     assert got == want, report(got, want)
 
 
-@pytest.mark.parametrize("quant,route", [("q4", ""), ("q4", "mma"), ("fp8", "")])
+@pytest.mark.parametrize("quant,route", [("q4", ""), ("q4", "mma"), ("fp8", ""),
+                                         ("fp8", "mma")])
 def test_prefill_with_quantised_weights(oracle, quant, route, monkeypatch):
     """A 100-token prompt through vx_decoder_prefill of a decoder with Q4_0 or
     fp8 weights, then greedy steps: the oracle's tokens, which come from one
     step per prompt token. Then 37 single steps and the other 62 positions in
-    one pass. Q4_0 by both routes: a matrix unpacked to two bf16 terms for the
-    CTA-pair GEMM (the default), and the mma.sync kernel that unpacks the codes
-    in registers for sixteen positions (VXB_Q4_PREFILL=mma; fp8 always)."""
+    one pass. By both routes: a matrix unpacked to two (Q4_0) or three (fp8) bf16
+    terms for the CTA-pair GEMM (the default), and the mma.sync kernels that
+    unpack the codes in registers for sixteen positions (VXB_Q4_PREFILL=mma,
+    VXB_FP8_PREFILL=mma)."""
     from vx_b200 import ops
     from vx_b200.lib import lib
     if route:
-        monkeypatch.setenv("VXB_Q4_PREFILL", route)
+        monkeypatch.setenv("VXB_Q4_PREFILL" if quant == "q4" else "VXB_FP8_PREFILL", route)
     max_seq, steps = 128, 12
     dec, tensors = llama.nn_quant_model(quant, max_seq=max_seq, **WIDE_NN)
     hm = oracle.quant_model_from_tensors(tensors, WIDE_NN, max_seq, quant)

@@ -216,7 +216,8 @@ struct vx_decoder {
      sums */
   float *rows_x, *rows_q, *rows_partials;
   void *rows_terms;
-  /* Q4_0 weights: the matrix in hand as two bf16 terms, and the doubled terms */
+  /* quantised weights: the matrix in hand as two (Q4_0) or three (fp8) bf16
+     terms, and the activations' terms spread over six or seven segments */
   void *rows_w_terms, *rows_terms6;
   size_t rows_partial_floats;
   int32_t *rows_tokens;
@@ -976,30 +977,43 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
                         "of 64 (of 128 for fp8)");
     return -1;
   }
-  /* VXB_Q4_PREFILL=mma keeps the Q4_0 GEMMs on the mma.sync kernel (for
-     measurements); the default unpacks a matrix to two bf16 terms and runs the
-     CTA-pair GEMM. */
-  const char *route = getenv("VXB_Q4_PREFILL");
+  /* VXB_Q4_PREFILL=mma / VXB_FP8_PREFILL=mma keep the quantised GEMMs on the
+     mma.sync kernels (for measurements); the default unpacks a matrix to bf16
+     terms and runs the CTA-pair GEMM. */
+  const char *route = getenv("VXB_Q4_PREFILL"), *route8 = getenv("VXB_FP8_PREFILL");
   const bool q4_on_pairs = q4 && !(route && strcmp(route, "mma") == 0);
-  /* One GEMM of the prompt: on CTA pairs for bf16 weights; for Q4_0 on the
-     grouped kernel of the experts (one matrix, tiles of sixteen positions) and
-     for fp8 on its twin (gemm_fp8_rows.cu); every way sums[run][t][r] for the
-     finishing kernels. */
+  const bool fp8_on_pairs = fp8 && !(route8 && strcmp(route8, "mma") == 0);
+  const bool on_pairs = q4_on_pairs || fp8_on_pairs;
+  /* how many bf16 terms a weight becomes, and the segments the activations'
+     terms are spread over to meet them */
+  const int w_terms = q4_on_pairs ? 2 : 3, segments = q4_on_pairs ? 6 : 7;
+  static const int spread_q4[6] = {0, 0, 1, 1, 2, 2};
+  static const int spread_fp8[7] = {0, 0, 0, 1, 1, 1, 2};
+  /* One GEMM of the prompt, on CTA pairs: bf16 weights as they are, quantised
+     ones unpacked to bf16 terms first; or, when asked, Q4_0 on the grouped
+     kernel of the experts (one matrix, tiles of sixteen positions) and fp8 on
+     its twin (gemm_fp8_rows.cu). Every way sums[run][t][r] for the finishing
+     kernels. */
   auto gemm = [&](const void *w, const void *scales, int n, int cols, int *runs) {
     if (!q4 && !fp8)
       return vxb::rows_gemm(d->rows_terms, w, count, n, cols, d->rows_partials, runs,
                             d->stream);
-    if (q4 && q4_on_pairs) {
-      /* exact all the same: two bf16 terms a weight, three an activation, six
-         products on tcgen05 instead of three on mma.sync */
-      if (const char *why = vxb::rows_q4_two_terms(d->rows_w_terms, w, scales, n, cols,
-                                                   d->stream))
+    if (on_pairs) {
+      /* Q4_0: exact all the same, two bf16 terms a weight, three an activation,
+         six products on tcgen05 instead of three on mma.sync. fp8: the f32
+         value code * scale as three terms, the six products of an f32 product
+         and one more. */
+      const char *why =
+          q4 ? vxb::rows_q4_two_terms(d->rows_w_terms, w, scales, n, cols, d->stream)
+             : vxb::rows_fp8_three_terms(d->rows_w_terms, w, scales, n, cols, d->stream);
+      if (why)
         return why;
-      if (const char *why = vxb::rows_dup_terms(d->rows_terms6, d->rows_terms, count,
-                                                cols, d->stream))
+      why = vxb::rows_spread_terms(d->rows_terms6, d->rows_terms, count, cols, segments,
+                                   q4 ? spread_q4 : spread_fp8, d->stream);
+      if (why)
         return why;
-      return vxb::rows_gemm_of(d->rows_terms6, 6 * (int64_t)cols, d->rows_w_terms,
-                               2 * (int64_t)cols, count, n, d->rows_partials, runs,
+      return vxb::rows_gemm_of(d->rows_terms6, segments * (int64_t)cols, d->rows_w_terms,
+                               w_terms * (int64_t)cols, count, n, d->rows_partials, runs,
                                d->stream);
     }
     *runs = 1;
@@ -1020,20 +1034,20 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
     widest = att_cols;
   const int shapes[4][2] = {{qkv_rows, c.dim}, {c.dim, att_cols},
                             {2 * d->hidden_local, c.dim}, {c.dim, d->hidden_local}};
-  if (T > d->rows_cap || (q4_on_pairs && !d->rows_w_terms)) {
+  if (T > d->rows_cap || (on_pairs && !d->rows_w_terms)) {
     const int cap = T > d->rows_cap ? T : d->rows_cap;
     for (void *p : {(void *)d->rows_x, (void *)d->rows_q, d->rows_terms,
                     (void *)d->rows_tokens})
       cudaFree(p);
-    if (q4_on_pairs) {
+    if (on_pairs) {
       cudaFree(d->rows_w_terms);
       cudaFree(d->rows_terms6);
       size_t widest_matrix = 0;
       for (const auto &sh : shapes)
         if ((size_t)sh[0] * sh[1] > widest_matrix)
           widest_matrix = (size_t)sh[0] * sh[1];
-      d->rows_w_terms = dev_alloc<uint16_t>(2 * widest_matrix);
-      d->rows_terms6 = dev_alloc<uint16_t>((size_t)cap * 6 * widest);
+      d->rows_w_terms = dev_alloc<uint16_t>(w_terms * widest_matrix);
+      d->rows_terms6 = dev_alloc<uint16_t>((size_t)cap * segments * widest);
     }
     d->rows_x = dev_alloc<float>((size_t)cap * c.dim);
     d->rows_q = dev_alloc<float>((size_t)cap * att_cols);
@@ -1045,7 +1059,7 @@ int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count) 
      shorter prompt can ask for more of them than a longer one did. */
   size_t sums = 0;
   for (const auto &sh : shapes) {
-    const int64_t k_cols = (q4_on_pairs ? 6 : 3) * (int64_t)sh[1];
+    const int64_t k_cols = (on_pairs ? segments : 3) * (int64_t)sh[1];
     const size_t one = (size_t)vxb::rows_gemm_splits_of(T, sh[0], k_cols) * T * sh[0];
     if (one > sums)
       sums = one;

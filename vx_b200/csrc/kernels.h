@@ -322,19 +322,24 @@ size_t rows_gemm_partial_floats(int t, int n, int cols);
 const char *rows_gemm(const void *terms, const void *w, int t, int n, int cols,
                       float *partials, int *splits_out, cudaStream_t stream);
 /* The same GEMM for any two bf16 matrices: terms [t, term_cols], w [n, w_cols];
-   K block kb of the terms meets K block kb mod (w_cols / 64) of w. */
+   K block kb of the terms meets K block kb mod (w_cols / 64) of w (term_cols
+   need not be a multiple of w_cols). */
 int rows_gemm_splits_of(int t, int n, int64_t term_cols);
 const char *rows_gemm_of(const void *terms, int64_t term_cols, const void *w,
                          int64_t w_cols, int t, int n, float *partials,
                          int *splits_out, cudaStream_t stream);
-/* For Q4_0 weights on that GEMM: a matrix [n, cols] as [n, 2 cols] bf16 = w1 | w2
-   with w1 + w2 = (code - 8) * scale exactly, and terms [t, 3 cols] doubled to
-   [t, 6 cols] = x1 | x1 | x2 | x2 | x3 | x3; rows_gemm_of(doubled, 6 cols, two,
-   2 cols, ...) then sums all six products. */
+/* For quantised weights on that GEMM. Q4_0: a matrix [n, cols] as [n, 2 cols]
+   bf16 = w1 | w2 with w1 + w2 = (code - 8) * scale exactly, against terms spread
+   to x1 | x1 | x2 | x2 | x3 | x3 (segments 6, from {0,0,1,1,2,2}). fp8: the f32
+   value code * scale as [n, 3 cols] = w1 | w2 | w3, against x1 | x1 | x1 | x2 |
+   x2 | x2 | x3. rows_gemm_of(spread, segments * cols, unpacked, 2 or 3 cols,
+   ...) then sums the products: the second operand's K blocks wrap round. */
 const char *rows_q4_two_terms(void *out, const void *codes, const void *scales, int n,
                               int cols, cudaStream_t stream);
-const char *rows_dup_terms(void *out, const void *terms, int t, int cols,
-                           cudaStream_t stream);
+const char *rows_fp8_three_terms(void *out, const void *codes, const void *scales,
+                                 int n, int cols, cudaStream_t stream);
+const char *rows_spread_terms(void *out, const void *terms, int t, int cols,
+                              int segments, const int *from, cudaStream_t stream);
 /* terms of RMSNorm(x[t]) * w for every position (nn_rms_norm_rows). */
 const char *rows_norm_terms(void *terms, const float *x, const void *w, int t,
                             int dim, float eps, cudaStream_t stream);

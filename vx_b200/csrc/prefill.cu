@@ -680,21 +680,56 @@ q4_two_terms_kernel(__nv_bfloat16 *out, const uint32_t *codes, const __half *sca
   }
 }
 
-/* [t, 3 cols] = x1 | x2 | x3  ->  [t, 6 cols] = x1 | x1 | x2 | x2 | x3 | x3 */
+/* An fp8 weight is the value of its e4m3 code times the f32 scale of its block
+ * of 128 x 128, rounded to f32 as a plain multiplication rounds it; that f32 is
+ * three bf16 terms exactly. A matrix goes to a scratch as [n, 3 cols] =
+ * w1 | w2 | w3, the activations' terms are laid out as
+ * x1 | x1 | x1 | x2 | x2 | x2 | x3, and the seven segments meet w1 w2 w3 w1 w2 w3
+ * w1: the six products an f32 product needs, and x2 w3 besides. */
 __global__ void __launch_bounds__(256)
-dup_terms_kernel(uint4 *out, const uint4 *in, int64_t quads_total, int cols) {
+fp8_three_terms_kernel(__nv_bfloat16 *out, const uint2 *codes, const float *scales,
+                       int64_t eights_total, int cols) {
+  chain_release();
+  chain_wait();
+  const int eights = cols / 8;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < eights_total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / eights;
+    const int e8 = (int)(i - r * eights);
+    const uint2 eight = codes[i];
+    const float scale = scales[(r >> 7) * (cols / 128) + e8 / 16];
+    const uint32_t word[2] = {eight.x, eight.y};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const unsigned short two = (unsigned short)(word[j >> 1] >> (16 * (j & 1)));
+      uint32_t halves;
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(halves) : "h"(two));
+      v[2 * j] = __half2float(__ushort_as_half((unsigned short)(halves & 0xffffu))) * scale;
+      v[2 * j + 1] = __half2float(__ushort_as_half((unsigned short)(halves >> 16))) * scale;
+    }
+    store_terms8(out, cols, r, e8 * 8, v);
+  }
+}
+
+/* [t, 3 cols] = x1 | x2 | x3  ->  [t, segments cols], segment s a copy of term
+   from[s] */
+struct SpreadPlan {
+  int segments;
+  int from[8];
+};
+__global__ void __launch_bounds__(256)
+spread_terms_kernel(uint4 *out, const uint4 *in, int64_t quads_total, int cols,
+                    const SpreadPlan plan) {
   chain_release();
   chain_wait();
   const int per_term = cols / 8;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < quads_total;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / (3 * per_term);
-    const int rest = (int)(i - row * 3 * per_term);
-    const int k = rest / per_term, c = rest - k * per_term;
-    const uint4 v = in[i];
-    uint4 *dst = out + row * 6 * per_term + 2 * k * per_term + c;
-    dst[0] = v;
-    dst[per_term] = v;
+    const int64_t row = i / (plan.segments * per_term);
+    const int rest = (int)(i - row * plan.segments * per_term);
+    const int seg = rest / per_term, c = rest - seg * per_term;
+    out[i] = in[row * 3 * per_term + plan.from[seg] * per_term + c];
   }
 }
 
@@ -773,7 +808,7 @@ const char *rows_gemm(const void *terms, const void *w, int t, int n, int cols,
 const char *rows_gemm_of(const void *terms, int64_t term_cols, const void *w,
                          int64_t w_cols, int t, int n, float *partials,
                          int *splits_out, cudaStream_t stream) {
-  if (term_cols % BK != 0 || w_cols % BK != 0 || term_cols % w_cols != 0)
+  if (term_cols % BK != 0 || w_cols % BK != 0)
     return "the multi-position projections need columns in multiples of 64";
   if (allow_dynamic_smem((const void *)rows_gemm_kernel, SMEM_BYTES) != cudaSuccess)
     return "the multi-position GEMM could not get its shared memory";
@@ -816,17 +851,39 @@ const char *rows_q4_two_terms(void *out, const void *codes, const void *scales, 
   return last_launch("the Q4_0 weights as two bf16 terms");
 }
 
-const char *rows_dup_terms(void *out, const void *terms, int t, int cols,
-                           cudaStream_t stream) {
-  if (cols % 8 != 0 || (((uintptr_t)out | (uintptr_t)terms) & 15))
-    return "terms come in multiples of 8 columns";
-  const int64_t quads = (int64_t)t * 3 * (cols / 8);
+const char *rows_fp8_three_terms(void *out, const void *codes, const void *scales,
+                                 int n, int cols, cudaStream_t stream) {
+  if (cols % 128 != 0 || (((uintptr_t)out | (uintptr_t)codes) & 15))
+    return "an fp8 matrix has columns in multiples of 128";
+  const int64_t eights = (int64_t)n * (cols / 8);
+  int blocks = (int)((eights + 255) / 256);
+  if (blocks > 148 * 16)
+    blocks = 148 * 16;
+  launch_chained(fp8_three_terms_kernel, dim3(blocks), dim3(256), 0, stream,
+                 (__nv_bfloat16 *)out, (const uint2 *)codes, (const float *)scales,
+                 eights, cols);
+  return last_launch("the fp8 weights as three bf16 terms");
+}
+
+const char *rows_spread_terms(void *out, const void *terms, int t, int cols,
+                              int segments, const int *from, cudaStream_t stream) {
+  if (cols % 8 != 0 || (((uintptr_t)out | (uintptr_t)terms) & 15) || segments < 1 ||
+      segments > 8)
+    return "terms come in multiples of 8 columns, spread over at most 8 segments";
+  SpreadPlan plan{};
+  plan.segments = segments;
+  for (int s = 0; s < segments; ++s) {
+    if (from[s] < 0 || from[s] > 2)
+      return "a segment is a copy of term 0, 1 or 2";
+    plan.from[s] = from[s];
+  }
+  const int64_t quads = (int64_t)t * segments * (cols / 8);
   int blocks = (int)((quads + 255) / 256);
   if (blocks > 148 * 16)
     blocks = 148 * 16;
-  launch_chained(dup_terms_kernel, dim3(blocks), dim3(256), 0, stream, (uint4 *)out,
-                 (const uint4 *)terms, quads, cols);
-  return last_launch("the doubled terms");
+  launch_chained(spread_terms_kernel, dim3(blocks), dim3(256), 0, stream, (uint4 *)out,
+                 (const uint4 *)terms, quads, cols, plan);
+  return last_launch("the spread terms");
 }
 
 const char *rows_norm_terms(void *terms, const float *x, const void *w, int t,
