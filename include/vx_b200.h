@@ -280,9 +280,12 @@ int32_t vx_decoder_step(vx_decoder *d, const int32_t *tokens_in,
    than 32: the caller steps through those), or -1 with vx_b200_last_error()
    for a decoder that cannot (needs batch 1, one rank, bf16, fp8 or Q4_0
    weights with the q/k/v rows in one matrix and the gate/up rows in one,
-   head_dim 128, widths in multiples of 64, of 128 for fp8). With Q4_0 or fp8
-   weights the GEMMs unpack the codes once for sixteen positions (the kernel
-   of the grouped experts, and its fp8 twin). */
+   head_dim 128, widths in multiples of 64, of 128 for fp8). Quantised weights
+   are unpacked, a matrix at a time, to bf16 terms for the same GEMM (Q4_0: two
+   terms, exactly; fp8: the f32 value code * scale as three); with
+   VXB_Q4_PREFILL=mma / VXB_FP8_PREFILL=mma in the environment the GEMMs
+   unpack the codes in registers instead, once for sixteen positions (the
+   kernel of the grouped experts, and its fp8 twin). */
 int32_t vx_decoder_prefill(vx_decoder *d, const int32_t *tokens, int32_t count);
 /* The logits of the last step: device memory, [batch, vocab] f32. */
 const float *vx_decoder_logits(const vx_decoder *d);
